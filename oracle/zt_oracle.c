@@ -1,0 +1,503 @@
+/*
+ * CPU oracle for Z-TRANSFORMER's attention hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file restates, in plain C, the reference's CPU arithmetic for the three
+ * functions the CUDA kernels of this repository replace.  It is the checker the
+ * parity tests, the smoke test and the benchmark's CPU baseline use; nothing in
+ * the shipped library links, loads or calls it.
+ *
+ * Followed, loop for loop (paths are within the reference project):
+ *   src/attention.zig:60-153   forwardWith      -> zto_attention_forward
+ *   src/autograd.zig:636-842   attentionBackward-> zto_attention_backward
+ *   src/decode.zig:326-392     attnStep         -> zto_attn_step
+ *   src/kv_cache.zig:60-135    Layer            -> zto_layer_*
+ *   src/cuda/device.zig:162-182,489-501  bytesFor/toCInt/forwardBounds
+ *                                               -> zto_bytes_for / zto_forward_bounds
+ *
+ * Arithmetic contract kept from the reference: f32 storage; every dot product,
+ * score, exponential, denominator and probability-weighted sum is carried in
+ * f64 and narrowed to f32 once, at the store.  The one exception is the
+ * backward's dk/dv, which the reference accumulates IN f32 with one f64->f32
+ * narrowing per term (autograd.zig:829-836); that order (head outer, query row,
+ * then key ascending) is kept so the roundings land where the reference's do.
+ *
+ * Parity status: the forward is pinned by the reference's own known-answer
+ * tests (src/attention_test.zig), restated in tests/test_oracle_kat.py.  The
+ * backward has no literal vectors anywhere in the reference (it is pinned there
+ * only by whole-model finite differences), so here it is pinned by central
+ * differences against the forward above and by an independent float64 autograd.
+ * The reference itself needs Zig 0.16 and cannot be built beside this file, so
+ * there is no oracle/_ref binary: backward parity is "pinned by derivation, not
+ * by reference-run vectors".
+ *
+ * The reference's Zig uses @exp/@sqrt on f64; glibc exp/sqrt in double are used
+ * here.  A last-ulp difference in exp() disappears under the f32 store.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ZTO_OK 0
+#define ZTO_INVALID_HEAD_CONFIG 1 /* attention.zig:71-73  error.InvalidHeadConfig */
+#define ZTO_DIMENSION_MISMATCH 2  /* attention.zig:74-79  error.DimensionMismatch */
+#define ZTO_OUT_OF_MEMORY 3
+#define ZTO_FULL 4                /* kv_cache.zig Error.Full */
+#define ZTO_SHAPE_TOO_LARGE 5     /* device.zig Error.ShapeTooLarge */
+#define ZTO_DEGENERATE_SHAPE 6    /* device.zig Error.DegenerateShape */
+
+/* One (head, query row) of the forward: attention.zig:113-149 with the key
+ * bound generalised from `t + 1` to `n_vis`, which is also decode.zig:363-390.
+ * `scores` is caller scratch of at least n_vis doubles. */
+static void zto_row(const float *q_head, const float *k, const float *v, size_t kv_cols,
+                    size_t kv_off, size_t dim, size_t n_vis, double scale, double *scores,
+                    float *out_head, float *lse) {
+    double row_max = -INFINITY;
+    for (size_t s = 0; s < n_vis; ++s) {
+        const float *k_head = k + s * kv_cols + kv_off;
+        double dot = 0.0;
+        for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
+        const double score = dot * scale;
+        scores[s] = score;
+        if (score > row_max) row_max = score;
+    }
+    double denom = 0.0;
+    for (size_t s = 0; s < n_vis; ++s) {
+        scores[s] = exp(scores[s] - row_max);
+        denom += scores[s];
+    }
+    for (size_t s = 0; s < n_vis; ++s) scores[s] /= denom;
+    for (size_t j = 0; j < dim; ++j) {
+        double acc = 0.0;
+        for (size_t s = 0; s < n_vis; ++s) acc += scores[s] * (double)v[s * kv_cols + kv_off + j];
+        out_head[j] = (float)acc;
+    }
+    /* The reference's CPU path never emits a log-sum-exp; it is defined here by
+     * restatement as row_max + ln(denom), both still in f64. */
+    if (lse) *lse = (float)(row_max + log(denom));
+}
+
+/*
+ * attention.forwardWith (src/attention.zig:60-153), null sink.
+ * q is [q_rows, q_cols], k is [k_rows, k_cols], v is [v_rows, v_cols], out is
+ * [q_rows, n_heads*dim]; lse (optional, may be NULL) is [q_rows, n_heads].
+ * The shapes are passed separately so the reference's refusals can be restated.
+ * threads > 1 spreads the (head) loop over OpenMP threads; every (head, row) is
+ * computed by exactly one thread in the same order, so results do not depend on it.
+ */
+int zto_attention_forward(const float *q, size_t q_rows, size_t q_cols, const float *k,
+                          size_t k_rows, size_t k_cols, const float *v, size_t v_rows,
+                          size_t v_cols, size_t n_heads, size_t n_kv_heads, size_t dim,
+                          float *out, float *lse, int threads) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (k_rows != v_rows || k_rows != q_rows || k_cols != n_kv_heads * dim || v_cols != k_cols ||
+        q_cols != n_heads * dim)
+        return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const double scale = 1.0 / sqrt((double)dim);
+    const size_t T = q_rows;
+    if (T == 0) return ZTO_OK;
+    int failed = 0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads)
+    {
+        double *scores = (double *)malloc(sizeof(double) * T);
+        if (!scores) {
+#pragma omp atomic write
+            failed = 1;
+        }
+        /* (head, row-block) units so that more threads than heads still help;
+         * rows are independent, so the split changes no value. */
+        const size_t blk = 64;
+        const size_t n_blk = (T + blk - 1) / blk;
+        const long units = (long)(n_heads * n_blk);
+#pragma omp for schedule(dynamic, 1)
+        for (long u = 0; u < units; ++u) {
+            if (!scores) continue;
+            const size_t h = (size_t)u / n_blk;
+            /* later row blocks are heavier; walk them first for balance */
+            const size_t b = n_blk - 1 - (size_t)u % n_blk;
+            const size_t kv = h / group;
+            const size_t t_end = (b + 1) * blk < T ? (b + 1) * blk : T;
+            for (size_t t = b * blk; t < t_end; ++t) {
+                zto_row(q + t * q_cols + h * dim, k, v, k_cols, kv * dim, dim, t + 1, scale, scores,
+                        out + t * q_cols + h * dim, lse ? lse + t * n_heads + h : NULL);
+            }
+        }
+        free(scores);
+    }
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
+/*
+ * The C ABI's general forward (q_offset / n_keys form), stated on the CPU so the
+ * decode use of zt_attn_forward has a checker: query row t sits at absolute
+ * position q_offset + t and sees keys 0 .. min(n_keys, q_offset + t + 1) - 1
+ * (src/cuda/attn_kernels.cu:276-283,310-321).  With q_offset = 0, n_keys = T it
+ * is zto_attention_forward; with T = 1, q_offset = n_keys - 1 it is zto_attn_step.
+ */
+int zto_attention_forward_at(const float *q, const float *k, const float *v, float *out, float *lse,
+                             size_t T, size_t n_heads, size_t n_kv_heads, size_t dim,
+                             size_t q_offset, size_t n_keys, int threads) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (T < 1 || n_keys < 1 || q_offset + T > n_keys) return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const size_t q_cols = n_heads * dim, kv_cols = n_kv_heads * dim;
+    const double scale = 1.0 / sqrt((double)dim);
+    int failed = 0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads)
+    {
+        double *scores = (double *)malloc(sizeof(double) * n_keys);
+        if (!scores) {
+#pragma omp atomic write
+            failed = 1;
+        }
+        const long units = (long)(n_heads * T);
+#pragma omp for schedule(dynamic, 1)
+        for (long u = 0; u < units; ++u) {
+            if (!scores) continue;
+            const size_t h = (size_t)u / T, t = (size_t)u % T;
+            size_t n_vis = q_offset + t + 1;
+            if (n_vis > n_keys) n_vis = n_keys;
+            zto_row(q + t * q_cols + h * dim, k, v, kv_cols, (h / group) * dim, dim, n_vis, scale,
+                    scores, out + t * q_cols + h * dim, lse ? lse + t * n_heads + h : NULL);
+        }
+        free(scores);
+    }
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
+/*
+ * decode.attnStep (src/decode.zig:326-392): one query row over the filled prefix
+ * of one layer's cache.  k_cache/v_cache are [n_ctx, cache_cols] row-major and
+ * n_keys = layer.visible() rows of them are filled, the newest being this
+ * token's own (append-before-attend, decode.zig:259).
+ */
+int zto_attn_step(const float *q, size_t q_cols, const float *k_cache, const float *v_cache,
+                  size_t k_cols, size_t v_cols, size_t n_keys, size_t n_heads, size_t n_kv_heads,
+                  size_t dim, float *out, float *lse, int threads) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (q_cols != n_heads * dim || k_cols != n_kv_heads * dim || v_cols != n_kv_heads * dim)
+        return ZTO_DIMENSION_MISMATCH;
+    if (n_keys < 1) return ZTO_DIMENSION_MISMATCH; /* decode.zig:350 */
+    const size_t group = n_heads / n_kv_heads;
+    const double scale = 1.0 / sqrt((double)dim);
+    int failed = 0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads)
+    {
+        double *scores = (double *)malloc(sizeof(double) * n_keys);
+        if (!scores) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (long h = 0; h < (long)n_heads; ++h) {
+            if (!scores) continue;
+            zto_row(q + (size_t)h * dim, k_cache, v_cache, k_cols, ((size_t)h / group) * dim, dim,
+                    n_keys, scale, scores, out + (size_t)h * dim, lse ? lse + h : NULL);
+        }
+        free(scores);
+    }
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
+/*
+ * autograd.attentionBackward (src/autograd.zig:636-842), one KV head's group.
+ *
+ * The reference unrolls four loops eight ways without ever adding one lane to
+ * another (autograd.zig:622-635), so the scalar loops below run the same terms
+ * into the same accumulator chains in the same order.
+ *
+ * dq is assigned (one f64 chain per element, `* scale` applied per term, one
+ * narrowing).  dk and dv are f32 accumulators that receive one f32-narrowed term
+ * per (head of the group, query row >= key), heads outer, rows ascending.
+ * probs, d_probs and p_ds are caller scratch of T doubles each.
+ */
+static void zto_backward_group(const float *q, const float *k, const float *v, const float *dout,
+                               size_t T, size_t q_cols, size_t k_cols, size_t dim, size_t group,
+                               size_t kv, double scale, double *probs, double *d_probs,
+                               double *p_ds, float *dq, float *dk, float *dv) {
+    for (size_t h = kv * group; h < (kv + 1) * group; ++h) {
+        for (size_t t = 0; t < T; ++t) {
+            const float *q_head = q + t * q_cols + h * dim;
+            const float *dh = dout + t * q_cols + h * dim;
+            /* softmax rebuild, autograd.zig:735-770 */
+            double row_max = -INFINITY;
+            for (size_t s = 0; s <= t; ++s) {
+                const float *k_head = k + s * k_cols + kv * dim;
+                double dot = 0.0;
+                for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
+                probs[s] = dot * scale;
+                if (probs[s] > row_max) row_max = probs[s];
+            }
+            double denom = 0.0;
+            for (size_t s = 0; s <= t; ++s) {
+                probs[s] = exp(probs[s] - row_max);
+                denom += probs[s];
+            }
+            for (size_t s = 0; s <= t; ++s) probs[s] /= denom;
+            /* d p and the Jacobian's dot, autograd.zig:774-797 */
+            double dot_pp = 0.0;
+            for (size_t s = 0; s <= t; ++s) {
+                const float *v_head = v + s * k_cols + kv * dim;
+                double acc = 0.0;
+                for (size_t j = 0; j < dim; ++j) acc += (double)dh[j] * (double)v_head[j];
+                d_probs[s] = acc;
+                dot_pp += probs[s] * acc;
+            }
+            for (size_t s = 0; s <= t; ++s) p_ds[s] = probs[s] * (d_probs[s] - dot_pp);
+            /* dq, autograd.zig:803-820 */
+            for (size_t j = 0; j < dim; ++j) {
+                double acc = 0.0;
+                for (size_t s = 0; s <= t; ++s)
+                    acc += p_ds[s] * (double)k[s * k_cols + kv * dim + j] * scale;
+                dq[t * q_cols + h * dim + j] = (float)acc;
+            }
+            /* dk, dv: f32 read-modify-write of an f32-narrowed term,
+             * autograd.zig:821-838 */
+            for (size_t s = 0; s <= t; ++s) {
+                float *dk_row = dk + s * k_cols + kv * dim;
+                float *dv_row = dv + s * k_cols + kv * dim;
+                const double p_ds_s = p_ds[s];
+                const double probs_s = probs[s];
+                for (size_t j = 0; j < dim; ++j) {
+                    dk_row[j] += (float)(p_ds_s * (double)q_head[j] * scale);
+                    dv_row[j] += (float)(probs_s * (double)dh[j]);
+                }
+            }
+        }
+    }
+}
+
+/*
+ * autograd.attentionBackward, whole tensors, with the reference's refusals
+ * (autograd.zig:659-685).  Heads of different KV groups touch disjoint dk/dv
+ * columns, so the OpenMP split is over KV heads and keeps the reference's order
+ * inside each; the result does not depend on the thread count.
+ */
+int zto_attention_backward(const float *q, size_t q_rows, size_t q_cols, const float *k,
+                           size_t k_rows, size_t k_cols, const float *v, size_t v_rows,
+                           size_t v_cols, const float *dout, size_t dout_rows, size_t dout_cols,
+                           size_t n_heads, size_t n_kv_heads, size_t dim, float *dq, float *dk,
+                           float *dv, int threads) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (k_rows != v_rows || k_rows != q_rows || k_cols != n_kv_heads * dim || v_cols != k_cols ||
+        q_cols != n_heads * dim)
+        return ZTO_DIMENSION_MISMATCH;
+    if (dout_rows != q_rows || dout_cols != n_heads * dim) return ZTO_DIMENSION_MISMATCH;
+    const size_t T = q_rows;
+    const size_t group = n_heads / n_kv_heads;
+    const double scale = 1.0 / sqrt((double)dim);
+    /* Tensor.init zeroes (autograd.zig:700-704). */
+    memset(dq, 0, sizeof(float) * T * q_cols);
+    memset(dk, 0, sizeof(float) * T * k_cols);
+    memset(dv, 0, sizeof(float) * T * k_cols);
+    if (T == 0) return ZTO_OK;
+    int failed = 0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads)
+    {
+        double *probs = (double *)malloc(sizeof(double) * T);
+        double *d_probs = (double *)malloc(sizeof(double) * T);
+        double *p_ds = (double *)malloc(sizeof(double) * T);
+        const int ok = probs && d_probs && p_ds;
+        if (!ok) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (long kv = 0; kv < (long)n_kv_heads; ++kv) {
+            if (!ok) continue;
+            zto_backward_group(q, k, v, dout, T, q_cols, k_cols, dim, group, (size_t)kv, scale,
+                               probs, d_probs, p_ds, dq, dk, dv);
+        }
+        free(probs);
+        free(d_probs);
+        free(p_ds);
+    }
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
+/*
+ * One KV group of the backward only (all rows): the unit a CPU baseline times
+ * when the whole tensor would take hours.  Writes dq columns of the group's
+ * query heads and dk/dv columns of KV head `kv`; everything else is untouched.
+ */
+int zto_attention_backward_kv_group(const float *q, const float *k, const float *v,
+                                    const float *dout, size_t T, size_t n_heads, size_t n_kv_heads,
+                                    size_t dim, size_t kv, float *dq, float *dk, float *dv) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (kv >= n_kv_heads) return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const size_t q_cols = n_heads * dim, k_cols = n_kv_heads * dim;
+    const double scale = 1.0 / sqrt((double)dim);
+    double *probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+    double *d_probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+    double *p_ds = (double *)malloc(sizeof(double) * (T ? T : 1));
+    if (!probs || !d_probs || !p_ds) {
+        free(probs);
+        free(d_probs);
+        free(p_ds);
+        return ZTO_OUT_OF_MEMORY;
+    }
+    for (size_t s = 0; s < T; ++s)
+        for (size_t j = 0; j < dim; ++j) {
+            dk[s * k_cols + kv * dim + j] = 0.0f;
+            dv[s * k_cols + kv * dim + j] = 0.0f;
+        }
+    zto_backward_group(q, k, v, dout, T, q_cols, k_cols, dim, group, kv, scale, probs, d_probs,
+                       p_ds, dq, dk, dv);
+    free(probs);
+    free(d_probs);
+    free(p_ds);
+    return ZTO_OK;
+}
+
+/*
+ * One (head, row range) of the forward: the unit a CPU baseline times when the
+ * whole tensor would take hours.  Rows [t0, t1) of head h, training shape.
+ */
+int zto_attention_forward_rows(const float *q, const float *k, const float *v, float *out,
+                               float *lse, size_t T, size_t n_heads, size_t n_kv_heads, size_t dim,
+                               size_t h, size_t t0, size_t t1) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (h >= n_heads || t0 > t1 || t1 > T) return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const size_t q_cols = n_heads * dim, k_cols = n_kv_heads * dim;
+    const double scale = 1.0 / sqrt((double)dim);
+    double *scores = (double *)malloc(sizeof(double) * (T ? T : 1));
+    if (!scores) return ZTO_OUT_OF_MEMORY;
+    for (size_t t = t0; t < t1; ++t)
+        zto_row(q + t * q_cols + h * dim, k, v, k_cols, (h / group) * dim, dim, t + 1, scale, scores,
+                out + t * q_cols + h * dim, lse ? lse + t * n_heads + h : NULL);
+    free(scores);
+    return ZTO_OK;
+}
+
+/* ---- kv_cache.Layer (src/kv_cache.zig:60-135), storage semantics only ------ */
+
+typedef struct {
+    float *k; /* [n_ctx, width] */
+    float *v; /* [n_ctx, width] */
+    size_t n_ctx, width, len;
+} zto_layer;
+
+int zto_layer_init(zto_layer *l, size_t n_ctx, size_t width) {
+    if (n_ctx == 0 || width == 0) return ZTO_DIMENSION_MISMATCH; /* kv_cache.zig:66 */
+    l->k = (float *)calloc(n_ctx * width, sizeof(float));
+    l->v = (float *)calloc(n_ctx * width, sizeof(float));
+    if (!l->k || !l->v) {
+        free(l->k);
+        free(l->v);
+        l->k = l->v = NULL;
+        return ZTO_OUT_OF_MEMORY;
+    }
+    l->n_ctx = n_ctx;
+    l->width = width;
+    l->len = 0;
+    return ZTO_OK;
+}
+
+void zto_layer_deinit(zto_layer *l) {
+    free(l->k);
+    free(l->v);
+    l->k = l->v = NULL;
+    l->len = 0;
+}
+
+/* kv_cache.zig:88-95: width check first, then Full, and nothing is written on
+ * either refusal. */
+int zto_layer_append(zto_layer *l, const float *k_row, size_t k_len, const float *v_row,
+                     size_t v_len) {
+    if (k_len != l->width || v_len != l->width) return ZTO_DIMENSION_MISMATCH;
+    if (l->len >= l->n_ctx) return ZTO_FULL;
+    memcpy(l->k + l->len * l->width, k_row, sizeof(float) * l->width);
+    memcpy(l->v + l->len * l->width, v_row, sizeof(float) * l->width);
+    l->len += 1;
+    return ZTO_OK;
+}
+
+size_t zto_layer_visible(const zto_layer *l) { return l->len; }
+size_t zto_layer_bytes(const zto_layer *l) { return 2 * l->n_ctx * l->width * sizeof(float); }
+
+/* ---- device.zig's pure host arithmetic ------------------------------------ */
+
+/* bytesFor (src/cuda/device.zig:162-171). kind: 0 query_headed, 1 kv_headed, 2 per_row. */
+int zto_bytes_for(int kind, uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim,
+                  uint64_t *out_bytes) {
+    if (t == 0 || dim == 0 || n_heads == 0 || n_kv_heads == 0) return ZTO_DEGENERATE_SHAPE;
+    uint64_t cols;
+    if (kind == 0) {
+        if (__builtin_mul_overflow(n_heads, dim, &cols)) return ZTO_SHAPE_TOO_LARGE;
+    } else if (kind == 1) {
+        if (__builtin_mul_overflow(n_kv_heads, dim, &cols)) return ZTO_SHAPE_TOO_LARGE;
+    } else {
+        cols = n_heads;
+    }
+    uint64_t elems, bytes;
+    if (__builtin_mul_overflow(t, cols, &elems)) return ZTO_SHAPE_TOO_LARGE;
+    if (__builtin_mul_overflow(elems, (uint64_t)sizeof(float), &bytes)) return ZTO_SHAPE_TOO_LARGE;
+    *out_bytes = bytes;
+    return ZTO_OK;
+}
+
+/* forwardBounds (src/cuda/device.zig:489-501): 0 = addressable. */
+int zto_forward_bounds(int c_t, int q_offset, int n_keys, int t) {
+    if (n_keys < 1 || n_keys > c_t) return ZTO_SHAPE_TOO_LARGE;
+    if (t < 1 || t > c_t) return ZTO_SHAPE_TOO_LARGE;
+    if (q_offset < 0 || q_offset > c_t || t > c_t - q_offset) return ZTO_SHAPE_TOO_LARGE;
+    if (q_offset + t > n_keys) return ZTO_SHAPE_TOO_LARGE;
+    return ZTO_OK;
+}
+
+/* ---- seeded inputs --------------------------------------------------------- */
+
+/* The reference's fixture generator (src/cuda/attn_twin.zig:283-289): a 32-bit
+ * LCG, value = (x >> 8) / 2^24 - 0.5. */
+void zto_fill_lcg(float *data, size_t n, uint32_t seed) {
+    uint32_t x = seed;
+    for (size_t i = 0; i < n; ++i) {
+        x = x * 1664525u + 1013904223u;
+        data[i] = (float)(x >> 8) / 16777216.0f - 0.5f;
+    }
+}
+
+/* The decode test's index hash in [-1, 1) (src/decode_test.zig:35-42). The
+ * reference multiplies a usize and truncates to u32, which equals the product
+ * taken modulo 2^32. */
+float zto_fill_hash(uint64_t i) {
+    uint32_t x = (uint32_t)(i * 2654435761ull);
+    x ^= x >> 15;
+    x *= 2246822519u;
+    x ^= x >> 13;
+    return (float)(x >> 8) / 8388608.0f - 1.0f;
+}
+
+/* i.i.d. N(0,1) in f32 for the benchmark configurations: splitmix64 counter ->
+ * two uniforms -> Box-Muller in f64 -> narrow. Element i of stream `stream`
+ * depends only on (seed, stream, i), so any slice can be regenerated anywhere. */
+static uint64_t zto_splitmix(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+void zto_fill_normal(float *data, size_t n, uint64_t seed, uint64_t stream, uint64_t first) {
+    const uint64_t key = zto_splitmix(seed * 4u + stream);
+#pragma omp parallel for schedule(static)
+    for (long ii = 0; ii < (long)n; ++ii) {
+        const uint64_t i = first + (uint64_t)ii;
+        const uint64_t pair = i >> 1;
+        const uint64_t a = zto_splitmix(key ^ (2 * pair));
+        const uint64_t b = zto_splitmix(key ^ (2 * pair + 1));
+        const double u1 = ((double)(a >> 11) + 1.0) * (1.0 / 9007199254740992.0); /* (0,1] */
+        const double u2 = (double)(b >> 11) * (1.0 / 9007199254740992.0);         /* [0,1) */
+        const double r = sqrt(-2.0 * log(u1));
+        const double th = 6.283185307179586476925286766559 * u2;
+        data[ii] = (float)((i & 1) ? r * sin(th) : r * cos(th));
+    }
+}

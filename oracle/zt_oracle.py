@@ -1,0 +1,253 @@
+"""ctypes binding of the CPU oracle (oracle/zt_oracle.c).  TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this
+module; the shipped library never does.  Arrays are numpy float32, C-contiguous.
+The functions mirror the reference's Zig API closely enough that the tests read
+like the reference's own: errors come back as exceptions named after the Zig
+error values (src/attention.zig:71-79, src/kv_cache.zig Error, src/cuda/device.zig Error).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libzt_oracle.so")
+
+
+class InvalidHeadConfig(Exception):
+    pass
+
+
+class DimensionMismatch(Exception):
+    pass
+
+
+class Full(Exception):
+    pass
+
+
+class ShapeTooLarge(Exception):
+    pass
+
+
+class DegenerateShape(Exception):
+    pass
+
+
+_ERR = {1: InvalidHeadConfig, 2: DimensionMismatch, 3: MemoryError, 4: Full, 5: ShapeTooLarge,
+        6: DegenerateShape}
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with gcc if the shared object is missing or stale."""
+    src = os.path.join(_HERE, "zt_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(
+            ["gcc", "-O3", "-fno-fast-math", "-ffp-contract=off", "-fopenmp", "-fPIC", "-Wall",
+             "-Wextra", "-std=c11", "-shared", "-o", _SO, src, "-lm"])
+    return _SO
+
+
+_lib = None
+_fp = C.POINTER(C.c_float)
+_sz = C.c_size_t
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.zto_attention_forward.argtypes = [_fp, _sz, _sz, _fp, _sz, _sz, _fp, _sz, _sz, _sz, _sz,
+                                               _sz, _fp, _fp, C.c_int]
+        _lib.zto_attention_forward_at.argtypes = [_fp, _fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
+                                                  _sz, C.c_int]
+        _lib.zto_attn_step.argtypes = [_fp, _sz, _fp, _fp, _sz, _sz, _sz, _sz, _sz, _sz, _fp, _fp,
+                                       C.c_int]
+        _lib.zto_attention_backward.argtypes = [_fp, _sz, _sz, _fp, _sz, _sz, _fp, _sz, _sz, _fp, _sz,
+                                                _sz, _sz, _sz, _sz, _fp, _fp, _fp, C.c_int]
+        _lib.zto_attention_backward_kv_group.argtypes = [_fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
+                                                         _fp, _fp, _fp]
+        _lib.zto_attention_forward_rows.argtypes = [_fp, _fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
+                                                    _sz, _sz]
+        _lib.zto_bytes_for.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                       C.POINTER(C.c_uint64)]
+        _lib.zto_forward_bounds.argtypes = [C.c_int] * 4
+        _lib.zto_fill_lcg.argtypes = [_fp, _sz, C.c_uint32]
+        _lib.zto_fill_lcg.restype = None
+        _lib.zto_fill_hash.argtypes = [C.c_uint64]
+        _lib.zto_fill_hash.restype = C.c_float
+        _lib.zto_fill_normal.argtypes = [_fp, _sz, C.c_uint64, C.c_uint64, C.c_uint64]
+        _lib.zto_fill_normal.restype = None
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise _ERR.get(rc, RuntimeError)(f"oracle error {rc}")
+
+
+def _f32(a) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(_fp)
+
+
+def _2d(a):
+    a = _f32(a)
+    if a.ndim != 2:
+        raise ValueError("expected a [rows, cols] array")
+    return a
+
+
+def attention_forward(q, k, v, n_heads: int, n_kv_heads: int, head_dim: int, *, want_lse=False,
+                      threads: int = 1):
+    """attention.forward (src/attention.zig:36-153). Returns out, or (out, lse)."""
+    q, k, v = _2d(q), _2d(k), _2d(v)
+    out = np.zeros((q.shape[0], n_heads * head_dim), dtype=np.float32)
+    lse = np.zeros((q.shape[0], n_heads), dtype=np.float32) if want_lse else None
+    _check(lib().zto_attention_forward(_p(q), q.shape[0], q.shape[1], _p(k), k.shape[0], k.shape[1],
+                                       _p(v), v.shape[0], v.shape[1], n_heads, n_kv_heads, head_dim,
+                                       _p(out), _p(lse) if want_lse else None, threads))
+    return (out, lse) if want_lse else out
+
+
+def attention_forward_at(q, k, v, n_heads, n_kv_heads, head_dim, q_offset, n_keys, *,
+                         want_lse=False, threads=1):
+    """The C ABI's q_offset/n_keys forward on the CPU (src/cuda/attn_kernels.cu:276-321)."""
+    q, k, v = _2d(q), _2d(k), _2d(v)
+    T = q.shape[0]
+    assert q.shape[1] == n_heads * head_dim and k.shape[1] == n_kv_heads * head_dim
+    assert k.shape[0] >= n_keys and v.shape[0] >= n_keys
+    out = np.zeros((T, n_heads * head_dim), dtype=np.float32)
+    lse = np.zeros((T, n_heads), dtype=np.float32) if want_lse else None
+    _check(lib().zto_attention_forward_at(_p(q), _p(k), _p(v), _p(out),
+                                          _p(lse) if want_lse else None, T, n_heads, n_kv_heads,
+                                          head_dim, q_offset, n_keys, threads))
+    return (out, lse) if want_lse else out
+
+
+def attention_backward(q, k, v, dout, n_heads, n_kv_heads, head_dim, *, threads=1):
+    """autograd.attentionBackward (src/autograd.zig:636-842). Returns dq, dk, dv."""
+    q, k, v, dout = _2d(q), _2d(k), _2d(v), _2d(dout)
+    dq = np.zeros_like(q)
+    dk = np.zeros_like(k)
+    dv = np.zeros_like(v)
+    _check(lib().zto_attention_backward(_p(q), q.shape[0], q.shape[1], _p(k), k.shape[0], k.shape[1],
+                                        _p(v), v.shape[0], v.shape[1], _p(dout), dout.shape[0],
+                                        dout.shape[1], n_heads, n_kv_heads, head_dim, _p(dq), _p(dk),
+                                        _p(dv), threads))
+    return dq, dk, dv
+
+
+def attention_backward_kv_group(q, k, v, dout, n_heads, n_kv_heads, head_dim, kv):
+    """One KV head's share of attentionBackward; other columns come back as zeros."""
+    q, k, v, dout = _2d(q), _2d(k), _2d(v), _2d(dout)
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    _check(lib().zto_attention_backward_kv_group(_p(q), _p(k), _p(v), _p(dout), q.shape[0], n_heads,
+                                                 n_kv_heads, head_dim, kv, _p(dq), _p(dk), _p(dv)))
+    return dq, dk, dv
+
+
+def attention_forward_rows(q, k, v, n_heads, n_kv_heads, head_dim, h, t0, t1):
+    """Rows [t0, t1) of head h of attention.forward; returns ([t1-t0, D], [t1-t0])."""
+    q, k, v = _2d(q), _2d(k), _2d(v)
+    out = np.zeros_like(q)
+    lse = np.zeros((q.shape[0], n_heads), dtype=np.float32)
+    _check(lib().zto_attention_forward_rows(_p(q), _p(k), _p(v), _p(out), _p(lse), q.shape[0],
+                                            n_heads, n_kv_heads, head_dim, h, t0, t1))
+    return out[t0:t1, h * head_dim:(h + 1) * head_dim].copy(), lse[t0:t1, h].copy()
+
+
+class Layer:
+    """kv_cache.Layer (src/kv_cache.zig:60-135): k, v [n_ctx, width] and a fill count."""
+
+    def __init__(self, n_ctx: int, width: int):
+        if n_ctx == 0 or width == 0:
+            raise DimensionMismatch("kv_cache.Layer.init")
+        self.k = np.zeros((n_ctx, width), dtype=np.float32)
+        self.v = np.zeros((n_ctx, width), dtype=np.float32)
+        self.len = 0
+
+    def append(self, k_row, v_row) -> None:
+        k_row, v_row = _f32(k_row).ravel(), _f32(v_row).ravel()
+        if k_row.size != self.k.shape[1] or v_row.size != self.v.shape[1]:
+            raise DimensionMismatch("kv_cache.Layer.append")
+        if self.len >= self.k.shape[0]:
+            raise Full("kv_cache.Layer.append")
+        self.k[self.len] = k_row
+        self.v[self.len] = v_row
+        self.len += 1
+
+    def visible(self) -> int:
+        return self.len
+
+    def bytes(self) -> int:
+        return (self.k.size + self.v.size) * 4
+
+
+def attn_step(q, layer: Layer, n_heads, n_kv_heads, head_dim, *, want_lse=False, threads=1):
+    """decode.attnStep (src/decode.zig:326-392): q is [1, n_heads*head_dim]."""
+    q = _2d(q)
+    out = np.zeros((1, n_heads * head_dim), dtype=np.float32)
+    lse = np.zeros((1, n_heads), dtype=np.float32) if want_lse else None
+    _check(lib().zto_attn_step(_p(q), q.shape[1], _p(layer.k), _p(layer.v), layer.k.shape[1],
+                               layer.v.shape[1], layer.visible(), n_heads, n_kv_heads, head_dim,
+                               _p(out), _p(lse) if want_lse else None, threads))
+    return (out, lse) if want_lse else out
+
+
+def attn_step_raw(q, k_cache, v_cache, n_keys, n_heads, n_kv_heads, head_dim, *, threads=1):
+    """attnStep over bare cache arrays [n_ctx, n_kv_heads*head_dim]; returns (out[H*D], lse[H])."""
+    q = _f32(q).reshape(1, -1)
+    k_cache, v_cache = _2d(k_cache), _2d(v_cache)
+    out = np.zeros((n_heads * head_dim,), dtype=np.float32)
+    lse = np.zeros((n_heads,), dtype=np.float32)
+    _check(lib().zto_attn_step(_p(q), q.shape[1], _p(k_cache), _p(v_cache), k_cache.shape[1],
+                               v_cache.shape[1], n_keys, n_heads, n_kv_heads, head_dim, _p(out),
+                               _p(lse), threads))
+    return out, lse
+
+
+KIND_QUERY_HEADED, KIND_KV_HEADED, KIND_PER_ROW = 0, 1, 2
+
+
+def bytes_for(kind: int, t: int, n_heads: int, n_kv_heads: int, dim: int) -> int:
+    """device.bytesFor (src/cuda/device.zig:162-171)."""
+    out = C.c_uint64(0)
+    _check(lib().zto_bytes_for(kind, t, n_heads, n_kv_heads, dim, C.byref(out)))
+    return out.value
+
+
+def forward_bounds(c_t: int, q_offset: int, n_keys: int, t: int) -> None:
+    """device.forwardBounds (src/cuda/device.zig:489-501); raises ShapeTooLarge."""
+    _check(lib().zto_forward_bounds(c_t, q_offset, n_keys, t))
+
+
+def fill_lcg(n: int, seed: int) -> np.ndarray:
+    """attn_twin.zig's fixture generator (src/cuda/attn_twin.zig:283-289)."""
+    a = np.empty(n, dtype=np.float32)
+    lib().zto_fill_lcg(_p(a), n, seed)
+    return a
+
+
+def fill_hash(i: int) -> float:
+    """decode_test.zig's index hash (src/decode_test.zig:35-42)."""
+    return float(lib().zto_fill_hash(i))
+
+
+def fill_normal(shape, seed: int, stream: int, first: int = 0, out: np.ndarray | None = None):
+    """i.i.d. N(0,1) f32: element i of a stream depends only on (seed, stream, first+i).
+
+    Streams by convention: 0 q, 1 k, 2 v, 3 dout.
+    """
+    n = int(np.prod(shape))
+    a = out if out is not None else np.empty(n, dtype=np.float32)
+    lib().zto_fill_normal(a.ctypes.data_as(_fp), n, seed, stream, first)
+    return a.reshape(shape)
