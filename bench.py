@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gather]
+
+One "step" is one causal GQA forward + backward pass over one batch of the sweep
+configuration (batch 8, 32 query heads over 8 KV heads, head_dim 128, T 4096, f32,
+i.i.d. N(0,1) inputs), i.e. 3.5 * 2*B*H*D*T*(T+1) floating-point operations by the
+reference's own count (src/scale.zig:157-163; the backward is 5 GEMMs against the
+forward's 2).  The line printed also carries the decode configuration (batch 64,
+context 8192, Llama-3-8B heads) in GB/s, the roofline of the dominant kernel, the CPU
+baseline (the oracle port timed on a bounded sample) and the end-to-end figure through
+the reference-facing C ABI with host buffers.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU
+workload on its own batch -- sequences are independent, so there is no data-path
+collective -- and the value is the whole job's rate over the slowest rank's time.
+`--gather` adds the NCCL all-gather that returns the sharded outputs to every rank.
+
+`--impl reference` times the reference's CPU implementation of the same step (the C
+restatement under oracle/, the reference itself being Zig and not buildable here) on the
+host cores, on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# The sweep point the headline is quoted on, and the decode configuration.
+PREFILL = dict(batch=8, T=4096, n_heads=32, n_kv_heads=8, head_dim=128)
+DECODE = dict(batch=64, n_ctx=8192, n_heads=32, n_kv_heads=8, head_dim=128)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def fwd_flops(batch, T, n_heads, head_dim):
+    return 2.0 * batch * n_heads * head_dim * T * (T + 1)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = f"/tmp/zt_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the CPU port on a bounded sample
+# ------------------------------------------------------------------------------------------------
+
+def cpu_sample(threads: int, row_stride: int, repeats: int, warmup: int):
+    """Times every row_stride-th query row of the prefill step on the host.  Returns
+    (flops per sample, [seconds per timed sample])."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import zt_oracle as oracle
+    c = PREFILL
+    B, T, H, Hkv, D = c["batch"], c["T"], c["n_heads"], c["n_kv_heads"], c["head_dim"]
+    q = oracle.fill_normal((B, T, H * D), 0, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 0, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 0, 2)
+    do = oracle.fill_normal((B, T, H * D), 0, 3)
+    times, flops = [], 0.0
+    for i in range(warmup + repeats):
+        t0 = time.perf_counter()
+        flops, *_ = oracle.sampled_step(q, k, v, do, H, Hkv, D, row_stride, row_stride - 1, threads=threads)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return flops, times
+
+
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    threads = host_threads()
+    # about 1/256 of the rows: ~15 GFLOP per sample, a second or so on a few dozen cores
+    stride = 256
+    flops, times = cpu_sample(threads, stride, args.steps, min(args.warmup, 1))
+    sec = sum(times) / len(times)
+    value = flops / sec / 1e12
+    c = PREFILL
+    line = {
+        "impl": "reference", "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64-accumulate/f32-store",
+        "data": "synthetic",
+        "config": {"workload": "causal GQA attention fwd+bwd, batch 8, 32/8 heads, head_dim 128, T 4096, f32",
+                   **c},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"every {stride}th query row of every head of the batch "
+                                   f"({flops / 1e9:.2f} GFLOP per step, exact count), OpenMP over (item, KV head)"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "C restatement of src/attention.zig + autograd.attentionBackward (oracle/zt_oracle.c); the Zig "
+                "reference needs Zig 0.16 and cannot be built on this box",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    zt = importlib.import_module("z-transformer_b200")
+    L = zt.lib.load()
+    peaks, peak_kind = load_peaks()
+
+    c = PREFILL
+    B, T, H, Hkv, D = c["batch"], c["T"], c["n_heads"], c["n_kv_heads"], c["head_dim"]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    q, do = (torch.randn((B, T, H * D), generator=gen, device=dev) for _ in range(2))
+    k, v = (torch.randn((B, T, Hkv * D), generator=gen, device=dev) for _ in range(2))
+    out, dq = torch.empty_like(q), torch.empty_like(q)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    lse, delta = (torch.empty((B, T, H), device=dev) for _ in range(2))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, H, Hkv, D)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+    def step():
+        rc = L.zt_attn_forward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                       B, T, H, Hkv, D, stream)
+        rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                         do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                         delta.data_ptr(), ws.data_ptr(), ws_bytes, B, T, H, Hkv, D, stream)
+        if rc != 0:
+            raise RuntimeError("libztattn refused the step: " + zt.lib.last_error())
+        if args.gather and world > 1:
+            for x in (out, dq, dk, dv):
+                zt.sharding.gather_batch(x, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    zt.lib.profile(True)
+    zt.lib.profile_read()
+    launches0 = zt.lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = zt.lib.launch_count() - launches0
+    kernels = zt.lib.profile_read()
+    zt.lib.profile(False)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    F = fwd_flops(B, T, H, D)
+    value = world * 3.5 * F / (ms_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (by summed device time over the timed region) ----------
+    # Algorithmic operations credited per launch: forward 2 GEMMs = F; key-outer backward kernel
+    # S, dP, dV, dK = 2 F; query-outer backward kernel dQ = 0.5 F (its recomputed S and dP are
+    # overhead, not credited); together the backward's 2.5 F.
+    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
+              "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
+    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+    total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
+    klist = []
+    for name, (n, ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
+        entry = {"kernel": name, "launches": n, "ms_per_launch": ms / n, "share": ms / total_kernel_ms}
+        if name in credit:
+            entry["tflops"] = credit[name] / (ms / n * 1e-3) / 1e12
+            entry["frac_of_tf32_peak"] = entry["tflops"] / tf32_peak
+        klist.append(entry)
+    dom = klist[0] if klist else None
+    roofline = None
+    if dom and "tflops" in dom:
+        roofline = {"bound": "tensor", "kernel": dom["kernel"], "achieved": dom["tflops"], "peak": tf32_peak,
+                    "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_peak, "traffic": None,
+                    "peak_source": f"{peak_kind}: TF32 dense = bf16_tflops_sustained ({peaks['bf16_tflops_sustained']}) / 2",
+                    "step_frac": value / world / tf32_peak}
+
+    # ---- end to end through the reference-facing C ABI with host buffers (rank-local) ------------
+    # device.Attn's call pattern (src/model.zig:481-514): upload q, k, v (and dout), launch, download.
+    # One batch item per zt_attn_forward / zt_attn_backward call, as the reference ABI has no batch.
+    e2e_steps = max(1, min(args.steps, 3))
+    hq, hdo = (torch.randn((B, T, H * D)).pin_memory() for _ in range(2))
+    hk, hv = (torch.randn((B, T, Hkv * D)).pin_memory() for _ in range(2))
+    hout, hdq = (torch.empty((B, T, H * D)).pin_memory() for _ in range(2))
+    hdk, hdv = (torch.empty((B, T, Hkv * D)).pin_memory() for _ in range(2))
+    holder = zt.Attn(T, H, Hkv, D, device=dev)
+
+    def e2e_step():
+        for b in range(B):
+            holder.q.copy_(hq[b].view(-1), non_blocking=True)
+            holder.k.copy_(hk[b].view(-1), non_blocking=True)
+            holder.v.copy_(hv[b].view(-1), non_blocking=True)
+            holder.dout.copy_(hdo[b].view(-1), non_blocking=True)
+            holder.forward(1, 64)
+            holder.backward(64)
+            hout[b].view(-1).copy_(holder.out, non_blocking=True)
+            hdq[b].view(-1).copy_(holder.dq, non_blocking=True)
+            hdk[b].view(-1).copy_(holder.dk, non_blocking=True)
+            hdv[b].view(-1).copy_(holder.dv, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    # the reference ABI's backward recomputes the forward (it is given neither out nor lse);
+    # the credited work is still forward + backward = 3.5 F
+    e2e_value = world * 3.5 * F / (e2e_ms * 1e-3) / 1e12
+    h2d = (2 * hq[0].numel() + 2 * hk[0].numel()) * 4 * B
+    d2h = h2d
+    del hq, hdo, hk, hv, hout, hdq, hdk, hdv, holder
+
+    # ---- decode configuration -------------------------------------------------------------------
+    d = DECODE
+    Bd, n_ctx = d["batch"], d["n_ctx"]
+    kc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
+    vc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
+    qd = torch.randn((Bd, H * D), generator=gen, device=dev)
+    n_keys = torch.full((Bd,), n_ctx, dtype=torch.int32, device=dev)
+    wsd = zt.DecodeWorkspace(Bd, n_ctx, H, Hkv, D, dev)
+    outd = torch.empty_like(qd)
+    dsteps = max(args.steps, 10)
+
+    def dstep():
+        zt.decode_attention(qd, kc, vc, n_keys, H, Hkv, D, workspace=wsd, out=outd)
+
+    for _ in range(max(args.warmup, 3)):
+        dstep()
+    barrier()
+    zt.lib.profile(True)
+    zt.lib.profile_read()
+    e0.record()
+    for _ in range(dsteps):
+        dstep()
+    e1.record()
+    barrier()
+    dk_prof = zt.lib.profile_read()
+    zt.lib.profile(False)
+    d_ms = e0.elapsed_time(e1) / dsteps
+    if world > 1:
+        t = torch.tensor([d_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        d_ms = float(t.item())
+    d_bytes = float(Bd) * n_ctx * 2 * Hkv * D * 4 + 2.0 * Bd * H * D * 4
+    d_gbs = world * d_bytes / (d_ms * 1e-3) / 1e9
+    dn, dms = dk_prof.get("decode_splitk_kernel", (1, d_ms))
+    d_kernel_gbs = d_bytes / (dms / dn * 1e-3) / 1e9
+    decode = {"metric": "decode_attn_hbm_gbs", "value": d_gbs, "unit": "GB/s", "ms_per_step": d_ms,
+              "config": {"workload": "KV-cache decode attention, batch 64, context 8192 (new token's row included), "
+                                     "32/8 heads, head_dim 128, f32", **d},
+              "bytes_per_step": d_bytes,
+              "roofline": {"bound": "hbm", "kernel": "decode_splitk_kernel", "achieved": d_kernel_gbs,
+                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d_kernel_gbs / peaks["hbm_gbs"],
+                           "traffic": None, "peak_source": f"{peak_kind}: hbm_gbs"},
+              "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in dk_prof.items()}}
+    # decode end to end with host buffers: q up, out down; the cache stays resident in HBM
+    hqd, houtd = torch.randn((Bd, H * D)).pin_memory(), torch.empty((Bd, H * D)).pin_memory()
+    barrier()
+    e0.record()
+    for _ in range(dsteps):
+        qd.copy_(hqd, non_blocking=True)
+        dstep()
+        houtd.copy_(outd, non_blocking=True)
+    e1.record()
+    barrier()
+    decode["e2e"] = {"value": world * d_bytes / (e0.elapsed_time(e1) / dsteps * 1e-3) / 1e9, "unit": "GB/s",
+                     "h2d_bytes_per_step": hqd.numel() * 4, "d2h_bytes_per_step": houtd.numel() * 4}
+    del kc, vc
+
+    # ---- CPU baseline on rank 0 at N = 1 --------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = host_threads()
+        stride = 128
+        flops, times = cpu_sample(threads, stride, 1, 0)
+        cpu = {"value": flops / times[0] / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"every {stride}th query row of every head of the batch, fwd+bwd "
+                         f"({flops / 1e9:.1f} GFLOP, exact count), one pass, {times[0]:.1f} s"}
+
+    if rank == 0:
+        line = {
+            "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "causal GQA attention fwd+bwd, batch 8 per GPU, 32/8 heads, head_dim 128, "
+                                   "T 4096, f32", **c, "l2": "inputs (1.25 GiB per step) exceed the 126 MB L2",
+                       "gather": bool(args.gather and world > 1)},
+            "roofline": roofline, "kernels": klist, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "api": "zt_attn_forward + zt_attn_backward per batch item, pinned host buffers"},
+            "gpu_launches": int(launches), "clocks": clocks, "decode": decode,
+            "paths": {"prefill": [k_["kernel"] for k_ in klist]},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--gather", action="store_true", help="time the all-gather of sharded outputs too")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

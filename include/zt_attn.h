@@ -1,0 +1,171 @@
+/*
+ * zt_attn.h -- C ABI of libztattn, a Blackwell (sm_100a) implementation of
+ * Z-TRANSFORMER's attention hot path.
+ *
+ * The first six functions are the reference library's own entry points, with the
+ * reference's names, argument order, types and return conventions, so that the
+ * reference's Zig holder (src/cuda/device.zig:58-105, `extern fn zt_attn_*`)
+ * links against this library unchanged.  The rest are additive extensions for
+ * the batched, log-sum-exp-saving, KV-cache-decode and sharded uses that the
+ * reference's single-sequence ABI cannot express.
+ *
+ * Conventions (from src/cuda/attn_kernels.cu:21-54, kept):
+ *   - every pointer is a DEVICE pointer unless its name starts with `host_`;
+ *   - the caller owns all buffers; entry points taking a `workspace` argument
+ *     never allocate.  The six reference entry points take no workspace; the
+ *     only memory they may create is one small per-device arena, made once on
+ *     first use (see zt_attn_forward below);
+ *   - return 0: the work was enqueued on `stream` (no synchronisation);
+ *     return 1: refused, with the reason on stderr and in zt_attn_last_error();
+ *     nothing was launched and no buffer was touched;
+ *   - no entry point ever ends the process.
+ *   - there is no CPU fallback anywhere: without a CUDA device every launching
+ *     entry point returns 1.
+ *
+ * Layouts: q, out, dout, dq are [T, n_heads*dim] row-major f32 with head h in
+ * columns h*dim .. (h+1)*dim-1; k, v, dk, dv are [T, n_kv_heads*dim]; query
+ * head h reads KV head h / (n_heads / n_kv_heads) (src/attention.zig:29-35).
+ * Batched forms hold `batch` such items back to back.
+ */
+#ifndef ZT_ATTN_H
+#define ZT_ATTN_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in the CUDA headers (it is `struct CUstream_st *`). */
+typedef struct CUstream_st *zt_stream_t;
+
+/* ------------------------------------------------------------------------- */
+/* The reference's six entry points                                           */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces src/cuda/attn_kernels.cu:648-659 (Zig: device.zig:58).
+ * 1 iff dim is even and 32 <= dim <= 256.  Prints nothing. */
+int zt_attn_dim_ok(int dim);
+
+/* Replace src/cuda/attn_kernels.cu:697-706 (Zig: device.zig:65-67).  The
+ * reference exports its kernels' shared-memory byte counts; the Zig side never
+ * calls them.  They keep the reference's formulas so a caller comparing numbers
+ * sees the same ones; this library's kernels size their own shared memory. */
+size_t zt_attn_forward_shmem(int dim, int tile, int group_q);
+size_t zt_attn_bwd_dq_shmem(int dim, int tile);
+size_t zt_attn_bwd_dkdv_shmem(int dim);
+
+/* Replaces src/cuda/attn_kernels.cu:833-938 (Zig: device.zig:69-86).
+ * Fused causal GQA forward.  T query rows; n_keys rows of k and v exist;
+ * q_offset is the absolute position of query row 0; key j is visible to query
+ * row t iff j <= q_offset + t and j < n_keys.  Training shape: q_offset 0,
+ * n_keys T.  Decode step: T 1, q_offset n_keys - 1.
+ * group_q and max_tile are validated exactly as the reference validates them
+ * and are otherwise advisory: tiling is this library's own business.
+ * Refusals, in the reference's order: T < 1; dim not ok; heads not a group;
+ * n_heads > 65535; group_q outside [1, 64] or dim*group_q > 1024;
+ * q_offset < 0, n_keys < 1 or q_offset > n_keys - T; max_tile < 1.
+ * A decode-shaped call (T == 1) splits the context over many blocks and keeps
+ * its partial results in a per-device arena of 16 MiB that is allocated once,
+ * on the first such call on that device. */
+int zt_attn_forward(const float *q, const float *k, const float *v, float *out, int T, int n_heads,
+                    int n_kv_heads, int dim, int group_q, int max_tile, int q_offset, int n_keys,
+                    zt_stream_t stream);
+
+/* Replaces src/cuda/attn_kernels.cu:952-1036 (Zig: device.zig:88-105).
+ * Backward of the training-shaped forward.  dq, dk, dv are ASSIGNED (no
+ * zeroing needed, nothing accumulated into).  row_max, row_den, row_del are
+ * caller scratch of [T, n_heads] floats each; on return row_max holds each
+ * row's log-sum-exp, row_den is 1 and row_del holds sum_j dout*out.  dq is used
+ * as scratch for the recomputed forward output before it receives dq.
+ * Refusals: T < 1; dim not ok; heads not a group; n_heads > 65535; max_tile < 1. */
+int zt_attn_backward(const float *q, const float *k, const float *v, const float *dout, float *dq,
+                     float *dk, float *dv, float *row_max, float *row_den, float *row_del, int T,
+                     int n_heads, int n_kv_heads, int dim, int max_tile, zt_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Extensions                                                                 */
+/* ------------------------------------------------------------------------- */
+
+/* The reason of the calling thread's most recent refusal ("" if none).  The
+ * reference only prints to stderr (src/cuda/attn_kernels.cu:21-37); bindings
+ * that cannot capture stderr read it here. */
+const char *zt_attn_last_error(void);
+
+/* 1 when stderr diagnostics are wanted (default), 0 to keep refusals silent
+ * (the return code and zt_attn_last_error() still report them). */
+void zt_attn_set_verbose(int on);
+
+/* Which implementation the next launches use: 0 = automatic (tensor-core
+ * kernels where the shape allows, SIMT elsewhere), 1 = SIMT only.  For tests
+ * and for bisecting a parity failure; returns the previous value. */
+int zt_attn_set_path(int path);
+
+/* Batched training-shaped forward: `batch` independent sequences of T rows,
+ * the batch loop around attention.forward (src/attention.zig:36-153).  Also
+ * writes lse[batch, T, n_heads] = row max + ln(denominator) of the scaled
+ * scores when lse is not NULL.  Same refusals as zt_attn_forward, plus batch < 1. */
+int zt_attn_forward_batched(const float *q, const float *k, const float *v, float *out, float *lse,
+                            int batch, int T, int n_heads, int n_kv_heads, int dim,
+                            zt_stream_t stream);
+
+/* Batched backward that consumes the forward's out and lse instead of
+ * recomputing them (autograd.attentionBackward, src/autograd.zig:636-842, is the
+ * arithmetic it must match).  delta is caller scratch [batch, T, n_heads].
+ * dq, dk, dv are assigned.  workspace/workspace_bytes: see
+ * zt_attn_backward_workspace_bytes; may be NULL/0 when that returns 0. */
+int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
+                             const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                             float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                             int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
+size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
+
+/* KV-cache decode attention for a batch of sequences: decode.attnStep
+ * (src/decode.zig:326-392) for every sequence at once, over device-resident
+ * caches laid out as kv_cache.Layer lays them out (src/kv_cache.zig:60-95):
+ * k_cache, v_cache are [batch, n_ctx, n_kv_heads*dim]; n_keys[b] in [1, n_ctx]
+ * is how many rows of sequence b are filled, INCLUDING the new token's own row
+ * (append before attend, src/decode.zig:259); q and out are
+ * [batch, n_heads*dim]; lse (may be NULL) is [batch, n_heads].
+ * The context is split over many blocks; partial results live in `workspace`
+ * (zt_attn_decode_workspace_bytes) and are merged by log-sum-exp.
+ * A sequence whose n_keys is outside [1, n_ctx] is not computed: its out row is
+ * filled with NaN and (after the stream has been synchronised)
+ * zt_attn_decode_status reports it. */
+int zt_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *n_keys,
+                   float *out, float *lse, void *workspace, size_t workspace_bytes, int batch,
+                   int n_ctx, int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
+size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim);
+
+/* After synchronising: number of sequences the last zt_attn_decode that used
+ * `workspace` skipped for a bad n_keys (the count is kept inside the workspace). */
+int zt_attn_decode_status(const void *workspace, int *host_bad_sequences);
+
+/* kv_cache.Layer.append for a batch of device-resident caches
+ * (src/kv_cache.zig:88-95): copies one new row per sequence into row n_keys[b]
+ * of its cache and increments n_keys[b].  A sequence that is full
+ * (n_keys[b] >= n_ctx) is left untouched and counted in *full_count (device int,
+ * may be NULL), the reference's Error.Full. */
+int zt_kv_append(float *k_cache, float *v_cache, int *n_keys, const float *k_new,
+                 const float *v_new, int *full_count, int batch, int n_ctx, int n_kv_heads, int dim,
+                 zt_stream_t stream);
+
+/* Number of kernels this library has launched in this process (all threads);
+ * benchmarks report the difference over their timed region. */
+unsigned long long zt_attn_launch_count(void);
+
+/* Per-kernel device timing for benchmarks.  zt_attn_profile(1) makes every later launch
+ * record a pair of CUDA events on its stream; zt_attn_profile_read waits for them, writes one
+ * line per kernel name ("name launches total_ms\n") into host_buf, forgets them, and returns
+ * the number of lines.  Off by default; when off, no event is ever created. */
+void zt_attn_profile(int on);
+int zt_attn_profile_read(char *host_buf, size_t cap);
+
+/* Name of the kernel family the most recent launching call on this thread used
+ * ("tcgen05", "simt", "decode-splitk", ...). */
+const char *zt_attn_last_path(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZT_ATTN_H */

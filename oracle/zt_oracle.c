@@ -205,7 +205,8 @@ int zto_attn_step(const float *q, size_t q_cols, const float *k_cache, const flo
 }
 
 /*
- * autograd.attentionBackward (src/autograd.zig:636-842), one KV head's group.
+ * autograd.attentionBackward (src/autograd.zig:636-842): the body of its (head, row)
+ * loop, for one query row t of head h.
  *
  * The reference unrolls four loops eight ways without ever adding one lane to
  * another (autograd.zig:622-635), so the scalar loops below run the same terms
@@ -213,63 +214,68 @@ int zto_attn_step(const float *q, size_t q_cols, const float *k_cache, const flo
  *
  * dq is assigned (one f64 chain per element, `* scale` applied per term, one
  * narrowing).  dk and dv are f32 accumulators that receive one f32-narrowed term
- * per (head of the group, query row >= key), heads outer, rows ascending.
- * probs, d_probs and p_ds are caller scratch of T doubles each.
+ * per (head of the group, query row >= key).
+ * probs, d_probs and p_ds are caller scratch of at least t + 1 doubles each.
  */
+static void zto_backward_row(const float *q, const float *k, const float *v, const float *dout,
+                             size_t q_cols, size_t k_cols, size_t dim, size_t h, size_t kv,
+                             size_t t, double scale, double *probs, double *d_probs, double *p_ds,
+                             float *dq, float *dk, float *dv) {
+    const float *q_head = q + t * q_cols + h * dim;
+    const float *dh = dout + t * q_cols + h * dim;
+    /* softmax rebuild, autograd.zig:735-770 */
+    double row_max = -INFINITY;
+    for (size_t s = 0; s <= t; ++s) {
+        const float *k_head = k + s * k_cols + kv * dim;
+        double dot = 0.0;
+        for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
+        probs[s] = dot * scale;
+        if (probs[s] > row_max) row_max = probs[s];
+    }
+    double denom = 0.0;
+    for (size_t s = 0; s <= t; ++s) {
+        probs[s] = exp(probs[s] - row_max);
+        denom += probs[s];
+    }
+    for (size_t s = 0; s <= t; ++s) probs[s] /= denom;
+    /* d p and the Jacobian's dot, autograd.zig:774-797 */
+    double dot_pp = 0.0;
+    for (size_t s = 0; s <= t; ++s) {
+        const float *v_head = v + s * k_cols + kv * dim;
+        double acc = 0.0;
+        for (size_t j = 0; j < dim; ++j) acc += (double)dh[j] * (double)v_head[j];
+        d_probs[s] = acc;
+        dot_pp += probs[s] * acc;
+    }
+    for (size_t s = 0; s <= t; ++s) p_ds[s] = probs[s] * (d_probs[s] - dot_pp);
+    /* dq, autograd.zig:803-820 */
+    for (size_t j = 0; j < dim; ++j) {
+        double acc = 0.0;
+        for (size_t s = 0; s <= t; ++s) acc += p_ds[s] * (double)k[s * k_cols + kv * dim + j] * scale;
+        dq[t * q_cols + h * dim + j] = (float)acc;
+    }
+    /* dk, dv: f32 read-modify-write of an f32-narrowed term, autograd.zig:821-838 */
+    for (size_t s = 0; s <= t; ++s) {
+        float *dk_row = dk + s * k_cols + kv * dim;
+        float *dv_row = dv + s * k_cols + kv * dim;
+        const double p_ds_s = p_ds[s];
+        const double probs_s = probs[s];
+        for (size_t j = 0; j < dim; ++j) {
+            dk_row[j] += (float)(p_ds_s * (double)q_head[j] * scale);
+            dv_row[j] += (float)(probs_s * (double)dh[j]);
+        }
+    }
+}
+
+/* One KV head's group: heads outer, rows ascending (autograd.zig:723-725). */
 static void zto_backward_group(const float *q, const float *k, const float *v, const float *dout,
                                size_t T, size_t q_cols, size_t k_cols, size_t dim, size_t group,
                                size_t kv, double scale, double *probs, double *d_probs,
                                double *p_ds, float *dq, float *dk, float *dv) {
-    for (size_t h = kv * group; h < (kv + 1) * group; ++h) {
-        for (size_t t = 0; t < T; ++t) {
-            const float *q_head = q + t * q_cols + h * dim;
-            const float *dh = dout + t * q_cols + h * dim;
-            /* softmax rebuild, autograd.zig:735-770 */
-            double row_max = -INFINITY;
-            for (size_t s = 0; s <= t; ++s) {
-                const float *k_head = k + s * k_cols + kv * dim;
-                double dot = 0.0;
-                for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
-                probs[s] = dot * scale;
-                if (probs[s] > row_max) row_max = probs[s];
-            }
-            double denom = 0.0;
-            for (size_t s = 0; s <= t; ++s) {
-                probs[s] = exp(probs[s] - row_max);
-                denom += probs[s];
-            }
-            for (size_t s = 0; s <= t; ++s) probs[s] /= denom;
-            /* d p and the Jacobian's dot, autograd.zig:774-797 */
-            double dot_pp = 0.0;
-            for (size_t s = 0; s <= t; ++s) {
-                const float *v_head = v + s * k_cols + kv * dim;
-                double acc = 0.0;
-                for (size_t j = 0; j < dim; ++j) acc += (double)dh[j] * (double)v_head[j];
-                d_probs[s] = acc;
-                dot_pp += probs[s] * acc;
-            }
-            for (size_t s = 0; s <= t; ++s) p_ds[s] = probs[s] * (d_probs[s] - dot_pp);
-            /* dq, autograd.zig:803-820 */
-            for (size_t j = 0; j < dim; ++j) {
-                double acc = 0.0;
-                for (size_t s = 0; s <= t; ++s)
-                    acc += p_ds[s] * (double)k[s * k_cols + kv * dim + j] * scale;
-                dq[t * q_cols + h * dim + j] = (float)acc;
-            }
-            /* dk, dv: f32 read-modify-write of an f32-narrowed term,
-             * autograd.zig:821-838 */
-            for (size_t s = 0; s <= t; ++s) {
-                float *dk_row = dk + s * k_cols + kv * dim;
-                float *dv_row = dv + s * k_cols + kv * dim;
-                const double p_ds_s = p_ds[s];
-                const double probs_s = probs[s];
-                for (size_t j = 0; j < dim; ++j) {
-                    dk_row[j] += (float)(p_ds_s * (double)q_head[j] * scale);
-                    dv_row[j] += (float)(probs_s * (double)dh[j]);
-                }
-            }
-        }
-    }
+    for (size_t h = kv * group; h < (kv + 1) * group; ++h)
+        for (size_t t = 0; t < T; ++t)
+            zto_backward_row(q, k, v, dout, q_cols, k_cols, dim, h, kv, t, scale, probs, d_probs,
+                             p_ds, dq, dk, dv);
 }
 
 /*
@@ -375,6 +381,67 @@ int zto_attention_forward_rows(const float *q, const float *k, const float *v, f
                 out + t * q_cols + h * dim, lse ? lse + t * n_heads + h : NULL);
     free(scores);
     return ZTO_OK;
+}
+
+/*
+ * A bounded sample of one forward+backward pass over a batch, for timing the CPU
+ * path at sizes where the whole pass takes hours: of every head of every batch item,
+ * only query rows t with t % row_stride == row_phase are computed (forward row,
+ * then backward row).  The arithmetic of a computed row is exactly the reference's;
+ * dk/dv therefore hold only the sampled rows' contributions.  (batch item, KV head)
+ * units run on separate OpenMP threads; they touch disjoint outputs.
+ * Returns through *flops the reference's own operation count for the rows computed:
+ * 4 * dim * (t + 1) per forward row (2*H*D*T*(T+1) over a whole pass,
+ * src/scale.zig:157-163) and 2.5 times that for the backward row.
+ */
+int zto_sampled_step(const float *q, const float *k, const float *v, const float *dout, float *out,
+                     float *dq, float *dk, float *dv, size_t batch, size_t T, size_t n_heads,
+                     size_t n_kv_heads, size_t dim, size_t row_stride, size_t row_phase,
+                     int do_backward, int threads, double *flops) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (row_stride == 0 || row_phase >= row_stride) return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const size_t q_cols = n_heads * dim, k_cols = n_kv_heads * dim;
+    const double scale = 1.0 / sqrt((double)dim);
+    int failed = 0;
+    double total = 0.0;
+    if (threads < 1) threads = 1;
+#pragma omp parallel num_threads(threads) reduction(+ : total)
+    {
+        double *probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+        double *d_probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+        double *p_ds = (double *)malloc(sizeof(double) * (T ? T : 1));
+        const int ok = probs && d_probs && p_ds;
+        if (!ok) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (long u = 0; u < (long)(batch * n_kv_heads); ++u) {
+            if (!ok) continue;
+            const size_t b = (size_t)u / n_kv_heads, kv = (size_t)u % n_kv_heads;
+            const float *qb = q + b * T * q_cols, *kb = k + b * T * k_cols, *vb = v + b * T * k_cols;
+            const float *gb = dout + b * T * q_cols;
+            float *ob = out + b * T * q_cols, *dqb = dq + b * T * q_cols;
+            float *dkb = dk + b * T * k_cols, *dvb = dv + b * T * k_cols;
+            for (size_t h = kv * group; h < (kv + 1) * group; ++h)
+                for (size_t t = row_phase; t < T; t += row_stride) {
+                    zto_row(qb + t * q_cols + h * dim, kb, vb, k_cols, kv * dim, dim, t + 1, scale,
+                            probs, ob + t * q_cols + h * dim, NULL);
+                    total += 4.0 * (double)dim * (double)(t + 1);
+                    if (do_backward) {
+                        zto_backward_row(qb, kb, vb, gb, q_cols, k_cols, dim, h, kv, t, scale, probs,
+                                         d_probs, p_ds, dqb, dkb, dvb);
+                        total += 10.0 * (double)dim * (double)(t + 1);
+                    }
+                }
+        }
+        free(probs);
+        free(d_probs);
+        free(p_ds);
+    }
+    *flops = total;
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
 }
 
 /* ---- kv_cache.Layer (src/kv_cache.zig:60-135), storage semantics only ------ */

@@ -73,6 +73,8 @@ def lib():
                                                          _fp, _fp, _fp]
         _lib.zto_attention_forward_rows.argtypes = [_fp, _fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
                                                     _sz, _sz]
+        _lib.zto_sampled_step.argtypes = [_fp] * 8 + [_sz] * 7 + [C.c_int, C.c_int,
+                                                               C.POINTER(C.c_double)]
         _lib.zto_bytes_for.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
                                        C.POINTER(C.c_uint64)]
         _lib.zto_forward_bounds.argtypes = [C.c_int] * 4
@@ -163,6 +165,20 @@ def attention_forward_rows(q, k, v, n_heads, n_kv_heads, head_dim, h, t0, t1):
     _check(lib().zto_attention_forward_rows(_p(q), _p(k), _p(v), _p(out), _p(lse), q.shape[0],
                                             n_heads, n_kv_heads, head_dim, h, t0, t1))
     return out[t0:t1, h * head_dim:(h + 1) * head_dim].copy(), lse[t0:t1, h].copy()
+
+
+def sampled_step(q, k, v, dout, n_heads, n_kv_heads, head_dim, row_stride, row_phase, *,
+                 backward=True, threads=1):
+    """Every row_stride-th query row of a [B, T, ...] forward(+backward) pass; returns the
+    reference's operation count for the rows computed and the partially filled outputs."""
+    q, k, v, dout = (_f32(x) for x in (q, k, v, dout))
+    B, T = q.shape[0], q.shape[1]
+    out, dq, dk, dv = np.zeros_like(q), np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    flops = C.c_double(0.0)
+    _check(lib().zto_sampled_step(_p(q), _p(k), _p(v), _p(dout), _p(out), _p(dq), _p(dk), _p(dv), B, T,
+                                  n_heads, n_kv_heads, head_dim, row_stride, row_phase,
+                                  1 if backward else 0, threads, C.byref(flops)))
+    return flops.value, out, dq, dk, dv
 
 
 class Layer:

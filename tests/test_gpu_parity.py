@@ -1,0 +1,386 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Tolerance everywhere (the stated bar for this path): |got - ref| <= 1e-5 + 1e-4 |ref|,
+element-wise, NaN counted as a failure -- for out, log-sum-exp, dq, dk and dv.
+"""
+import ctypes
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+RTOL, ATOL = 1e-4, 1e-5
+
+
+def close(got, ref, what=""):
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    err = np.abs(got - ref)
+    bad = ~(err <= ATOL + RTOL * np.abs(ref))
+    if bad.any():
+        i = int(np.argmax(np.where(np.isnan(err), np.inf, err)))
+        raise AssertionError(f"{what}: {int(bad.sum())}/{err.size} outside tolerance; worst at flat "
+                             f"index {i}: got {got.ravel()[i]!r} want {ref.ravel()[i]!r}")
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def cu(x, dev):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+
+def lcg_inputs(oracle, T, H, Hkv, D):
+    q = oracle.fill_lcg(T * H * D, 0xBEEF).reshape(T, H * D)
+    k = oracle.fill_lcg(T * Hkv * D, 0x1234).reshape(T, Hkv * D)
+    v = oracle.fill_lcg(T * Hkv * D, 0x5678).reshape(T, Hkv * D)
+    do = oracle.fill_lcg(T * H * D, 0x9ABC).reshape(T, H * D)
+    return q, k, v, do
+
+
+def normal_inputs(oracle, T, H, Hkv, D, seed):
+    return (oracle.fill_normal((T, H * D), seed, 0), oracle.fill_normal((T, Hkv * D), seed, 1),
+            oracle.fill_normal((T, Hkv * D), seed, 2), oracle.fill_normal((T, H * D), seed, 3))
+
+
+def run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D):
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    torch.cuda.synchronize()
+    return [x.cpu().numpy() for x in (o, lse, dq, dk, dv)]
+
+
+# ---- the reference's known-answer tests, through the C ABI ------------------------------------
+# The C ABI admits head_dim >= 32 only (src/cuda/attn_kernels.cu:147-148), so the literals of
+# src/attention_test.zig (head_dim 2) are embedded in the first columns of a 32-wide head with
+# zeros behind them; every expectation used below does not depend on the 1/sqrt(D) scale.
+
+def pad(a, H, d_small, D=32):
+    a = np.asarray(a, dtype=np.float32).reshape(-1, H, d_small)
+    out = np.zeros((a.shape[0], H, D), dtype=np.float32)
+    out[:, :, :d_small] = a
+    return out.reshape(a.shape[0], H * D)
+
+
+def abi_forward(zt, dev, q, k, v, H, Hkv, D):
+    holder = zt.Attn(q.shape[0], H, Hkv, D, device=dev)
+    holder.upload(holder.q, q)
+    holder.upload(holder.k, k)
+    holder.upload(holder.v, v)
+    holder.forward(1, 64)
+    return holder.download(q.size, holder.out).reshape(q.shape)
+
+
+def test_kat_one_token_returns_v_exactly(zt, dev):
+    """src/attention_test.zig:15-28"""
+    out = abi_forward(zt, dev, pad([1, 2], 1, 2), pad([3, 4], 1, 2), pad([5, 6], 1, 2), 1, 1, 32)
+    assert np.array_equal(out, pad([5, 6], 1, 2))
+
+
+def test_kat_two_tokens_hand_computed(zt, dev):
+    """src/attention_test.zig:30-44"""
+    out = abi_forward(zt, dev, pad([1, 0, 0, 0], 1, 2), pad([1, 0, 0, 0], 1, 2), pad([1, 0, 3, 4], 1, 2),
+                      1, 1, 32)
+    close(out, pad([1, 0, 2, 2], 1, 2), "two tokens")
+
+
+def test_kat_causality_bit_equality(zt, dev):
+    """src/attention_test.zig:46-72"""
+    q = pad([1, 0, 0, 1, 1, 1, 1, 0, 0, 1, 1, -1], 2, 2)
+    k = pad([1, 0, 0, 1, 1, 1], 1, 2)
+    v = pad([1, 2, 3, 4, 5, 6], 1, 2)
+    before = abi_forward(zt, dev, q, k, v, 2, 1, 32)
+    k2, v2 = k.copy(), v.copy()
+    k2[1, :2] = [99, 98]
+    v2[1, :2] = [97, 96]
+    after = abi_forward(zt, dev, q, k2, v2, 2, 1, 32)
+    assert np.array_equal(before[0].view(np.uint32), after[0].view(np.uint32))
+    assert after[1, 0] != before[1, 0]
+
+
+def test_kat_gqa_head_mapping(zt, dev):
+    """src/attention_test.zig:74-95"""
+    q = pad([1, 0, 1, 0, 0, 1, 0, 1, 0, 1, 0, 1, 1, 0, 1, 0], 4, 2)
+    k = pad([1, 0, 2, 0, 0, 1, 0, 2], 2, 2)
+    v = pad([1, 2, 3, 4, 5, 6, 7, 8], 2, 2)
+    out = abi_forward(zt, dev, q, k, v, 4, 2, 32).reshape(2, 4, 32)
+    assert np.array_equal(out[0, 0, :2], [1, 2]) and np.array_equal(out[0, 2, :2], [3, 4])
+    for t in range(2):
+        assert np.array_equal(out[t, 0], out[t, 1])
+        assert out[t, 0, 0] != out[t, 2, 0]
+
+
+def test_kat_weights_sum_to_one_and_prefix_means(zt, dev):
+    """src/attention_test.zig:97-128"""
+    out = abi_forward(zt, dev, pad([1, 0, 0, 1, 1, 1, 0, -1], 1, 2), pad([1, 1, 0, 1, -1, 0, 2, 1], 1, 2),
+                      pad([1] * 8, 1, 2), 1, 1, 32)
+    assert np.all(np.abs(out[:, :2] - 1.0) <= 1e-5)
+    out = abi_forward(zt, dev, pad([1, 0] * 4, 1, 2), pad([0] * 8, 1, 2), pad([1, 2, 3, 4, 5, 6, 7, 8], 1, 2),
+                      1, 1, 32)
+    assert np.all(np.abs(out[:, :2].ravel() - np.array([1, 2, 2, 3, 3, 4, 4, 5])) <= 1e-6)
+
+
+def test_kat_survives_exp_overflow(zt, dev):
+    """src/attention_test.zig:149-164: 100*100/sqrt(32) = 1768 would overflow an unshifted exp."""
+    out = abi_forward(zt, dev, pad([100, 0, 100, 0], 1, 2), pad([100, 0, 0, 0], 1, 2),
+                      pad([3, 5, 7, 9], 1, 2), 1, 1, 32)
+    assert np.array_equal(out[:, :2].ravel(), np.array([3, 5, 3, 5], dtype=np.float32))
+
+
+def test_kat_f64_accumulator_case(zt, dev, oracle):
+    """src/attention_test.zig:230-295 at head_dim 32: 1/3 and 1/7 fill, T = 512."""
+    T, D = 512, 32
+    tj = np.add.outer(np.arange(T), np.arange(D))
+    x = np.where(tj % 2 == 0, np.float32(1) / np.float32(3), np.float32(1) / np.float32(7)).astype(np.float32)
+    ref = oracle.attention_forward(x, x, x, 1, 1, D)
+    close(abi_forward(zt, dev, x, x, x, 1, 1, D), ref, "1/3 1/7 fill")
+
+
+def test_bit_reproducible_run_to_run(zt, dev, oracle):
+    """src/attention_test.zig:297-318"""
+    q, k, v, do = normal_inputs(oracle, 130, 4, 2, 32, 11)
+    a = run_fwd_bwd(zt, dev, q, k, v, do, 4, 2, 32)
+    b = run_fwd_bwd(zt, dev, q, k, v, do, 4, 2, 32)
+    for x, y in zip(a, b):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
+# ---- golden vectors and the twin's geometries -----------------------------------------------
+
+spec = importlib.util.spec_from_file_location("make_golden", os.path.join(HERE, "golden", "make_golden.py"))
+make_golden = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(make_golden)
+
+
+@pytest.mark.parametrize("tag,T,H,Hkv,D", make_golden.CASES)
+def test_golden_vectors(zt, dev, tag, T, H, Hkv, D):
+    g = np.load(os.path.join(HERE, "golden", f"{tag}.npz"))
+    q, k, v, do = make_golden.inputs(T, H, Hkv, D)
+    o, lse, dq, dk, dv = run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D)
+    for name, got in (("y", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        close(got, g[name], f"{tag} {name}")
+
+
+TWIN_SHAPES = [  # src/cuda/attn_twin.zig:82-111, the rows that finish in seconds on the CPU
+    ("ctx256", 256, 4, 2, 32), ("ctx512", 512, 4, 2, 32), ("llama3-T256", 256, 32, 8, 128),
+    ("gqa-96-T256", 256, 32, 8, 96), ("mha-192-T256", 256, 16, 16, 192), ("gqa-256-T256", 256, 8, 4, 256),
+]
+
+
+@pytest.mark.parametrize("tag,T,H,Hkv,D", TWIN_SHAPES)
+def test_twin_shapes_forward_backward(zt, dev, oracle, tag, T, H, Hkv, D):
+    q, k, v, do = lcg_inputs(oracle, T, H, Hkv, D)
+    ref_o, ref_lse = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
+    ref = [ref_o, ref_lse, *oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)]
+    got = run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D)
+    for name, g, r in zip(("out", "lse", "dq", "dk", "dv"), got, ref):
+        close(g, r, f"{tag} {name}")
+    # the reference's own gates, for comparison (src/cuda/attn.cu:51,114): absolute 1e-4 / 1e-5
+    assert np.max(np.abs(got[0] - ref[0])) <= 1e-4
+    for g, r in zip(got[2:], ref[2:]):
+        assert np.max(np.abs(g - r)) <= 1e-5
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 17, 31, 32, 33, 64, 127, 129, 200])
+@pytest.mark.parametrize("H,Hkv,D", [(4, 2, 32), (6, 2, 64), (2, 1, 34)])
+def test_ragged_lengths_and_tails(zt, dev, oracle, T, H, Hkv, D):
+    q, k, v, do = normal_inputs(oracle, T, H, Hkv, D, seed=T)
+    ref_o, ref_lse = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=4)
+    ref = [ref_o, ref_lse, *oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=4)]
+    got = run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D)
+    for name, g, r in zip(("out", "lse", "dq", "dk", "dv"), got, ref):
+        close(g, r, f"T={T} {name}")
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D", [(3, 70, 4, 2, 32), (2, 129, 8, 2, 128), (5, 33, 2, 2, 64)])
+def test_batched_items_are_independent(zt, dev, oracle, B, T, H, Hkv, D):
+    q = oracle.fill_normal((B, T, H * D), 21, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 21, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 21, 2)
+    do = oracle.fill_normal((B, T, H * D), 21, 3)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    for b in range(B):
+        ro, rl = oracle.attention_forward(q[b], k[b], v[b], H, Hkv, D, want_lse=True, threads=4)
+        rdq, rdk, rdv = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D, threads=4)
+        for name, g, r in (("out", o, ro), ("lse", lse, rl), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+            close(g[b].cpu().numpy(), r, f"item {b} {name}")
+
+
+def test_reference_abi_backward(zt, dev, oracle):
+    """zt_attn_backward as device.Attn.backward calls it (src/cuda/device.zig:403-406): no out,
+    no lse, caller scratch for the three per-row buffers, outputs assigned over garbage."""
+    T, H, Hkv, D = 150, 8, 4, 64
+    q, k, v, do = lcg_inputs(oracle, T, H, Hkv, D)
+    holder = zt.Attn(T, H, Hkv, D, device=dev)
+    for name, x in (("q", q), ("k", k), ("v", v), ("dout", do)):
+        holder.upload(getattr(holder, name), x)
+    for name in ("dq", "dk", "dv"):
+        getattr(holder, name).fill_(float("nan"))   # assigned, not accumulated into
+    holder.forward(1, 64)
+    holder.backward(64)
+    ref_o, ref_lse = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
+    rdq, rdk, rdv = oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)
+    close(holder.download(q.size, holder.out).reshape(q.shape), ref_o, "out")
+    close(holder.download(q.size, holder.dq).reshape(q.shape), rdq, "dq")
+    close(holder.download(k.size, holder.dk).reshape(k.shape), rdk, "dk")
+    close(holder.download(k.size, holder.dv).reshape(k.shape), rdv, "dv")
+    close(holder.download(T * H, holder.row_max).reshape(T, H), ref_lse, "row_max = lse")
+    assert np.all(holder.download(T * H, holder.row_den) == 1.0)
+    delta = (ref_o.astype(np.float64) * do).reshape(T, H, D).sum(-1)
+    close(holder.download(T * H, holder.row_del).reshape(T, H), delta, "row_del")
+    assert holder.total_bytes() == 4 * q.nbytes + 4 * k.nbytes + 3 * T * H * 4
+
+
+def test_forward_at_offsets_and_key_counts(zt, dev, oracle):
+    """q_offset / n_keys semantics (src/cuda/attn_kernels.cu:276-321) away from the two usual shapes."""
+    H, Hkv, D, c_t = 4, 2, 32, 96
+    q, k, v, _ = normal_inputs(oracle, c_t, H, Hkv, D, 31)
+    holder = zt.Attn(c_t, H, Hkv, D, device=dev)
+    for (t, q_off, n_keys) in ((5, 7, 12), (5, 7, 40), (33, 0, 96), (1, 0, 1), (1, 50, 96), (40, 56, 96)):
+        holder.upload(holder.q, q[:t])
+        holder.upload(holder.k, k[:n_keys])
+        holder.upload(holder.v, v[:n_keys])
+        holder.forward_at(1, 64, q_off, n_keys, t)
+        got = holder.download(t * H * D, holder.out).reshape(t, H * D)
+        ref = oracle.attention_forward_at(q[:t], k[:n_keys], v[:n_keys], H, Hkv, D, q_off, n_keys)
+        close(got, ref, f"t={t} q_offset={q_off} n_keys={n_keys}")
+    with pytest.raises(zt.device.ShapeTooLarge):
+        holder.forward_at(1, 64, 0, c_t + 1, 1)
+    with pytest.raises(zt.device.ShapeTooLarge):
+        holder.forward_at(1, 64, c_t, c_t, 1)
+
+
+def test_decode_step_at_every_position_of_a_filling_cache(zt, dev, oracle):
+    """src/decode_test.zig:222-319: the CUDA decode step against attnStep at every position,
+    per-row distinct hashed data, through the reference ABI (T = 1, q_offset = n_keys - 1)."""
+    H, Hkv, D, n_ctx = 4, 2, 32, 32  # src/decode_test.zig:12-20
+    kdata = np.array([oracle.fill_hash(7000 + i) for i in range(n_ctx * Hkv * D)], dtype=np.float32).reshape(n_ctx, -1)
+    vdata = np.array([oracle.fill_hash(90000 + i) for i in range(n_ctx * Hkv * D)], dtype=np.float32).reshape(n_ctx, -1)
+    qdata = np.array([oracle.fill_hash(300000 + i) for i in range(n_ctx * H * D)], dtype=np.float32).reshape(n_ctx, -1)
+    holder = zt.Attn(n_ctx, H, Hkv, D, device=dev)
+    layer = oracle.Layer(n_ctx, Hkv * D)
+    dlayer = zt.kv_cache.Layer(n_ctx, Hkv * D, batch=1, device=dev)
+    for pos in range(n_ctx):
+        layer.append(kdata[pos], vdata[pos])
+        dlayer.append(cu(kdata[pos:pos + 1], dev), cu(vdata[pos:pos + 1], dev))
+        n_keys = layer.visible()
+        ref = oracle.attn_step(qdata[pos:pos + 1], layer, H, Hkv, D)
+        holder.upload(holder.q, qdata[pos])
+        holder.upload(holder.k, layer.k[:n_keys])
+        holder.upload(holder.v, layer.v[:n_keys])
+        holder.forward_at(1, 64, n_keys - 1, n_keys, 1)
+        got = holder.download(H * D, holder.out)
+        # the reference's gate is relative to the largest reference value (src/decode_test.zig:330)
+        assert np.max(np.abs(got - ref[0])) <= 1e-4 * np.max(np.abs(ref))
+        close(got, ref[0], f"pos {pos} (reference ABI)")
+        got2 = zt.kv_cache.attn_step(cu(qdata[pos:pos + 1], dev), dlayer, H, Hkv, D)
+        close(got2[0].cpu().numpy(), ref[0], f"pos {pos} (resident cache)")
+    assert int(dlayer.visible()[0]) == n_ctx
+    with pytest.raises(zt.kv_cache.Full):
+        dlayer.append(cu(kdata[:1], dev), cu(vdata[:1], dev))
+    assert np.array_equal(dlayer.k[0].cpu().numpy(), layer.k)
+
+
+DECODE_SHAPES = [  # B, n_ctx, H, Hkv, D
+    (5, 300, 32, 8, 128), (4, 257, 4, 2, 32), (3, 200, 8, 8, 64), (3, 130, 16, 2, 64),
+    (2, 150, 12, 4, 96), (2, 90, 8, 4, 256), (3, 70, 6, 2, 192), (2, 64, 4, 2, 34), (2, 1500, 32, 8, 128),
+    (2, 100, 5, 1, 80),
+]
+
+
+@pytest.mark.parametrize("B,n_ctx,H,Hkv,D", DECODE_SHAPES)
+def test_batched_ragged_decode(zt, dev, oracle, B, n_ctx, H, Hkv, D):
+    rng = np.random.default_rng(B * 1000 + n_ctx)
+    n_keys = rng.integers(1, n_ctx + 1, size=B).astype(np.int32)
+    n_keys[0], n_keys[-1] = n_ctx, 1          # the two extremes always present
+    kc = oracle.fill_normal((B, n_ctx, Hkv * D), 41, 1)
+    vc = oracle.fill_normal((B, n_ctx, Hkv * D), 41, 2)
+    q = oracle.fill_normal((B, H * D), 41, 0)
+    ws = zt.DecodeWorkspace(B, n_ctx, H, Hkv, D, dev)
+    out, lse = zt.decode_attention(cu(q, dev), cu(kc, dev), cu(vc, dev), cu(n_keys, dev), H, Hkv, D,
+                                   workspace=ws, want_lse=True)
+    torch.cuda.synchronize()
+    assert ws.bad_sequences() == 0
+    for b in range(B):
+        ro, rl = oracle.attn_step_raw(q[b], kc[b], vc[b], int(n_keys[b]), H, Hkv, D, threads=4)
+        close(out[b].cpu().numpy(), ro, f"sequence {b} out (n_keys {n_keys[b]})")
+        close(lse[b].cpu().numpy(), rl, f"sequence {b} lse")
+
+
+def test_decode_refuses_an_empty_or_overlong_prefix(zt, dev, oracle):
+    """decode.attnStep refuses n_keys < 1 (src/decode.zig:350); on the device the refusal is a NaN
+    row and a count, and the other sequences are still computed."""
+    B, n_ctx, H, Hkv, D = 4, 64, 8, 2, 64
+    kc = oracle.fill_normal((B, n_ctx, Hkv * D), 43, 1)
+    vc = oracle.fill_normal((B, n_ctx, Hkv * D), 43, 2)
+    q = oracle.fill_normal((B, H * D), 43, 0)
+    n_keys = np.array([0, 64, 65, 10], dtype=np.int32)
+    ws = zt.DecodeWorkspace(B, n_ctx, H, Hkv, D, dev)
+    out = zt.decode_attention(cu(q, dev), cu(kc, dev), cu(vc, dev), cu(n_keys, dev), H, Hkv, D, workspace=ws)
+    torch.cuda.synchronize()
+    assert ws.bad_sequences() == 2
+    out = out.cpu().numpy()
+    assert np.all(np.isnan(out[0])) and np.all(np.isnan(out[2]))
+    for b in (1, 3):
+        ro, _ = oracle.attn_step_raw(q[b], kc[b], vc[b], int(n_keys[b]), H, Hkv, D)
+        close(out[b], ro, f"sequence {b}")
+    with pytest.raises(oracle.DimensionMismatch):
+        oracle.attn_step_raw(q[0], kc[0], vc[0], 0, H, Hkv, D)
+
+
+def test_kv_append_semantics(zt, dev, oracle):
+    """src/kv_cache.zig:88-95 and its tests :239-290, for a batch of resident caches."""
+    with pytest.raises(zt.ops.DimensionMismatch):
+        zt.kv_cache.Layer(0, 8, device=dev)
+    layer = zt.kv_cache.Layer(3, 8, batch=2, device=dev)
+    assert layer.bytes() == 2 * 2 * 3 * 8 * 4
+    with pytest.raises(zt.ops.DimensionMismatch):
+        layer.append(torch.zeros(2, 8, device=dev), torch.zeros(2, 4, device=dev))
+    assert layer.visible().tolist() == [0, 0]
+    for i in range(3):
+        layer.append(torch.full((2, 8), float(i), device=dev), torch.full((2, 8), float(-i), device=dev))
+    assert layer.visible().tolist() == [3, 3]
+    with pytest.raises(zt.kv_cache.Full):
+        layer.append(torch.zeros(2, 8, device=dev), torch.zeros(2, 8, device=dev))
+    assert layer.visible().tolist() == [3, 3] and float(layer.k[1, 2, 0]) == 2.0 and float(layer.v[0, 1, 7]) == -1.0
+    # the C entry point itself: a full sequence is skipped and counted, the other one advances
+    n_keys = torch.tensor([3, 1], dtype=torch.int32, device=dev)
+    full = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = zt.lib.load().zt_kv_append(layer.k.data_ptr(), layer.v.data_ptr(), n_keys.data_ptr(),
+                                    torch.full((2, 8), 9.0, device=dev).data_ptr(),
+                                    torch.full((2, 8), 8.0, device=dev).data_ptr(), full.data_ptr(),
+                                    2, 3, 1, 8, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and n_keys.tolist() == [3, 2] and int(full) == 1
+    assert float(layer.k[1, 1, 0]) == 9.0 and float(layer.k[0, 2, 0]) == 2.0
+
+
+def test_library_is_the_thing_that_ran(zt, dev, oracle):
+    before = zt.lib.launch_count()
+    q, k, v, do = normal_inputs(oracle, 40, 4, 2, 32, 2)
+    run_fwd_bwd(zt, dev, q, k, v, do, 4, 2, 32)
+    assert zt.lib.launch_count() - before >= 4
+    assert zt.lib.last_path() != "none"
+
+
+def test_refused_call_touches_nothing(zt, dev):
+    L = zt.lib.load()
+    L.zt_attn_set_verbose(0)
+    out = torch.full((4, 128), 7.0, device=dev)
+    x = torch.zeros((4, 128), device=dev)
+    rc = L.zt_attn_forward(x.data_ptr(), x.data_ptr(), x.data_ptr(), out.data_ptr(), 4, 4, 2, 33, 1, 64, 0, 4, None)
+    torch.cuda.synchronize()
+    L.zt_attn_set_verbose(1)
+    assert rc == 1 and torch.all(out == 7.0)

@@ -131,3 +131,27 @@ def test_backward_threads_and_group_split_change_no_bit(oracle):
         assert np.array_equal(dq[:, kv * g * D:(kv + 1) * g * D], one[0][:, kv * g * D:(kv + 1) * g * D])
         assert np.array_equal(dk[:, kv * D:(kv + 1) * D], one[1][:, kv * D:(kv + 1) * D])
         assert np.array_equal(dv[:, kv * D:(kv + 1) * D], one[2][:, kv * D:(kv + 1) * D])
+
+
+def test_sampled_step_rows_are_the_full_pass_rows(oracle):
+    """The benchmark's CPU sample computes a subset of rows with the full pass's arithmetic."""
+    B, T, H, Hkv, D = 2, 21, 4, 2, 8
+    q = oracle.fill_normal((B, T, H * D), 9, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 9, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 9, 2)
+    do = oracle.fill_normal((B, T, H * D), 9, 3)
+    flops, out, dq, dk, dv = oracle.sampled_step(q, k, v, do, H, Hkv, D, 4, 3, threads=3)
+    rows = list(range(3, T, 4))
+    assert flops == sum(14.0 * D * (t + 1) for t in rows) * B * H
+    for b in range(B):
+        fo = oracle.attention_forward(q[b], k[b], v[b], H, Hkv, D)
+        fdq, _, _ = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D)
+        assert np.array_equal(out[b][rows], fo[rows]) and np.array_equal(dq[b][rows], fdq[rows])
+        others = [t for t in range(T) if t not in rows]
+        assert not out[b][others].any()
+    # with stride 1 it is the whole pass, dk/dv included
+    flops1, out1, dq1, dk1, dv1 = oracle.sampled_step(q, k, v, do, H, Hkv, D, 1, 0, threads=2)
+    for b in range(B):
+        _, fdk, fdv = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D)
+        assert np.array_equal(dk1[b], fdk) and np.array_equal(dv1[b], fdv)
+    assert flops1 == 3.5 * 2 * B * H * D * T * (T + 1)

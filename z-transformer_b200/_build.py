@@ -1,0 +1,56 @@
+"""Compiles the CUDA library in-tree for sm_100a (nvcc cross-compiles without a GPU)."""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_PATH = os.path.join(HERE, "libztattn.so")
+HOST_LIB_PATH = os.path.join(HERE, "libzthost.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
+
+
+def _nvcc() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: the CUDA library cannot be built")
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def _sources() -> list[str]:
+    out = [os.path.join(HERE, "..", "include", "zt_attn.h")]
+    for root, _, files in os.walk(CSRC):
+        out += [os.path.join(root, f) for f in files if f.endswith((".cu", ".cuh", ".hpp", ".cpp", ".h"))]
+    return out
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    """nvcc -> libztattn.so (kernels + C ABI) and libzthost.so (C++ host mirror + its C shim)."""
+    srcs = _sources()
+    if force or _stale(LIB_PATH, srcs):
+        cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(CSRC, "zt_attn.cu"), "-lcuda"]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        subprocess.check_call(cmd)
+    host_src = os.path.join(CSRC, "host", "zt_host.cpp")
+    if os.path.exists(host_src) and (force or _stale(HOST_LIB_PATH, srcs)):
+        cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared",
+               "-o", HOST_LIB_PATH, host_src, "-L" + HERE, "-lztattn",
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        subprocess.check_call(cmd)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build_library(force=True, verbose=True))

@@ -1,0 +1,336 @@
+// libztattn: the C ABI declared in include/zt_attn.h.
+//
+// This file holds only argument checking and dispatch; the kernels live in
+// simt_kernels.cuh (CUDA-core, any admissible shape), decode_kernels.cuh
+// (bandwidth-bound split-K decode) and tc_fwd.cuh (tcgen05/TMEM forward).
+// There is no CPU path: every launching entry point needs a CUDA device.
+//
+// The refusal order and wording follow the reference's launchers
+// (src/cuda/attn_kernels.cu:843-929 forward, :962-1011 backward) so that a caller
+// probing the boundary sees the same answers from either library.
+#include "../../include/zt_attn.h"
+
+#include "decode_kernels.cuh"
+#include "simt_kernels.cuh"
+#include "zt_common.cuh"
+#ifdef ZT_WITH_TC
+#include "tc_fwd.cuh"
+#endif
+
+#include <mutex>
+
+namespace zt {
+
+constexpr int kMinDim = 32, kMaxDim = 256;  // src/cuda/attn_kernels.cu:147-148
+constexpr size_t kArenaBytes = 16u << 20;
+
+// One arena per device, created on the first decode-shaped zt_attn_forward call on
+// that device and kept until the process ends.  The reference's entry points take
+// no workspace argument, and a per-call allocation would synchronise the device.
+static void *device_arena() {
+    static void *arena[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!arena[dev]) {
+        if (cudaMalloc(&arena[dev], kArenaBytes) != cudaSuccess) {
+            cudaGetLastError();
+            arena[dev] = nullptr;
+        }
+    }
+    return arena[dev];
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The checks both reference launchers share, in the reference's order.
+static int check_geometry(int T, int n_heads, int n_kv_heads, int dim) {
+    if (T < 1)
+        return refuse("T %d is not launchable. A zero or negative query count gives a grid with no "
+                      "blocks, or one the driver cannot form.", T);
+    if (!zt_attn_dim_ok(dim))
+        return refuse("head_dim %d is refused. It must be even and in [%d, %d].", dim, kMinDim, kMaxDim);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        return refuse("%d heads over %d kv heads is not a group.", n_heads, n_kv_heads);
+    if (n_heads > 65535) return refuse("%d heads exceeds the 65535 gridDim.y limit.", n_heads);
+    return 0;
+}
+
+static int need_device() {
+    if (!device_info()) return refuse("no usable CUDA device (this library has no CPU path).");
+    return 0;
+}
+
+static int forward_impl(const float *q, const float *k, const float *v, float *out, float *lse,
+                        int batch, int T, int n_heads, int n_kv_heads, int dim, int q_offset,
+                        int n_keys, cudaStream_t stream) {
+    const float scale_log2 = kLog2e / sqrtf((float)dim);
+    const long long q_bs = (long long)T * n_heads * dim;
+    const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
+#ifdef ZT_WITH_TC
+    if (g_path.load() == 0 &&
+        tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
+        return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
+    }
+#endif
+    SimtFwdParams p{};
+    p.q = q, p.k = k, p.v = v, p.out = out, p.lse = lse;
+    p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+    p.q_offset = q_offset, p.n_keys = n_keys;
+    p.q_batch_stride = q_bs, p.kv_batch_stride = kv_bs, p.lse_batch_stride = (long long)T * n_heads;
+    p.scale_log2 = scale_log2;
+    p.n_keys_dev = nullptr, p.bad_count = nullptr;
+    return launch_fwd_simt(p, batch, stream);
+}
+
+static int backward_impl(const float *q, const float *k, const float *v, const float *lse,
+                         const float *delta, const float *dout, float *dq, float *dk, float *dv,
+                         int batch, int T, int n_heads, int n_kv_heads, int dim,
+                         cudaStream_t stream) {
+    SimtBwdParams p{};
+    p.q = q, p.k = k, p.v = v, p.dout = dout, p.lse = lse, p.delta = delta;
+    p.dq = dq, p.dk = dk, p.dv = dv;
+    p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+    p.q_batch_stride = (long long)T * n_heads * dim;
+    p.kv_batch_stride = (long long)T * n_kv_heads * dim;
+    p.lse_batch_stride = (long long)T * n_heads;
+    p.scale = 1.0f / sqrtf((float)dim);
+    p.scale_log2 = kLog2e / sqrtf((float)dim);
+    return launch_bwd_simt(p, batch, stream);
+}
+
+}  // namespace zt
+
+using namespace zt;
+
+extern "C" {
+
+int zt_attn_dim_ok(int dim) { return !(dim < kMinDim || dim > kMaxDim || (dim & 1) != 0); }
+
+// The reference's formulas (src/cuda/attn_kernels.cu:103-104,375-376,697-706), kept so
+// that the numbers a caller reads are the reference's numbers.
+size_t zt_attn_forward_shmem(int dim, int tile, int group_q) {
+    const size_t base = (size_t)dim + (size_t)tile + 2u * (size_t)tile * ((size_t)dim + 1u);
+    return (base + (size_t)(group_q - 1) * (size_t)(dim + tile)) * sizeof(float);
+}
+size_t zt_attn_bwd_dq_shmem(int dim, int tile) {
+    return (2u * (size_t)dim + 2u * (size_t)tile + 2u * (size_t)tile * ((size_t)dim + 1u)) * sizeof(float);
+}
+size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float); }
+
+const char *zt_attn_last_error(void) { return g_last_error; }
+const char *zt_attn_last_path(void) { return g_last_path; }
+void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
+int zt_attn_set_path(int path) { return g_path.exchange(path == 1 ? 1 : 0); }
+unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
+
+void zt_attn_profile(int on) { g_profile.store(on ? 1 : 0); }
+
+int zt_attn_profile_read(char *host_buf, size_t cap) {
+    std::vector<ProfEntry> taken;
+    {
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        taken.swap(g_prof);
+    }
+    struct Row { std::string name; int n; double ms; };
+    std::vector<Row> rows;
+    for (const ProfEntry &e : taken) {
+        float ms = 0.f;
+        if (e.name && cudaEventSynchronize(e.stop) == cudaSuccess &&
+            cudaEventElapsedTime(&ms, e.start, e.stop) == cudaSuccess) {
+            bool found = false;
+            for (Row &r : rows)
+                if (r.name == e.name) { r.n += 1, r.ms += ms, found = true; break; }
+            if (!found) rows.push_back(Row{e.name, 1, (double)ms});
+        } else {
+            cudaGetLastError();
+        }
+        cudaEventDestroy(e.start);
+        cudaEventDestroy(e.stop);
+    }
+    std::string text;
+    char line[256];
+    for (const Row &r : rows) {
+        snprintf(line, sizeof(line), "%s %d %.6f\n", r.name.c_str(), r.n, r.ms);
+        text += line;
+    }
+    if (host_buf && cap > 0) {
+        const size_t n = text.size() < cap - 1 ? text.size() : cap - 1;
+        memcpy(host_buf, text.data(), n);
+        host_buf[n] = 0;
+    }
+    return (int)rows.size();
+}
+
+int zt_attn_forward(const float *q, const float *k, const float *v, float *out, int T, int n_heads,
+                    int n_kv_heads, int dim, int group_q, int max_tile, int q_offset, int n_keys,
+                    zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (group_q < 1 || group_q > 64 || (size_t)dim * (size_t)group_q > 1024)
+        return refuse("group_q %d at head_dim %d is not launchable.", group_q, dim);
+    // `q_offset > n_keys - T`, not `q_offset + T > n_keys`: the sum can overflow int, the
+    // difference cannot once T >= 1 and n_keys >= 1 (src/cuda/attn_kernels.cu:886-899).
+    if (q_offset < 0 || n_keys < 1 || q_offset > n_keys - T)
+        return refuse("q_offset %d, n_keys %d is not launchable.", q_offset, n_keys);
+    if (max_tile < 1)
+        return refuse("max_tile %d is not launchable. A tile of zero never advances the key loop.",
+                      max_tile);
+    if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
+    if (need_device()) return 1;
+
+    if (T == 1 && dim % 4 == 0 && aligned16(q) && aligned16(k) && aligned16(v)) {
+        // A decode step: split the context over many blocks.  The one query row sits at
+        // q_offset and sees keys 0 .. q_offset (q_offset <= n_keys - 1 was checked above).
+        n_keys = q_offset + 1;
+        const DecodePlan pl = decode_plan(1, n_keys, n_heads, n_kv_heads, dim);
+        void *arena = pl.total_bytes <= kArenaBytes ? device_arena() : nullptr;
+        if (arena) {
+            DecodeParams p{};
+            p.q = q, p.k_cache = k, p.v_cache = v, p.n_keys = nullptr, p.n_keys_all = n_keys;
+            p.out = out, p.lse = nullptr;
+            p.batch = 1, p.n_ctx = n_keys, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+            p.cache_batch_stride = 0;
+            p.scale_log2 = kLog2e / sqrtf((float)dim);
+            return launch_decode(p, pl, arena, (cudaStream_t)stream);
+        }
+    }
+    return forward_impl(q, k, v, out, nullptr, 1, T, n_heads, n_kv_heads, dim, q_offset, n_keys,
+                        (cudaStream_t)stream);
+}
+
+int zt_attn_backward(const float *q, const float *k, const float *v, const float *dout, float *dq,
+                     float *dk, float *dv, float *row_max, float *row_den, float *row_del, int T,
+                     int n_heads, int n_kv_heads, int dim, int max_tile, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (max_tile < 1)
+        return refuse("max_tile %d is not launchable. A tile of zero never advances the key loop.",
+                      max_tile);
+    if (!q || !k || !v || !dout || !dq || !dk || !dv || !row_max || !row_den || !row_del)
+        return refuse("a null device pointer was passed.");
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    // The reference's backward sees neither the forward's output nor its log-sum-exp, so
+    // both are rebuilt here: the forward runs into dq (same shape as out, assigned later)
+    // with the log-sum-exp into row_max, then row_del = sum_j dout * out.
+    if (forward_impl(q, k, v, dq, row_max, 1, T, n_heads, n_kv_heads, dim, 0, T, s)) return 1;
+    if (launch_delta(dq, dout, row_del, (long long)T * n_heads, dim, s)) return 1;
+    const long long n = (long long)T * n_heads;
+    if (ZT_LAUNCH("fill_kernel", s, fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(row_den, n, 1.0f)))
+        return 1;
+    return backward_impl(q, k, v, row_max, row_del, dout, dq, dk, dv, 1, T, n_heads, n_kv_heads, dim, s);
+}
+
+int zt_attn_forward_batched(const float *q, const float *k, const float *v, float *out, float *lse,
+                            int batch, int T, int n_heads, int n_kv_heads, int dim,
+                            zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
+    if (need_device()) return 1;
+    return forward_impl(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, 0, T,
+                        (cudaStream_t)stream);
+}
+
+size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    (void)batch, (void)T, (void)n_heads, (void)n_kv_heads, (void)dim;
+    return 0;
+}
+
+int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
+                             const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                             float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                             int n_heads, int n_kv_heads, int dim, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv || !delta)
+        return refuse("a null device pointer was passed.");
+    const size_t need = zt_attn_backward_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return refuse("the backward needs %zu bytes of workspace, %zu were given.", need, workspace_bytes);
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
+    return backward_impl(q, k, v, lse, delta, dout, dq, dk, dv, batch, T, n_heads, n_kv_heads, dim, s);
+}
+
+size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim) {
+    if (batch < 1 || n_ctx < 1 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 ||
+        !zt_attn_dim_ok(dim))
+        return 0;
+    return decode_plan(batch, n_ctx, n_heads, n_kv_heads, dim).total_bytes;
+}
+
+int zt_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *n_keys,
+                   float *out, float *lse, void *workspace, size_t workspace_bytes, int batch,
+                   int n_ctx, int n_heads, int n_kv_heads, int dim, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (n_ctx < 1) return refuse("n_ctx %d is not a cache.", n_ctx);
+    if (check_geometry(1, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k_cache || !v_cache || !n_keys || !out)
+        return refuse("a null device pointer was passed.");
+    const DecodePlan pl = decode_plan(batch, n_ctx, n_heads, n_kv_heads, dim);
+    if (!workspace || workspace_bytes < pl.total_bytes)
+        return refuse("decode needs %zu bytes of workspace, %zu were given.", pl.total_bytes,
+                      workspace_bytes);
+    if (!aligned16(workspace)) return refuse("the decode workspace must be 16-byte aligned.");
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dim % 4 == 0 && aligned16(q) && aligned16(k_cache) && aligned16(v_cache)) {
+        DecodeParams p{};
+        p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.n_keys = n_keys, p.n_keys_all = 0;
+        p.out = out, p.lse = lse;
+        p.batch = batch, p.n_ctx = n_ctx, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+        p.cache_batch_stride = (long long)n_ctx * n_kv_heads * dim;
+        p.scale_log2 = kLog2e / sqrtf((float)dim);
+        return launch_decode(p, pl, workspace, s);
+    }
+    // A width that is not a multiple of four floats (or unaligned buffers) cannot use
+    // 128-bit loads: the general forward kernel runs one query row per sequence instead.
+    if (cudaMemsetAsync(workspace, 0, kDecodeHeaderBytes, s) != cudaSuccess) {
+        cudaGetLastError();
+        return refuse("could not clear the decode workspace header");
+    }
+    SimtFwdParams p{};
+    p.q = q, p.k = k_cache, p.v = v_cache, p.out = out, p.lse = lse;
+    p.T = 1, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+    p.q_offset = 0, p.n_keys = n_ctx;
+    p.q_batch_stride = (long long)n_heads * dim;
+    p.kv_batch_stride = (long long)n_ctx * n_kv_heads * dim;
+    p.lse_batch_stride = n_heads;
+    p.scale_log2 = kLog2e / sqrtf((float)dim);
+    p.n_keys_dev = n_keys, p.bad_count = reinterpret_cast<int *>(workspace);
+    return launch_fwd_simt(p, batch, s);
+}
+
+int zt_attn_decode_status(const void *workspace, int *host_bad_sequences) {
+    if (!workspace || !host_bad_sequences) return refuse("a null pointer was passed.");
+    if (cudaMemcpy(host_bad_sequences, workspace, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        return refuse("reading the decode status failed: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int zt_kv_append(float *k_cache, float *v_cache, int *n_keys, const float *k_new,
+                 const float *v_new, int *full_count, int batch, int n_ctx, int n_kv_heads, int dim,
+                 zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1) return refuse("batch %d is not launchable.", batch);
+    // kv_cache.Layer.init refuses a zero context or width (src/kv_cache.zig:66).
+    if (n_ctx < 1 || n_kv_heads < 1 || dim < 1) return refuse("a cache of %d x %d x %d is degenerate.", n_ctx, n_kv_heads, dim);
+    if (!k_cache || !v_cache || !n_keys || !k_new || !v_new) return refuse("a null device pointer was passed.");
+    if (need_device()) return 1;
+    g_last_path = "kv-append";
+    cudaStream_t s = (cudaStream_t)stream;
+    return ZT_LAUNCH("kv_append_kernel", s,
+                     kv_append_kernel<<<(unsigned)batch, 256, 0, s>>>(k_cache, v_cache, n_keys, k_new, v_new,
+                                                                      full_count, n_ctx, n_kv_heads * dim));
+}
+
+}  // extern "C"

@@ -1,0 +1,146 @@
+"""Thin wrappers that hand torch CUDA tensors to the C ABI (include/zt_attn.h).
+
+Each function checks shapes the way the reference's CPU functions do
+(src/attention.zig:71-79, src/autograd.zig:659-685, src/decode.zig:338-350) and
+raises the mirror of the Zig error; the arithmetic happens only in libztattn.
+"""
+from __future__ import annotations
+
+from . import lib as _lib
+from .device import ConfigRefused
+
+
+class InvalidHeadConfig(Exception):
+    """error.InvalidHeadConfig (src/attention.zig:71-73)."""
+
+
+class DimensionMismatch(Exception):
+    """error.DimensionMismatch (src/attention.zig:74-79)."""
+
+
+def _stream(t):
+    import torch
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda_f32(*tensors):
+    import torch
+    for x in tensors:
+        if x is None:
+            continue
+        if not x.is_cuda:
+            raise RuntimeError("libztattn has no CPU path: tensors must live on a CUDA device")
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise DimensionMismatch("tensors must be contiguous float32")
+
+
+def _head_config(n_heads, n_kv_heads, head_dim):
+    if n_kv_heads == 0 or head_dim == 0 or n_heads % n_kv_heads != 0:
+        raise InvalidHeadConfig(f"{n_heads}/{n_kv_heads} heads, head_dim {head_dim}")
+
+
+def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False):
+    """Batched attention.forward.  q [B, T, H*D] (or [T, H*D]); returns out (and lse [B, T, H])."""
+    import torch
+    _head_config(n_heads, n_kv_heads, head_dim)
+    squeeze = q.dim() == 2
+    if squeeze:
+        q, k, v = q[None], k[None], v[None]
+    _need_cuda_f32(q, k, v)
+    B, T = q.shape[0], q.shape[1]
+    if (k.shape[0] != B or v.shape[0] != B or k.shape[1] != T or v.shape[1] != T
+            or k.shape[2] != n_kv_heads * head_dim or v.shape[2] != k.shape[2]
+            or q.shape[2] != n_heads * head_dim):
+        raise DimensionMismatch("q/k/v shapes disagree with the head configuration")
+    out = torch.empty_like(q)
+    lse = torch.empty((B, T, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
+    if T == 0:
+        return (out[0] if squeeze else out, lse) if want_lse else (out[0] if squeeze else out)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_forward_batched(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+            lse.data_ptr() if want_lse else None, B, T, n_heads, n_kv_heads, head_dim, _stream(q))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    if squeeze:
+        out = out[0]
+        lse = lse[0] if want_lse else None
+    return (out, lse) if want_lse else out
+
+
+def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim):
+    """Batched autograd.attentionBackward from the forward's out and lse; returns dq, dk, dv."""
+    import torch
+    _head_config(n_heads, n_kv_heads, head_dim)
+    squeeze = q.dim() == 2
+    if squeeze:
+        q, k, v, out, lse, dout = q[None], k[None], v[None], out[None], lse[None], dout[None]
+    _need_cuda_f32(q, k, v, out, lse, dout)
+    B, T = q.shape[0], q.shape[1]
+    if (k.shape[1] != T or v.shape[1] != T or k.shape[2] != n_kv_heads * head_dim
+            or v.shape[2] != k.shape[2] or q.shape[2] != n_heads * head_dim):
+        raise DimensionMismatch("q/k/v shapes disagree with the head configuration")
+    if dout.shape != q.shape or out.shape != q.shape or lse.shape != (B, T, n_heads):
+        raise DimensionMismatch("dout/out/lse shapes disagree with q")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty_like(lse)
+    L = _lib.load()
+    ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, n_heads, n_kv_heads, head_dim)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device) if ws_bytes else None
+    with torch.cuda.device(q.device):
+        rc = L.zt_attn_backward_batched(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+            ws.data_ptr() if ws is not None else None, ws_bytes, B, T, n_heads, n_kv_heads, head_dim,
+            _stream(q))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    if squeeze:
+        return dq[0], dk[0], dv[0]
+    return dq, dk, dv
+
+
+class DecodeWorkspace:
+    """Caller-owned scratch of zt_attn_decode for one (batch, n_ctx, heads, dim) shape."""
+
+    def __init__(self, batch, n_ctx, n_heads, n_kv_heads, head_dim, device="cuda"):
+        import torch
+        self.shape = (batch, n_ctx, n_heads, n_kv_heads, head_dim)
+        self.nbytes = int(_lib.load().zt_attn_decode_workspace_bytes(*self.shape))
+        if self.nbytes == 0:
+            raise ConfigRefused("the decode shape is not admissible")
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+
+    def bad_sequences(self) -> int:
+        import ctypes
+        n = ctypes.c_int(0)
+        if _lib.load().zt_attn_decode_status(self.buf.data_ptr(), ctypes.byref(n)) != 0:
+            raise RuntimeError(_lib.last_error())
+        return n.value
+
+
+def decode_attention(q, k_cache, v_cache, n_keys, n_heads, n_kv_heads, head_dim, *, workspace=None,
+                     want_lse=False, out=None):
+    """decode.attnStep for a batch: q [B, H*D], caches [B, n_ctx, Hkv*D], n_keys int32 [B]."""
+    import torch
+    _head_config(n_heads, n_kv_heads, head_dim)
+    _need_cuda_f32(q, k_cache, v_cache)
+    B, n_ctx = k_cache.shape[0], k_cache.shape[1]
+    if (q.shape != (B, n_heads * head_dim) or k_cache.shape[2] != n_kv_heads * head_dim
+            or v_cache.shape != k_cache.shape):
+        raise DimensionMismatch("q/cache shapes disagree with the head configuration")
+    if n_keys.dtype != torch.int32 or n_keys.shape != (B,) or not n_keys.is_cuda:
+        raise DimensionMismatch("n_keys must be an int32 CUDA tensor of one count per sequence")
+    if workspace is None:
+        workspace = DecodeWorkspace(B, n_ctx, n_heads, n_kv_heads, head_dim, q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    lse = torch.empty((B, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_decode(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), n_keys.data_ptr(), out.data_ptr(),
+            lse.data_ptr() if want_lse else None, workspace.buf.data_ptr(), workspace.nbytes, B, n_ctx,
+            n_heads, n_kv_heads, head_dim, _stream(q))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return (out, lse) if want_lse else out
