@@ -358,10 +358,10 @@ def test_kv_append_semantics(zt, dev, oracle):
     # the C entry point itself: a full sequence is skipped and counted, the other one advances
     n_keys = torch.tensor([3, 1], dtype=torch.int32, device=dev)
     full = torch.zeros(1, dtype=torch.int32, device=dev)
+    k_new, v_new = torch.full((2, 8), 9.0, device=dev), torch.full((2, 8), 8.0, device=dev)
+    torch.cuda.synchronize()
     rc = zt.lib.load().zt_kv_append(layer.k.data_ptr(), layer.v.data_ptr(), n_keys.data_ptr(),
-                                    torch.full((2, 8), 9.0, device=dev).data_ptr(),
-                                    torch.full((2, 8), 8.0, device=dev).data_ptr(), full.data_ptr(),
-                                    2, 3, 1, 8, None)
+                                    k_new.data_ptr(), v_new.data_ptr(), full.data_ptr(), 2, 3, 1, 8, None)
     torch.cuda.synchronize()
     assert rc == 0 and n_keys.tolist() == [3, 2] and int(full) == 1
     assert float(layer.k[1, 1, 0]) == 9.0 and float(layer.k[0, 2, 0]) == 2.0
