@@ -137,6 +137,36 @@ int zt_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
                    int n_ctx, int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
 size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim);
 
+/* zt_attn_decode for callers that have no workspace to give and must not allocate one.
+ * (No counterpart in the reference: its decode arm has no split over the context and so needs
+ * no scratch.)
+ *
+ * Who this is for: a caller that follows the reference's contract to the letter -- every buffer
+ * is sized once, up front, and an entry point never allocates (src/cuda/attn_kernels.cu:39,50-54)
+ * -- has nowhere to get zt_attn_decode's workspace from in the middle of a generation loop.
+ * The same holds for a server that hands all of the device's memory to its own pool at start-up
+ * (a later cudaMalloc fails or fragments the pool), and for a latency-bound decode loop, where
+ * cudaMalloc/cudaFree stall because they synchronise the whole device.
+ *
+ * The scratch is a fixed 16 MiB array (zt_attn_decode_static_capacity()) compiled into the
+ * library; every GPU that loads the library carries it until the process exits.  This entry
+ * point calls no cudaMalloc, cudaFree or other allocating routine.  A shape whose split needs
+ * more than the capacity (zt_attn_decode_workspace_bytes tells) is refused with return 1, as
+ * are head widths that are not a multiple of 4 floats and q/cache pointers that are not
+ * 16-byte aligned (zt_attn_decode accepts those).  Arguments, results, NaN rows for a bad
+ * n_keys[b]: exactly zt_attn_decode's.
+ *
+ * Rules that come with a shared, permanent scratch:
+ *  - the first call made with a given device current looks up the array's address on that
+ *    device; make that first call before starting any stream capture;
+ *  - all calls on a device use the same array, which still holds the previous call's partial
+ *    results: two calls may not overlap on the GPU (different streams, or threads, without an
+ *    ordering between them race on it).  Calls queued on one stream are safe. */
+int zt_attn_decode_static(const float *q, const float *k_cache, const float *v_cache,
+                          const int *n_keys, float *out, float *lse, int batch, int n_ctx,
+                          int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
+size_t zt_attn_decode_static_capacity(void);
+
 /* After synchronising: number of sequences the last zt_attn_decode that used
  * `workspace` skipped for a bad n_keys (the count is kept inside the workspace). */
 int zt_attn_decode_status(const void *workspace, int *host_bad_sequences);

@@ -100,6 +100,40 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
     return launch_bwd_simt(p, batch, stream);
 }
 
+// ---- decode scratch that nobody allocates ---------------------------------------------------
+// Scratch for zt_attn_decode_static lives in the library image itself: a fixed array in device
+// global memory that exists on every GPU that loads this library, from load until the process
+// ends.  Host code cannot use the array's name as a pointer (on the host the name only stands
+// for the symbol); the device address is asked for once per device, below.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+// The array's address on the CURRENT device, looked up on the first call made with that device
+// current and remembered.  Returns nullptr (with the reason refused) when the lookup fails.
+static void *static_scratch_address() {
+    static void *address[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        refuse("the current CUDA device could not be read.");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!address[dev]) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_static_decode_scratch);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            refuse("the built-in decode scratch could not be located on device %d: %s", dev,
+                   cudaGetErrorString(e));
+            return nullptr;
+        }
+        address[dev] = ptr;
+    }
+    return address[dev];
+}
+
 }  // namespace zt
 
 using namespace zt;
@@ -306,6 +340,38 @@ int zt_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     p.n_keys_dev = n_keys, p.bad_count = reinterpret_cast<int *>(workspace);
     return launch_fwd_simt(p, batch, s);
+}
+
+size_t zt_attn_decode_static_capacity(void) { return kStaticScratchBytes; }
+
+int zt_attn_decode_static(const float *q, const float *k_cache, const float *v_cache,
+                          const int *n_keys, float *out, float *lse, int batch, int n_ctx,
+                          int n_heads, int n_kv_heads, int dim, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (n_ctx < 1) return refuse("n_ctx %d is not a cache.", n_ctx);
+    if (check_geometry(1, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k_cache || !v_cache || !n_keys || !out)
+        return refuse("a null device pointer was passed.");
+    if (dim % 4 != 0 || !aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache))
+        return refuse("zt_attn_decode_static needs head_dim %% 4 == 0 and 16-byte aligned q and caches "
+                      "(head_dim %d); use zt_attn_decode for other layouts.", dim);
+    const DecodePlan pl = decode_plan(batch, n_ctx, n_heads, n_kv_heads, dim);
+    if (pl.total_bytes > kStaticScratchBytes)
+        return refuse("this decode shape needs %zu bytes of scratch and the built-in scratch holds %zu; "
+                      "pass a workspace to zt_attn_decode instead.", pl.total_bytes, kStaticScratchBytes);
+    if (need_device()) return 1;
+    void *scratch = static_scratch_address();
+    if (!scratch) return 1;
+    DecodeParams p{};
+    p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.n_keys = n_keys, p.n_keys_all = 0;
+    p.out = out, p.lse = lse;
+    p.batch = batch, p.n_ctx = n_ctx, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.dim = dim;
+    p.cache_batch_stride = (long long)n_ctx * n_kv_heads * dim;
+    p.scale_log2 = kLog2e / sqrtf((float)dim);
+    // launch_decode clears the scratch's header (the bad-sequence counter) on `stream` first;
+    // every other word of the scratch that the combine step reads is written by this call.
+    return launch_decode(p, pl, scratch, (cudaStream_t)stream);
 }
 
 int zt_attn_decode_status(const void *workspace, int *host_bad_sequences) {

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "zt_attn_backward_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_decode": (_i, [_vp] * 7 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_decode_workspace_bytes": (_sz, [_i] * 5),
+    "zt_attn_decode_static": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),
+    "zt_attn_decode_static_capacity": (_sz, []),
     "zt_attn_decode_status": (_i, [_vp, C.POINTER(_i)]),
     "zt_kv_append": (_i, [_vp] * 6 + [_i] * 4 + [_vp]),
 }
