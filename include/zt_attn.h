@@ -184,6 +184,11 @@ int zt_kv_append(float *k_cache, float *v_cache, int *n_keys, const float *k_new
  * benchmarks report the difference over their timed region. */
 unsigned long long zt_attn_launch_count(void);
 
+/* After synchronising: 0 when no tensor-core kernel on the current device ever gave up on one
+ * of its bounded internal waits, else the code of the wait that did (its outputs are then
+ * invalid).  A correct run never sets it; tests assert 0. */
+int zt_attn_tc_status(int *host_status);
+
 /* Per-kernel device timing for benchmarks.  zt_attn_profile(1) makes every later launch
  * record a pair of CUDA events on its stream; zt_attn_profile_read waits for them, writes one
  * line per kernel name ("name launches total_ms\n") into host_buf, forgets them, and returns

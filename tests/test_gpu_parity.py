@@ -384,3 +384,62 @@ def test_refused_call_touches_nothing(zt, dev):
     torch.cuda.synchronize()
     L.zt_attn_set_verbose(1)
     assert rc == 1 and torch.all(out == 7.0)
+
+
+# ---- tensor-core (tcgen05) forward ---------------------------------------------------------------
+
+TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, several key tiles
+    (1, 128, 4, 2, 32), (2, 129, 4, 2, 64), (1, 200, 8, 2, 128), (2, 256, 4, 4, 128), (1, 321, 6, 3, 64),
+    (1, 384, 4, 1, 32), (1, 640, 8, 8, 128), (2, 513, 4, 2, 128),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
+def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D):
+    q = oracle.fill_normal((B, T, H * D), 51, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 51, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 51, 2)
+    zt.lib.load().zt_attn_set_path(0)
+    o, lse = zt.attention_forward(cu(q, dev), cu(k, dev), cu(v, dev), H, Hkv, D, want_lse=True)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05"
+    assert zt.lib.tc_status() == 0
+    for b in range(B):
+        ro, rl = oracle.attention_forward(q[b], k[b], v[b], H, Hkv, D, want_lse=True, threads=8)
+        close(o[b].cpu().numpy(), ro, f"item {b} out")
+        close(lse[b].cpu().numpy(), rl, f"item {b} lse")
+
+
+def test_tensor_core_and_simt_paths_agree(zt, dev, oracle):
+    B, T, H, Hkv, D = 2, 700, 8, 2, 128
+    q = cu(oracle.fill_normal((B, T, H * D), 52, 0), dev)
+    k = cu(oracle.fill_normal((B, T, Hkv * D), 52, 1), dev)
+    v = cu(oracle.fill_normal((B, T, Hkv * D), 52, 2), dev)
+    L = zt.lib.load()
+    L.zt_attn_set_path(1)
+    o_simt = zt.attention_forward(q, k, v, H, Hkv, D)
+    assert zt.lib.last_path() == "simt"
+    L.zt_attn_set_path(0)
+    o_tc = zt.attention_forward(q, k, v, H, Hkv, D)
+    assert zt.lib.last_path() == "tcgen05"
+    torch.cuda.synchronize()
+    assert zt.lib.tc_status() == 0
+    close(o_tc.cpu().numpy(), o_simt.cpu().numpy(), "tcgen05 vs simt")
+
+
+def test_tensor_core_large_magnitudes_and_peaked_rows(zt, dev, oracle):
+    """Scores far apart (a few dominant keys per row, maxima that keep growing past the lazy
+    rescale threshold) and large |v|: the hi/lo split of P and the lazily moved maximum must
+    still land inside the tolerance.  (Scores are kept below ~2^5: every f32-accumulating
+    kernel loses |score| * 2^-23 per accumulation, which the exponential turns into a relative
+    error of P.)"""
+    T, H, Hkv, D = 300, 4, 2, 64
+    q = oracle.fill_normal((T, H * D), 53, 0) * np.float32(2.5)
+    k = oracle.fill_normal((T, Hkv * D), 53, 1) * np.float32(2.5)
+    v = oracle.fill_normal((T, Hkv * D), 53, 2) * np.float32(100.0)
+    o, lse = zt.attention_forward(cu(q, dev), cu(k, dev), cu(v, dev), H, Hkv, D, want_lse=True)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0
+    ro, rl = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
+    close(o.cpu().numpy(), ro, "peaked out")
+    close(lse.cpu().numpy(), rl, "peaked lse")

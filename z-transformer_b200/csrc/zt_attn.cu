@@ -13,7 +13,7 @@
 #include "decode_kernels.cuh"
 #include "simt_kernels.cuh"
 #include "zt_common.cuh"
-#ifdef ZT_WITH_TC
+#ifndef ZT_NO_TC
 #include "tc_fwd.cuh"
 #endif
 
@@ -68,7 +68,7 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const float scale_log2 = kLog2e / sqrtf((float)dim);
     const long long q_bs = (long long)T * n_heads * dim;
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
-#ifdef ZT_WITH_TC
+#ifndef ZT_NO_TC
     if (g_path.load() == 0 &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
@@ -158,6 +158,20 @@ const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
 int zt_attn_set_path(int path) { return g_path.exchange(path == 1 ? 1 : 0); }
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
+
+int zt_attn_tc_status(int *host_status) {
+    if (!host_status) return refuse("a null pointer was passed.");
+#ifndef ZT_NO_TC
+    if (need_device()) return 1;
+    if (tc_status_read(host_status)) {
+        const cudaError_t e = cudaGetLastError();
+        return refuse("reading the tensor-core status failed: %s", cudaGetErrorString(e));
+    }
+#else
+    *host_status = 0;
+#endif
+    return 0;
+}
 
 void zt_attn_profile(int on) { g_profile.store(on ? 1 : 0); }
 

@@ -26,6 +26,7 @@ _SIGNATURES = {
     "zt_attn_set_verbose": (None, [_i]),
     "zt_attn_set_path": (_i, [_i]),
     "zt_attn_launch_count": (C.c_ulonglong, []),
+    "zt_attn_tc_status": (_i, [C.POINTER(_i)]),
     "zt_attn_profile": (None, [_i]),
     "zt_attn_profile_read": (_i, [C.c_char_p, _sz]),
     "zt_attn_forward_batched": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
@@ -81,6 +82,14 @@ def profile_read() -> dict:
         name, n, ms = line.split()
         out[name] = (int(n), float(ms))
     return out
+
+
+def tc_status() -> int:
+    """0 unless a tensor-core kernel gave up on a bounded wait (synchronise first)."""
+    v = C.c_int(0)
+    if load().zt_attn_tc_status(C.byref(v)) != 0:
+        raise RuntimeError(last_error())
+    return v.value
 
 
 def launch_count() -> int:
