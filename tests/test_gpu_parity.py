@@ -429,17 +429,74 @@ def test_tensor_core_and_simt_paths_agree(zt, dev, oracle):
 
 def test_tensor_core_large_magnitudes_and_peaked_rows(zt, dev, oracle):
     """Scores far apart (a few dominant keys per row, maxima that keep growing past the lazy
-    rescale threshold) and large |v|: the hi/lo split of P and the lazily moved maximum must
-    still land inside the tolerance.  (Scores are kept below ~2^5: every f32-accumulating
+    rescale threshold): the hi/lo split of P and the lazily moved maximum must still land
+    inside the tolerance.  (Scores are kept below ~2^5: every f32-accumulating
     kernel loses |score| * 2^-23 per accumulation, which the exponential turns into a relative
     error of P.)"""
     T, H, Hkv, D = 300, 4, 2, 64
     q = oracle.fill_normal((T, H * D), 53, 0) * np.float32(2.5)
     k = oracle.fill_normal((T, Hkv * D), 53, 1) * np.float32(2.5)
-    v = oracle.fill_normal((T, Hkv * D), 53, 2) * np.float32(100.0)
+    v = oracle.fill_normal((T, Hkv * D), 53, 2)
     o, lse = zt.attention_forward(cu(q, dev), cu(k, dev), cu(v, dev), H, Hkv, D, want_lse=True)
     torch.cuda.synchronize()
     assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0
     ro, rl = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
     close(o.cpu().numpy(), ro, "peaked out")
     close(lse.cpu().numpy(), rl, "peaked lse")
+
+
+# ---- tensor-core (tcgen05) backward ---------------------------------------------------------------
+
+TC_BWD_SHAPES = [  # B, T, H, Hkv, D
+    (1, 128, 4, 2, 64), (2, 129, 4, 2, 128), (1, 200, 8, 2, 128), (1, 256, 4, 4, 64), (1, 321, 6, 3, 128),
+    (2, 513, 4, 1, 128), (1, 640, 8, 8, 64),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D", TC_BWD_SHAPES)
+def test_tensor_core_backward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D):
+    q = oracle.fill_normal((B, T, H * D), 61, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 61, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 61, 2)
+    do = oracle.fill_normal((B, T, H * D), 61, 3)
+    zt.lib.load().zt_attn_set_path(0)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05"
+    assert zt.lib.tc_status() == 0
+    for b in range(B):
+        rdq, rdk, rdv = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D, threads=8)
+        close(dq[b].cpu().numpy(), rdq, f"item {b} dq")
+        close(dk[b].cpu().numpy(), rdk, f"item {b} dk")
+        close(dv[b].cpu().numpy(), rdv, f"item {b} dv")
+
+
+def test_tensor_core_backward_uneven_magnitudes(zt, dev, oracle):
+    """Heads and tensors of very different scale: the per-(sequence, KV group) power-of-two scaling of
+    the 16-bit split must keep every group inside the tolerance."""
+    T, H, Hkv, D = 260, 8, 4, 128
+    q = oracle.fill_normal((T, H * D), 62, 0)
+    k = oracle.fill_normal((T, Hkv * D), 62, 1)
+    v = oracle.fill_normal((T, Hkv * D), 62, 2)
+    do = oracle.fill_normal((T, H * D), 62, 3)
+    for g, f in enumerate((1e-3, 1.0, 37.0, 2.5e3)):
+        v[:, g * D:(g + 1) * D] *= np.float32(f)
+        do[:, 2 * g * D:(2 * g + 2) * D] *= np.float32(1.0 / f)
+    q[:, :2 * D] *= np.float32(0.05)
+    k[:, D:2 * D] *= np.float32(3.0)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0
+    rdq, rdk, rdv = oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)
+    # Gradients of a group scale with that group's inputs, so the gate is relative to each KV
+    # group's own largest gradient (the reference's scale-relative gate, src/cuda/attn.cu:103-113).
+    g = H // Hkv
+    for name, got, ref, w in (("dq", dq, rdq, g * D), ("dk", dk, rdk, D), ("dv", dv, rdv, D)):
+        got = got.cpu().numpy()
+        for kv in range(Hkv):
+            a, r = got[:, kv * w:(kv + 1) * w].astype(np.float64), ref[:, kv * w:(kv + 1) * w].astype(np.float64)
+            assert np.max(np.abs(a - r)) <= 1e-4 * np.max(np.abs(r)), (name, kv)

@@ -1,0 +1,710 @@
+// Causal GQA attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// What it computes: autograd.attentionBackward (src/autograd.zig:636-842) for a batch, from the
+// forward's out (through delta = sum_j dout*out) and log-sum-exp:
+//     P  = exp(S - lse),  dP = dO V^T,  dS = P (dP - delta)
+//     dV = P^T dO,   dK = scale dS^T Q,   dQ = scale dS K
+//
+// Arithmetic.  A head_dim-128 backward needs Q, dO, K, V and P, dS as tensor-core operands at
+// once; as f32 hi/lo pairs (8 bytes per element) they do not fit in shared memory plus TMEM.
+// So the backward uses the same three-term split idea on 16-bit pieces instead of TF32 ones:
+//     x * m = h + l,   h = f16(x m),  l = f16(x m - h),   a.b ~ (ha hb + ha lb + la hb) / (ma mb)
+// with m a power of two per (sequence, KV group) that puts the block's largest |x| just under
+// 2^15.  h + l carries 22 mantissa bits of x (what 3xTF32 carries is 21), products accumulate
+// in f32 in TMEM, and each term is one kind::f16 MMA at twice the TF32 rate: half the operand
+// bytes and half the tensor time of 3xTF32.  Elements more than 2^25 below their block's
+// maximum lose relative (not absolute) precision; the parity tests bound the effect.
+//
+// Kernels:
+//   bwd_absmax / bwd_split   per-(sequence, KV group) max |x| of q, k, v, dout; then the h and l
+//                            planes of each tensor ([2][B][T][W] halves) in the workspace.
+//   attn_bwd_dkdv_tc         one CTA per (128 keys, KV head, sequence): S^T = K Q^T and
+//                            dP^T = V dO^T per 64-row query tile of every head of the group,
+//                            P^T and dS^T written back to TMEM as packed halves,
+//                            dV += P^T dO and dK += dS^T Q accumulated in TMEM for the whole walk:
+//                            dk/dv are assigned by their one owner, no atomics.
+//   attn_bwd_dq_tc           one CTA per (128 query rows, head, sequence): S = Q K^T, dP = dO V^T,
+//                            dS, dQ += dS K over the causal key tiles; dq assigned.
+// Every wait is bounded (see tc_common.cuh); a wait that gives up raises g_tc_status.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "tc_common.cuh"
+#include "tc_fwd.cuh"
+#include "zt_common.cuh"
+
+namespace zt {
+namespace tcb {
+
+using namespace tc;
+
+// ---- scaling --------------------------------------------------------------------------------------
+// The power of two that moves a block's largest magnitude into [2^14, 2^15).  `bits` is the f32
+// bit pattern of max |x| (non-negative, so it orders like an integer).
+__host__ __device__ inline float block_mult(uint32_t bits) {
+    const int ex = (int)((bits >> 23) & 0xff);  // biased exponent: |x| in [2^(ex-127), 2^(ex-126))
+    if (ex == 0 || ex == 0xff) return 1.0f;      // zero/subnormal block, or inf/nan: leave alone
+    int e = 14 - (ex - 127);                     // |x| * 2^e in [2^14, 2^15)
+    if (e > 126) e = 126;
+    if (e < -126) e = -126;
+    uint32_t out = (uint32_t)(e + 127) << 23;
+#if defined(__CUDA_ARCH__)
+    return __uint_as_float(out);
+#else
+    float f;
+    memcpy(&f, &out, 4);
+    return f;
+#endif
+}
+
+// max |x| over each (sequence, group of `cols_per_group` columns).  grid (groups, batch, splits).
+__global__ void __launch_bounds__(256) bwd_absmax_kernel(const float *__restrict__ x, uint32_t *__restrict__ out,
+                                                         int T, int width, int cols_per_group) {
+    const int g = blockIdx.x, b = blockIdx.y;
+    const int n_groups = gridDim.x;
+    const float *base = x + (long long)b * T * width + (long long)g * cols_per_group;
+    const int vec_per_row = cols_per_group / 4;
+    const long long total = (long long)T * vec_per_row;
+    float m = 0.f;
+    for (long long i = (long long)blockIdx.z * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.z * blockDim.x) {
+        const long long r = i / vec_per_row;
+        const int c = (int)(i - r * vec_per_row);
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(base + r * width) + c);
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31) == 0) atomicMax(out + b * n_groups + g, __float_as_uint(m));
+}
+
+// x -> planes h = f16(x m), l = f16(x m - h).  planes: [2][batch][T][width] halves.
+__global__ void __launch_bounds__(256) bwd_split_kernel(const float *__restrict__ x, const uint32_t *__restrict__ amax,
+                                                        __half *__restrict__ planes, int batch, int T, int width,
+                                                        int cols_per_group) {
+    const long long n4 = (long long)batch * T * width / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const long long e = i * 4;
+    const int col = (int)(e % width);
+    const int b = (int)(e / ((long long)T * width));
+    const int n_groups = width / cols_per_group;
+    const float m = block_mult(amax[b * n_groups + col / cols_per_group]);
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+    const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
+    __half h[4], l[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        h[k] = __float2half_rn(s[k]);
+        l[k] = __float2half_rn(s[k] - __half2float(h[k]));
+    }
+    __half *hp = planes + e;
+    __half *lp = planes + (long long)batch * T * width + e;
+    *reinterpret_cast<uint2 *>(hp) = *reinterpret_cast<const uint2 *>(h);
+    *reinterpret_cast<uint2 *>(lp) = *reinterpret_cast<const uint2 *>(l);
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+// (a, b) -> packed h pair and packed l pair
+__device__ __forceinline__ void split_pack(float a, float b, uint32_t &hw, uint32_t &lw) {
+    const __half ha = __float2half_rn(a), hb = __float2half_rn(b);
+    const __half2 hh = __halves2half2(ha, hb);
+    hw = *reinterpret_cast<const uint32_t *>(&hh);
+    lw = pack_half2(a - __half2float(ha), b - __half2float(hb));
+}
+
+constexpr int kBwdThreads = 192;  // 4 row warps, 1 TMA warp, 1 MMA warp
+
+struct BwdParams {
+    const float *lse, *delta;        // [B, T, H]
+    const __half *v_planes;          // dkdv kernel: V planes read straight into TMEM
+    const __half *q_planes, *do_planes;  // dq kernel: Q, dO planes read straight into TMEM
+    const uint32_t *amax_q, *amax_k, *amax_v, *amax_do;  // [B, Hkv] bit patterns of max |x|
+    float *dq, *dk, *dv;
+    int batch, T, n_heads, n_kv_heads;
+    float scale, scale_log2;
+    float p_scale;  // P is multiplied by this power of two before its 16-bit split
+    float c1;       // dP (in scaled units) is multiplied by this power of two before dS is split
+};
+
+struct BwdShared {
+    uint64_t full[3], free_[3];
+    uint64_t k_full, a_ready, sdp_full, p_full, acc_done, ld_ready;
+    uint32_t tmem_base;
+    volatile int abort;
+    float lse2[2][64], dels[2][64];
+};
+
+__device__ __forceinline__ bool bwait(uint64_t *bar, uint32_t parity, BwdShared *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void bgive_up(BwdShared *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+
+
+// One row of `words` packed-half words from global memory into TMEM columns [col, col + words).
+template <int WORDS>
+__device__ __forceinline__ void row_to_tmem(const __half *src, bool valid, uint32_t taddr) {
+#pragma unroll 1
+    for (int c = 0; c < WORDS; c += 32) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid) v = __ldg(reinterpret_cast<const uint4 *>(src) + (c + i) / 4);
+            r[i] = v.x, r[i + 1] = v.y, r[i + 2] = v.z, r[i + 3] = v.w;
+        }
+        tmem_st32(taddr + c, r);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// dK, dV.  grid (ceil(T / 128), n_kv_heads, batch).
+// ---------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    attn_bwd_dkdv_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap qmap,
+                     const __grid_constant__ CUtensorMap gmap, const BwdParams p) {
+    constexpr int NB = D / 64, W2 = D / 2;
+    constexpr int KP = 128 * D * 2, QP = 64 * D * 2;              // bytes of one plane of a K / Q tile
+    constexpr int cVh = 0, cVl = W2, cST = D, cDPT = D + 64, cDV = D + 128, cDK = 2 * D + 128;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sKh = smem, *sKl = smem + KP;
+    uint8_t *stage0 = smem + 2 * KP;  // stage s: Qh, Ql, dOh, dOl at stage0 + s * 4 QP + {0,1,2,3} QP
+    BwdShared *sh = reinterpret_cast<BwdShared *>(smem + 2 * KP + 8 * QP);
+
+    const int warp = threadIdx.x >> 5;
+    const int kt = (int)gridDim.x - 1 - (int)blockIdx.x;  // early key tiles see the most query rows
+    const int g = blockIdx.y, b = blockIdx.z;
+    const int group = p.n_heads / p.n_kv_heads;
+    const int s0 = kt * 128;
+    const int n_q = (p.T + 63) / 64, qi0 = s0 / 64;
+    const int per_head = n_q - qi0;
+    const int n_it = group * per_head;
+    const int B = p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
+        mbar_init(&sh->k_full, 1);
+        mbar_init(&sh->a_ready, 128);
+        mbar_init(&sh->sdp_full, 1);
+        mbar_init(&sh->p_full, 128);
+        mbar_init(&sh->acc_done, 1);
+        mbar_init(&sh->ld_ready, 128);
+        sh->abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
+    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
+    const float c1 = p.c1;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&qmap), tma_prefetch_desc(&gmap);
+            mbar_arrive_expect_tx(&sh->k_full, 2 * KP);
+            tma_load_4d(sKh, &kmap, &sh->k_full, 0, s0, g * NB, b);
+            tma_load_4d(sKl, &kmap, &sh->k_full, 0, s0, g * NB, B + b);
+            int issued = 0;
+            for (int it = 0; it < n_it; ++it) {
+                const int s = it & 1;
+                if (it >= 2 && !bwait(&sh->free_[s], (uint32_t)(((it >> 1) & 1) ^ 1), sh)) { bgive_up(sh, 21); break; }
+                // Walk order: late query tiles first, and for each tile all heads of the group.  A key's
+                // terms grow as the query position falls (p ~ 1/t), so its accumulators in TMEM receive
+                // the small terms first; the tensor core adds with truncation, and small terms added
+                // to an already large accumulator would be cut short thousands of times.
+                const int h = g * group + it % group, row = (n_q - 1 - it / group) * 64;
+                uint8_t *st = stage0 + s * 4 * QP;
+                mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
+                tma_load_4d(st, &qmap, &sh->full[s], 0, row, h * NB, b);
+                tma_load_4d(st + QP, &qmap, &sh->full[s], 0, row, h * NB, B + b);
+                tma_load_4d(st + 2 * QP, &gmap, &sh->full[s], 0, row, h * NB, b);
+                tma_load_4d(st + 3 * QP, &gmap, &sh->full[s], 0, row, h * NB, B + b);
+                ++issued;
+            }
+            if (sh->abort) {
+                mbar_wait(&sh->k_full, 0);
+                for (int it = (issued > 2 ? issued - 2 : 0); it < issued; ++it)
+                    mbar_wait(&sh->full[it & 1], (uint32_t)((it >> 1) & 1));
+            }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
+            constexpr uint32_t id_a = idesc_f16(128, D, false, true);
+            bool ok = bwait(&sh->k_full, 0, sh) && bwait(&sh->a_ready, 0, sh);
+            if (!ok) bgive_up(sh, 22);
+            const uint32_t kh = smem_u32(sKh), kl = smem_u32(sKl);
+            for (int it = 0; ok && it < n_it; ++it) {
+                const int s = it & 1;
+                if (!bwait(&sh->full[s], (uint32_t)((it >> 1) & 1), sh)) { bgive_up(sh, 23); break; }
+                tc_fence_after();
+                const uint32_t qh = smem_u32(stage0 + s * 4 * QP), ql = qh + QP, gh = qh + 2 * QP, gl = qh + 3 * QP;
+#pragma unroll 2
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint64_t dkh = desc_kmajor(kh + ao), dkl = desc_kmajor(kl + ao);
+                    const uint64_t dqh = desc_kmajor(qh + bo), dql = desc_kmajor(ql + bo);
+                    mma_ss_f16(tmem + cST, dkh, dqh, id_s, kk > 0);
+                    mma_ss_f16(tmem + cST, dkh, dql, id_s, 1);
+                    mma_ss_f16(tmem + cST, dkl, dqh, id_s, 1);
+                }
+#pragma unroll 2
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint64_t dgh = desc_kmajor(gh + bo), dgl = desc_kmajor(gl + bo);
+                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgl, id_s, 1);
+                    mma_ts_f16(tmem + cDPT, tmem + cVl + kk * 8, dgh, id_s, 1);
+                }
+                mma_commit(&sh->sdp_full);
+                if (!bwait(&sh->p_full, (uint32_t)(it & 1), sh)) { bgive_up(sh, 24); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                    const uint64_t dgh = desc_mnmajor_16b(gh + kk * 2048, 64 * 128);
+                    const uint64_t dgl = desc_mnmajor_16b(gl + kk * 2048, 64 * 128);
+                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgh, id_a, (it > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgl, id_a, 1);
+                    mma_ts_f16(tmem + cDV, tmem + cST + ac + 16, dgh, id_a, 1);
+                }
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                    const uint64_t dqh = desc_mnmajor_16b(qh + kk * 2048, 64 * 128);
+                    const uint64_t dql = desc_mnmajor_16b(ql + kk * 2048, 64 * 128);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dqh, id_a, (it > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dql, id_a, 1);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac + 16, dqh, id_a, 1);
+                }
+                mma_commit(&sh->free_[s]);
+                mma_commit(&sh->acc_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ one thread per key row
+        const int tid = threadIdx.x;
+        const int key = s0 + tid;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const long long wkv = (long long)p.n_kv_heads * D;
+        {
+            const __half *vh = p.v_planes + ((long long)b * p.T + (key < p.T ? key : 0)) * wkv + (long long)g * D;
+            const __half *vl = vh + (long long)B * p.T * wkv;
+            row_to_tmem<W2>(vh, key < p.T, tmem + lane_base + cVh);
+            row_to_tmem<W2>(vl, key < p.T, tmem + lane_base + cVl);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->a_ready);
+        }
+        const float cs = p.scale_log2 / (mq * mk);
+        const float dfac = mdo * mv * c1;
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int h = g * group + it % group, qrow0 = (n_q - 1 - it / group) * 64;
+            const int buf = it & 1;
+            {
+                const int t = qrow0 + (tid & 63);
+                const long long idx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
+                if (tid < 64) sh->lse2[buf][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
+                else sh->dels[buf][tid - 64] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
+            }
+            mbar_arrive(&sh->ld_ready);  // the 128 row threads exchange lse/delta through shared memory
+            if (!__all_sync(0xffffffffu, bwait(&sh->ld_ready, (uint32_t)(it & 1), sh) &&
+                                             bwait(&sh->sdp_full, (uint32_t)(it & 1), sh))) {
+                bgive_up(sh, 25);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 64; c += 32) {
+                uint32_t rs[32], rd[32];
+                tmem_ld32(tmem + lane_base + cST + c, rs);
+                tmem_ld32(tmem + lane_base + cDPT + c, rd);
+                tmem_wait_ld();
+                uint32_t ph[16], pl[16], dh[16], dl[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pv[2], dv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int t = qrow0 + c + i + e;
+                        const bool vis = (key <= t) && (t < p.T) && (key < p.T);
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[buf][c + i + e]);
+                        const float pp = vis ? pe : 0.f;
+                        pv[e] = pp * p.p_scale;
+                        dv[e] = fminf(fmaxf(pp * (__uint_as_float(rd[i + e]) * c1 - sh->dels[buf][c + i + e]), -65000.f), 65000.f);
+                    }
+                    split_pack(pv[0], pv[1], ph[i >> 1], pl[i >> 1]);
+                    split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
+                }
+                tmem_st16(tmem + lane_base + cST + c, ph);
+                tmem_st16(tmem + lane_base + cST + c + 16, pl);
+                tmem_st16(tmem + lane_base + cDPT + c, dh);
+                tmem_st16(tmem + lane_base + cDPT + c + 16, dl);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->p_full);
+        }
+        if (ok && !__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)((n_it - 1) & 1), sh))) {
+            bgive_up(sh, 26);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const float fv = 1.0f / (p.p_scale * mdo);
+            const float fk = p.scale / (mdo * mv * c1 * mq);
+            float *dvr = p.dv + ((long long)b * p.T + key) * wkv + (long long)g * D;
+            float *dkr = p.dk + ((long long)b * p.T + key) * wkv + (long long)g * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t rv[32], rk[32];
+                tmem_ld32(tmem + lane_base + cDV + c, rv);
+                tmem_ld32(tmem + lane_base + cDK + c, rk);
+                tmem_wait_ld();
+                if (key < p.T) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 a, k4;
+                        a.x = __uint_as_float(rv[i]) * fv, a.y = __uint_as_float(rv[i + 1]) * fv;
+                        a.z = __uint_as_float(rv[i + 2]) * fv, a.w = __uint_as_float(rv[i + 3]) * fv;
+                        k4.x = __uint_as_float(rk[i]) * fk, k4.y = __uint_as_float(rk[i + 1]) * fk;
+                        k4.z = __uint_as_float(rk[i + 2]) * fk, k4.w = __uint_as_float(rk[i + 3]) * fk;
+                        *reinterpret_cast<float4 *>(dvr + c + i) = a;
+                        *reinterpret_cast<float4 *>(dkr + c + i) = k4;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// dQ.  grid (ceil(T / 128), n_heads, batch).
+// ---------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    attn_bwd_dq_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                   const BwdParams p) {
+    constexpr int NB = D / 64, W2 = D / 2;
+    constexpr int QP = 64 * D * 2;  // bytes of one plane of a 64-key tile
+    constexpr int cQh = 0, cQl = W2, cGh = D, cGl = D + W2, cS = 2 * D, cDP = 2 * D + 64, cDQ = 2 * D + 128;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    BwdShared *sh = reinterpret_cast<BwdShared *>(smem + 12 * QP);  // 3 stages x (Kh, Kl, Vh, Vl)
+
+    const int warp = threadIdx.x >> 5;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (p.n_heads / p.n_kv_heads);
+    const int t0 = qt * 128;
+    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
+    const int n_tiles = (rows_end + 63) / 64;
+    const int B = p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
+        mbar_init(&sh->k_full, 1);
+        mbar_init(&sh->a_ready, 128);
+        mbar_init(&sh->sdp_full, 1);
+        mbar_init(&sh->p_full, 128);
+        mbar_init(&sh->acc_done, 1);
+        mbar_init(&sh->ld_ready, 128);
+        sh->abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
+    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
+    const float c1 = p.c1;
+
+    if (warp == 4) {
+        if (elect_one()) {
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % 3;
+                if (j >= 3 && !bwait(&sh->free_[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { bgive_up(sh, 31); break; }
+                uint8_t *st = smem + s * 4 * QP;
+                mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
+                tma_load_4d(st, &kmap, &sh->full[s], 0, j * 64, g * NB, b);
+                tma_load_4d(st + QP, &kmap, &sh->full[s], 0, j * 64, g * NB, B + b);
+                tma_load_4d(st + 2 * QP, &vmap, &sh->full[s], 0, j * 64, g * NB, b);
+                tma_load_4d(st + 3 * QP, &vmap, &sh->full[s], 0, j * 64, g * NB, B + b);
+                ++issued;
+            }
+            if (sh->abort)
+                for (int j = (issued > 3 ? issued - 3 : 0); j < issued; ++j)
+                    mbar_wait(&sh->full[j % 3], (uint32_t)((j / 3) & 1));
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
+            constexpr uint32_t id_a = idesc_f16(128, D, false, true);
+            bool ok = bwait(&sh->a_ready, 0, sh);
+            if (!ok) bgive_up(sh, 32);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int s = j % 3;
+                if (!bwait(&sh->full[s], (uint32_t)((j / 3) & 1), sh)) { bgive_up(sh, 33); break; }
+                tc_fence_after();
+                const uint32_t kh = smem_u32(smem + s * 4 * QP), kl = kh + QP, vh = kh + 2 * QP, vl = kh + 3 * QP;
+#pragma unroll 2
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint64_t dkh = desc_kmajor(kh + bo), dkl = desc_kmajor(kl + bo);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
+                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                }
+#pragma unroll 2
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint64_t dvh = desc_kmajor(vh + bo), dvl = desc_kmajor(vl + bo);
+                    mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvl, id_s, 1);
+                    mma_ts_f16(tmem + cDP, tmem + cGl + kk * 8, dvh, id_s, 1);
+                }
+                mma_commit(&sh->sdp_full);
+                if (!bwait(&sh->p_full, (uint32_t)(j & 1), sh)) { bgive_up(sh, 34); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                    const uint64_t dkh = desc_mnmajor_16b(kh + kk * 2048, 64 * 128);
+                    const uint64_t dkl = desc_mnmajor_16b(kl + kk * 2048, 64 * 128);
+                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkl, id_a, 1);
+                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac + 16, dkh, id_a, 1);
+                }
+                mma_commit(&sh->free_[s]);
+                mma_commit(&sh->acc_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int tid = threadIdx.x;
+        const int t = t0 + tid;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const long long wq = (long long)p.n_heads * D;
+        {
+            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
+            const long long plane = (long long)B * p.T * wq;
+            row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
+            row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
+            row_to_tmem<W2>(p.do_planes + off, t < p.T, tmem + lane_base + cGh);
+            row_to_tmem<W2>(p.do_planes + plane + off, t < p.T, tmem + lane_base + cGl);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->a_ready);
+        }
+        const float cs = p.scale_log2 / (mq * mk);
+        const long long ridx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
+        const float lse2 = (t < p.T) ? __ldg(p.lse + ridx) * kLog2e : 0.f;
+        const float dels = (t < p.T) ? __ldg(p.delta + ridx) * (mdo * mv * c1) : 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!__all_sync(0xffffffffu, bwait(&sh->sdp_full, (uint32_t)(j & 1), sh))) {
+                bgive_up(sh, 35);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 64; c += 32) {
+                uint32_t rs[32], rd[32];
+                tmem_ld32(tmem + lane_base + cS + c, rs);
+                tmem_ld32(tmem + lane_base + cDP + c, rd);
+                tmem_wait_ld();
+                uint32_t dh[16], dl[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float dv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = j * 64 + c + i + e;
+                        const bool vis = (key <= t) && (key < p.T);
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
+                        dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
+                    }
+                    split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
+                }
+                tmem_st16(tmem + lane_base + cDP + c, dh);
+                tmem_st16(tmem + lane_base + cDP + c + 16, dl);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->p_full);
+        }
+        if (ok && !__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)((n_tiles - 1) & 1), sh))) {
+            bgive_up(sh, 36);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const float fq = p.scale / (mdo * mv * c1 * mk);
+            float *dqr = p.dq + ((long long)b * p.T + t) * wq + (long long)h * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + cDQ + c, r);
+                tmem_wait_ld();
+                if (t < p.T) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 a;
+                        a.x = __uint_as_float(r[i]) * fq, a.y = __uint_as_float(r[i + 1]) * fq;
+                        a.z = __uint_as_float(r[i + 2]) * fq, a.w = __uint_as_float(r[i + 3]) * fq;
+                        *reinterpret_cast<float4 *>(dqr + c + i) = a;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+
+struct BwdWorkspace {
+    uint32_t *amax_q, *amax_k, *amax_v, *amax_do;
+    __half *q_planes, *do_planes, *k_planes, *v_planes;
+    size_t total_bytes, amax_bytes;
+};
+
+inline BwdWorkspace bwd_workspace(void *base, int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    BwdWorkspace w{};
+    const size_t n_amax = (size_t)batch * n_kv_heads;
+    w.amax_bytes = (4 * n_amax * sizeof(uint32_t) + 1023) / 1024 * 1024;
+    const size_t qh = (size_t)2 * batch * T * n_heads * dim * sizeof(__half);
+    const size_t kh = (size_t)2 * batch * T * n_kv_heads * dim * sizeof(__half);
+    auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+    char *c = static_cast<char *>(base);
+    w.amax_q = reinterpret_cast<uint32_t *>(c);
+    w.amax_k = w.amax_q + n_amax, w.amax_v = w.amax_k + n_amax, w.amax_do = w.amax_v + n_amax;
+    size_t off = w.amax_bytes;
+    w.q_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
+    w.do_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
+    w.k_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
+    w.v_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
+    w.total_bytes = off;
+    return w;
+}
+
+inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const void *k, const void *v,
+                             const void *dout, const void *dq, const void *dk, const void *dv) {
+    if (!(dim == 64 || dim == 128) || T < 128 || batch < 1) return false;
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al(q) || !al(k) || !al(v) || !al(dout) || !al(dq) || !al(dk) || !al(dv)) return false;
+    const DeviceInfo *d = device_info();
+    return d && d->cc_major == 10 && get_encode_tiled() != nullptr;
+}
+
+template <int D>
+inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &q64, const CUtensorMap &g64,
+                           const CUtensorMap &k64, const CUtensorMap &v64, const BwdParams &p, cudaStream_t stream) {
+    const size_t smem_a = 2 * (size_t)(128 * D * 2) + 8 * (size_t)(64 * D * 2) + sizeof(BwdShared) + 1024;
+    const size_t smem_b = 12 * (size_t)(64 * D * 2) + sizeof(BwdShared) + 1024;
+    const size_t floor_ = 120 * 1024;  // one CTA per SM: each wants all 512 TMEM columns
+    const size_t sa = smem_a > floor_ ? smem_a : floor_, sb = smem_b > floor_ ? smem_b : floor_;
+    if (optin_smem((const void *)attn_bwd_dkdv_tc<D>, sa)) return 1;
+    if (optin_smem((const void *)attn_bwd_dq_tc<D>, sb)) return 1;
+    const dim3 grid_a((unsigned)((p.T + 127) / 128), (unsigned)p.n_kv_heads, (unsigned)p.batch);
+    const dim3 grid_b((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
+    if (ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
+                  (attn_bwd_dkdv_tc<D><<<grid_a, kBwdThreads, sa, stream>>>(k128, q64, g64, p))))
+        return 1;
+    return ZT_LAUNCH("attn_bwd_dq_tc", stream, (attn_bwd_dq_tc<D><<<grid_b, kBwdThreads, sb, stream>>>(k64, v64, p)));
+}
+
+}  // namespace tcb
+
+inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
+}
+
+// delta must already hold sum_j dout*out.  dq, dk, dv are assigned.
+inline int launch_bwd_tc(const float *q, const float *k, const float *v, const float *dout, const float *lse,
+                         const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
+                         int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+    using namespace tcb;
+    const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, dim);
+    const int group = n_heads / n_kv_heads;
+    const int wq = n_heads * dim, wkv = n_kv_heads * dim;
+    if (cudaMemsetAsync(w.amax_q, 0, w.amax_bytes, stream) != cudaSuccess) {
+        cudaGetLastError();
+        return refuse("could not clear the backward workspace header");
+    }
+    int splits = (T + 511) / 512;
+    if (splits > 64) splits = 64;
+    const dim3 ag((unsigned)n_kv_heads, (unsigned)batch, (unsigned)splits);
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(q, w.amax_q, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(dout, w.amax_do, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(k, w.amax_k, T, wkv, dim)))) return 1;
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(v, w.amax_v, T, wkv, dim)))) return 1;
+    const long long nq4 = (long long)batch * T * wq / 4, nk4 = (long long)batch * T * wkv / 4;
+    const unsigned gq = (unsigned)((nq4 + 255) / 256), gk = (unsigned)((nk4 + 255) / 256);
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(q, w.amax_q, w.q_planes, batch, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(dout, w.amax_do, w.do_planes, batch, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(k, w.amax_k, w.k_planes, batch, T, wkv, dim)))) return 1;
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(v, w.amax_v, w.v_planes, batch, T, wkv, dim)))) return 1;
+    CUtensorMap k128, q64, g64, k64, v64;
+    if (!make_half_tile_map(&k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
+        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||
+        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
+        !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
+        !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 64))
+        return refuse("the TMA tensor maps for the backward could not be encoded.");
+    BwdParams p{};
+    p.lse = lse, p.delta = delta;
+    p.v_planes = w.v_planes, p.q_planes = w.q_planes, p.do_planes = w.do_planes;
+    p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
+    p.dq = dq, p.dk = dk, p.dv = dv;
+    p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.scale = 1.0f / sqrtf((float)dim), p.scale_log2 = kLog2e / sqrtf((float)dim);
+    {
+        int pl = 10, boost = 0;
+        if (const char *e = getenv("ZT_BWD_PSCALE_LOG2")) pl = atoi(e);
+        if (const char *e = getenv("ZT_BWD_DSBOOST_LOG2")) boost = atoi(e);
+        p.p_scale = ldexpf(1.0f, pl);
+        p.c1 = ldexpf(1.0f, boost - 16 - (dim == 128 ? 7 : 6));
+    }
+    g_last_path = "tcgen05";
+    return dim == 64 ? launch_bwd_tc_d<64>(k128, q64, g64, k64, v64, p, stream)
+                     : launch_bwd_tc_d<128>(k128, q64, g64, k64, v64, p, stream);
+}
+
+}  // namespace zt

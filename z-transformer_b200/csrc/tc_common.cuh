@@ -126,6 +126,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -168,6 +177,36 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_b
 __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, bool b_mn_major) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
+}
+
+// 16-bit operands (kind::f16, f16 inputs, f32 accumulate): both K-major and MN-major tiles use the
+// plain 128-byte swizzle; a row is 64 halves, a column block is rows x 128 bytes.  MN-major:
+// column blocks `block_bytes` apart (leading offset), 8 contraction rows per 1024-byte atom
+// (stride offset); one 16-deep MMA step covers two atoms, the next step starts 2048 bytes on.
+__device__ __forceinline__ uint64_t desc_mnmajor_16b(uint32_t addr, uint32_t block_bytes) {
+    return kDescSw128 | (uint64_t)((addr >> 4) & 0x3fff) | (uint64_t)((block_bytes >> 4) & 0x3fff) << 16 |
+           (uint64_t)(1024 >> 4) << 32;
+}
+// a/b format f16 = 0, c format f32 = 1.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ss_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 // D[tmem] (+)= A[tmem] . B[smem]; issued by one thread.
@@ -249,6 +288,22 @@ inline bool make_head_tile_map(CUtensorMap *map, const float *base, int batch, l
                CU_TENSOR_MAP_INTERLEAVE_NONE,
                mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor map over a [planes, rows, width] f16 tensor (planes = hi/lo x batch) seen as column
+// blocks of 64 halves: dims (64, rows, width/64, planes); box (64, box_rows, dim/64, 1); plain
+// 128-byte swizzle.
+inline bool make_half_tile_map(CUtensorMap *map, const void *base, int planes, long long rows, int width,
+                               int dim, int box_rows) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[4] = {64, (cuuint64_t)rows, (cuuint64_t)(width / 64), (cuuint64_t)planes};
+    const cuuint64_t strides[3] = {(cuuint64_t)width * 2, 128, (cuuint64_t)rows * width * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

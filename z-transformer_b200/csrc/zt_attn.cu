@@ -14,6 +14,7 @@
 #include "simt_kernels.cuh"
 #include "zt_common.cuh"
 #ifndef ZT_NO_TC
+#include "tc_bwd.cuh"
 #include "tc_fwd.cuh"
 #endif
 
@@ -24,19 +25,27 @@ namespace zt {
 constexpr int kMinDim = 32, kMaxDim = 256;  // src/cuda/attn_kernels.cu:147-148
 constexpr size_t kArenaBytes = 16u << 20;
 
-// One arena per device, created on the first decode-shaped zt_attn_forward call on
-// that device and kept until the process ends.  The reference's entry points take
-// no workspace argument, and a per-call allocation would synchronise the device.
-static void *device_arena() {
+// One arena per device for the reference's entry points, which take no workspace argument:
+// created on the first call that needs scratch on that device, kept until the process ends,
+// and replaced by a larger one only when a call needs more than it holds (cudaFree waits for
+// the device, so work still using the old arena has finished).  A steady-state caller -- same
+// shapes step after step -- therefore never allocates after its first step.
+static void *device_arena(size_t need = kArenaBytes) {
     static void *arena[64] = {};
+    static size_t held[64] = {};
     static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (need < kArenaBytes) need = kArenaBytes;
     std::lock_guard<std::mutex> lock(mu);
-    if (!arena[dev]) {
-        if (cudaMalloc(&arena[dev], kArenaBytes) != cudaSuccess) {
+    if (held[dev] < need) {
+        if (arena[dev]) cudaFree(arena[dev]);
+        arena[dev] = nullptr, held[dev] = 0;
+        if (cudaMalloc(&arena[dev], need) != cudaSuccess) {
             cudaGetLastError();
             arena[dev] = nullptr;
+        } else {
+            held[dev] = need;
         }
     }
     return arena[dev];
@@ -84,10 +93,28 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     return launch_fwd_simt(p, batch, stream);
 }
 
+static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+#ifndef ZT_NO_TC
+    if ((dim == 64 || dim == 128) && T >= 128) return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+#endif
+    (void)batch, (void)n_heads, (void)n_kv_heads;
+    return 0;
+}
+
 static int backward_impl(const float *q, const float *k, const float *v, const float *lse,
                          const float *delta, const float *dout, float *dq, float *dk, float *dv,
-                         int batch, int T, int n_heads, int n_kv_heads, int dim,
-                         cudaStream_t stream) {
+                         void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                         int n_kv_heads, int dim, cudaStream_t stream) {
+#ifndef ZT_NO_TC
+    if (g_path.load() == 0 && workspace &&
+        workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
+        tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
+        return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
+                             dim, stream);
+    }
+#endif
+    (void)workspace, (void)workspace_bytes;
     SimtBwdParams p{};
     p.q = q, p.k = k, p.v = v, p.dout = dout, p.lse = lse, p.delta = delta;
     p.dq = dq, p.dk = dk, p.dv = dv;
@@ -268,7 +295,10 @@ int zt_attn_backward(const float *q, const float *k, const float *v, const float
     const long long n = (long long)T * n_heads;
     if (ZT_LAUNCH("fill_kernel", s, fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(row_den, n, 1.0f)))
         return 1;
-    return backward_impl(q, k, v, row_max, row_del, dout, dq, dk, dv, 1, T, n_heads, n_kv_heads, dim, s);
+    const size_t need = backward_workspace(1, T, n_heads, n_kv_heads, dim);
+    void *arena = need ? device_arena(need) : nullptr;
+    return backward_impl(q, k, v, row_max, row_del, dout, dq, dk, dv, arena, arena ? need : 0, 1, T, n_heads,
+                         n_kv_heads, dim, s);
 }
 
 int zt_attn_forward_batched(const float *q, const float *k, const float *v, float *out, float *lse,
@@ -284,8 +314,9 @@ int zt_attn_forward_batched(const float *q, const float *k, const float *v, floa
 }
 
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
-    (void)batch, (void)T, (void)n_heads, (void)n_kv_heads, (void)dim;
-    return 0;
+    if (batch < 1 || T < 1 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || !zt_attn_dim_ok(dim))
+        return 0;
+    return backward_workspace(batch, T, n_heads, n_kv_heads, dim);
 }
 
 int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
@@ -300,10 +331,13 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
     const size_t need = zt_attn_backward_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
     if (need > 0 && (!workspace || workspace_bytes < need))
         return refuse("the backward needs %zu bytes of workspace, %zu were given.", need, workspace_bytes);
+    if (need > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return refuse("the backward workspace must be 256-byte aligned.");
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
     if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
-    return backward_impl(q, k, v, lse, delta, dout, dq, dk, dv, batch, T, n_heads, n_kv_heads, dim, s);
+    return backward_impl(q, k, v, lse, delta, dout, dq, dk, dv, workspace, workspace_bytes, batch, T, n_heads,
+                         n_kv_heads, dim, s);
 }
 
 size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim) {
