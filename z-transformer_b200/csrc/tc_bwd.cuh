@@ -117,6 +117,11 @@ __device__ __forceinline__ void split_pack(float a, float b, uint32_t &hw, uint3
     lw = pack_half2(a - __half2float(ha), b - __half2float(hb));
 }
 
+__device__ __forceinline__ void red_add_v4(float *addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
 constexpr int kBwdThreads = 192;  // 4 row warps, 1 TMA warp, 1 MMA warp
 
 struct BwdParams {
@@ -133,7 +138,7 @@ struct BwdParams {
 
 struct BwdShared {
     uint64_t full[3], free_[3];
-    uint64_t k_full, a_ready, sdp_full, p_full, acc_done, ld_ready;
+    uint64_t k_full, a_ready, sdp_full, p_full, acc_done, ld_ready, flush_done;
     uint32_t tmem_base;
     volatile int abort;
     float lse2[2][64], dels[2][64];
@@ -151,6 +156,45 @@ __device__ __forceinline__ void bgive_up(BwdShared *sh, int code) {
     atomicMax(&g_tc_status, code);
 }
 
+
+// The dK/dV kernel's walk over (query tile, head of the group), and where its TMEM accumulators
+// are flushed to memory.
+//
+// The tensor core adds into its f32 accumulator with truncation, so every add made while the
+// accumulator is already large shaves a little off it, always toward zero.  Two measures keep
+// that below the f32 rounding noise of the answer:
+//  * order: a key's terms grow as the query position falls (p ~ 1/t), so the walk starts at
+//    the last query tile -- for each tile, all heads of the group -- and the accumulator stays
+//    small until the end;
+//  * flushes: the two query tiles that overlap the key tile carry the largest terms; they are
+//    walked head by head, and after each head the accumulators are added to dk/dv in memory
+//    (a rounded f32 add by the row threads) and restarted from zero, so no large partial sum
+//    sits in TMEM while further terms arrive.  The tiles beyond them are flushed every
+//    kFlushTiles query tiles for the same reason, which keeps the error flat in T.
+constexpr int kFlushTiles = 8;
+struct Walk {
+    int group, per_head, qi0, n_q, nd, nn;  // nd diagonal tiles (<= 2), nn tiles beyond them
+    __device__ __forceinline__ Walk(int group_, int per_head_, int qi0_, int n_q_)
+        : group(group_), per_head(per_head_), qi0(qi0_), n_q(n_q_) {
+        nd = per_head < 2 ? per_head : 2;
+        nn = per_head - nd;
+    }
+    __device__ __forceinline__ void at(int it, int &hh, int &qi) const {
+        const int na = nn * group;
+        if (it < na) {
+            hh = it % group, qi = n_q - 1 - it / group;
+        } else {
+            const int r = it - na;
+            hh = r / nd, qi = qi0 + nd - 1 - (r % nd);
+        }
+    }
+    __device__ __forceinline__ bool flush_after(int it) const {
+        const int na = nn * group;
+        if (it < na) return it == na - 1 || ((it + 1) % (kFlushTiles * group)) == 0;
+        return ((it - na) % nd) == nd - 1;
+    }
+    __device__ __forceinline__ bool fresh(int it) const { return it == 0 || flush_after(it - 1); }
+};
 
 // One row of `words` packed-half words from global memory into TMEM columns [col, col + words).
 template <int WORDS>
@@ -193,6 +237,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int per_head = n_q - qi0;
     const int n_it = group * per_head;
     const int B = p.batch;
+    const Walk walk(group, per_head, qi0, n_q);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
@@ -202,6 +247,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         mbar_init(&sh->p_full, 128);
         mbar_init(&sh->acc_done, 1);
         mbar_init(&sh->ld_ready, 128);
+        mbar_init(&sh->flush_done, 128);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -226,11 +272,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             for (int it = 0; it < n_it; ++it) {
                 const int s = it & 1;
                 if (it >= 2 && !bwait(&sh->free_[s], (uint32_t)(((it >> 1) & 1) ^ 1), sh)) { bgive_up(sh, 21); break; }
-                // Walk order: late query tiles first, and for each tile all heads of the group.  A key's
-                // terms grow as the query position falls (p ~ 1/t), so its accumulators in TMEM receive
-                // the small terms first; the tensor core adds with truncation, and small terms added
-                // to an already large accumulator would be cut short thousands of times.
-                const int h = g * group + it % group, row = (n_q - 1 - it / group) * 64;
+                int hh, qi;
+                walk.at(it, hh, qi);
+                const int h = g * group + hh, row = qi * 64;
                 uint8_t *st = stage0 + s * 4 * QP;
                 mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
                 tma_load_4d(st, &qmap, &sh->full[s], 0, row, h * NB, b);
@@ -254,6 +298,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             bool ok = bwait(&sh->k_full, 0, sh) && bwait(&sh->a_ready, 0, sh);
             if (!ok) bgive_up(sh, 22);
             const uint32_t kh = smem_u32(sKh), kl = smem_u32(sKl);
+            int n_flush = 0;
             for (int it = 0; ok && it < n_it; ++it) {
                 const int s = it & 1;
                 if (!bwait(&sh->full[s], (uint32_t)((it >> 1) & 1), sh)) { bgive_up(sh, 23); break; }
@@ -279,13 +324,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 }
                 mma_commit(&sh->sdp_full);
                 if (!bwait(&sh->p_full, (uint32_t)(it & 1), sh)) { bgive_up(sh, 24); break; }
+                const bool fresh = walk.fresh(it);
+                if (fresh && it > 0) {
+                    // the row threads are adding the accumulators to memory; restart only after that
+                    if (!bwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { bgive_up(sh, 27); break; }
+                }
+                if (walk.flush_after(it)) ++n_flush;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
                     const uint64_t dgh = desc_mnmajor_16b(gh + kk * 2048, 64 * 128);
                     const uint64_t dgl = desc_mnmajor_16b(gl + kk * 2048, 64 * 128);
-                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgh, id_a, (it > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgh, id_a, (!fresh || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cDV, tmem + cST + ac, dgl, id_a, 1);
                     mma_ts_f16(tmem + cDV, tmem + cST + ac + 16, dgh, id_a, 1);
                 }
@@ -294,7 +345,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
                     const uint64_t dqh = desc_mnmajor_16b(qh + kk * 2048, 64 * 128);
                     const uint64_t dql = desc_mnmajor_16b(ql + kk * 2048, 64 * 128);
-                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dqh, id_a, (it > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dqh, id_a, (!fresh || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dql, id_a, 1);
                     mma_ts_f16(tmem + cDK, tmem + cDPT + ac + 16, dqh, id_a, 1);
                 }
@@ -320,9 +371,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
         const float cs = p.scale_log2 / (mq * mk);
         const float dfac = mdo * mv * c1;
+        const float fv = 1.0f / (p.p_scale * mdo);
+        const float fk = p.scale / (mdo * mv * c1 * mq);
+        float *dvr = p.dv + ((long long)b * p.T + key) * wkv + (long long)g * D;
+        float *dkr = p.dk + ((long long)b * p.T + key) * wkv + (long long)g * D;
+        int n_flush = 0;
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            const int h = g * group + it % group, qrow0 = (n_q - 1 - it / group) * 64;
+            int hh, qi;
+            walk.at(it, hh, qi);
+            const int h = g * group + hh, qrow0 = qi * 64;
             const int buf = it & 1;
             {
                 const int t = qrow0 + (tid & 63);
@@ -368,37 +426,46 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sh->p_full);
-        }
-        if (ok && !__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)((n_it - 1) & 1), sh))) {
-            bgive_up(sh, 26);
-            ok = false;
-        }
-        if (ok) {
-            tc_fence_after();
-            const float fv = 1.0f / (p.p_scale * mdo);
-            const float fk = p.scale / (mdo * mv * c1 * mq);
-            float *dvr = p.dv + ((long long)b * p.T + key) * wkv + (long long)g * D;
-            float *dkr = p.dk + ((long long)b * p.T + key) * wkv + (long long)g * D;
+            if (walk.flush_after(it)) {
+                if (!__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)(it & 1), sh))) {
+                    bgive_up(sh, 26);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                uint32_t rv[32], rk[32];
-                tmem_ld32(tmem + lane_base + cDV + c, rv);
-                tmem_ld32(tmem + lane_base + cDK + c, rk);
-                tmem_wait_ld();
-                if (key < p.T) {
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t rv[32], rk[32];
+                    tmem_ld32(tmem + lane_base + cDV + c, rv);
+                    tmem_ld32(tmem + lane_base + cDK + c, rk);
+                    tmem_wait_ld();
+                    if (key < p.T) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        float4 a, k4;
-                        a.x = __uint_as_float(rv[i]) * fv, a.y = __uint_as_float(rv[i + 1]) * fv;
-                        a.z = __uint_as_float(rv[i + 2]) * fv, a.w = __uint_as_float(rv[i + 3]) * fv;
-                        k4.x = __uint_as_float(rk[i]) * fk, k4.y = __uint_as_float(rk[i + 1]) * fk;
-                        k4.z = __uint_as_float(rk[i + 2]) * fk, k4.w = __uint_as_float(rk[i + 3]) * fk;
-                        *reinterpret_cast<float4 *>(dvr + c + i) = a;
-                        *reinterpret_cast<float4 *>(dkr + c + i) = k4;
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 a, k4;
+                            a.x = __uint_as_float(rv[i]) * fv, a.y = __uint_as_float(rv[i + 1]) * fv;
+                            a.z = __uint_as_float(rv[i + 2]) * fv, a.w = __uint_as_float(rv[i + 3]) * fv;
+                            k4.x = __uint_as_float(rk[i]) * fk, k4.y = __uint_as_float(rk[i + 1]) * fk;
+                            k4.z = __uint_as_float(rk[i + 2]) * fk, k4.w = __uint_as_float(rk[i + 3]) * fk;
+                            if (n_flush == 0) {
+                                // the first flush assigns: dk/dv need no zeroing by the caller
+                                *reinterpret_cast<float4 *>(dvr + c + i) = a;
+                                *reinterpret_cast<float4 *>(dkr + c + i) = k4;
+                            } else {
+                                // later ones add in memory (a rounded f32 add, no reply to wait for);
+                                // this thread is the only writer of its row, so the order is its own
+                                red_add_v4(dvr + c + i, a);
+                                red_add_v4(dkr + c + i, k4);
+                            }
+                        }
                     }
                 }
+                ++n_flush;
+                tc_fence_before();
+                mbar_arrive(&sh->flush_done);
             }
         }
+        (void)ok;
     }
     tc_fence_before();
     __syncthreads();
@@ -436,6 +503,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         mbar_init(&sh->p_full, 128);
         mbar_init(&sh->acc_done, 1);
         mbar_init(&sh->ld_ready, 128);
+        mbar_init(&sh->flush_done, 128);
         sh->abort = 0;
         mbar_fence_init();
     }
