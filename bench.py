@@ -195,7 +195,9 @@ def run_ours(args):
     L = zt.lib.load()
     peaks, peak_kind = load_peaks()
 
-    c = PREFILL
+    c = dict(PREFILL)
+    if args.small:  # profiling case: same kernels and tile walk, a quarter of the batch
+        c["batch"] = 2
     B, T, H, Hkv, D = c["batch"], c["T"], c["n_heads"], c["n_kv_heads"], c["head_dim"]
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
@@ -281,6 +283,7 @@ def run_ours(args):
     # device.Attn's call pattern (src/model.zig:481-514): upload q, k, v (and dout), launch, download.
     # One batch item per zt_attn_forward / zt_attn_backward call, as the reference ABI has no batch.
     e2e_steps = max(1, min(args.steps, 3))
+    e2e_B = 1 if args.small else B
     hq, hdo = (torch.randn((B, T, H * D)).pin_memory() for _ in range(2))
     hk, hv = (torch.randn((B, T, Hkv * D)).pin_memory() for _ in range(2))
     hout, hdq = (torch.empty((B, T, H * D)).pin_memory() for _ in range(2))
@@ -288,7 +291,7 @@ def run_ours(args):
     holder = zt.Attn(T, H, Hkv, D, device=dev)
 
     def e2e_step():
-        for b in range(B):
+        for b in range(e2e_B):
             holder.q.copy_(hq[b].view(-1), non_blocking=True)
             holder.k.copy_(hk[b].view(-1), non_blocking=True)
             holder.v.copy_(hv[b].view(-1), non_blocking=True)
@@ -314,13 +317,15 @@ def run_ours(args):
         e2e_ms = float(t.item())
     # the reference ABI's backward recomputes the forward (it is given neither out nor lse);
     # the credited work is still forward + backward = 3.5 F
-    e2e_value = world * 3.5 * F / (e2e_ms * 1e-3) / 1e12
-    h2d = (2 * hq[0].numel() + 2 * hk[0].numel()) * 4 * B
+    e2e_value = world * 3.5 * F * (e2e_B / B) / (e2e_ms * 1e-3) / 1e12
+    h2d = (2 * hq[0].numel() + 2 * hk[0].numel()) * 4 * e2e_B
     d2h = h2d
     del hq, hdo, hk, hv, hout, hdq, hdk, hdv, holder
 
     # ---- decode configuration -------------------------------------------------------------------
-    d = DECODE
+    d = dict(DECODE)
+    if args.small:
+        d["batch"] = 8
     Bd, n_ctx = d["batch"], d["n_ctx"]
     kc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
     vc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
@@ -378,7 +383,7 @@ def run_ours(args):
 
     # ---- CPU baseline on rank 0 at N = 1 --------------------------------------------------------
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and not args.small:
         threads = host_threads()
         stride = 128
         flops, times = cpu_sample(threads, stride, 1, 0)
@@ -397,7 +402,7 @@ def run_ours(args):
             "roofline": roofline, "kernels": klist, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "api": "zt_attn_forward + zt_attn_backward per batch item, pinned host buffers"},
-            "gpu_launches": int(launches), "clocks": clocks, "decode": decode,
+            "gpu_launches": int(launches), "clocks": clocks, "decode": decode, "small": bool(args.small),
             "paths": {"prefill": [k_["kernel"] for k_ in klist]},
         }
         print(json.dumps(line), flush=True)
@@ -413,6 +418,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--gather", action="store_true", help="time the all-gather of sharded outputs too")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling case: batch 2 prefill and batch 8 decode (same kernels, a quarter of the work); "
+                         "its line is not a benchmark result")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
