@@ -262,6 +262,9 @@ def run_ours(args):
     # overhead, not credited); together the backward's 2.5 F.
     credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
               "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
+    # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the B=2 case
+    # (profiles/prefill_tensor_core_kernels_small_case.md), scaled by the batch: traffic is per sequence.
+    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_bwd_dkdv_tc": 401.3e6, "attn_bwd_dq_tc": 448.3e6}
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
     total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
     klist = []
@@ -275,7 +278,9 @@ def run_ours(args):
     roofline = None
     if dom and "tflops" in dom:
         roofline = {"bound": "tensor", "kernel": dom["kernel"], "achieved": dom["tflops"], "peak": tf32_peak,
-                    "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_peak, "traffic": None,
+                    "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_peak,
+                    "traffic": traffic_b2[dom["kernel"]] * B / 2 if dom["kernel"] in traffic_b2 else None,
+                    "traffic_source": "ncu capture at batch 2, scaled by batch",
                     "peak_source": f"{peak_kind}: TF32 dense = bf16_tflops_sustained ({peaks['bf16_tflops_sustained']}) / 2",
                     "step_frac": value / world / tf32_peak}
 
@@ -365,7 +370,8 @@ def run_ours(args):
               "bytes_per_step": d_bytes,
               "roofline": {"bound": "hbm", "kernel": "decode_splitk_kernel", "achieved": d_kernel_gbs,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d_kernel_gbs / peaks["hbm_gbs"],
-                           "traffic": None, "peak_source": f"{peak_kind}: hbm_gbs"},
+                           "traffic": 541.2e6 * Bd / 8, "traffic_source": "ncu capture at batch 8, scaled by batch",
+                           "peak_source": f"{peak_kind}: hbm_gbs"},
               "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in dk_prof.items()}}
     # decode end to end with host buffers: q up, out down; the cache stays resident in HBM
     hqd, houtd = torch.randn((Bd, H * D)).pin_memory(), torch.empty((Bd, H * D)).pin_memory()
