@@ -416,6 +416,125 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# every configuration of the benchmark definition, one JSON line each (not the headline contract)
+# ------------------------------------------------------------------------------------------------
+
+def run_all_configs(args):
+    """Throughput of every configuration on this rank's GPU: the GPT-mini forward, the 16-point
+    fwd+bwd sweep, the Llama-3 decode, the 32k prefill (KV heads sharded over the ranks) and the ragged
+    decode (sequences sharded over the ranks).  Device-resident inputs, CUDA events, max over ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    zt = importlib.import_module("z-transformer_b200")
+    zt.lib.load()
+    peaks, peak_kind = load_peaks()
+    tf32_peak, hbm_peak = peaks["bf16_tflops_sustained"] / 2.0, peaks["hbm_gbs"]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7 + rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def emit(**kw):
+        if rank == 0:
+            print(json.dumps({"n_gpus": world, "dtype": "f32", "data": "synthetic", **kw}), flush=True)
+
+    def prefill(tag, B, T, H, Hkv, D, backward, reps):
+        q, do = (torch.randn((B, T, H * D), generator=gen, device=dev) for _ in range(2))
+        k, v = (torch.randn((B, T, Hkv * D), generator=gen, device=dev) for _ in range(2))
+        state = {}
+
+        def fwd():
+            state["o"], state["lse"] = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+
+        ms_f = timed(fwd, reps)
+        path_f = zt.lib.last_path()
+        F = fwd_flops(B, T, H, D)
+        out = {"config": tag, "batch_per_gpu": B, "T": T, "n_heads": H, "n_kv_heads": Hkv, "head_dim": D,
+               "fwd_ms": ms_f, "fwd_tflops": F / ms_f / 1e9, "fwd_frac_tf32_peak": F / ms_f / 1e9 / tf32_peak,
+               "fwd_path": path_f}
+        if backward:
+            def bwd():
+                zt.attention_backward(q, k, v, state["o"], state["lse"], do, H, Hkv, D)
+            ms_b = timed(bwd, reps)
+            out.update({"bwd_ms": ms_b, "bwd_tflops": 2.5 * F / ms_b / 1e9, "bwd_path": zt.lib.last_path(),
+                        "fwd_bwd_tflops": 3.5 * F / (ms_f + ms_b) / 1e9,
+                        "fwd_bwd_frac_tf32_peak": 3.5 * F / (ms_f + ms_b) / 1e9 / tf32_peak})
+        return out
+
+    # 1. GPT-mini forward (replicated on every rank: it does not shard)
+    emit(**prefill("1 gpt-mini fwd", 1, 256, 4, 2, 32, False, 50), scaling="replicas only")
+    # 2. the sweep; the batch of 8 is split over the ranks
+    Bs = max(1, 8 // world)
+    for D in (32, 64, 128, 256):
+        for T in (512, 1024, 2048, 4096):
+            r = prefill(f"2 sweep D{D} T{T}", Bs, T, 32, 8, D, True, 5 if D < 256 else 2)
+            for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops"):
+                r[key + "_job"] = r[key] * world
+            emit(**r, scaling="strong (batch 8 split over ranks)")
+    # 3. Llama-3 decode, sequences split over the ranks
+    def decode(tag, B, n_ctx, nk_host):
+        H, Hkv, D = 32, 8, 128
+        kc = torch.empty((B, n_ctx, Hkv * D), device=dev)
+        vc = torch.empty_like(kc)
+        for i in range(0, B, 16):
+            kc[i:i + 16].normal_(generator=gen)
+            vc[i:i + 16].normal_(generator=gen)
+        qd = torch.randn((B, H * D), generator=gen, device=dev)
+        nk = torch.from_numpy(nk_host.astype(np.int32)).to(dev)
+        ws = zt.DecodeWorkspace(B, n_ctx, H, Hkv, D, dev)
+        outd = torch.empty_like(qd)
+        ms = timed(lambda: zt.decode_attention(qd, kc, vc, nk, H, Hkv, D, workspace=ws, out=outd), 20)
+        local_bytes = float(nk_host.sum()) * 2 * Hkv * D * 4 + 2.0 * B * H * D * 4
+        total = torch.tensor([local_bytes], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(total)
+        gbs = float(total.item()) / ms / 1e6
+        emit(config=tag, batch_per_gpu=B, n_ctx=n_ctx, ms=ms, bytes_per_step_job=float(total.item()), gbs_job=gbs,
+             gbs_per_gpu=gbs / world, frac_hbm_peak_per_gpu=gbs / world / hbm_peak, path=zt.lib.last_path(),
+             scaling="strong (sequences split over ranks)")
+        del kc, vc
+
+    decode("3 llama3 decode B64 ctx8192", 64 // world, 8192, np.full(64 // world, 8192))
+    # 4. 32k prefill, KV heads split over the ranks
+    sh = zt.sharding.shard_kv_heads(32, 8, world, rank)
+    r = prefill("4 prefill T32768 (KV heads sharded)", 1, 32768, sh.n_heads, sh.n_kv_heads, 128, True, 2)
+    for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops"):
+        r[key + "_job"] = r[key] * world
+    emit(**r, scaling="strong (8 KV heads split over ranks)")
+    # 5. ragged decode: lengths uniform in [1, 16384], longest-first balanced over the ranks
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(1, 16385, size=256)
+    assignment, _ = zt.sharding.balance_sequences(lengths, world)
+    decode("5 ragged decode B256 len U[1,16384]", 256 // world, 16384, lengths[np.array(assignment[rank])])
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -427,7 +546,12 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="profiling case: batch 2 prefill and batch 8 decode (same kernels, a quarter of the work); "
                          "its line is not a benchmark result")
+    ap.add_argument("--all-configs", action="store_true",
+                    help="run every configuration of the benchmark definition (one JSON line each) instead of "
+                         "the headline step")
     args = ap.parse_args()
+    if args.all_configs:
+        return run_all_configs(args)
     if args.impl == "reference":
         run_reference(args)
     else:
