@@ -96,8 +96,9 @@ const char *zt_attn_last_error(void);
  * (the return code and zt_attn_last_error() still report them). */
 void zt_attn_set_verbose(int on);
 
-/* Which implementation the next launches use: 0 = automatic (tensor-core
- * kernels where the shape allows, SIMT elsewhere), 1 = SIMT only.  For tests
+/* Which implementation the next launches use: 0 = automatic (the fastest tensor-core
+ * kernel the shape allows, CUDA-core kernels elsewhere), 1 = CUDA-core kernels only,
+ * 2 = as 0 but the forward uses the 3xTF32 kernel instead of the f16-split one.  For tests
  * and for bisecting a parity failure; returns the previous value. */
 int zt_attn_set_path(int path);
 

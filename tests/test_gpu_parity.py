@@ -394,13 +394,19 @@ TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, sev
 ]
 
 
+@pytest.mark.parametrize("path", [0, 2], ids=["f16split", "3xtf32"])
 @pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
-def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D):
+def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, path):
+    """Both tensor-core forwards: the pipelined f16-split kernel (path 0, head_dim 64/128) and the
+    3xTF32 kernel (path 2, and head_dim 32 always)."""
     q = oracle.fill_normal((B, T, H * D), 51, 0)
     k = oracle.fill_normal((B, T, Hkv * D), 51, 1)
     v = oracle.fill_normal((B, T, Hkv * D), 51, 2)
-    zt.lib.load().zt_attn_set_path(0)
-    o, lse = zt.attention_forward(cu(q, dev), cu(k, dev), cu(v, dev), H, Hkv, D, want_lse=True)
+    zt.lib.load().zt_attn_set_path(path)
+    try:
+        o, lse = zt.attention_forward(cu(q, dev), cu(k, dev), cu(v, dev), H, Hkv, D, want_lse=True)
+    finally:
+        zt.lib.load().zt_attn_set_path(0)
     torch.cuda.synchronize()
     assert zt.lib.last_path() == "tcgen05"
     assert zt.lib.tc_status() == 0
@@ -422,9 +428,13 @@ def test_tensor_core_and_simt_paths_agree(zt, dev, oracle):
     L.zt_attn_set_path(0)
     o_tc = zt.attention_forward(q, k, v, H, Hkv, D)
     assert zt.lib.last_path() == "tcgen05"
+    L.zt_attn_set_path(2)
+    o_tf32 = zt.attention_forward(q, k, v, H, Hkv, D)
+    L.zt_attn_set_path(0)
     torch.cuda.synchronize()
     assert zt.lib.tc_status() == 0
-    close(o_tc.cpu().numpy(), o_simt.cpu().numpy(), "tcgen05 vs simt")
+    close(o_tc.cpu().numpy(), o_simt.cpu().numpy(), "tcgen05 f16-split vs simt")
+    close(o_tf32.cpu().numpy(), o_simt.cpu().numpy(), "tcgen05 3xTF32 vs simt")
 
 
 def test_tensor_core_large_magnitudes_and_peaked_rows(zt, dev, oracle):

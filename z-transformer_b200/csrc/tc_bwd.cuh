@@ -122,7 +122,8 @@ __device__ __forceinline__ void red_add_v4(float *addr, float4 v) {
                  : "memory");
 }
 
-constexpr int kBwdThreads = 192;  // 4 row warps, 1 TMA warp, 1 MMA warp
+constexpr int kBwdThreads = 320;  // 8 row warps (two threads per tile row, 32 columns each), 1 TMA warp, 1 MMA warp
+constexpr int kRowWarps = 8;
 
 struct BwdParams {
     const float *lse, *delta;        // [B, T, H]
@@ -242,16 +243,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     if (threadIdx.x == 0) {
         for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
         mbar_init(&sh->k_full, 1);
-        mbar_init(&sh->a_ready, 128);
+        mbar_init(&sh->a_ready, kRowWarps);
         mbar_init(&sh->sdp_full, 1);
-        mbar_init(&sh->p_full, 128);
+        mbar_init(&sh->p_full, kRowWarps);
         mbar_init(&sh->acc_done, 1);
-        mbar_init(&sh->ld_ready, 128);
-        mbar_init(&sh->flush_done, 128);
+        mbar_init(&sh->ld_ready, kRowWarps);
+        mbar_init(&sh->flush_done, kRowWarps);
         sh->abort = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
     const float c1 = p.c1;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             tma_prefetch_desc(&kmap), tma_prefetch_desc(&qmap), tma_prefetch_desc(&gmap);
@@ -290,34 +291,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
             bool ok = bwait(&sh->k_full, 0, sh) && bwait(&sh->a_ready, 0, sh);
             if (!ok) bgive_up(sh, 22);
-            const uint32_t kh = smem_u32(sKh), kl = smem_u32(sKl);
+            const uint64_t bkh = desc_kmajor(smem_u32(sKh)), bkl = desc_kmajor(smem_u32(sKl));
             int n_flush = 0;
             for (int it = 0; ok && it < n_it; ++it) {
                 const int s = it & 1;
                 if (!bwait(&sh->full[s], (uint32_t)((it >> 1) & 1), sh)) { bgive_up(sh, 23); break; }
                 tc_fence_after();
                 const uint32_t qh = smem_u32(stage0 + s * 4 * QP), ql = qh + QP, gh = qh + 2 * QP, gl = qh + 3 * QP;
-#pragma unroll 2
+                const uint64_t bqh = desc_kmajor(qh), bql = desc_kmajor(ql), bgh = desc_kmajor(gh), bgl = desc_kmajor(gl);
+#pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
                     const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
-                    const uint64_t dkh = desc_kmajor(kh + ao), dkl = desc_kmajor(kl + ao);
-                    const uint64_t dqh = desc_kmajor(qh + bo), dql = desc_kmajor(ql + bo);
+                    const uint64_t dkh = desc_advance(bkh, ao), dkl = desc_advance(bkl, ao);
+                    const uint64_t dqh = desc_advance(bqh, bo), dql = desc_advance(bql, bo);
                     mma_ss_f16(tmem + cST, dkh, dqh, id_s, kk > 0);
                     mma_ss_f16(tmem + cST, dkh, dql, id_s, 1);
                     mma_ss_f16(tmem + cST, dkl, dqh, id_s, 1);
                 }
-#pragma unroll 2
+#pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
-                    const uint64_t dgh = desc_kmajor(gh + bo), dgl = desc_kmajor(gl + bo);
+                    const uint64_t dgh = desc_advance(bgh, bo), dgl = desc_advance(bgl, bo);
                     mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
                     mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgl, id_s, 1);
                     mma_ts_f16(tmem + cDPT, tmem + cVl + kk * 8, dgh, id_s, 1);
@@ -331,11 +333,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 }
                 if (walk.flush_after(it)) ++n_flush;
                 tc_fence_after();
+                const uint64_t mgh = desc_mnmajor_16b(gh, 64 * 128), mgl = desc_mnmajor_16b(gl, 64 * 128);
+                const uint64_t mqh = desc_mnmajor_16b(qh, 64 * 128), mql = desc_mnmajor_16b(ql, 64 * 128);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
-                    const uint64_t dgh = desc_mnmajor_16b(gh + kk * 2048, 64 * 128);
-                    const uint64_t dgl = desc_mnmajor_16b(gl + kk * 2048, 64 * 128);
+                    const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
                     mma_ts_f16(tmem + cDV, tmem + cST + ac, dgh, id_a, (!fresh || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cDV, tmem + cST + ac, dgl, id_a, 1);
                     mma_ts_f16(tmem + cDV, tmem + cST + ac + 16, dgh, id_a, 1);
@@ -343,8 +346,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
-                    const uint64_t dqh = desc_mnmajor_16b(qh + kk * 2048, 64 * 128);
-                    const uint64_t dql = desc_mnmajor_16b(ql + kk * 2048, 64 * 128);
+                    const uint64_t dqh = desc_advance(mqh, kk * 2048), dql = desc_advance(mql, kk * 2048);
                     mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dqh, id_a, (!fresh || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dql, id_a, 1);
                     mma_ts_f16(tmem + cDK, tmem + cDPT + ac + 16, dqh, id_a, 1);
@@ -356,18 +358,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ one thread per key row
-        const int tid = threadIdx.x;
+        // two threads per tile row: `half` picks which 32 of the tile's 64 columns this one handles
+        const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
         const int key = s0 + tid;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long wkv = (long long)p.n_kv_heads * D;
         {
             const __half *vh = p.v_planes + ((long long)b * p.T + (key < p.T ? key : 0)) * wkv + (long long)g * D;
             const __half *vl = vh + (long long)B * p.T * wkv;
-            row_to_tmem<W2>(vh, key < p.T, tmem + lane_base + cVh);
-            row_to_tmem<W2>(vl, key < p.T, tmem + lane_base + cVl);
+            if (half == 0) row_to_tmem<W2>(vh, key < p.T, tmem + lane_base + cVh);
+            else row_to_tmem<W2>(vl, key < p.T, tmem + lane_base + cVl);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->a_ready);
+            mbar_arrive_warp(&sh->a_ready);
         }
         const float cs = p.scale_log2 / (mq * mk);
         const float dfac = mdo * mv * c1;
@@ -385,10 +388,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             {
                 const int t = qrow0 + (tid & 63);
                 const long long idx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
-                if (tid < 64) sh->lse2[buf][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
-                else sh->dels[buf][tid - 64] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
+                if (half == 0) {
+                    if (tid < 64) sh->lse2[buf][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
+                    else sh->dels[buf][tid - 64] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
+                }
             }
-            mbar_arrive(&sh->ld_ready);  // the 128 row threads exchange lse/delta through shared memory
+            mbar_arrive_warp(&sh->ld_ready);  // the 128 row threads exchange lse/delta through shared memory
             if (!__all_sync(0xffffffffu, bwait(&sh->ld_ready, (uint32_t)(it & 1), sh) &&
                                              bwait(&sh->sdp_full, (uint32_t)(it & 1), sh))) {
                 bgive_up(sh, 25);
@@ -396,8 +401,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < 64; c += 32) {
+            {
+                const int c = 32 * half;
                 uint32_t rs[32], rd[32];
                 tmem_ld32(tmem + lane_base + cST + c, rs);
                 tmem_ld32(tmem + lane_base + cDPT + c, rd);
@@ -425,7 +430,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->p_full);
+            mbar_arrive_warp(&sh->p_full);
             if (walk.flush_after(it)) {
                 if (!__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)(it & 1), sh))) {
                     bgive_up(sh, 26);
@@ -434,7 +439,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
+                for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
                     uint32_t rv[32], rk[32];
                     tmem_ld32(tmem + lane_base + cDV + c, rv);
                     tmem_ld32(tmem + lane_base + cDK + c, rk);
@@ -462,14 +467,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 }
                 ++n_flush;
                 tc_fence_before();
-                mbar_arrive(&sh->flush_done);
+                mbar_arrive_warp(&sh->flush_done);
             }
         }
         (void)ok;
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, 512);
+    if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -498,16 +503,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     if (threadIdx.x == 0) {
         for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
         mbar_init(&sh->k_full, 1);
-        mbar_init(&sh->a_ready, 128);
+        mbar_init(&sh->a_ready, kRowWarps);
         mbar_init(&sh->sdp_full, 1);
-        mbar_init(&sh->p_full, 128);
+        mbar_init(&sh->p_full, kRowWarps);
         mbar_init(&sh->acc_done, 1);
-        mbar_init(&sh->ld_ready, 128);
-        mbar_init(&sh->flush_done, 128);
+        mbar_init(&sh->ld_ready, kRowWarps);
+        mbar_init(&sh->flush_done, kRowWarps);
         sh->abort = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -517,7 +522,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
     const float c1 = p.c1;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (elect_one()) {
             tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
             int issued = 0;
@@ -537,7 +542,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     mbar_wait(&sh->full[j % 3], (uint32_t)((j / 3) & 1));
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         if (elect_one()) {
             constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
@@ -548,18 +553,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 if (!bwait(&sh->full[s], (uint32_t)((j / 3) & 1), sh)) { bgive_up(sh, 33); break; }
                 tc_fence_after();
                 const uint32_t kh = smem_u32(smem + s * 4 * QP), kl = kh + QP, vh = kh + 2 * QP, vl = kh + 3 * QP;
-#pragma unroll 2
+                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kl), bvh = desc_kmajor(vh), bvl = desc_kmajor(vl);
+#pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
-                    const uint64_t dkh = desc_kmajor(kh + bo), dkl = desc_kmajor(kl + bo);
+                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
                     mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
                     mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
                     mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
                 }
-#pragma unroll 2
+#pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
-                    const uint64_t dvh = desc_kmajor(vh + bo), dvl = desc_kmajor(vl + bo);
+                    const uint64_t dvh = desc_advance(bvh, bo), dvl = desc_advance(bvl, bo);
                     mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvh, id_s, kk > 0);
                     mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvl, id_s, 1);
                     mma_ts_f16(tmem + cDP, tmem + cGl + kk * 8, dvh, id_s, 1);
@@ -567,11 +573,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 mma_commit(&sh->sdp_full);
                 if (!bwait(&sh->p_full, (uint32_t)(j & 1), sh)) { bgive_up(sh, 34); break; }
                 tc_fence_after();
+                const uint64_t mkh = desc_mnmajor_16b(kh, 64 * 128), mkl = desc_mnmajor_16b(kl, 64 * 128);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
-                    const uint64_t dkh = desc_mnmajor_16b(kh + kk * 2048, 64 * 128);
-                    const uint64_t dkl = desc_mnmajor_16b(kl + kk * 2048, 64 * 128);
+                    const uint64_t dkh = desc_advance(mkh, kk * 2048), dkl = desc_advance(mkl, kk * 2048);
                     mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkl, id_a, 1);
                     mma_ts_f16(tmem + cDQ, tmem + cDP + ac + 16, dkh, id_a, 1);
@@ -582,20 +588,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
         __syncwarp();
     } else {
-        const int tid = threadIdx.x;
+        // two threads per tile row: `half` picks which 32 of the tile's 64 columns this one handles
+        const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
         const int t = t0 + tid;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long wq = (long long)p.n_heads * D;
         {
             const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
             const long long plane = (long long)B * p.T * wq;
-            row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
-            row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
-            row_to_tmem<W2>(p.do_planes + off, t < p.T, tmem + lane_base + cGh);
-            row_to_tmem<W2>(p.do_planes + plane + off, t < p.T, tmem + lane_base + cGl);
+            if (half == 0) {
+                row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
+                row_to_tmem<W2>(p.do_planes + off, t < p.T, tmem + lane_base + cGh);
+            } else {
+                row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
+                row_to_tmem<W2>(p.do_planes + plane + off, t < p.T, tmem + lane_base + cGl);
+            }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->a_ready);
+            mbar_arrive_warp(&sh->a_ready);
         }
         const float cs = p.scale_log2 / (mq * mk);
         const long long ridx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
@@ -609,8 +619,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < 64; c += 32) {
+            {
+                const int c = 32 * half;
                 uint32_t rs[32], rd[32];
                 tmem_ld32(tmem + lane_base + cS + c, rs);
                 tmem_ld32(tmem + lane_base + cDP + c, rd);
@@ -633,7 +643,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->p_full);
+            mbar_arrive_warp(&sh->p_full);
         }
         if (ok && !__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)((n_tiles - 1) & 1), sh))) {
             bgive_up(sh, 36);
@@ -644,7 +654,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             const float fq = p.scale / (mdo * mv * c1 * mk);
             float *dqr = p.dq + ((long long)b * p.T + t) * wq + (long long)h * D;
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
+            for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem + lane_base + cDQ + c, r);
                 tmem_wait_ld();
@@ -662,7 +672,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, 512);
+    if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ---- host side ----------------------------------------------------------------------------------------

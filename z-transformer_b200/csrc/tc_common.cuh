@@ -38,6 +38,13 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for a whole warp: every lane's earlier writes are ordered before the elected
+// arrival by the warp barrier.  Hundreds of per-thread arrivals on one barrier word serialise
+// (each is a shared-memory atomic); per-warp arrival keeps a hand-off to a few of them.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t *bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -170,6 +177,11 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_b
     return kDescSw128Atom32 | (uint64_t)((addr >> 4) & 0x3fff) | (uint64_t)((block_bytes >> 4) & 0x3fff) << 16 |
            (uint64_t)(512 >> 4) << 32;
 }
+
+// A descriptor `bytes` further into the same tile (start-address field only; tiles sit below 256 KB,
+// so the 14-bit field cannot carry).  With a compile-time `bytes` this is one integer add per MMA,
+// which matters: one thread issues every MMA of a CTA, and an MMA of N = 64 executes in ~34 cycles.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
 
 // Instruction descriptor for kind::tf32, f32 accumulate, M x N, A K-major (or in TMEM).
 // c_format f32 = 1 at [4,6); a/b format tf32 = 2 at [7,10)/[10,13); b_major at 16; N >> 3 at

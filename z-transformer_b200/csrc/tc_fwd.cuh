@@ -115,13 +115,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&sh->vx_full[i], 1);
             mbar_init(&sh->vx_free[i], 1);
         }
-        mbar_init(&sh->klo_ready, 128);
+        mbar_init(&sh->klo_ready, 4);
         mbar_init(&sh->klo_free, 1);
-        mbar_init(&sh->vlo_ready, 128);
+        mbar_init(&sh->vlo_ready, 4);
         mbar_init(&sh->vlo_free, 1);
-        mbar_init(&sh->q_ready, 128);
+        mbar_init(&sh->q_ready, 4);
         mbar_init(&sh->s_full, 1);
-        mbar_init(&sh->p_full, 128);
+        mbar_init(&sh->p_full, 4);
         mbar_init(&sh->pv_done, 1);
         sh->abort = 0;
         mbar_fence_init();
@@ -176,11 +176,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                     break;
                 }
                 tc_fence_after();
-                const uint32_t khi = smem_u32(kx[s]), klo_a = smem_u32(klo);
-#pragma unroll 4
+                const uint64_t bkhi = desc_kmajor(smem_u32(kx[s])), bklo = desc_kmajor(smem_u32(klo));
+#pragma unroll
                 for (int kk = 0; kk < D / 8; ++kk) {
                     const uint32_t off = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
-                    const uint64_t dhi = desc_kmajor(khi + off), dlo = desc_kmajor(klo_a + off);
+                    const uint64_t dhi = desc_advance(bkhi, off), dlo = desc_advance(bklo, off);
                     mma_ts_tf32(tmem + C::kS, tmem + C::kQhi + kk * 8, dhi, idesc_s, kk > 0);
                     mma_ts_tf32(tmem + C::kS, tmem + C::kQhi + kk * 8, dlo, idesc_s, 1);
                     mma_ts_tf32(tmem + C::kS, tmem + C::kQlo + kk * 8, dhi, idesc_s, 1);
@@ -195,11 +195,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                     break;
                 }
                 tc_fence_after();
-                const uint32_t vhi = smem_u32(vx[s]), vlo_a = smem_u32(vlo);
-#pragma unroll 4
+                const uint64_t bvhi = desc_mnmajor(smem_u32(vx[s]), BN * 128), bvlo = desc_mnmajor(smem_u32(vlo), BN * 128);
+#pragma unroll
                 for (int kk = 0; kk < BN / 8; ++kk) {
-                    const uint64_t dhi = desc_mnmajor(vhi + kk * 1024, BN * 128);
-                    const uint64_t dlo = desc_mnmajor(vlo_a + kk * 1024, BN * 128);
+                    const uint64_t dhi = desc_advance(bvhi, kk * 1024), dlo = desc_advance(bvlo, kk * 1024);
                     mma_ts_tf32(tmem + C::kO, tmem + C::kS + kk * 8, dhi, idesc_o, (j > 0 || kk > 0) ? 1 : 0);
                     mma_ts_tf32(tmem + C::kO, tmem + C::kS + kk * 8, dlo, idesc_o, 1);
                     mma_ts_tf32(tmem + C::kO, tmem + C::kPlo + kk * 8, dhi, idesc_o, 1);
@@ -239,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     dst[tid + i * 128] = lo;
                 }
                 fence_async_smem();
-                mbar_arrive(ready);
+                mbar_arrive_warp(ready);
             }
         }
     } else {
@@ -272,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->q_ready);
+            mbar_arrive_warp(&sh->q_ready);
         }
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
@@ -352,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             l += psum;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->p_full);
+            mbar_arrive_warp(&sh->p_full);
         }
         if (ok) {
             if (!__all_sync(0xffffffffu, wait_or_abort(&sh->pv_done, (uint32_t)((n_tiles - 1) & 1), sh))) {

@@ -1,0 +1,376 @@
+// Causal GQA attention forward on the tensor cores with the three-term split on f16 pieces
+// (the arithmetic of tc_bwd.cuh) and a two-deep pipeline over the key tiles.
+//
+// Same result as attn_fwd_tc (tc_fwd.cuh, 3xTF32) and the same role -- attention.forward
+// (src/attention.zig:60-153) for a batch plus each row's log-sum-exp -- at roughly twice the
+// speed: an f16 term is half a TF32 MMA, operands take half the bytes (so a key tile of both K
+// and V, hi and lo, fits three times in shared memory), and two S tiles fit in TMEM, so the
+// softmax of tile j runs while the tensor core computes S of tile j+1 and P.V of tile j-1.
+//
+//   bwd_absmax / bwd_split   (tc_bwd.cuh) q, k, v -> f16 hi/lo planes with a power-of-two scale
+//                            per (sequence, KV group), in a workspace.
+//   TMA warp        K and V hi/lo tiles of 64 keys, three stages.
+//   MMA warp        S[j+1] = Qh.Kh + Qh.Kl + Ql.Kh  (A = Q from TMEM), then, once P[j] is in TMEM,
+//                   O += Ph.Vh + Ph.Vl + Pl.Vh      (A = P from TMEM, V tile as MN-major B).
+//   softmax warps   one thread per query row, as in the TF32 kernel: lazy reference maximum
+//                   (moved only when it grows by > 2^8), P scaled by 2^7 and split into packed
+//                   f16 pairs written over S.
+// TMEM columns: [0,D/2) Qh, [D/2,D) Ql, [D,2D) O, then two S/P tiles of 64 columns.
+#pragma once
+
+#include "tc_bwd.cuh"
+
+namespace zt {
+namespace tcf16 {
+
+using namespace tc;
+using tcb::block_mult;
+using tcb::row_to_tmem;
+using tcb::split_pack;
+
+constexpr int kThreads = 192;  // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr float kPScale = 128.0f;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct Shared {
+    uint64_t full[3], free_[3];
+    uint64_t a_ready, s_full[2], p_full[2], pv_done;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+
+struct Params {
+    const __half *q_planes;                     // [2][B][T][H*D]
+    const uint32_t *amax_q, *amax_k, *amax_v;   // [B, Hkv]
+    float *out, *lse;                           // lse may be null
+    int batch, T, n_heads, n_kv_heads;
+    float scale_log2;
+};
+
+__device__ __forceinline__ bool fwait(uint64_t *bar, uint32_t parity, Shared *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void fgive_up(Shared *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+    attn_fwd_tc16(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
+    constexpr int NB = D / 64, W2 = D / 2, BN = 64;
+    constexpr int KP = BN * D * 2;  // bytes of one plane of a key tile
+    constexpr int cQh = 0, cQl = W2, cO = D, cS0 = 2 * D;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Shared *sh = reinterpret_cast<Shared *>(smem + 12 * KP);  // 3 stages x (Kh, Kl, Vh, Vl)
+
+    const int warp = threadIdx.x >> 5;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (p.n_heads / p.n_kv_heads);
+    const int t0 = qt * 128;
+    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
+    const int n_tiles = (rows_end + BN - 1) / BN;
+    const int B = p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
+        mbar_init(&sh->a_ready, 4);
+        for (int i = 0; i < 2; ++i) mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 4);
+        mbar_init(&sh->pv_done, 1);
+        sh->abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
+    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % 3;
+                if (j >= 3 && !fwait(&sh->free_[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { fgive_up(sh, 41); break; }
+                uint8_t *st = smem + s * 4 * KP;
+                mbar_arrive_expect_tx(&sh->full[s], 4 * KP);
+                tma_load_4d(st, &kmap, &sh->full[s], 0, j * BN, g * NB, b);
+                tma_load_4d(st + KP, &kmap, &sh->full[s], 0, j * BN, g * NB, B + b);
+                tma_load_4d(st + 2 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, b);
+                tma_load_4d(st + 3 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, B + b);
+                ++issued;
+            }
+            if (sh->abort)
+                for (int j = (issued > 3 ? issued - 3 : 0); j < issued; ++j)
+                    mbar_wait(&sh->full[j % 3], (uint32_t)((j / 3) & 1));
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
+            constexpr uint32_t id_o = idesc_f16(128, D, false, true);
+            bool ok = fwait(&sh->a_ready, 0, sh);
+            if (!ok) fgive_up(sh, 42);
+            // S of tile j into buffer j & 1
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % 3;
+                if (!fwait(&sh->full[s], (uint32_t)((j / 3) & 1), sh)) return false;
+                tc_fence_after();
+                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
+                const uint32_t cS = cS0 + (j & 1) * BN;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
+                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
+                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                }
+                mma_commit(&sh->s_full[j & 1]);
+                return true;
+            };
+            if (ok && !issue_qk(0)) { fgive_up(sh, 43); ok = false; }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) { fgive_up(sh, 43); break; }
+                if (!fwait(&sh->p_full[j & 1], (uint32_t)((j >> 1) & 1), sh)) { fgive_up(sh, 44); break; }
+                tc_fence_after();
+                const int s = j % 3;
+                const uint32_t vh = smem_u32(smem + s * 4 * KP + 2 * KP);
+                const uint64_t mvh = desc_mnmajor_16b(vh, BN * 128), mvl = desc_mnmajor_16b(vh + KP, BN * 128);
+                const uint32_t cS = cS0 + (j & 1) * BN;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                    const uint64_t dvh = desc_advance(mvh, kk * 2048), dvl = desc_advance(mvl, kk * 2048);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
+                }
+                mma_commit(&sh->free_[s]);
+                mma_commit(&sh->pv_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ softmax rows
+        const int tid = threadIdx.x;
+        const int t = t0 + tid;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const long long wq = (long long)p.n_heads * D;
+        {
+            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
+            const long long plane = (long long)B * p.T * wq;
+            row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
+            row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->a_ready);
+        }
+        const float cs = p.scale_log2 / (mq * mk);
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int buf = j & 1;
+            const uint32_t cS = cS0 + buf * BN;
+            if (!__all_sync(0xffffffffu, fwait(&sh->s_full[buf], (uint32_t)((j >> 1) & 1), sh))) {
+                fgive_up(sh, 45);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int s0 = j * BN;
+            const bool diag = (s0 + BN - 1 > t0);
+            float mt = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + cS + c, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (!diag || s0 + c + i <= t) mt = fmaxf(mt, __uint_as_float(r[i]) * cs);
+            }
+            float factor = 1.f;
+            if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
+                factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
+                m_ref = mt;
+            }
+            l *= factor;
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O may only be touched once P.V of tile j-1 has retired (S of tile j being complete
+                // implies only that tile j-2's has)
+                if (!__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((j - 1) & 1), sh))) {
+                    fgive_up(sh, 46);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + lane_base + cO + c, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                    tmem_st32(tmem + lane_base + cO + c, r);
+                }
+            }
+            const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float psum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32], ph[16], pl[16];
+                tmem_ld32(tmem + lane_base + cS + c, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pe[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        pe[e] = ex2(__uint_as_float(r[i + e]) * cs - mref_safe);
+                        if (diag && s0 + c + i + e > t) pe[e] = 0.f;
+                        psum += pe[e];
+                    }
+                    split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
+                }
+                tmem_st16(tmem + lane_base + cS + c, ph);
+                tmem_st16(tmem + lane_base + cS + c + 16, pl);
+            }
+            l += psum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->p_full[buf]);
+        }
+        // P.V of the last tile: the phase before it may still be open, so wait for it first (a parity
+        // wait can only name the current phase or the one before it).
+        if (ok && n_tiles >= 2 &&
+            !__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((n_tiles - 2) & 1), sh))) {
+            fgive_up(sh, 47);
+            ok = false;
+        }
+        if (ok && !__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((n_tiles - 1) & 1), sh))) {
+            fgive_up(sh, 48);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / (l * kPScale * mv);
+            float *orow = p.out + ((long long)b * p.T + t) * wq + (long long)h * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + cO + c, r);
+                tmem_wait_ld();
+                if (t < p.T) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o4;
+                        o4.x = __uint_as_float(r[i]) * inv, o4.y = __uint_as_float(r[i + 1]) * inv;
+                        o4.z = __uint_as_float(r[i + 2]) * inv, o4.w = __uint_as_float(r[i + 3]) * inv;
+                        *reinterpret_cast<float4 *>(orow + c + i) = o4;
+                    }
+                }
+            }
+            if (p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (m_ref + log2f(l)) * kLn2;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, 512);
+}
+
+struct Workspace {
+    uint32_t *amax_q, *amax_k, *amax_v;
+    __half *q_planes, *k_planes, *v_planes;
+    size_t total_bytes, amax_bytes;
+};
+
+inline Workspace workspace(void *base, int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    Workspace w{};
+    const size_t n_amax = (size_t)batch * n_kv_heads;
+    w.amax_bytes = (3 * n_amax * sizeof(uint32_t) + 1023) / 1024 * 1024;
+    auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+    const size_t qh = (size_t)2 * batch * T * n_heads * dim * sizeof(__half);
+    const size_t kh = (size_t)2 * batch * T * n_kv_heads * dim * sizeof(__half);
+    char *c = static_cast<char *>(base);
+    w.amax_q = reinterpret_cast<uint32_t *>(c), w.amax_k = w.amax_q + n_amax, w.amax_v = w.amax_k + n_amax;
+    size_t off = w.amax_bytes;
+    w.q_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
+    w.k_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
+    w.v_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
+    w.total_bytes = off;
+    return w;
+}
+
+template <int D>
+inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Params &p, cudaStream_t stream) {
+    size_t smem = 12 * (size_t)(64 * D * 2) + sizeof(Shared) + 1024;
+    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
+    if (optin_smem((const void *)attn_fwd_tc16<D>, smem)) return 1;
+    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
+    return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, p)));
+}
+
+}  // namespace tcf16
+
+inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    return tcf16::workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
+}
+
+inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_keys, const void *q, const void *k,
+                               const void *v, const void *out) {
+    if (!(dim == 64 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al(q) || !al(k) || !al(v) || !al(out)) return false;
+    const DeviceInfo *d = device_info();
+    return d && d->cc_major == 10 && get_encode_tiled() != nullptr;
+}
+
+inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
+                           int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+    using namespace tcb;
+    const tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, dim);
+    const int group = n_heads / n_kv_heads;
+    const int wq = n_heads * dim, wkv = n_kv_heads * dim;
+    if (cudaMemsetAsync(w.amax_q, 0, w.amax_bytes, stream) != cudaSuccess) {
+        cudaGetLastError();
+        return refuse("could not clear the forward workspace header");
+    }
+    int splits = (T + 511) / 512;
+    if (splits > 64) splits = 64;
+    const dim3 ag((unsigned)n_kv_heads, (unsigned)batch, (unsigned)splits);
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(q, w.amax_q, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(k, w.amax_k, T, wkv, dim)))) return 1;
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(v, w.amax_v, T, wkv, dim)))) return 1;
+    const long long nq4 = (long long)batch * T * wq / 4, nk4 = (long long)batch * T * wkv / 4;
+    const unsigned gq = (unsigned)((nq4 + 255) / 256), gk = (unsigned)((nk4 + 255) / 256);
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(q, w.amax_q, w.q_planes, batch, T, wq, group * dim)))) return 1;
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(k, w.amax_k, w.k_planes, batch, T, wkv, dim)))) return 1;
+    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(v, w.amax_v, w.v_planes, batch, T, wkv, dim)))) return 1;
+    CUtensorMap kmap, vmap;
+    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
+        !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, dim, 64))
+        return refuse("the TMA tensor maps for the forward could not be encoded.");
+    tcf16::Params p{};
+    p.q_planes = w.q_planes, p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v;
+    p.out = out, p.lse = lse;
+    p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.scale_log2 = kLog2e / sqrtf((float)dim);
+    g_last_path = "tcgen05";
+    return dim == 64 ? tcf16::launch_d<64>(kmap, vmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, p, stream);
+}
+
+}  // namespace zt

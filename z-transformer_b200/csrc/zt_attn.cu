@@ -16,6 +16,7 @@
 #ifndef ZT_NO_TC
 #include "tc_bwd.cuh"
 #include "tc_fwd.cuh"
+#include "tc_fwd16.cuh"
 #endif
 
 #include <mutex>
@@ -78,7 +79,15 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long q_bs = (long long)T * n_heads * dim;
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
-    if (g_path.load() == 0 &&
+    const int path = g_path.load();
+    if (path == 0 && tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
+        // The f16-split forward keeps its operand planes in the per-device arena (no entry point
+        // of the forward takes a workspace); see device_arena for when that allocates.
+        const size_t need = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+        if (void *arena = device_arena(need))
+            return launch_fwd_tc16(q, k, v, out, lse, arena, batch, T, n_heads, n_kv_heads, dim, stream);
+    }
+    if ((path == 0 || path == 2) &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
     }
@@ -106,7 +115,7 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
                          void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
                          int n_kv_heads, int dim, cudaStream_t stream) {
 #ifndef ZT_NO_TC
-    if (g_path.load() == 0 && workspace &&
+    if (g_path.load() != 1 && workspace &&
         workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
         tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
@@ -183,7 +192,7 @@ size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float)
 const char *zt_attn_last_error(void) { return g_last_error; }
 const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
-int zt_attn_set_path(int path) { return g_path.exchange(path == 1 ? 1 : 0); }
+int zt_attn_set_path(int path) { return g_path.exchange((path == 1 || path == 2) ? path : 0); }
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
 
 int zt_attn_tc_status(int *host_status) {
