@@ -479,17 +479,41 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
 // ---------------------------------------------------------------------------------------------------
 // dQ.  grid (ceil(T / 128), n_heads, batch).
+//
+// Key tiles of 32, two S/dP buffers in TMEM: while the row threads turn S and dP of tile j into dS,
+// the tensor core already computes S and dP of tile j+1 and dQ of tile j-1.  The eight row warps
+// form two sets of four; set (j & 1) owns tile j, so each set has two tile periods for its work.
 // ---------------------------------------------------------------------------------------------------
+constexpr int kDqStages = 6;
+
+struct DqShared {
+    uint64_t full[kDqStages], free_[kDqStages];
+    uint64_t a_ready, sdp_full[2], p_full[2], all_done;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+__device__ __forceinline__ bool dwait(uint64_t *bar, uint32_t parity, DqShared *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void dgive_up(DqShared *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
     attn_bwd_dq_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                    const BwdParams p) {
-    constexpr int NB = D / 64, W2 = D / 2;
-    constexpr int QP = 64 * D * 2;  // bytes of one plane of a 64-key tile
+    constexpr int NB = D / 64, W2 = D / 2, BN = 32, NS = kDqStages;
+    constexpr int KP = BN * D * 2;  // bytes of one plane of a 32-key tile
     constexpr int cQh = 0, cQl = W2, cGh = D, cGl = D + W2, cS = 2 * D, cDP = 2 * D + 64, cDQ = 2 * D + 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    BwdShared *sh = reinterpret_cast<BwdShared *>(smem + 12 * QP);  // 3 stages x (Kh, Kl, Vh, Vl)
+    DqShared *sh = reinterpret_cast<DqShared *>(smem + NS * 4 * KP);  // NS stages x (Kh, Kl, Vh, Vl)
 
     const int warp = threadIdx.x >> 5;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
@@ -497,18 +521,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int g = h / (p.n_heads / p.n_kv_heads);
     const int t0 = qt * 128;
     const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
-    const int n_tiles = (rows_end + 63) / 64;
+    const int n_tiles = (rows_end + BN - 1) / BN;
     const int B = p.batch;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
-        mbar_init(&sh->k_full, 1);
+        for (int i = 0; i < NS; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
         mbar_init(&sh->a_ready, kRowWarps);
-        mbar_init(&sh->sdp_full, 1);
-        mbar_init(&sh->p_full, kRowWarps);
-        mbar_init(&sh->acc_done, 1);
-        mbar_init(&sh->ld_ready, kRowWarps);
-        mbar_init(&sh->flush_done, kRowWarps);
+        for (int i = 0; i < 2; ++i) mbar_init(&sh->sdp_full[i], 1), mbar_init(&sh->p_full[i], 4);
+        mbar_init(&sh->all_done, 1);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -527,68 +547,80 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
             int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % 3;
-                if (j >= 3 && !bwait(&sh->free_[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { bgive_up(sh, 31); break; }
-                uint8_t *st = smem + s * 4 * QP;
-                mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
-                tma_load_4d(st, &kmap, &sh->full[s], 0, j * 64, g * NB, b);
-                tma_load_4d(st + QP, &kmap, &sh->full[s], 0, j * 64, g * NB, B + b);
-                tma_load_4d(st + 2 * QP, &vmap, &sh->full[s], 0, j * 64, g * NB, b);
-                tma_load_4d(st + 3 * QP, &vmap, &sh->full[s], 0, j * 64, g * NB, B + b);
+                const int s = j % NS;
+                if (j >= NS && !dwait(&sh->free_[s], (uint32_t)(((j / NS) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
+                uint8_t *st = smem + s * 4 * KP;
+                mbar_arrive_expect_tx(&sh->full[s], 4 * KP);
+                tma_load_4d(st, &kmap, &sh->full[s], 0, j * BN, g * NB, b);
+                tma_load_4d(st + KP, &kmap, &sh->full[s], 0, j * BN, g * NB, B + b);
+                tma_load_4d(st + 2 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, b);
+                tma_load_4d(st + 3 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, B + b);
                 ++issued;
             }
             if (sh->abort)
-                for (int j = (issued > 3 ? issued - 3 : 0); j < issued; ++j)
-                    mbar_wait(&sh->full[j % 3], (uint32_t)((j / 3) & 1));
+                for (int j = (issued > NS ? issued - NS : 0); j < issued; ++j)
+                    mbar_wait(&sh->full[j % NS], (uint32_t)((j / NS) & 1));
         }
         __syncwarp();
     } else if (warp == 9) {
         if (elect_one()) {
-            constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
+            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
-            bool ok = bwait(&sh->a_ready, 0, sh);
-            if (!ok) bgive_up(sh, 32);
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int s = j % 3;
-                if (!bwait(&sh->full[s], (uint32_t)((j / 3) & 1), sh)) { bgive_up(sh, 33); break; }
+            bool ok = dwait(&sh->a_ready, 0, sh);
+            if (!ok) dgive_up(sh, 32);
+            auto issue_sdp = [&](int j) -> bool {
+                const int s = j % NS;
+                if (!dwait(&sh->full[s], (uint32_t)((j / NS) & 1), sh)) return false;
                 tc_fence_after();
-                const uint32_t kh = smem_u32(smem + s * 4 * QP), kl = kh + QP, vh = kh + 2 * QP, vl = kh + 3 * QP;
-                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kl), bvh = desc_kmajor(vh), bvl = desc_kmajor(vl);
+                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
+                const uint64_t bvh = desc_kmajor(kh + 2 * KP), bvl = desc_kmajor(kh + 3 * KP);
+                const uint32_t oS = cS + (j & 1) * BN, oP = cDP + (j & 1) * BN;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
                     const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
-                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                    mma_ts_f16(tmem + oS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
+                    mma_ts_f16(tmem + oS, tmem + cQh + kk * 8, dkl, id_s, 1);
+                    mma_ts_f16(tmem + oS, tmem + cQl + kk * 8, dkh, id_s, 1);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
                     const uint64_t dvh = desc_advance(bvh, bo), dvl = desc_advance(bvl, bo);
-                    mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvh, id_s, kk > 0);
-                    mma_ts_f16(tmem + cDP, tmem + cGh + kk * 8, dvl, id_s, 1);
-                    mma_ts_f16(tmem + cDP, tmem + cGl + kk * 8, dvh, id_s, 1);
+                    mma_ts_f16(tmem + oP, tmem + cGh + kk * 8, dvh, id_s, kk > 0);
+                    mma_ts_f16(tmem + oP, tmem + cGh + kk * 8, dvl, id_s, 1);
+                    mma_ts_f16(tmem + oP, tmem + cGl + kk * 8, dvh, id_s, 1);
                 }
-                mma_commit(&sh->sdp_full);
-                if (!bwait(&sh->p_full, (uint32_t)(j & 1), sh)) { bgive_up(sh, 34); break; }
+                mma_commit(&sh->sdp_full[j & 1]);
+                return true;
+            };
+            if (ok && !issue_sdp(0)) { dgive_up(sh, 33); ok = false; }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles && !issue_sdp(j + 1)) { dgive_up(sh, 33); break; }
+                if (!dwait(&sh->p_full[j & 1], (uint32_t)((j >> 1) & 1), sh)) { dgive_up(sh, 34); break; }
                 tc_fence_after();
-                const uint64_t mkh = desc_mnmajor_16b(kh, 64 * 128), mkl = desc_mnmajor_16b(kl, 64 * 128);
+                const int s = j % NS;
+                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const uint64_t mkh = desc_mnmajor_16b(kh, BN * 128), mkl = desc_mnmajor_16b(kh + KP, BN * 128);
+                const uint32_t oP = cDP + (j & 1) * BN;
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t dkh = desc_advance(mkh, kk * 2048), dkl = desc_advance(mkl, kk * 2048);
-                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac, dkl, id_a, 1);
-                    mma_ts_f16(tmem + cDQ, tmem + cDP + ac + 16, dkh, id_a, 1);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 8, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 8, dkl, id_a, 1);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + 16 + kk * 8, dkh, id_a, 1);
                 }
                 mma_commit(&sh->free_[s]);
-                mma_commit(&sh->acc_done);
+                // completes once, when every MMA of this CTA has retired: a barrier that counted
+                // tiles could be several phases ahead of a waiting row set, and a parity wait can
+                // only tell the current phase from the one before it
+                if (j == n_tiles - 1) mma_commit(&sh->all_done);
             }
         }
         __syncwarp();
     } else {
-        // two threads per tile row: `half` picks which 32 of the tile's 64 columns this one handles
+        // two sets of four row warps; set `half` owns the tiles of its parity
         const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
         const int t = t0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -612,41 +644,41 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const float lse2 = (t < p.T) ? __ldg(p.lse + ridx) * kLog2e : 0.f;
         const float dels = (t < p.T) ? __ldg(p.delta + ridx) * (mdo * mv * c1) : 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            if (!__all_sync(0xffffffffu, bwait(&sh->sdp_full, (uint32_t)(j & 1), sh))) {
-                bgive_up(sh, 35);
+        int last = -1;  // the last tile this set handled
+        for (int j = half; j < n_tiles; j += 2) {
+            if (!__all_sync(0xffffffffu, dwait(&sh->sdp_full[half], (uint32_t)((j >> 1) & 1), sh))) {
+                dgive_up(sh, 35);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            {
-                const int c = 32 * half;
-                uint32_t rs[32], rd[32];
-                tmem_ld32(tmem + lane_base + cS + c, rs);
-                tmem_ld32(tmem + lane_base + cDP + c, rd);
-                tmem_wait_ld();
-                uint32_t dh[16], dl[16];
+            uint32_t rs[32], rd[32];
+            tmem_ld32(tmem + lane_base + cS + half * BN, rs);
+            tmem_ld32(tmem + lane_base + cDP + half * BN, rd);
+            tmem_wait_ld();
+            uint32_t dh[16], dl[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float dv[2];
+            for (int i = 0; i < 32; i += 2) {
+                float dv[2];
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int key = j * 64 + c + i + e;
-                        const bool vis = (key <= t) && (key < p.T);
-                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
-                        dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
-                    }
-                    split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
+                for (int e = 0; e < 2; ++e) {
+                    const int key = j * BN + i + e;
+                    const bool vis = (key <= t) && (key < p.T);
+                    const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
+                    dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
                 }
-                tmem_st16(tmem + lane_base + cDP + c, dh);
-                tmem_st16(tmem + lane_base + cDP + c + 16, dl);
+                split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
             }
+            tmem_st16(tmem + lane_base + cDP + half * BN, dh);
+            tmem_st16(tmem + lane_base + cDP + half * BN + 16, dl);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive_warp(&sh->p_full);
+            mbar_arrive_warp(&sh->p_full[half]);
+            last = j;
         }
-        if (ok && !__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)((n_tiles - 1) & 1), sh))) {
-            bgive_up(sh, 36);
+        (void)last;
+        if (ok && !__all_sync(0xffffffffu, dwait(&sh->all_done, 0, sh))) {
+            dgive_up(sh, 36);
             ok = false;
         }
         if (ok) {
@@ -715,7 +747,7 @@ template <int D>
 inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &q64, const CUtensorMap &g64,
                            const CUtensorMap &k64, const CUtensorMap &v64, const BwdParams &p, cudaStream_t stream) {
     const size_t smem_a = 2 * (size_t)(128 * D * 2) + 8 * (size_t)(64 * D * 2) + sizeof(BwdShared) + 1024;
-    const size_t smem_b = 12 * (size_t)(64 * D * 2) + sizeof(BwdShared) + 1024;
+    const size_t smem_b = kDqStages * 4 * (size_t)(32 * D * 2) + sizeof(DqShared) + 1024;
     const size_t floor_ = 120 * 1024;  // one CTA per SM: each wants all 512 TMEM columns
     const size_t sa = smem_a > floor_ ? smem_a : floor_, sb = smem_b > floor_ ? smem_b : floor_;
     if (optin_smem((const void *)attn_bwd_dkdv_tc<D>, sa)) return 1;
@@ -763,8 +795,8 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     if (!make_half_tile_map(&k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
         !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||
         !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
-        !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
-        !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 64))
+        !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 32) ||   // the dQ kernel's 32-key tiles
+        !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 32))
         return refuse("the TMA tensor maps for the backward could not be encoded.");
     BwdParams p{};
     p.lse = lse, p.delta = delta;

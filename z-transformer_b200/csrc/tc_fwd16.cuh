@@ -34,7 +34,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Shared {
     uint64_t full[3], free_[3];
-    uint64_t a_ready, s_full[2], p_full[2], pv_done;
+    uint64_t a_ready, s_full[2], p_full[2], pv_done, all_done;
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init(&sh->a_ready, 4);
         for (int i = 0; i < 2; ++i) mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 4);
         mbar_init(&sh->pv_done, 1);
+        mbar_init(&sh->all_done, 1);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -161,6 +162,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 mma_commit(&sh->free_[s]);
                 mma_commit(&sh->pv_done);
+                // completes once, after the last P.V: pv_done counts tiles and may be two phases ahead
+                // of a row thread by the time it gets here, which a parity wait cannot tell apart
+                if (j == n_tiles - 1) mma_commit(&sh->all_done);
             }
         }
         __syncwarp();
@@ -254,14 +258,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_before();
             mbar_arrive_warp(&sh->p_full[buf]);
         }
-        // P.V of the last tile: the phase before it may still be open, so wait for it first (a parity
-        // wait can only name the current phase or the one before it).
-        if (ok && n_tiles >= 2 &&
-            !__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((n_tiles - 2) & 1), sh))) {
-            fgive_up(sh, 47);
-            ok = false;
-        }
-        if (ok && !__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((n_tiles - 1) & 1), sh))) {
+        if (ok && !__all_sync(0xffffffffu, fwait(&sh->all_done, 0, sh))) {
             fgive_up(sh, 48);
             ok = false;
         }
