@@ -460,6 +460,9 @@ def test_tensor_core_large_magnitudes_and_peaked_rows(zt, dev, oracle):
 TC_BWD_SHAPES = [  # B, T, H, Hkv, D
     (1, 128, 4, 2, 64), (2, 129, 4, 2, 128), (1, 200, 8, 2, 128), (1, 256, 4, 4, 64), (1, 321, 6, 3, 128),
     (2, 513, 4, 1, 128), (1, 640, 8, 8, 64),
+    # a last key tile with a single query tile: every step of its walk is a flush, handed between the two
+    # row-warp sets (a hand-off that once raced)
+    (1, 150, 8, 4, 64), (1, 160, 16, 4, 64), (1, 150, 8, 4, 128), (3, 133, 8, 8, 64),
 ]
 
 

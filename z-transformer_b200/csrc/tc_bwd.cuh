@@ -172,12 +172,15 @@ __device__ __forceinline__ void bgive_up(BwdShared *sh, int code) {
 //    (a rounded f32 add by the row threads) and restarted from zero, so no large partial sum
 //    sits in TMEM while further terms arrive.  The tiles beyond them are flushed every
 //    kFlushTiles query tiles for the same reason, which keeps the error flat in T.
-constexpr int kFlushTiles = 8;
+//    (Before the periodic flushes, with a flush only per head: 12-26 of 524288 dk/dv elements
+//    outside the tolerance at T = 4096; with them: none.)
+constexpr int kFlushTiles = 16;  // query tiles of 32 rows between flushes (512 rows)
+constexpr int kDiagTiles = 4;    // query tiles that overlap a 128-key tile
 struct Walk {
-    int group, per_head, qi0, n_q, nd, nn;  // nd diagonal tiles (<= 2), nn tiles beyond them
+    int group, per_head, qi0, n_q, nd, nn;  // nd diagonal tiles (<= kDiagTiles), nn tiles beyond them
     __device__ __forceinline__ Walk(int group_, int per_head_, int qi0_, int n_q_)
         : group(group_), per_head(per_head_), qi0(qi0_), n_q(n_q_) {
-        nd = per_head < 2 ? per_head : 2;
+        nd = per_head < kDiagTiles ? per_head : kDiagTiles;
         nn = per_head - nd;
     }
     __device__ __forceinline__ void at(int it, int &hh, int &qi) const {
@@ -215,40 +218,68 @@ __device__ __forceinline__ void row_to_tmem(const __half *src, bool valid, uint3
 
 // ---------------------------------------------------------------------------------------------------
 // dK, dV.  grid (ceil(T / 128), n_kv_heads, batch).
+//
+// Query tiles of 32 rows, two S^T/dP^T buffers in TMEM: while one set of four row warps turns S^T and
+// dP^T of step `it` into P^T and dS^T, the tensor core computes S^T and dP^T of step it+1 and the
+// dV/dK updates of step it-1.  Row-warp set (it & 1) owns step `it`.
 // ---------------------------------------------------------------------------------------------------
+constexpr int kKvStages = 4;
+
+struct KvShared {
+    uint64_t full[kKvStages], free_[kKvStages];
+    uint64_t k_full, a_ready, sdp_full[2], p_full[2], ld_ready[2], flush_ready[2], flush_done;
+    uint32_t tmem_base;
+    volatile int abort;
+    float lse2[2][2][32], dels[2][2][32];  // [row set][buffer][query row of the tile]
+};
+__device__ __forceinline__ bool kwait(uint64_t *bar, uint32_t parity, KvShared *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void kgive_up(KvShared *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
     attn_bwd_dkdv_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap qmap,
                      const __grid_constant__ CUtensorMap gmap, const BwdParams p) {
-    constexpr int NB = D / 64, W2 = D / 2;
-    constexpr int KP = 128 * D * 2, QP = 64 * D * 2;              // bytes of one plane of a K / Q tile
+    constexpr int NB = D / 64, W2 = D / 2, BQ = 32, NS = kKvStages;
+    constexpr int KP = 128 * D * 2, QP = BQ * D * 2;  // bytes of one plane of a K tile / a query tile
     constexpr int cVh = 0, cVl = W2, cST = D, cDPT = D + 64, cDV = D + 128, cDK = 2 * D + 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sKh = smem, *sKl = smem + KP;
     uint8_t *stage0 = smem + 2 * KP;  // stage s: Qh, Ql, dOh, dOl at stage0 + s * 4 QP + {0,1,2,3} QP
-    BwdShared *sh = reinterpret_cast<BwdShared *>(smem + 2 * KP + 8 * QP);
+    KvShared *sh = reinterpret_cast<KvShared *>(smem + 2 * KP + NS * 4 * QP);
 
     const int warp = threadIdx.x >> 5;
     const int kt = (int)gridDim.x - 1 - (int)blockIdx.x;  // early key tiles see the most query rows
     const int g = blockIdx.y, b = blockIdx.z;
     const int group = p.n_heads / p.n_kv_heads;
     const int s0 = kt * 128;
-    const int n_q = (p.T + 63) / 64, qi0 = s0 / 64;
+    const int n_q = (p.T + BQ - 1) / BQ, qi0 = s0 / BQ;
     const int per_head = n_q - qi0;
     const int n_it = group * per_head;
     const int B = p.batch;
     const Walk walk(group, per_head, qi0, n_q);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
+        for (int i = 0; i < NS; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
         mbar_init(&sh->k_full, 1);
         mbar_init(&sh->a_ready, kRowWarps);
-        mbar_init(&sh->sdp_full, 1);
-        mbar_init(&sh->p_full, kRowWarps);
-        mbar_init(&sh->acc_done, 1);
-        mbar_init(&sh->ld_ready, kRowWarps);
-        mbar_init(&sh->flush_done, kRowWarps);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh->sdp_full[i], 1);
+            mbar_init(&sh->p_full[i], 4);
+            mbar_init(&sh->ld_ready[i], 4);
+        }
+        mbar_init(&sh->flush_ready[0], 1);
+        mbar_init(&sh->flush_ready[1], 1);
+        mbar_init(&sh->flush_done, 4);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -271,11 +302,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             tma_load_4d(sKl, &kmap, &sh->k_full, 0, s0, g * NB, B + b);
             int issued = 0;
             for (int it = 0; it < n_it; ++it) {
-                const int s = it & 1;
-                if (it >= 2 && !bwait(&sh->free_[s], (uint32_t)(((it >> 1) & 1) ^ 1), sh)) { bgive_up(sh, 21); break; }
+                const int s = it % NS;
+                if (it >= NS && !kwait(&sh->free_[s], (uint32_t)(((it / NS) & 1) ^ 1), sh)) { kgive_up(sh, 21); break; }
                 int hh, qi;
                 walk.at(it, hh, qi);
-                const int h = g * group + hh, row = qi * 64;
+                const int h = g * group + hh, row = qi * BQ;
                 uint8_t *st = stage0 + s * 4 * QP;
                 mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
                 tma_load_4d(st, &qmap, &sh->full[s], 0, row, h * NB, b);
@@ -286,79 +317,93 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             if (sh->abort) {
                 mbar_wait(&sh->k_full, 0);
-                for (int it = (issued > 2 ? issued - 2 : 0); it < issued; ++it)
-                    mbar_wait(&sh->full[it & 1], (uint32_t)((it >> 1) & 1));
+                for (int it = (issued > NS ? issued - NS : 0); it < issued; ++it)
+                    mbar_wait(&sh->full[it % NS], (uint32_t)((it / NS) & 1));
             }
         }
         __syncwarp();
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
-            constexpr uint32_t id_s = idesc_f16(128, 64, false, false);
+            constexpr uint32_t id_s = idesc_f16(128, BQ, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
-            bool ok = bwait(&sh->k_full, 0, sh) && bwait(&sh->a_ready, 0, sh);
-            if (!ok) bgive_up(sh, 22);
+            bool ok = kwait(&sh->k_full, 0, sh) && kwait(&sh->a_ready, 0, sh);
+            if (!ok) kgive_up(sh, 22);
             const uint64_t bkh = desc_kmajor(smem_u32(sKh)), bkl = desc_kmajor(smem_u32(sKl));
-            int n_flush = 0;
-            for (int it = 0; ok && it < n_it; ++it) {
-                const int s = it & 1;
-                if (!bwait(&sh->full[s], (uint32_t)((it >> 1) & 1), sh)) { bgive_up(sh, 23); break; }
+            auto issue_sdp = [&](int it) -> bool {
+                const int s = it % NS;
+                if (!kwait(&sh->full[s], (uint32_t)((it / NS) & 1), sh)) return false;
                 tc_fence_after();
-                const uint32_t qh = smem_u32(stage0 + s * 4 * QP), ql = qh + QP, gh = qh + 2 * QP, gl = qh + 3 * QP;
-                const uint64_t bqh = desc_kmajor(qh), bql = desc_kmajor(ql), bgh = desc_kmajor(gh), bgl = desc_kmajor(gl);
+                const uint32_t qh = smem_u32(stage0 + s * 4 * QP);
+                const uint64_t bqh = desc_kmajor(qh), bql = desc_kmajor(qh + QP);
+                const uint64_t bgh = desc_kmajor(qh + 2 * QP), bgl = desc_kmajor(qh + 3 * QP);
+                const uint32_t oS = cST + (it & 1) * BQ, oP = cDPT + (it & 1) * BQ;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BQ * 128) + (kk & 3) * 32);
                     const uint64_t dkh = desc_advance(bkh, ao), dkl = desc_advance(bkl, ao);
                     const uint64_t dqh = desc_advance(bqh, bo), dql = desc_advance(bql, bo);
-                    mma_ss_f16(tmem + cST, dkh, dqh, id_s, kk > 0);
-                    mma_ss_f16(tmem + cST, dkh, dql, id_s, 1);
-                    mma_ss_f16(tmem + cST, dkl, dqh, id_s, 1);
+                    mma_ss_f16(tmem + oS, dkh, dqh, id_s, kk > 0);
+                    mma_ss_f16(tmem + oS, dkh, dql, id_s, 1);
+                    mma_ss_f16(tmem + oS, dkl, dqh, id_s, 1);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (64 * 128) + (kk & 3) * 32);
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BQ * 128) + (kk & 3) * 32);
                     const uint64_t dgh = desc_advance(bgh, bo), dgl = desc_advance(bgl, bo);
-                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
-                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgl, id_s, 1);
-                    mma_ts_f16(tmem + cDPT, tmem + cVl + kk * 8, dgh, id_s, 1);
+                    mma_ts_f16(tmem + oP, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
+                    mma_ts_f16(tmem + oP, tmem + cVh + kk * 8, dgl, id_s, 1);
+                    mma_ts_f16(tmem + oP, tmem + cVl + kk * 8, dgh, id_s, 1);
                 }
-                mma_commit(&sh->sdp_full);
-                if (!bwait(&sh->p_full, (uint32_t)(it & 1), sh)) { bgive_up(sh, 24); break; }
+                mma_commit(&sh->sdp_full[it & 1]);
+                return true;
+            };
+            int n_flush = 0;
+            if (ok && !issue_sdp(0)) { kgive_up(sh, 23); ok = false; }
+            for (int it = 0; ok && it < n_it; ++it) {
+                if (it + 1 < n_it && !issue_sdp(it + 1)) { kgive_up(sh, 23); break; }
+                if (!kwait(&sh->p_full[it & 1], (uint32_t)((it >> 1) & 1), sh)) { kgive_up(sh, 24); break; }
                 const bool fresh = walk.fresh(it);
                 if (fresh && it > 0) {
-                    // the row threads are adding the accumulators to memory; restart only after that
-                    if (!bwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { bgive_up(sh, 27); break; }
+                    // a row set is adding the accumulators to memory; restart them only after that
+                    if (!kwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { kgive_up(sh, 27); break; }
                 }
-                if (walk.flush_after(it)) ++n_flush;
                 tc_fence_after();
-                const uint64_t mgh = desc_mnmajor_16b(gh, 64 * 128), mgl = desc_mnmajor_16b(gl, 64 * 128);
-                const uint64_t mqh = desc_mnmajor_16b(qh, 64 * 128), mql = desc_mnmajor_16b(ql, 64 * 128);
+                const int s = it % NS;
+                const uint32_t qh = smem_u32(stage0 + s * 4 * QP);
+                const uint64_t mqh = desc_mnmajor_16b(qh, BQ * 128), mql = desc_mnmajor_16b(qh + QP, BQ * 128);
+                const uint64_t mgh = desc_mnmajor_16b(qh + 2 * QP, BQ * 128), mgl = desc_mnmajor_16b(qh + 3 * QP, BQ * 128);
+                const uint32_t oS = cST + (it & 1) * BQ, oP = cDPT + (it & 1) * BQ;
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                for (int kk = 0; kk < BQ / 16; ++kk) {
                     const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
-                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgh, id_a, (!fresh || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDV, tmem + cST + ac, dgl, id_a, 1);
-                    mma_ts_f16(tmem + cDV, tmem + cST + ac + 16, dgh, id_a, 1);
+                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 8, dgh, id_a, (!fresh || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 8, dgl, id_a, 1);
+                    mma_ts_f16(tmem + cDV, tmem + oS + 16 + kk * 8, dgh, id_a, 1);
                 }
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                for (int kk = 0; kk < BQ / 16; ++kk) {
                     const uint64_t dqh = desc_advance(mqh, kk * 2048), dql = desc_advance(mql, kk * 2048);
-                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dqh, id_a, (!fresh || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac, dql, id_a, 1);
-                    mma_ts_f16(tmem + cDK, tmem + cDPT + ac + 16, dqh, id_a, 1);
+                    mma_ts_f16(tmem + cDK, tmem + oP + kk * 8, dqh, id_a, (!fresh || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDK, tmem + oP + kk * 8, dql, id_a, 1);
+                    mma_ts_f16(tmem + cDK, tmem + oP + 16 + kk * 8, dqh, id_a, 1);
                 }
                 mma_commit(&sh->free_[s]);
-                mma_commit(&sh->acc_done);
+                if (walk.flush_after(it)) {
+                    // One barrier per flush parity.  A parity wait can only tell a barrier's current
+                    // phase from the one before it; the set that has to do flush f may get to its wait
+                    // while flushes f-1 and f-2 are still open, but never further behind than that, so
+                    // a barrier that completes on every second flush is unambiguous.
+                    mma_commit(&sh->flush_ready[n_flush & 1]);
+                    ++n_flush;
+                }
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ one thread per key row
-        // two threads per tile row: `half` picks which 32 of the tile's 64 columns this one handles
+        // ------------------------------------------------------------------ one thread per key row;
+        // two sets of four warps, set `half` owns the steps of its parity
         const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
         const int key = s0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -378,34 +423,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const float fk = p.scale / (mdo * mv * c1 * mq);
         float *dvr = p.dv + ((long long)b * p.T + key) * wkv + (long long)g * D;
         float *dkr = p.dk + ((long long)b * p.T + key) * wkv + (long long)g * D;
-        int n_flush = 0;
+        int n_flush = 0;  // flushes requested by steps before the current one (either set's)
         bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
+        for (int it = half; it < n_it; it += 2) {
+            if (it >= 1 && walk.flush_after(it - 1)) ++n_flush;  // the other set's step
             int hh, qi;
             walk.at(it, hh, qi);
-            const int h = g * group + hh, qrow0 = qi * 64;
-            const int buf = it & 1;
+            const int h = g * group + hh, qrow0 = qi * BQ;
+            const uint32_t ph1 = (uint32_t)((it >> 1) & 1);
             {
-                const int t = qrow0 + (tid & 63);
+                const int t = qrow0 + (tid & 31);
                 const long long idx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
-                if (half == 0) {
-                    if (tid < 64) sh->lse2[buf][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
-                    else sh->dels[buf][tid - 64] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
-                }
+                // buffer ph1: a fast thread's write for the set's next step must not land on values a
+                // slower thread of the set is still reading
+                if (tid < 32) sh->lse2[half][ph1][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
+                else if (tid < 64) sh->dels[half][ph1][tid - 32] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
             }
-            mbar_arrive_warp(&sh->ld_ready);  // the 128 row threads exchange lse/delta through shared memory
-            if (!__all_sync(0xffffffffu, bwait(&sh->ld_ready, (uint32_t)(it & 1), sh) &&
-                                             bwait(&sh->sdp_full, (uint32_t)(it & 1), sh))) {
-                bgive_up(sh, 25);
+            mbar_arrive_warp(&sh->ld_ready[half]);  // the set's 128 threads exchange lse/delta through smem
+            if (!__all_sync(0xffffffffu, kwait(&sh->ld_ready[half], ph1, sh) && kwait(&sh->sdp_full[half], ph1, sh))) {
+                kgive_up(sh, 25);
                 ok = false;
                 break;
             }
             tc_fence_after();
             {
-                const int c = 32 * half;
                 uint32_t rs[32], rd[32];
-                tmem_ld32(tmem + lane_base + cST + c, rs);
-                tmem_ld32(tmem + lane_base + cDPT + c, rd);
+                tmem_ld32(tmem + lane_base + cST + half * BQ, rs);
+                tmem_ld32(tmem + lane_base + cDPT + half * BQ, rd);
                 tmem_wait_ld();
                 uint32_t ph[16], pl[16], dh[16], dl[16];
 #pragma unroll
@@ -413,33 +457,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     float pv[2], dv[2];
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int t = qrow0 + c + i + e;
+                        const int t = qrow0 + i + e;
                         const bool vis = (key <= t) && (t < p.T) && (key < p.T);
-                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[buf][c + i + e]);
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[half][ph1][i + e]);
                         const float pp = vis ? pe : 0.f;
                         pv[e] = pp * p.p_scale;
-                        dv[e] = fminf(fmaxf(pp * (__uint_as_float(rd[i + e]) * c1 - sh->dels[buf][c + i + e]), -65000.f), 65000.f);
+                        dv[e] = fminf(fmaxf(pp * (__uint_as_float(rd[i + e]) * c1 - sh->dels[half][ph1][i + e]), -65000.f), 65000.f);
                     }
                     split_pack(pv[0], pv[1], ph[i >> 1], pl[i >> 1]);
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
-                tmem_st16(tmem + lane_base + cST + c, ph);
-                tmem_st16(tmem + lane_base + cST + c + 16, pl);
-                tmem_st16(tmem + lane_base + cDPT + c, dh);
-                tmem_st16(tmem + lane_base + cDPT + c + 16, dl);
+                tmem_st16(tmem + lane_base + cST + half * BQ, ph);
+                tmem_st16(tmem + lane_base + cST + half * BQ + 16, pl);
+                tmem_st16(tmem + lane_base + cDPT + half * BQ, dh);
+                tmem_st16(tmem + lane_base + cDPT + half * BQ + 16, dl);
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive_warp(&sh->p_full);
+            mbar_arrive_warp(&sh->p_full[half]);
             if (walk.flush_after(it)) {
-                if (!__all_sync(0xffffffffu, bwait(&sh->acc_done, (uint32_t)(it & 1), sh))) {
-                    bgive_up(sh, 26);
+                if (!__all_sync(0xffffffffu, kwait(&sh->flush_ready[n_flush & 1], (uint32_t)((n_flush >> 1) & 1), sh))) {
+                    kgive_up(sh, 26);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
+                for (int c = 0; c < D; c += 32) {
                     uint32_t rv[32], rk[32];
                     tmem_ld32(tmem + lane_base + cDV + c, rv);
                     tmem_ld32(tmem + lane_base + cDK + c, rk);
@@ -457,8 +501,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                                 *reinterpret_cast<float4 *>(dvr + c + i) = a;
                                 *reinterpret_cast<float4 *>(dkr + c + i) = k4;
                             } else {
-                                // later ones add in memory (a rounded f32 add, no reply to wait for);
-                                // this thread is the only writer of its row, so the order is its own
+                                // later ones add in memory (a rounded f32 add, no reply to wait for).  A
+                                // row's flushes may come from either set's thread for this key; they are
+                                // ordered by the flush_done / flush_ready hand-offs through the MMA warp.
                                 red_add_v4(dvr + c + i, a);
                                 red_add_v4(dkr + c + i, k4);
                             }
@@ -466,6 +511,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     }
                 }
                 ++n_flush;
+                __threadfence();
                 tc_fence_before();
                 mbar_arrive_warp(&sh->flush_done);
             }
@@ -746,7 +792,7 @@ inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const voi
 template <int D>
 inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &q64, const CUtensorMap &g64,
                            const CUtensorMap &k64, const CUtensorMap &v64, const BwdParams &p, cudaStream_t stream) {
-    const size_t smem_a = 2 * (size_t)(128 * D * 2) + 8 * (size_t)(64 * D * 2) + sizeof(BwdShared) + 1024;
+    const size_t smem_a = 2 * (size_t)(128 * D * 2) + kKvStages * 4 * (size_t)(32 * D * 2) + sizeof(KvShared) + 1024;
     const size_t smem_b = kDqStages * 4 * (size_t)(32 * D * 2) + sizeof(DqShared) + 1024;
     const size_t floor_ = 120 * 1024;  // one CTA per SM: each wants all 512 TMEM columns
     const size_t sa = smem_a > floor_ ? smem_a : floor_, sb = smem_b > floor_ ? smem_b : floor_;
@@ -793,8 +839,8 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(v, w.amax_v, w.v_planes, batch, T, wkv, dim)))) return 1;
     CUtensorMap k128, q64, g64, k64, v64;
     if (!make_half_tile_map(&k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||
-        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
+        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 32) ||    // the dK/dV kernel's 32-row tiles
+        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 32) ||
         !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 32) ||   // the dQ kernel's 32-key tiles
         !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 32))
         return refuse("the TMA tensor maps for the backward could not be encoded.");
