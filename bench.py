@@ -260,7 +260,7 @@ def run_ours(args):
     # Algorithmic operations credited per launch: forward 2 GEMMs = F; key-outer backward kernel
     # S, dP, dV, dK = 2 F; query-outer backward kernel dQ = 0.5 F (its recomputed S and dP are
     # overhead, not credited); together the backward's 2.5 F.
-    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
+    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_fwd_tc16": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
               "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
     # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the B=2 case
     # (profiles/prefill_tensor_core_kernels_small_case.md), scaled by the batch: traffic is per sequence.

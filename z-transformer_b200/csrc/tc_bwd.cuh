@@ -58,51 +58,90 @@ __host__ __device__ inline float block_mult(uint32_t bits) {
 #endif
 }
 
-// max |x| over each (sequence, group of `cols_per_group` columns).  grid (groups, batch, splits).
-__global__ void __launch_bounds__(256) bwd_absmax_kernel(const float *__restrict__ x, uint32_t *__restrict__ out,
-                                                         int T, int width, int cols_per_group) {
-    const int g = blockIdx.x, b = blockIdx.y;
-    const int n_groups = gridDim.x;
-    const float *base = x + (long long)b * T * width + (long long)g * cols_per_group;
-    const int vec_per_row = cols_per_group / 4;
-    const long long total = (long long)T * vec_per_row;
-    float m = 0.f;
-    for (long long i = (long long)blockIdx.z * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.z * blockDim.x) {
-        const long long r = i / vec_per_row;
-        const int c = (int)(i - r * vec_per_row);
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(base + r * width) + c);
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+// The pre-pass over up to four tensors in one launch each: max |x| per (sequence, column group), then
+// the 16-bit planes.  Tensor z is [batch][T][width] floats; its groups are `cols_per_group` columns wide.
+struct PrepassTensor {
+    const float *x;
+    uint32_t *amax;   // [batch][width / cols_per_group] bit patterns of max |x|, zeroed by the caller
+    __half *planes;   // [2][batch][T][width]
+    int width, cols_per_group;
+};
+struct PrepassArgs {
+    PrepassTensor t[4];
+    int n, batch, T;
+};
+constexpr int kPrepassRows = 32;      // rows of one sequence per absmax CTA
+constexpr int kPrepassMaxGroups = 256;
+
+// grid (ceil(T / kPrepassRows), batch, n tensors).  A thread keeps to its columns, so its group is fixed
+// and the row loop is nothing but independent loads.
+__global__ void __launch_bounds__(256) bwd_absmax_kernel(const PrepassArgs a) {
+    __shared__ uint32_t gmax[kPrepassMaxGroups];
+    const PrepassTensor t = a.t[blockIdx.z];
+    const int b = blockIdx.y, r0 = blockIdx.x * kPrepassRows;
+    const int w4 = t.width / 4, n_groups = t.width / t.cols_per_group;
+    for (int i = threadIdx.x; i < n_groups; i += 256) gmax[i] = 0u;
+    __syncthreads();
+    const int r1 = min(r0 + kPrepassRows, a.T);
+    const float4 *base = reinterpret_cast<const float4 *>(t.x + (long long)b * a.T * t.width);
+    for (int c4 = threadIdx.x; c4 < w4; c4 += 256) {
+        float m = 0.f;
+#pragma unroll 8
+        for (int r = r0; r < r1; ++r) {
+            const float4 v = __ldg(base + (long long)r * w4 + c4);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+        atomicMax(&gmax[(c4 * 4) / t.cols_per_group], __float_as_uint(m));
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    if ((threadIdx.x & 31) == 0) atomicMax(out + b * n_groups + g, __float_as_uint(m));
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_groups; i += 256)
+        if (gmax[i]) atomicMax(t.amax + b * n_groups + i, gmax[i]);
 }
 
-// x -> planes h = f16(x m), l = f16(x m - h).  planes: [2][batch][T][width] halves.
-__global__ void __launch_bounds__(256) bwd_split_kernel(const float *__restrict__ x, const uint32_t *__restrict__ amax,
-                                                        __half *__restrict__ planes, int batch, int T, int width,
-                                                        int cols_per_group) {
-    const long long n4 = (long long)batch * T * width / 4;
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n4) return;
-    const long long e = i * 4;
-    const int col = (int)(e % width);
-    const int b = (int)(e / ((long long)T * width));
-    const int n_groups = width / cols_per_group;
-    const float m = block_mult(amax[b * n_groups + col / cols_per_group]);
-    const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
-    const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
-    __half h[4], l[4];
+// x -> planes h = f16(x m), l = f16(x m - h).  grid (ceil(T width / 4 / 2048), batch, n tensors): a CTA
+// converts 2048 consecutive float4 of one sequence, eight per thread.
+constexpr int kSplitPerCta = 2048;
+__global__ void __launch_bounds__(256) bwd_split_kernel(const PrepassArgs a) {
+    const PrepassTensor t = a.t[blockIdx.z];
+    const int b = blockIdx.y;
+    const int w4 = t.width / 4, n_groups = t.width / t.cols_per_group;
+    const long long seq4 = (long long)a.T * w4;  // float4 per sequence
+    const long long first = (long long)blockIdx.x * kSplitPerCta;
+    if (first >= seq4) return;
+    const float4 *src = reinterpret_cast<const float4 *>(t.x) + b * seq4;
+    uint2 *hp = reinterpret_cast<uint2 *>(t.planes) + b * seq4;
+    uint2 *lp = hp + (long long)a.batch * seq4;
+    const uint32_t *amax = t.amax + b * n_groups;
+    const unsigned col0 = (unsigned)(first % w4);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        h[k] = __float2half_rn(s[k]);
-        l[k] = __float2half_rn(s[k] - __half2float(h[k]));
+    for (int k = 0; k < kSplitPerCta / 256; ++k) {
+        const int o = k * 256 + threadIdx.x;
+        const long long i = first + o;
+        if (i >= seq4) break;
+        const unsigned c4 = (col0 + (unsigned)o) % (unsigned)w4;
+        const float m = block_mult(amax[(c4 * 4u) / (unsigned)t.cols_per_group]);
+        const float4 v = __ldg(src + i);
+        const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
+        __half h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            h[e] = __float2half_rn(s[e]);
+            l[e] = __float2half_rn(s[e] - __half2float(h[e]));
+        }
+        hp[i] = *reinterpret_cast<const uint2 *>(h);
+        lp[i] = *reinterpret_cast<const uint2 *>(l);
     }
-    __half *hp = planes + e;
-    __half *lp = planes + (long long)batch * T * width + e;
-    *reinterpret_cast<uint2 *>(hp) = *reinterpret_cast<const uint2 *>(h);
-    *reinterpret_cast<uint2 *>(lp) = *reinterpret_cast<const uint2 *>(l);
+}
+
+// Both passes for the tensors in `a` (amax already zeroed).
+inline int launch_prepass(const PrepassArgs &a, cudaStream_t stream) {
+    int wmax = 0;
+    for (int i = 0; i < a.n; ++i) wmax = a.t[i].width > wmax ? a.t[i].width : wmax;
+    const dim3 ga((unsigned)((a.T + kPrepassRows - 1) / kPrepassRows), (unsigned)a.batch, (unsigned)a.n);
+    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ga, 256, 0, stream>>>(a)))) return 1;
+    const long long seq4 = (long long)a.T * (wmax / 4);
+    const dim3 gs((unsigned)((seq4 + kSplitPerCta - 1) / kSplitPerCta), (unsigned)a.batch, (unsigned)a.n);
+    return ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gs, 256, 0, stream>>>(a)));
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -127,7 +166,7 @@ constexpr int kRowWarps = 8;
 
 struct BwdParams {
     const float *lse, *delta;        // [B, T, H]
-    const __half *v_planes;          // dkdv kernel: V planes read straight into TMEM
+    const __half *k_planes, *v_planes;   // dkdv kernel: the hi planes of K and V are read straight into TMEM
     const __half *q_planes, *do_planes;  // dq kernel: Q, dO planes read straight into TMEM
     const uint32_t *amax_q, *amax_k, *amax_v, *amax_do;  // [B, Hkv] bit patterns of max |x|
     float *dq, *dk, *dv;
@@ -136,27 +175,6 @@ struct BwdParams {
     float p_scale;  // P is multiplied by this power of two before its 16-bit split
     float c1;       // dP (in scaled units) is multiplied by this power of two before dS is split
 };
-
-struct BwdShared {
-    uint64_t full[3], free_[3];
-    uint64_t k_full, a_ready, sdp_full, p_full, acc_done, ld_ready, flush_done;
-    uint32_t tmem_base;
-    volatile int abort;
-    float lse2[2][64], dels[2][64];
-};
-
-__device__ __forceinline__ bool bwait(uint64_t *bar, uint32_t parity, BwdShared *sh) {
-    for (uint32_t i = 0; i < (1u << 20); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && sh->abort) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void bgive_up(BwdShared *sh, int code) {
-    sh->abort = code;
-    atomicMax(&g_tc_status, code);
-}
-
 
 // The dK/dV kernel's walk over (query tile, head of the group), and where its TMEM accumulators
 // are flushed to memory.
@@ -174,30 +192,42 @@ __device__ __forceinline__ void bgive_up(BwdShared *sh, int code) {
 //    kFlushTiles query tiles for the same reason, which keeps the error flat in T.
 //    (Before the periodic flushes, with a flush only per head: 12-26 of 524288 dk/dv elements
 //    outside the tolerance at T = 4096; with them: none.)
-constexpr int kFlushTiles = 16;  // query tiles of 32 rows between flushes (512 rows)
-constexpr int kDiagTiles = 4;    // query tiles that overlap a 128-key tile
+constexpr int kFlushTiles = 8;  // query tiles of 64 rows between flushes (512 rows)
+constexpr int kDiagTiles = 2;   // query tiles that overlap a 128-key tile
+// An iterator: step `it` is (head hh of the group, query tile qi); `flush` says the accumulators are
+// flushed after it, `fresh` that they restart from zero at it.  No divisions per step: every role of
+// the kernel walks it in lockstep.
 struct Walk {
-    int group, per_head, qi0, n_q, nd, nn;  // nd diagonal tiles (<= kDiagTiles), nn tiles beyond them
-    __device__ __forceinline__ Walk(int group_, int per_head_, int qi0_, int n_q_)
-        : group(group_), per_head(per_head_), qi0(qi0_), n_q(n_q_) {
+    int group, qi0, nd, na;  // nd diagonal tiles (<= kDiagTiles); na steps over the tiles beyond them
+    int it, hh, qi, cnt;     // cnt: steps since the last flush, while it < na
+    bool flush, fresh;
+    __device__ __forceinline__ Walk(int group_, int per_head, int qi0_, int n_q) : group(group_), qi0(qi0_) {
         nd = per_head < kDiagTiles ? per_head : kDiagTiles;
-        nn = per_head - nd;
+        na = (per_head - nd) * group;
+        it = 0, hh = 0, cnt = 0;
+        qi = na > 0 ? n_q - 1 : qi0 + nd - 1;
+        fresh = true;
+        set_flush();
     }
-    __device__ __forceinline__ void at(int it, int &hh, int &qi) const {
-        const int na = nn * group;
+    __device__ __forceinline__ void set_flush() {
+        flush = it < na ? (it == na - 1 || cnt + 1 == kFlushTiles * group) : (qi == qi0);
+    }
+    __device__ __forceinline__ void next() {
+        fresh = flush;
+        ++it;
         if (it < na) {
-            hh = it % group, qi = n_q - 1 - it / group;
+            // region A: tiles from the last one down, every head of the group on each
+            cnt = (cnt + 1 == kFlushTiles * group) ? 0 : cnt + 1;
+            if (++hh == group) hh = 0, --qi;
+        } else if (it == na) {
+            hh = 0, qi = qi0 + nd - 1;
         } else {
-            const int r = it - na;
-            hh = r / nd, qi = qi0 + nd - 1 - (r % nd);
+            // region B: the diagonal tiles, head by head
+            if (qi == qi0) qi = qi0 + nd - 1, ++hh;
+            else --qi;
         }
+        set_flush();
     }
-    __device__ __forceinline__ bool flush_after(int it) const {
-        const int na = nn * group;
-        if (it < na) return it == na - 1 || ((it + 1) % (kFlushTiles * group)) == 0;
-        return ((it - na) % nd) == nd - 1;
-    }
-    __device__ __forceinline__ bool fresh(int it) const { return it == 0 || flush_after(it - 1); }
 };
 
 // One row of `words` packed-half words from global memory into TMEM columns [col, col + words).
@@ -217,20 +247,27 @@ __device__ __forceinline__ void row_to_tmem(const __half *src, bool valid, uint3
 }
 
 // ---------------------------------------------------------------------------------------------------
-// dK, dV.  grid (ceil(T / 128), n_kv_heads, batch).
+// dK, dV.  grid (ceil(T / 128), n_kv_heads, batch), 576 threads: 16 row warps, a TMA warp, an MMA warp.
 //
-// Query tiles of 32 rows, two S^T/dP^T buffers in TMEM: while one set of four row warps turns S^T and
-// dP^T of step `it` into P^T and dS^T, the tensor core computes S^T and dP^T of step it+1 and the
-// dV/dK updates of step it-1.  Row-warp set (it & 1) owns step `it`.
+// Query tiles of 64 rows.  tcgen05.mma has a floor of about 50 clocks per instruction whatever its N
+// (measured: M = 128, K = 16 takes 49-54 clocks at N = 32 and at N = 64, 64 at N = 128), so S^T and
+// dP^T want the widest tile the 512 TMEM columns allow: 64 rows with S^T in two buffers and dP^T in
+// one, beside the two D-column accumulators and V's hi plane.  The tensor core's order per step is
+//     dK(it), dP^T(it+1), dV(it), S^T(it+2)
+// so the row threads' exp of step it+1 runs under the MMAs of step it, and their dS part, which has
+// to wait for dP^T(it+1), runs under dV(it) and S^T(it+2).  The row warps are four sets of four; a
+// set handles 16 of the step's 64 query columns (one 16-deep MMA step of dV / dK), which keeps the
+// serial part of the hand-off short.
 // ---------------------------------------------------------------------------------------------------
-constexpr int kKvStages = 4;
+constexpr int kKvRowWarps = 16;
+constexpr int kKvThreads = (kKvRowWarps + 2) * 32;
 
 struct KvShared {
-    uint64_t full[kKvStages], free_[kKvStages];
-    uint64_t k_full, a_ready, sdp_full[2], p_full[2], ld_ready[2], flush_ready[2], flush_done;
+    uint64_t full_q[4], full_g[4], free_q[4], free_g[4];  // a stage's Q planes and dO planes have lives of their own
+    uint64_t k_full, a_ready, st_full[2], dp_full, p_full, ld_ready, flush_ready, flush_done;
     uint32_t tmem_base;
     volatile int abort;
-    float lse2[2][2][32], dels[2][2][32];  // [row set][buffer][query row of the tile]
+    float lse2[2][64], dels[2][64];  // [buffer][query row of the tile]
 };
 __device__ __forceinline__ bool kwait(uint64_t *bar, uint32_t parity, KvShared *sh) {
     for (uint32_t i = 0; i < (1u << 20); ++i) {
@@ -243,19 +280,38 @@ __device__ __forceinline__ void kgive_up(KvShared *sh, int code) {
     sh->abort = code;
     atomicMax(&g_tc_status, code);
 }
+template <int D>
+__host__ __device__ constexpr int kv_stages() { return D == 128 ? 2 : 4; }
+template <int D>
+__host__ __device__ constexpr size_t kv_smem_bytes() {
+    return 3 * (size_t)(128 * D * 2) + kv_stages<D>() * 4 * (size_t)(64 * D * 2) + sizeof(KvShared) + 1024;
+}
+
+// 16 packed-half words of one row from global memory into TMEM columns [taddr, taddr + 16).
+__device__ __forceinline__ void row_to_tmem16(const __half *src, bool valid, uint32_t taddr) {
+    uint32_t r[16];
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) v = __ldg(reinterpret_cast<const uint4 *>(src) + i / 4);
+        r[i] = v.x, r[i + 1] = v.y, r[i + 2] = v.z, r[i + 3] = v.w;
+    }
+    tmem_st16(taddr, r);
+}
 
 template <int D>
-__global__ void __launch_bounds__(kBwdThreads, 1)
-    attn_bwd_dkdv_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap qmap,
-                     const __grid_constant__ CUtensorMap gmap, const BwdParams p) {
-    constexpr int NB = D / 64, W2 = D / 2, BQ = 32, NS = kKvStages;
+__global__ void __launch_bounds__(kKvThreads, 1)
+    attn_bwd_dkdv_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                     const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap gmap,
+                     const BwdParams p) {
+    constexpr int NB = D / 64, W2 = D / 2, BQ = 64, NS = kv_stages<D>();
     constexpr int KP = 128 * D * 2, QP = BQ * D * 2;  // bytes of one plane of a K tile / a query tile
-    constexpr int cVh = 0, cVl = W2, cST = D, cDPT = D + 64, cDV = D + 128, cDK = 2 * D + 128;
+    constexpr int cVh = 0, cST = 64, cDPT = 192, cDV = 256, cDK = 256 + D;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sKh = smem, *sKl = smem + KP;
-    uint8_t *stage0 = smem + 2 * KP;  // stage s: Qh, Ql, dOh, dOl at stage0 + s * 4 QP + {0,1,2,3} QP
-    KvShared *sh = reinterpret_cast<KvShared *>(smem + 2 * KP + NS * 4 * QP);
+    uint8_t *sKh = smem, *sKl = smem + KP, *sVl = smem + 2 * KP;  // V's hi plane sits in TMEM
+    uint8_t *stage0 = smem + 3 * KP;  // stage s: Qh, Ql, dOh, dOl at stage0 + s * 4 QP + {0,1,2,3} QP
+    KvShared *sh = reinterpret_cast<KvShared *>(smem + 3 * KP + NS * 4 * QP);
 
     const int warp = threadIdx.x >> 5;
     const int kt = (int)gridDim.x - 1 - (int)blockIdx.x;  // early key tiles see the most query rows
@@ -266,24 +322,26 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int per_head = n_q - qi0;
     const int n_it = group * per_head;
     const int B = p.batch;
-    const Walk walk(group, per_head, qi0, n_q);
+    Walk walk(group, per_head, qi0, n_q);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NS; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
-        mbar_init(&sh->k_full, 1);
-        mbar_init(&sh->a_ready, kRowWarps);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&sh->sdp_full[i], 1);
-            mbar_init(&sh->p_full[i], 4);
-            mbar_init(&sh->ld_ready[i], 4);
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(&sh->full_q[i], 1), mbar_init(&sh->full_g[i], 1);
+            mbar_init(&sh->free_q[i], 1), mbar_init(&sh->free_g[i], 1);
         }
-        mbar_init(&sh->flush_ready[0], 1);
-        mbar_init(&sh->flush_ready[1], 1);
-        mbar_init(&sh->flush_done, 4);
+        mbar_init(&sh->k_full, 1);
+        mbar_init(&sh->a_ready, kKvRowWarps);
+        mbar_init(&sh->st_full[0], 1);
+        mbar_init(&sh->st_full[1], 1);
+        mbar_init(&sh->dp_full, 1);
+        mbar_init(&sh->p_full, kKvRowWarps);
+        mbar_init(&sh->ld_ready, kKvRowWarps);
+        mbar_init(&sh->flush_ready, 1);
+        mbar_init(&sh->flush_done, kKvRowWarps);
         sh->abort = 0;
         mbar_fence_init();
     }
-    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == kKvRowWarps + 1) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -293,51 +351,60 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
     const float c1 = p.c1;
 
-    if (warp == 8) {
+    if (warp == kKvRowWarps) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            tma_prefetch_desc(&kmap), tma_prefetch_desc(&qmap), tma_prefetch_desc(&gmap);
-            mbar_arrive_expect_tx(&sh->k_full, 2 * KP);
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap), tma_prefetch_desc(&qmap), tma_prefetch_desc(&gmap);
+            mbar_arrive_expect_tx(&sh->k_full, 3 * KP);
             tma_load_4d(sKh, &kmap, &sh->k_full, 0, s0, g * NB, b);
             tma_load_4d(sKl, &kmap, &sh->k_full, 0, s0, g * NB, B + b);
+            tma_load_4d(sVl, &vmap, &sh->k_full, 0, s0, g * NB, B + b);
             int issued = 0;
-            for (int it = 0; it < n_it; ++it) {
+            for (int it = 0; it < n_it; ++it, walk.next()) {
                 const int s = it % NS;
-                if (it >= NS && !kwait(&sh->free_[s], (uint32_t)(((it / NS) & 1) ^ 1), sh)) { kgive_up(sh, 21); break; }
-                int hh, qi;
-                walk.at(it, hh, qi);
-                const int h = g * group + hh, row = qi * BQ;
+                const uint32_t free_par = (uint32_t)(((it / NS) & 1) ^ 1);
+                const int h = g * group + walk.hh, row = walk.qi * BQ;
                 uint8_t *st = stage0 + s * 4 * QP;
-                mbar_arrive_expect_tx(&sh->full[s], 4 * QP);
-                tma_load_4d(st, &qmap, &sh->full[s], 0, row, h * NB, b);
-                tma_load_4d(st + QP, &qmap, &sh->full[s], 0, row, h * NB, B + b);
-                tma_load_4d(st + 2 * QP, &gmap, &sh->full[s], 0, row, h * NB, b);
-                tma_load_4d(st + 3 * QP, &gmap, &sh->full[s], 0, row, h * NB, B + b);
+                // Q's planes are released by dK(it - NS), early in that step, and wanted first (S^T runs
+                // two steps ahead); dO's are released by dV and wanted a step later
+                if (it >= NS && !kwait(&sh->free_q[s], free_par, sh)) { kgive_up(sh, 21); break; }
+                mbar_arrive_expect_tx(&sh->full_q[s], 2 * QP);
+                tma_load_4d(st, &qmap, &sh->full_q[s], 0, row, h * NB, b);
+                tma_load_4d(st + QP, &qmap, &sh->full_q[s], 0, row, h * NB, B + b);
+                ++issued;
+                if (it >= NS && !kwait(&sh->free_g[s], free_par, sh)) { kgive_up(sh, 21); break; }
+                mbar_arrive_expect_tx(&sh->full_g[s], 2 * QP);
+                tma_load_4d(st + 2 * QP, &gmap, &sh->full_g[s], 0, row, h * NB, b);
+                tma_load_4d(st + 3 * QP, &gmap, &sh->full_g[s], 0, row, h * NB, B + b);
                 ++issued;
             }
             if (sh->abort) {
+                // let the copies in flight land before the CTA's shared memory goes away: `issued` counts
+                // half-stages, Q's then dO's of step issued / 2
                 mbar_wait(&sh->k_full, 0);
-                for (int it = (issued > NS ? issued - NS : 0); it < issued; ++it)
-                    mbar_wait(&sh->full[it % NS], (uint32_t)((it / NS) & 1));
+                for (int c = (issued > 2 * NS ? issued - 2 * NS : 0); c < issued; ++c) {
+                    const int it = c >> 1;
+                    mbar_wait((c & 1) ? &sh->full_g[it % NS] : &sh->full_q[it % NS], (uint32_t)((it / NS) & 1));
+                }
             }
         }
         __syncwarp();
-    } else if (warp == 9) {
+    } else if (warp == kKvRowWarps + 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t id_s = idesc_f16(128, BQ, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
             bool ok = kwait(&sh->k_full, 0, sh) && kwait(&sh->a_ready, 0, sh);
             if (!ok) kgive_up(sh, 22);
+            tc_fence_after();
             const uint64_t bkh = desc_kmajor(smem_u32(sKh)), bkl = desc_kmajor(smem_u32(sKl));
-            auto issue_sdp = [&](int it) -> bool {
-                const int s = it % NS;
-                if (!kwait(&sh->full[s], (uint32_t)((it / NS) & 1), sh)) return false;
-                tc_fence_after();
-                const uint32_t qh = smem_u32(stage0 + s * 4 * QP);
+            const uint64_t bvl = desc_kmajor(smem_u32(sVl));
+            const uint32_t stage_u32 = smem_u32(stage0);
+            // S^T(it) = K Q^T into buffer it & 1
+            auto issue_st = [&](int it) {
+                const uint32_t qh = stage_u32 + (uint32_t)((it % NS) * 4 * QP);
                 const uint64_t bqh = desc_kmajor(qh), bql = desc_kmajor(qh + QP);
-                const uint64_t bgh = desc_kmajor(qh + 2 * QP), bgl = desc_kmajor(qh + 3 * QP);
-                const uint32_t oS = cST + (it & 1) * BQ, oP = cDPT + (it & 1) * BQ;
+                const uint32_t oS = cST + (it & 1) * BQ;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
@@ -348,165 +415,248 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     mma_ss_f16(tmem + oS, dkh, dql, id_s, 1);
                     mma_ss_f16(tmem + oS, dkl, dqh, id_s, 1);
                 }
+                mma_commit(&sh->st_full[it & 1]);
+            };
+            // dP^T(it) = V dO^T
+            auto issue_dp = [&](int it) {
+                const uint32_t qh = stage_u32 + (uint32_t)((it % NS) * 4 * QP);
+                const uint64_t bgh = desc_kmajor(qh + 2 * QP), bgl = desc_kmajor(qh + 3 * QP);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
                     const uint32_t bo = (uint32_t)((kk >> 2) * (BQ * 128) + (kk & 3) * 32);
+                    const uint64_t dvl = desc_advance(bvl, ao);
                     const uint64_t dgh = desc_advance(bgh, bo), dgl = desc_advance(bgl, bo);
-                    mma_ts_f16(tmem + oP, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
-                    mma_ts_f16(tmem + oP, tmem + cVh + kk * 8, dgl, id_s, 1);
-                    mma_ts_f16(tmem + oP, tmem + cVl + kk * 8, dgh, id_s, 1);
+                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgl, id_s, 1);
+                    mma_ss_f16(tmem + cDPT, dvl, dgh, id_s, 1);
                 }
-                mma_commit(&sh->sdp_full[it & 1]);
+                mma_commit(&sh->dp_full);
+            };
+            auto stage_ready = [&](int it) -> bool {  // Q's planes of step `it`
+                return mbar_try_wait(&sh->full_q[it % NS], (uint32_t)((it / NS) & 1));
+            };
+            auto stage_wait = [&](int it) -> bool {
+                if (!kwait(&sh->full_q[it % NS], (uint32_t)((it / NS) & 1), sh)) return false;
+                tc_fence_after();
+                return true;
+            };
+            auto stage_wait_g = [&](int it) -> bool {  // dO's planes
+                if (!kwait(&sh->full_g[it % NS], (uint32_t)((it / NS) & 1), sh)) return false;
+                tc_fence_after();
                 return true;
             };
             int n_flush = 0;
-            if (ok && !issue_sdp(0)) { kgive_up(sh, 23); ok = false; }
-            for (int it = 0; ok && it < n_it; ++it) {
-                if (it + 1 < n_it && !issue_sdp(it + 1)) { kgive_up(sh, 23); break; }
-                if (!kwait(&sh->p_full[it & 1], (uint32_t)((it >> 1) & 1), sh)) { kgive_up(sh, 24); break; }
-                const bool fresh = walk.fresh(it);
-                if (fresh && it > 0) {
-                    // a row set is adding the accumulators to memory; restart them only after that
+            int pending_st = -1;  // an S^T whose operands had not landed when its turn came
+            if (ok) {
+                if (!stage_wait(0) || !stage_wait_g(0)) { kgive_up(sh, 23); ok = false; }
+                else {
+                    issue_st(0), issue_dp(0);
+                    if (n_it > 1) {
+                        if (!stage_wait(1)) { kgive_up(sh, 23); ok = false; }
+                        else issue_st(1);
+                    }
+                }
+            }
+            for (int it = 0; ok && it < n_it; ++it, walk.next()) {
+                // wait for P^T(it) and dS^T(it); a pending S^T goes out as soon as its operands land,
+                // so that the row threads' exp of that step is not left for after the next dV/dK
+                {
+                    bool got = false;
+                    for (uint32_t i = 0; i < (1u << 20); ++i) {
+                        if (mbar_try_wait(&sh->p_full, (uint32_t)(it & 1))) { got = true; break; }
+                        if (pending_st >= 0 && stage_ready(pending_st)) {
+                            tc_fence_after();
+                            issue_st(pending_st);
+                            pending_st = -1;
+                        }
+                        if ((i & 255u) == 255u && sh->abort) break;
+                    }
+                    if (!got) { kgive_up(sh, 24); break; }
+                }
+                if (walk.fresh && it > 0) {
+                    // the row threads are adding the accumulators to memory; restart them only after that
                     if (!kwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { kgive_up(sh, 27); break; }
                 }
                 tc_fence_after();
                 const int s = it % NS;
-                const uint32_t qh = smem_u32(stage0 + s * 4 * QP);
+                const uint32_t qh = stage_u32 + (uint32_t)(s * 4 * QP);
                 const uint64_t mqh = desc_mnmajor_16b(qh, BQ * 128), mql = desc_mnmajor_16b(qh + QP, BQ * 128);
                 const uint64_t mgh = desc_mnmajor_16b(qh + 2 * QP, BQ * 128), mgl = desc_mnmajor_16b(qh + 3 * QP, BQ * 128);
-                const uint32_t oS = cST + (it & 1) * BQ, oP = cDPT + (it & 1) * BQ;
-#pragma unroll
-                for (int kk = 0; kk < BQ / 16; ++kk) {
-                    const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
-                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 8, dgh, id_a, (!fresh || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 8, dgl, id_a, 1);
-                    mma_ts_f16(tmem + cDV, tmem + oS + 16 + kk * 8, dgh, id_a, 1);
-                }
+                const uint32_t oS = cST + (it & 1) * BQ;
+                const uint32_t acc0 = walk.fresh ? 0u : 1u;
+                // P^T / dS^T: the set of query columns [16 c, 16 c + 16), one MMA step deep, left its hi
+                // halves in the first 8 columns of its 16-column window and its lo halves in the last 8.
+                // dK first: it frees dS^T's columns for dP^T(it+1), which the row threads wait for.
 #pragma unroll
                 for (int kk = 0; kk < BQ / 16; ++kk) {
                     const uint64_t dqh = desc_advance(mqh, kk * 2048), dql = desc_advance(mql, kk * 2048);
-                    mma_ts_f16(tmem + cDK, tmem + oP + kk * 8, dqh, id_a, (!fresh || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDK, tmem + oP + kk * 8, dql, id_a, 1);
-                    mma_ts_f16(tmem + cDK, tmem + oP + 16 + kk * 8, dqh, id_a, 1);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + kk * 16, dqh, id_a, kk > 0 ? 1u : acc0);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + kk * 16, dql, id_a, 1);
+                    mma_ts_f16(tmem + cDK, tmem + cDPT + kk * 16 + 8, dqh, id_a, 1);
                 }
-                mma_commit(&sh->free_[s]);
-                if (walk.flush_after(it)) {
-                    // One barrier per flush parity.  A parity wait can only tell a barrier's current
-                    // phase from the one before it; the set that has to do flush f may get to its wait
-                    // while flushes f-1 and f-2 are still open, but never further behind than that, so
-                    // a barrier that completes on every second flush is unambiguous.
-                    mma_commit(&sh->flush_ready[n_flush & 1]);
+                mma_commit(&sh->free_q[s]);
+                if (it + 1 < n_it) {
+                    if (pending_st == it + 1) {  // (its S^T has not gone out either: operands still in flight)
+                        if (!stage_wait(it + 1)) { kgive_up(sh, 23); break; }
+                        issue_st(it + 1);
+                        pending_st = -1;
+                    }
+                    if (!stage_wait_g(it + 1)) { kgive_up(sh, 23); break; }
+                    issue_dp(it + 1);
+                }
+#pragma unroll
+                for (int kk = 0; kk < BQ / 16; ++kk) {
+                    const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
+                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 16, dgh, id_a, kk > 0 ? 1u : acc0);
+                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 16, dgl, id_a, 1);
+                    mma_ts_f16(tmem + cDV, tmem + oS + kk * 16 + 8, dgh, id_a, 1);
+                }
+                mma_commit(&sh->free_g[s]);
+                if (walk.flush) {
+                    // the row threads wait for every flush in turn, so one barrier's parity is enough
+                    mma_commit(&sh->flush_ready);
                     ++n_flush;
+                }
+                if (it + 2 < n_it) {
+                    // S^T(it+2) overwrites the buffer dV(it) has just read.  With two stages its operands
+                    // have been on their way since dK(it) retired: if they have not landed yet, it goes
+                    // out from the wait loop of the next step.
+                    if (NS > 2) {
+                        if (!stage_wait(it + 2)) { kgive_up(sh, 23); break; }
+                        issue_st(it + 2);
+                    } else if (stage_ready(it + 2)) {
+                        tc_fence_after();
+                        issue_st(it + 2);
+                    } else {
+                        pending_st = it + 2;
+                    }
                 }
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ one thread per key row;
-        // two sets of four warps, set `half` owns the steps of its parity
-        const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
+        // ------------------------------------------------------------------ one thread per key row and
+        // 16 of the step's query columns: set `set` handles columns [16 set, 16 set + 16)
+        const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
         const int key = s0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long wkv = (long long)p.n_kv_heads * D;
         {
-            const __half *vh = p.v_planes + ((long long)b * p.T + (key < p.T ? key : 0)) * wkv + (long long)g * D;
-            const __half *vl = vh + (long long)B * p.T * wkv;
-            if (half == 0) row_to_tmem<W2>(vh, key < p.T, tmem + lane_base + cVh);
-            else row_to_tmem<W2>(vl, key < p.T, tmem + lane_base + cVl);
+            // V's hi plane -> TMEM, 16 words of the row per set
+            const long long off = ((long long)b * p.T + (key < p.T ? key : 0)) * wkv + (long long)g * D;
+            if (set * 16 < W2) row_to_tmem16(p.v_planes + off + set * 32, key < p.T, tmem + lane_base + cVh + set * 16);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(&sh->a_ready);
         }
         const float cs = p.scale_log2 / (mq * mk);
         const float dfac = mdo * mv * c1;
-        const float fv = 1.0f / (p.p_scale * mdo);
-        const float fk = p.scale / (mdo * mv * c1 * mq);
-        float *dvr = p.dv + ((long long)b * p.T + key) * wkv + (long long)g * D;
-        float *dkr = p.dk + ((long long)b * p.T + key) * wkv + (long long)g * D;
-        int n_flush = 0;  // flushes requested by steps before the current one (either set's)
+        // lse (set 0's first 64 threads) and delta (set 1's) of a step's 64 query rows, fetched one step
+        // ahead into a register and published through shared memory
+        auto fetch = [&](const Walk &w, int it) -> float {
+            if (threadIdx.x >= 256 || tid >= 64 || it >= n_it) return 0.f;
+            const int t = w.qi * BQ + tid;
+            if (t >= p.T) return 0.f;
+            const long long idx = ((long long)b * p.T + t) * p.n_heads + g * group + w.hh;
+            return set == 0 ? __ldg(p.lse + idx) * kLog2e : __ldg(p.delta + idx) * dfac;
+        };
+        auto publish = [&](int it, float v) {
+            if (threadIdx.x < 256 && tid < 64) (set == 0 ? sh->lse2 : sh->dels)[it & 1][tid] = v;
+            mbar_arrive_warp(&sh->ld_ready);
+        };
+        Walk ahead = walk;  // one step ahead of `walk`
+        publish(0, fetch(ahead, 0));
+        ahead.next();
+        int n_flush = 0;
         bool ok = true;
-        for (int it = half; it < n_it; it += 2) {
-            if (it >= 1 && walk.flush_after(it - 1)) ++n_flush;  // the other set's step
-            int hh, qi;
-            walk.at(it, hh, qi);
-            const int h = g * group + hh, qrow0 = qi * BQ;
-            const uint32_t ph1 = (uint32_t)((it >> 1) & 1);
-            {
-                const int t = qrow0 + (tid & 31);
-                const long long idx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
-                // buffer ph1: a fast thread's write for the set's next step must not land on values a
-                // slower thread of the set is still reading
-                if (tid < 32) sh->lse2[half][ph1][tid] = (t < p.T) ? __ldg(p.lse + idx) * kLog2e : 0.f;
-                else if (tid < 64) sh->dels[half][ph1][tid - 32] = (t < p.T) ? __ldg(p.delta + idx) * dfac : 0.f;
-            }
-            mbar_arrive_warp(&sh->ld_ready[half]);  // the set's 128 threads exchange lse/delta through smem
-            if (!__all_sync(0xffffffffu, kwait(&sh->ld_ready[half], ph1, sh) && kwait(&sh->sdp_full[half], ph1, sh))) {
+        for (int it = 0; it < n_it; ++it, walk.next(), ahead.next()) {
+            const int t0 = walk.qi * BQ + set * 16;
+            const uint32_t par = (uint32_t)(it & 1);
+            const float nxt = fetch(ahead, it + 1);
+            if (!__all_sync(0xffffffffu, kwait(&sh->ld_ready, par, sh) && kwait(&sh->st_full[it & 1], (uint32_t)((it >> 1) & 1), sh))) {
                 kgive_up(sh, 25);
                 ok = false;
                 break;
             }
             tc_fence_after();
+            const uint32_t wS = tmem + lane_base + cST + (it & 1) * BQ + set * 16;
+            const uint32_t wP = tmem + lane_base + cDPT + set * 16;
+            float pr[16];
             {
-                uint32_t rs[32], rd[32];
-                tmem_ld32(tmem + lane_base + cST + half * BQ, rs);
-                tmem_ld32(tmem + lane_base + cDPT + half * BQ, rd);
+                uint32_t rs[16];
+                tmem_ld16(wS, rs);
                 tmem_wait_ld();
-                uint32_t ph[16], pl[16], dh[16], dl[16];
+                uint32_t ph[8], pl[8];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pv[2], dv[2];
+                for (int i = 0; i < 16; i += 2) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int t = qrow0 + i + e;
+                        const int t = t0 + i + e;
                         const bool vis = (key <= t) && (t < p.T) && (key < p.T);
-                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[half][ph1][i + e]);
-                        const float pp = vis ? pe : 0.f;
-                        pv[e] = pp * p.p_scale;
-                        dv[e] = fminf(fmaxf(pp * (__uint_as_float(rd[i + e]) * c1 - sh->dels[half][ph1][i + e]), -65000.f), 65000.f);
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
+                        pr[i + e] = vis ? pe : 0.f;
                     }
-                    split_pack(pv[0], pv[1], ph[i >> 1], pl[i >> 1]);
+                    split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
+                }
+                tmem_st8(wS, ph);
+                tmem_st8(wS + 8, pl);
+            }
+            if (!__all_sync(0xffffffffu, kwait(&sh->dp_full, par, sh))) {
+                kgive_up(sh, 28);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            // dP^T(it) is issued only after every row warp has finished step it-1, so the staging
+            // buffer of step it+1 (last read in step it-1) is free now
+            if (it + 1 < n_it) publish(it + 1, nxt);
+            {
+                uint32_t rd[16];
+                tmem_ld16(wP, rd);
+                tmem_wait_ld();
+                uint32_t dh[8], dl[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float dv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        dv[e] = fminf(fmaxf(pr[i + e] * (__uint_as_float(rd[i + e]) * c1 - sh->dels[it & 1][set * 16 + i + e]), -65000.f), 65000.f);
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
-                tmem_st16(tmem + lane_base + cST + half * BQ, ph);
-                tmem_st16(tmem + lane_base + cST + half * BQ + 16, pl);
-                tmem_st16(tmem + lane_base + cDPT + half * BQ, dh);
-                tmem_st16(tmem + lane_base + cDPT + half * BQ + 16, dl);
+                tmem_st8(wP, dh);
+                tmem_st8(wP + 8, dl);
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive_warp(&sh->p_full[half]);
-            if (walk.flush_after(it)) {
-                if (!__all_sync(0xffffffffu, kwait(&sh->flush_ready[n_flush & 1], (uint32_t)((n_flush >> 1) & 1), sh))) {
+            mbar_arrive_warp(&sh->p_full);
+            if (walk.flush) {
+                if (!__all_sync(0xffffffffu, kwait(&sh->flush_ready, (uint32_t)(n_flush & 1), sh))) {
                     kgive_up(sh, 26);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
+                // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's
+                const int c0 = (set & 1) * (D / 2);
+                const uint32_t acc = tmem + lane_base + (set < 2 ? cDV : cDK) + c0;
+                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + key) * wkv + (long long)g * D + c0;
+                const float f = set < 2 ? 1.0f / (p.p_scale * mdo) : p.scale / (mdo * mv * c1 * mq);
 #pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t rv[32], rk[32];
-                    tmem_ld32(tmem + lane_base + cDV + c, rv);
-                    tmem_ld32(tmem + lane_base + cDK + c, rk);
+                for (int c = 0; c < D / 2; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(acc + c, r);
                     tmem_wait_ld();
                     if (key < p.T) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
-                            float4 a, k4;
-                            a.x = __uint_as_float(rv[i]) * fv, a.y = __uint_as_float(rv[i + 1]) * fv;
-                            a.z = __uint_as_float(rv[i + 2]) * fv, a.w = __uint_as_float(rv[i + 3]) * fv;
-                            k4.x = __uint_as_float(rk[i]) * fk, k4.y = __uint_as_float(rk[i + 1]) * fk;
-                            k4.z = __uint_as_float(rk[i + 2]) * fk, k4.w = __uint_as_float(rk[i + 3]) * fk;
-                            if (n_flush == 0) {
-                                // the first flush assigns: dk/dv need no zeroing by the caller
-                                *reinterpret_cast<float4 *>(dvr + c + i) = a;
-                                *reinterpret_cast<float4 *>(dkr + c + i) = k4;
-                            } else {
-                                // later ones add in memory (a rounded f32 add, no reply to wait for).  A
-                                // row's flushes may come from either set's thread for this key; they are
-                                // ordered by the flush_done / flush_ready hand-offs through the MMA warp.
-                                red_add_v4(dvr + c + i, a);
-                                red_add_v4(dkr + c + i, k4);
-                            }
+                            float4 a;
+                            a.x = __uint_as_float(r[i]) * f, a.y = __uint_as_float(r[i + 1]) * f;
+                            a.z = __uint_as_float(r[i + 2]) * f, a.w = __uint_as_float(r[i + 3]) * f;
+                            // the first flush assigns (dk/dv need no zeroing by the caller); later ones
+                            // add in memory: a rounded f32 add with no reply to wait for
+                            if (n_flush == 0) *reinterpret_cast<float4 *>(dst + c + i) = a;
+                            else red_add_v4(dst + c + i, a);
                         }
                     }
                 }
@@ -520,7 +670,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem, 512);
+    if (warp == kKvRowWarps + 1) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -790,9 +940,9 @@ inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const voi
 }
 
 template <int D>
-inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &q64, const CUtensorMap &g64,
+inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &v128, const CUtensorMap &q64, const CUtensorMap &g64,
                            const CUtensorMap &k64, const CUtensorMap &v64, const BwdParams &p, cudaStream_t stream) {
-    const size_t smem_a = 2 * (size_t)(128 * D * 2) + kKvStages * 4 * (size_t)(32 * D * 2) + sizeof(KvShared) + 1024;
+    const size_t smem_a = kv_smem_bytes<D>();
     const size_t smem_b = kDqStages * 4 * (size_t)(32 * D * 2) + sizeof(DqShared) + 1024;
     const size_t floor_ = 120 * 1024;  // one CTA per SM: each wants all 512 TMEM columns
     const size_t sa = smem_a > floor_ ? smem_a : floor_, sb = smem_b > floor_ ? smem_b : floor_;
@@ -801,7 +951,7 @@ inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &q64, cons
     const dim3 grid_a((unsigned)((p.T + 127) / 128), (unsigned)p.n_kv_heads, (unsigned)p.batch);
     const dim3 grid_b((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
     if (ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
-                  (attn_bwd_dkdv_tc<D><<<grid_a, kBwdThreads, sa, stream>>>(k128, q64, g64, p))))
+                  (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(k128, v128, q64, g64, p))))
         return 1;
     return ZT_LAUNCH("attn_bwd_dq_tc", stream, (attn_bwd_dq_tc<D><<<grid_b, kBwdThreads, sb, stream>>>(k64, v64, p)));
 }
@@ -824,29 +974,24 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
         cudaGetLastError();
         return refuse("could not clear the backward workspace header");
     }
-    int splits = (T + 511) / 512;
-    if (splits > 64) splits = 64;
-    const dim3 ag((unsigned)n_kv_heads, (unsigned)batch, (unsigned)splits);
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(q, w.amax_q, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(dout, w.amax_do, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(k, w.amax_k, T, wkv, dim)))) return 1;
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(v, w.amax_v, T, wkv, dim)))) return 1;
-    const long long nq4 = (long long)batch * T * wq / 4, nk4 = (long long)batch * T * wkv / 4;
-    const unsigned gq = (unsigned)((nq4 + 255) / 256), gk = (unsigned)((nk4 + 255) / 256);
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(q, w.amax_q, w.q_planes, batch, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(dout, w.amax_do, w.do_planes, batch, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(k, w.amax_k, w.k_planes, batch, T, wkv, dim)))) return 1;
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(v, w.amax_v, w.v_planes, batch, T, wkv, dim)))) return 1;
-    CUtensorMap k128, q64, g64, k64, v64;
+    PrepassArgs pa{};
+    pa.n = 4, pa.batch = batch, pa.T = T;
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq, group * dim};
+    pa.t[1] = {dout, w.amax_do, w.do_planes, wq, group * dim};
+    pa.t[2] = {k, w.amax_k, w.k_planes, wkv, dim};
+    pa.t[3] = {v, w.amax_v, w.v_planes, wkv, dim};
+    if (launch_prepass(pa, stream)) return 1;
+    CUtensorMap k128, v128, q64, g64, k64, v64;
     if (!make_half_tile_map(&k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 32) ||    // the dK/dV kernel's 32-row tiles
-        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 32) ||
+        !make_half_tile_map(&v128, w.v_planes, 2 * batch, T, wkv, dim, 128) ||
+        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||    // the dK/dV kernel's 64-row tiles
+        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
         !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 32) ||   // the dQ kernel's 32-key tiles
         !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 32))
         return refuse("the TMA tensor maps for the backward could not be encoded.");
     BwdParams p{};
     p.lse = lse, p.delta = delta;
-    p.v_planes = w.v_planes, p.q_planes = w.q_planes, p.do_planes = w.do_planes;
+    p.k_planes = w.k_planes, p.v_planes = w.v_planes, p.q_planes = w.q_planes, p.do_planes = w.do_planes;
     p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
     p.dq = dq, p.dk = dk, p.dv = dv;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
@@ -859,8 +1004,8 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
         p.c1 = ldexpf(1.0f, boost - 16 - (dim == 128 ? 7 : 6));
     }
     g_last_path = "tcgen05";
-    return dim == 64 ? launch_bwd_tc_d<64>(k128, q64, g64, k64, v64, p, stream)
-                     : launch_bwd_tc_d<128>(k128, q64, g64, k64, v64, p, stream);
+    return dim == 64 ? launch_bwd_tc_d<64>(k128, v128, q64, g64, k64, v64, p, stream)
+                     : launch_bwd_tc_d<128>(k128, v128, q64, g64, k64, v64, p, stream);
 }
 
 }  // namespace zt

@@ -346,17 +346,12 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
         cudaGetLastError();
         return refuse("could not clear the forward workspace header");
     }
-    int splits = (T + 511) / 512;
-    if (splits > 64) splits = 64;
-    const dim3 ag((unsigned)n_kv_heads, (unsigned)batch, (unsigned)splits);
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(q, w.amax_q, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(k, w.amax_k, T, wkv, dim)))) return 1;
-    if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ag, 256, 0, stream>>>(v, w.amax_v, T, wkv, dim)))) return 1;
-    const long long nq4 = (long long)batch * T * wq / 4, nk4 = (long long)batch * T * wkv / 4;
-    const unsigned gq = (unsigned)((nq4 + 255) / 256), gk = (unsigned)((nk4 + 255) / 256);
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gq, 256, 0, stream>>>(q, w.amax_q, w.q_planes, batch, T, wq, group * dim)))) return 1;
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(k, w.amax_k, w.k_planes, batch, T, wkv, dim)))) return 1;
-    if (ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gk, 256, 0, stream>>>(v, w.amax_v, w.v_planes, batch, T, wkv, dim)))) return 1;
+    PrepassArgs pa{};
+    pa.n = 3, pa.batch = batch, pa.T = T;
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq, group * dim};
+    pa.t[1] = {k, w.amax_k, w.k_planes, wkv, dim};
+    pa.t[2] = {v, w.amax_v, w.v_planes, wkv, dim};
+    if (launch_prepass(pa, stream)) return 1;
     CUtensorMap kmap, vmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
         !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, dim, 64))

@@ -80,7 +80,8 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
     const int path = g_path.load();
-    if (path == 0 && tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
+    if (path == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
+        tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
         // The f16-split forward keeps its operand planes in the per-device arena (no entry point
         // of the forward takes a workspace); see device_arena for when that allocates.
         const size_t need = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
@@ -118,7 +119,7 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
     if (g_path.load() != 1 && workspace &&
         workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
-        tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
+        n_kv_heads <= tcb::kPrepassMaxGroups && tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
                              dim, stream);
     }
