@@ -28,6 +28,7 @@ import importlib
 import json
 import os
 import statistics
+import threading
 import subprocess
 import sys
 import time
@@ -55,7 +56,10 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 50 ms while the timed region runs."""
+    """SM clock, power and throttle reasons of one GPU, read through NVML (the library nvidia-smi itself
+    reads) every 2 ms from a thread while the timed region runs; `nvidia-smi -lms 50` when the NVML
+    binding is absent.  A timed region of a few tens of milliseconds holds too few nvidia-smi samples
+    to say anything about the clock under load."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -64,9 +68,41 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
+        self.thread = None
+        self.rows = []   # (sm MHz, max MHz, watts, reason bits)
         self.path = f"/tmp/zt_clocks_{os.getpid()}.csv"
 
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.gpu_index < len(ids) and ids[self.gpu_index].isdigit():
+                return int(ids[self.gpu_index])
+        return self.gpu_index
+
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            self._stop = False
+
+            def loop():
+                while not self._stop:
+                    try:
+                        self.rows.append((pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM), mx,
+                                          pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0,
+                                          pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)))
+                    except pynvml.NVMLError:
+                        pass
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
@@ -76,6 +112,22 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=5)
+            # NVML reason bits: 0x4 sw_power_cap, 0x8 hw_slowdown, 0x20 sw_thermal, 0x40 hw_thermal
+            bits = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+            reasons = set()
+            for row in self.rows:
+                for bit, name in bits.items():
+                    if row[3] & bit:
+                        reasons.add(name)
+            sm = [r[0] for r in self.rows]
+            return {"sm_mhz": statistics.median(sm) if sm else None,
+                    "sm_min_mhz": min(sm) if sm else None,
+                    "sm_max_mhz": self.rows[0][1] if self.rows else None,
+                    "power_w": statistics.median([r[2] for r in self.rows]) if self.rows else None,
+                    "samples": len(sm), "source": "nvml, 2 ms", "reasons": sorted(reasons)}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -104,7 +156,7 @@ class ClockSampler:
         except OSError:
             pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "source": "nvidia-smi -lms 50", "reasons": sorted(reasons)}
 
 
 def dist_env():
@@ -538,7 +590,7 @@ def run_all_configs(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--gather", action="store_true", help="time the all-gather of sharded outputs too")

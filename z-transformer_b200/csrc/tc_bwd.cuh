@@ -161,8 +161,6 @@ __device__ __forceinline__ void red_add_v4(float *addr, float4 v) {
                  : "memory");
 }
 
-constexpr int kBwdThreads = 320;  // 8 row warps (two threads per tile row, 32 columns each), 1 TMA warp, 1 MMA warp
-constexpr int kRowWarps = 8;
 
 struct BwdParams {
     const float *lse, *delta;        // [B, T, H]
@@ -674,17 +672,20 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------------------
-// dQ.  grid (ceil(T / 128), n_heads, batch).
+// dQ.  grid (ceil(T / 128), n_heads, batch), 576 threads: 16 row warps, a TMA warp, an MMA warp.
 //
-// Key tiles of 32, two S/dP buffers in TMEM: while the row threads turn S and dP of tile j into dS,
-// the tensor core already computes S and dP of tile j+1 and dQ of tile j-1.  The eight row warps
-// form two sets of four; set (j & 1) owns tile j, so each set has two tile periods for its work.
+// Key tiles of 64, S and dP in two TMEM buffers each: while the row threads turn S and dP of tile j
+// into dS, the tensor core computes dQ of tile j-1 and S, dP of tile j+1.  The hi planes of the Q and
+// dO tiles are TMEM operands, their lo planes (used by one of the three split terms) stay in shared
+// memory.  K tiles live from S(j), issued two tiles ahead, to dQ(j): a ring of three; V tiles only for
+// dP(j): a ring of two.  The row warps are four sets of four; a set handles 16 of the tile's 64 keys
+// (one 16-deep MMA step of dQ).
 // ---------------------------------------------------------------------------------------------------
-constexpr int kDqStages = 6;
+constexpr int kDqKSlots = 3, kDqVSlots = 2;
 
 struct DqShared {
-    uint64_t full[kDqStages], free_[kDqStages];
-    uint64_t a_ready, sdp_full[2], p_full[2], all_done;
+    uint64_t full_k[kDqKSlots], free_k[kDqKSlots], full_v[kDqVSlots], free_v[kDqVSlots];
+    uint64_t ql_full, a_ready, sdp_full[2], p_full[2], all_done;
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -699,17 +700,26 @@ __device__ __forceinline__ void dgive_up(DqShared *sh, int code) {
     sh->abort = code;
     atomicMax(&g_tc_status, code);
 }
+template <int D>
+__host__ __device__ constexpr size_t dq_smem_bytes() {
+    return 2 * (size_t)(128 * D * 2) + (kDqKSlots + kDqVSlots) * 2 * (size_t)(64 * D * 2) + sizeof(DqShared) + 1024;
+}
 
 template <int D>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kKvThreads, 1)
     attn_bwd_dq_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                   const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap gmap,
                    const BwdParams p) {
-    constexpr int NB = D / 64, W2 = D / 2, BN = 32, NS = kDqStages;
-    constexpr int KP = BN * D * 2;  // bytes of one plane of a 32-key tile
-    constexpr int cQh = 0, cQl = W2, cGh = D, cGl = D + W2, cS = 2 * D, cDP = 2 * D + 64, cDQ = 2 * D + 128;
+    constexpr int NB = D / 64, W2 = D / 2, BN = 64;
+    constexpr int QP = 128 * D * 2;  // bytes of one plane of the 128-row Q / dO tile
+    constexpr int KP = BN * D * 2;   // bytes of one plane of a 64-key tile
+    constexpr int cQh = 0, cGh = 64, cS = 128, cDP = 256, cDQ = 384;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    DqShared *sh = reinterpret_cast<DqShared *>(smem + NS * 4 * KP);  // NS stages x (Kh, Kl, Vh, Vl)
+    uint8_t *sQl = smem, *sGl = smem + QP;
+    uint8_t *sK = smem + 2 * QP;               // slot s: Kh, Kl at sK + s * 2 KP + {0, 1} KP
+    uint8_t *sV = sK + kDqKSlots * 2 * KP;     // slot s: Vh, Vl
+    DqShared *sh = reinterpret_cast<DqShared *>(sV + kDqVSlots * 2 * KP);
 
     const int warp = threadIdx.x >> 5;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
@@ -721,14 +731,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int B = p.batch;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NS; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
-        mbar_init(&sh->a_ready, kRowWarps);
-        for (int i = 0; i < 2; ++i) mbar_init(&sh->sdp_full[i], 1), mbar_init(&sh->p_full[i], 4);
+        for (int i = 0; i < kDqKSlots; ++i) mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
+        for (int i = 0; i < kDqVSlots; ++i) mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
+        mbar_init(&sh->ql_full, 1);
+        mbar_init(&sh->a_ready, kKvRowWarps);
+        for (int i = 0; i < 2; ++i) mbar_init(&sh->sdp_full[i], 1), mbar_init(&sh->p_full[i], kKvRowWarps);
         mbar_init(&sh->all_done, 1);
         sh->abort = 0;
         mbar_fence_init();
     }
-    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == kKvRowWarps + 1) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -738,98 +750,122 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
     const float c1 = p.c1;
 
-    if (warp == 8) {
+    if (warp == kKvRowWarps) {
+        // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
-            int issued = 0;
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap), tma_prefetch_desc(&qmap), tma_prefetch_desc(&gmap);
+            mbar_arrive_expect_tx(&sh->ql_full, 2 * QP);
+            tma_load_4d(sQl, &qmap, &sh->ql_full, 0, t0, h * NB, B + b);
+            tma_load_4d(sGl, &gmap, &sh->ql_full, 0, t0, h * NB, B + b);
+            int issued = 0;  // half-steps: K of tile issued / 2, then V
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % NS;
-                if (j >= NS && !dwait(&sh->free_[s], (uint32_t)(((j / NS) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
-                uint8_t *st = smem + s * 4 * KP;
-                mbar_arrive_expect_tx(&sh->full[s], 4 * KP);
-                tma_load_4d(st, &kmap, &sh->full[s], 0, j * BN, g * NB, b);
-                tma_load_4d(st + KP, &kmap, &sh->full[s], 0, j * BN, g * NB, B + b);
-                tma_load_4d(st + 2 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, b);
-                tma_load_4d(st + 3 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, B + b);
+                const int ks = j % kDqKSlots, vs = j % kDqVSlots;
+                if (j >= kDqKSlots && !dwait(&sh->free_k[ks], (uint32_t)(((j / kDqKSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
+                mbar_arrive_expect_tx(&sh->full_k[ks], 2 * KP);
+                tma_load_4d(sK + ks * 2 * KP, &kmap, &sh->full_k[ks], 0, j * BN, g * NB, b);
+                tma_load_4d(sK + ks * 2 * KP + KP, &kmap, &sh->full_k[ks], 0, j * BN, g * NB, B + b);
+                ++issued;
+                if (j >= kDqVSlots && !dwait(&sh->free_v[vs], (uint32_t)(((j / kDqVSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
+                mbar_arrive_expect_tx(&sh->full_v[vs], 2 * KP);
+                tma_load_4d(sV + vs * 2 * KP, &vmap, &sh->full_v[vs], 0, j * BN, g * NB, b);
+                tma_load_4d(sV + vs * 2 * KP + KP, &vmap, &sh->full_v[vs], 0, j * BN, g * NB, B + b);
                 ++issued;
             }
-            if (sh->abort)
-                for (int j = (issued > NS ? issued - NS : 0); j < issued; ++j)
-                    mbar_wait(&sh->full[j % NS], (uint32_t)((j / NS) & 1));
+            if (sh->abort) {
+                // let the copies in flight land before the CTA's shared memory goes away
+                mbar_wait(&sh->ql_full, 0);
+                const int n_k = (issued + 1) / 2, n_v = issued / 2;
+                for (int j = (n_k > kDqKSlots ? n_k - kDqKSlots : 0); j < n_k; ++j)
+                    mbar_wait(&sh->full_k[j % kDqKSlots], (uint32_t)((j / kDqKSlots) & 1));
+                for (int j = (n_v > kDqVSlots ? n_v - kDqVSlots : 0); j < n_v; ++j)
+                    mbar_wait(&sh->full_v[j % kDqVSlots], (uint32_t)((j / kDqVSlots) & 1));
+            }
         }
         __syncwarp();
-    } else if (warp == 9) {
+    } else if (warp == kKvRowWarps + 1) {
+        // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
             constexpr uint32_t id_a = idesc_f16(128, D, false, true);
-            bool ok = dwait(&sh->a_ready, 0, sh);
+            bool ok = dwait(&sh->ql_full, 0, sh) && dwait(&sh->a_ready, 0, sh);
             if (!ok) dgive_up(sh, 32);
+            tc_fence_after();
+            const uint64_t bql = desc_kmajor(smem_u32(sQl)), bgl = desc_kmajor(smem_u32(sGl));
+            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
+            // S(j) = Q K^T and dP(j) = dO V^T into buffers j & 1
             auto issue_sdp = [&](int j) -> bool {
-                const int s = j % NS;
-                if (!dwait(&sh->full[s], (uint32_t)((j / NS) & 1), sh)) return false;
+                const int ks = j % kDqKSlots, vs = j % kDqVSlots;
+                if (!dwait(&sh->full_k[ks], (uint32_t)((j / kDqKSlots) & 1), sh)) return false;
                 tc_fence_after();
-                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const uint32_t kh = k_u32 + (uint32_t)(ks * 2 * KP);
                 const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
-                const uint64_t bvh = desc_kmajor(kh + 2 * KP), bvl = desc_kmajor(kh + 3 * KP);
                 const uint32_t oS = cS + (j & 1) * BN, oP = cDP + (j & 1) * BN;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
                     const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
                     const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
                     mma_ts_f16(tmem + oS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
                     mma_ts_f16(tmem + oS, tmem + cQh + kk * 8, dkl, id_s, 1);
-                    mma_ts_f16(tmem + oS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                    mma_ss_f16(tmem + oS, desc_advance(bql, ao), dkh, id_s, 1);
                 }
+                if (!dwait(&sh->full_v[vs], (uint32_t)((j / kDqVSlots) & 1), sh)) return false;
+                tc_fence_after();
+                const uint32_t vh = v_u32 + (uint32_t)(vs * 2 * KP);
+                const uint64_t bvh = desc_kmajor(vh), bvl = desc_kmajor(vh + KP);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t ao = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32);
                     const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
                     const uint64_t dvh = desc_advance(bvh, bo), dvl = desc_advance(bvl, bo);
                     mma_ts_f16(tmem + oP, tmem + cGh + kk * 8, dvh, id_s, kk > 0);
                     mma_ts_f16(tmem + oP, tmem + cGh + kk * 8, dvl, id_s, 1);
-                    mma_ts_f16(tmem + oP, tmem + cGl + kk * 8, dvh, id_s, 1);
+                    mma_ss_f16(tmem + oP, desc_advance(bgl, ao), dvh, id_s, 1);
                 }
+                mma_commit(&sh->free_v[vs]);
                 mma_commit(&sh->sdp_full[j & 1]);
                 return true;
             };
             if (ok && !issue_sdp(0)) { dgive_up(sh, 33); ok = false; }
+            if (ok && n_tiles > 1 && !issue_sdp(1)) { dgive_up(sh, 33); ok = false; }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles && !issue_sdp(j + 1)) { dgive_up(sh, 33); break; }
                 if (!dwait(&sh->p_full[j & 1], (uint32_t)((j >> 1) & 1), sh)) { dgive_up(sh, 34); break; }
                 tc_fence_after();
-                const int s = j % NS;
-                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const int ks = j % kDqKSlots;
+                const uint32_t kh = k_u32 + (uint32_t)(ks * 2 * KP);
                 const uint64_t mkh = desc_mnmajor_16b(kh, BN * 128), mkl = desc_mnmajor_16b(kh + KP, BN * 128);
                 const uint32_t oP = cDP + (j & 1) * BN;
+                // dS: the set of keys [16 c, 16 c + 16), one MMA step deep, left its hi halves in the first
+                // 8 columns of its 16-column window and its lo halves in the last 8
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t dkh = desc_advance(mkh, kk * 2048), dkl = desc_advance(mkl, kk * 2048);
-                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 8, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 8, dkl, id_a, 1);
-                    mma_ts_f16(tmem + cDQ, tmem + oP + 16 + kk * 8, dkh, id_a, 1);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 16, dkh, id_a, (j > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 16, dkl, id_a, 1);
+                    mma_ts_f16(tmem + cDQ, tmem + oP + kk * 16 + 8, dkh, id_a, 1);
                 }
-                mma_commit(&sh->free_[s]);
+                mma_commit(&sh->free_k[ks]);
                 // completes once, when every MMA of this CTA has retired: a barrier that counted
                 // tiles could be several phases ahead of a waiting row set, and a parity wait can
                 // only tell the current phase from the one before it
                 if (j == n_tiles - 1) mma_commit(&sh->all_done);
+                if (j + 2 < n_tiles && !issue_sdp(j + 2)) { dgive_up(sh, 33); break; }
             }
         }
         __syncwarp();
     } else {
-        // two sets of four row warps; set `half` owns the tiles of its parity
-        const int tid = threadIdx.x & 127, half = threadIdx.x >> 7;
+        // ------------------------------------------------------------------ one thread per query row and
+        // 16 of the tile's keys: set `set` handles keys [16 set, 16 set + 16) of every tile
+        const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
         const int t = t0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long wq = (long long)p.n_heads * D;
         {
+            // the hi planes of the Q and dO rows -> TMEM, 16 words of each per set
             const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
-            const long long plane = (long long)B * p.T * wq;
-            if (half == 0) {
-                row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
-                row_to_tmem<W2>(p.do_planes + off, t < p.T, tmem + lane_base + cGh);
-            } else {
-                row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
-                row_to_tmem<W2>(p.do_planes + plane + off, t < p.T, tmem + lane_base + cGl);
+            if (set * 16 < W2) {
+                row_to_tmem16(p.q_planes + off + set * 32, t < p.T, tmem + lane_base + cQh + set * 16);
+                row_to_tmem16(p.do_planes + off + set * 32, t < p.T, tmem + lane_base + cGh + set * 16);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -840,67 +876,73 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const float lse2 = (t < p.T) ? __ldg(p.lse + ridx) * kLog2e : 0.f;
         const float dels = (t < p.T) ? __ldg(p.delta + ridx) * (mdo * mv * c1) : 0.f;
         bool ok = true;
-        int last = -1;  // the last tile this set handled
-        for (int j = half; j < n_tiles; j += 2) {
-            if (!__all_sync(0xffffffffu, dwait(&sh->sdp_full[half], (uint32_t)((j >> 1) & 1), sh))) {
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!__all_sync(0xffffffffu, dwait(&sh->sdp_full[j & 1], (uint32_t)((j >> 1) & 1), sh))) {
                 dgive_up(sh, 35);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            uint32_t rs[32], rd[32];
-            tmem_ld32(tmem + lane_base + cS + half * BN, rs);
-            tmem_ld32(tmem + lane_base + cDP + half * BN, rd);
+            const uint32_t wS = tmem + lane_base + cS + (j & 1) * BN + set * 16;
+            const uint32_t wP = tmem + lane_base + cDP + (j & 1) * BN + set * 16;
+            uint32_t rs[16], rd[16];
+            tmem_ld16(wS, rs);
+            tmem_ld16(wP, rd);
             tmem_wait_ld();
-            uint32_t dh[16], dl[16];
+            uint32_t dh[8], dl[8];
+            const int key0 = j * BN + set * 16;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
+            for (int i = 0; i < 16; i += 2) {
                 float dv[2];
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int key = j * BN + i + e;
+                    const int key = key0 + i + e;
                     const bool vis = (key <= t) && (key < p.T);
                     const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
                     dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
                 }
                 split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
             }
-            tmem_st16(tmem + lane_base + cDP + half * BN, dh);
-            tmem_st16(tmem + lane_base + cDP + half * BN + 16, dl);
+            tmem_st8(wP, dh);
+            tmem_st8(wP + 8, dl);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive_warp(&sh->p_full[half]);
-            last = j;
+            mbar_arrive_warp(&sh->p_full[j & 1]);
         }
-        (void)last;
         if (ok && !__all_sync(0xffffffffu, dwait(&sh->all_done, 0, sh))) {
             dgive_up(sh, 36);
             ok = false;
         }
         if (ok) {
             tc_fence_after();
+            // each set writes a quarter of the row's columns
+            constexpr int CW = D / 4;  // 32 or 16
             const float fq = p.scale / (mdo * mv * c1 * mk);
-            float *dqr = p.dq + ((long long)b * p.T + t) * wq + (long long)h * D;
-#pragma unroll 1
-            for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + cDQ + c, r);
-                tmem_wait_ld();
-                if (t < p.T) {
+            float *dqr = p.dq + ((long long)b * p.T + t) * wq + (long long)h * D + set * CW;
+            uint32_t r[32];
+            if (CW == 32) {
+                tmem_ld32(tmem + lane_base + cDQ + set * CW, r);
+            } else {
+                uint32_t r16[16];
+                tmem_ld16(tmem + lane_base + cDQ + set * CW, r16);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        float4 a;
-                        a.x = __uint_as_float(r[i]) * fq, a.y = __uint_as_float(r[i + 1]) * fq;
-                        a.z = __uint_as_float(r[i + 2]) * fq, a.w = __uint_as_float(r[i + 3]) * fq;
-                        *reinterpret_cast<float4 *>(dqr + c + i) = a;
-                    }
+                for (int i = 0; i < 16; ++i) r[i] = r16[i];
+            }
+            tmem_wait_ld();
+            if (t < p.T) {
+#pragma unroll
+                for (int i = 0; i < CW; i += 4) {
+                    float4 a;
+                    a.x = __uint_as_float(r[i]) * fq, a.y = __uint_as_float(r[i + 1]) * fq;
+                    a.z = __uint_as_float(r[i + 2]) * fq, a.w = __uint_as_float(r[i + 3]) * fq;
+                    *reinterpret_cast<float4 *>(dqr + i) = a;
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem, 512);
+    if (warp == kKvRowWarps + 1) tmem_dealloc(tmem, 512);
 }
 
 // ---- host side ----------------------------------------------------------------------------------------
@@ -939,21 +981,25 @@ inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const voi
     return d && d->cc_major == 10 && get_encode_tiled() != nullptr;
 }
 
+struct BwdMaps {
+    CUtensorMap k128, v128, q64, g64;   // dK/dV kernel: 128-key K and V tiles, 64-row Q and dO tiles
+    CUtensorMap k64, v64, q128, g128;   // dQ kernel: 64-key K and V tiles, 128-row Q and dO tiles
+};
+
 template <int D>
-inline int launch_bwd_tc_d(const CUtensorMap &k128, const CUtensorMap &v128, const CUtensorMap &q64, const CUtensorMap &g64,
-                           const CUtensorMap &k64, const CUtensorMap &v64, const BwdParams &p, cudaStream_t stream) {
-    const size_t smem_a = kv_smem_bytes<D>();
-    const size_t smem_b = kDqStages * 4 * (size_t)(32 * D * 2) + sizeof(DqShared) + 1024;
+inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t stream) {
     const size_t floor_ = 120 * 1024;  // one CTA per SM: each wants all 512 TMEM columns
-    const size_t sa = smem_a > floor_ ? smem_a : floor_, sb = smem_b > floor_ ? smem_b : floor_;
+    const size_t sa = kv_smem_bytes<D>() > floor_ ? kv_smem_bytes<D>() : floor_;
+    const size_t sb = dq_smem_bytes<D>() > floor_ ? dq_smem_bytes<D>() : floor_;
     if (optin_smem((const void *)attn_bwd_dkdv_tc<D>, sa)) return 1;
     if (optin_smem((const void *)attn_bwd_dq_tc<D>, sb)) return 1;
     const dim3 grid_a((unsigned)((p.T + 127) / 128), (unsigned)p.n_kv_heads, (unsigned)p.batch);
     const dim3 grid_b((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
     if (ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
-                  (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(k128, v128, q64, g64, p))))
+                  (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(m.k128, m.v128, m.q64, m.g64, p))))
         return 1;
-    return ZT_LAUNCH("attn_bwd_dq_tc", stream, (attn_bwd_dq_tc<D><<<grid_b, kBwdThreads, sb, stream>>>(k64, v64, p)));
+    return ZT_LAUNCH("attn_bwd_dq_tc", stream,
+                     (attn_bwd_dq_tc<D><<<grid_b, kKvThreads, sb, stream>>>(m.k64, m.v64, m.q128, m.g128, p)));
 }
 
 }  // namespace tcb
@@ -981,13 +1027,15 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     pa.t[2] = {k, w.amax_k, w.k_planes, wkv, dim};
     pa.t[3] = {v, w.amax_v, w.v_planes, wkv, dim};
     if (launch_prepass(pa, stream)) return 1;
-    CUtensorMap k128, v128, q64, g64, k64, v64;
-    if (!make_half_tile_map(&k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&v128, w.v_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||    // the dK/dV kernel's 64-row tiles
-        !make_half_tile_map(&g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
-        !make_half_tile_map(&k64, w.k_planes, 2 * batch, T, wkv, dim, 32) ||   // the dQ kernel's 32-key tiles
-        !make_half_tile_map(&v64, w.v_planes, 2 * batch, T, wkv, dim, 32))
+    BwdMaps m;
+    if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
+        !make_half_tile_map(&m.v128, w.v_planes, 2 * batch, T, wkv, dim, 128) ||
+        !make_half_tile_map(&m.q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||
+        !make_half_tile_map(&m.g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
+        !make_half_tile_map(&m.k64, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
+        !make_half_tile_map(&m.v64, w.v_planes, 2 * batch, T, wkv, dim, 64) ||
+        !make_half_tile_map(&m.q128, w.q_planes, 2 * batch, T, wq, dim, 128) ||
+        !make_half_tile_map(&m.g128, w.do_planes, 2 * batch, T, wq, dim, 128))
         return refuse("the TMA tensor maps for the backward could not be encoded.");
     BwdParams p{};
     p.lse = lse, p.delta = delta;
@@ -1004,8 +1052,7 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
         p.c1 = ldexpf(1.0f, boost - 16 - (dim == 128 ? 7 : 6));
     }
     g_last_path = "tcgen05";
-    return dim == 64 ? launch_bwd_tc_d<64>(k128, v128, q64, g64, k64, v64, p, stream)
-                     : launch_bwd_tc_d<128>(k128, v128, q64, g64, k64, v64, p, stream);
+    return dim == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
 }
 
 }  // namespace zt

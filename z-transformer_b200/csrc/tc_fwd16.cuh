@@ -28,15 +28,16 @@ using tcb::block_mult;
 using tcb::row_to_tmem;
 using tcb::split_pack;
 
-constexpr int kThreads = 192;  // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int kThreads = 320;  // 8 softmax warps (two sets of four), 1 TMA warp, 1 MMA warp
 constexpr float kPScale = 128.0f;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Shared {
-    uint64_t full[3], free_[3];
-    uint64_t a_ready, s_full[2], p_full[2], pv_done, all_done;
+    uint64_t full_k[3], free_k[3], full_v[3], free_v[3];
+    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], all_done;
     uint32_t tmem_base;
     volatile int abort;
+    float fin_m[2][128], fin_l[2][128];  // each set's reference maximum and sum, for the final merge
 };
 
 struct Params {
@@ -64,10 +65,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     attn_fwd_tc16(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
     constexpr int NB = D / 64, W2 = D / 2, BN = 64;
     constexpr int KP = BN * D * 2;  // bytes of one plane of a key tile
-    constexpr int cQh = 0, cQl = W2, cO = D, cS0 = 2 * D;
+    constexpr int cQh = 0, cQl = W2, cO0 = D, cS0 = 3 * D;  // O of set s at cO0 + s D, S/P of buffer i at cS0 + 64 i
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Shared *sh = reinterpret_cast<Shared *>(smem + 12 * KP);  // 3 stages x (Kh, Kl, Vh, Vl)
+    uint8_t *sK = smem, *sV = smem + 6 * KP;  // three slots of (hi, lo) each
+    Shared *sh = reinterpret_cast<Shared *>(smem + 12 * KP);
 
     const int warp = threadIdx.x >> 5;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
@@ -79,15 +81,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int B = p.batch;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 3; ++i) mbar_init(&sh->full[i], 1), mbar_init(&sh->free_[i], 1);
-        mbar_init(&sh->a_ready, 4);
-        for (int i = 0; i < 2; ++i) mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 4);
-        mbar_init(&sh->pv_done, 1);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
+            mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
+        }
+        mbar_init(&sh->a_ready, 8);
+        for (int i = 0; i < 2; ++i) mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 4), mbar_init(&sh->pv_done[i], 1);
         mbar_init(&sh->all_done, 1);
         sh->abort = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -96,40 +100,49 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
+        // K of tile j is free again once S(j) has retired, two tiles before its V: rings of their own
         if (elect_one()) {
             tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
-            int issued = 0;
+            int issued = 0;  // half-steps: K of tile issued / 2, then its V
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % 3;
-                if (j >= 3 && !fwait(&sh->free_[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { fgive_up(sh, 41); break; }
-                uint8_t *st = smem + s * 4 * KP;
-                mbar_arrive_expect_tx(&sh->full[s], 4 * KP);
-                tma_load_4d(st, &kmap, &sh->full[s], 0, j * BN, g * NB, b);
-                tma_load_4d(st + KP, &kmap, &sh->full[s], 0, j * BN, g * NB, B + b);
-                tma_load_4d(st + 2 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, b);
-                tma_load_4d(st + 3 * KP, &vmap, &sh->full[s], 0, j * BN, g * NB, B + b);
+                const uint32_t free_par = (uint32_t)(((j / 3) & 1) ^ 1);
+                if (j >= 3 && !fwait(&sh->free_k[s], free_par, sh)) { fgive_up(sh, 41); break; }
+                mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
+                tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
+                tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
+                ++issued;
+                if (j >= 3 && !fwait(&sh->free_v[s], free_par, sh)) { fgive_up(sh, 41); break; }
+                mbar_arrive_expect_tx(&sh->full_v[s], 2 * KP);
+                tma_load_4d(sV + s * 2 * KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, b);
+                tma_load_4d(sV + s * 2 * KP + KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, B + b);
                 ++issued;
             }
-            if (sh->abort)
-                for (int j = (issued > 3 ? issued - 3 : 0); j < issued; ++j)
-                    mbar_wait(&sh->full[j % 3], (uint32_t)((j / 3) & 1));
+            if (sh->abort) {
+                // let the copies in flight land before the CTA's shared memory goes away
+                const int n_k = (issued + 1) / 2, n_v = issued / 2;
+                for (int j = (n_k > 3 ? n_k - 3 : 0); j < n_k; ++j) mbar_wait(&sh->full_k[j % 3], (uint32_t)((j / 3) & 1));
+                for (int j = (n_v > 3 ? n_v - 3 : 0); j < n_v; ++j) mbar_wait(&sh->full_v[j % 3], (uint32_t)((j / 3) & 1));
+            }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
             constexpr uint32_t id_o = idesc_f16(128, D, false, true);
             bool ok = fwait(&sh->a_ready, 0, sh);
             if (!ok) fgive_up(sh, 42);
+            tc_fence_after();
+            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
             // S of tile j into buffer j & 1
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % 3;
-                if (!fwait(&sh->full[s], (uint32_t)((j / 3) & 1), sh)) return false;
+                if (!fwait(&sh->full_k[s], (uint32_t)((j / 3) & 1), sh)) return false;
                 tc_fence_after();
-                const uint32_t kh = smem_u32(smem + s * 4 * KP);
+                const uint32_t kh = k_u32 + (uint32_t)(s * 2 * KP);
                 const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
                 const uint32_t cS = cS0 + (j & 1) * BN;
 #pragma unroll
@@ -140,56 +153,61 @@ __global__ void __launch_bounds__(kThreads, 1)
                     mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
                     mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
                 }
+                mma_commit(&sh->free_k[s]);
                 mma_commit(&sh->s_full[j & 1]);
                 return true;
             };
             if (ok && !issue_qk(0)) { fgive_up(sh, 43); ok = false; }
+            if (ok && n_tiles > 1 && !issue_qk(1)) { fgive_up(sh, 43); ok = false; }
             for (int j = 0; ok && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles && !issue_qk(j + 1)) { fgive_up(sh, 43); break; }
-                if (!fwait(&sh->p_full[j & 1], (uint32_t)((j >> 1) & 1), sh)) { fgive_up(sh, 44); break; }
+                const int s = j % 3, set = j & 1;
+                if (!fwait(&sh->p_full[set], (uint32_t)((j >> 1) & 1), sh) ||
+                    !fwait(&sh->full_v[s], (uint32_t)((j / 3) & 1), sh)) { fgive_up(sh, 44); break; }
                 tc_fence_after();
-                const int s = j % 3;
-                const uint32_t vh = smem_u32(smem + s * 4 * KP + 2 * KP);
+                const uint32_t vh = v_u32 + (uint32_t)(s * 2 * KP);
                 const uint64_t mvh = desc_mnmajor_16b(vh, BN * 128), mvl = desc_mnmajor_16b(vh + KP, BN * 128);
-                const uint32_t cS = cS0 + (j & 1) * BN;
+                const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
                     const uint64_t dvh = desc_advance(mvh, kk * 2048), dvl = desc_advance(mvl, kk * 2048);
-                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 0 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 1 || kk > 0) ? 1 : 0);
                     mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
                     mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
                 }
-                mma_commit(&sh->free_[s]);
-                mma_commit(&sh->pv_done);
-                // completes once, after the last P.V: pv_done counts tiles and may be two phases ahead
-                // of a row thread by the time it gets here, which a parity wait cannot tell apart
+                mma_commit(&sh->free_v[s]);
+                mma_commit(&sh->pv_done[set]);
+                // completes once, after the last P.V: a barrier that counts tiles may be two phases ahead
+                // of a row thread by the time it gets there, which a parity wait cannot tell apart
                 if (j == n_tiles - 1) mma_commit(&sh->all_done);
+                // S(j+2) overwrites the P tile this P.V has just read
+                if (j + 2 < n_tiles && !issue_qk(j + 2)) { fgive_up(sh, 43); break; }
             }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------ softmax rows
-        const int tid = threadIdx.x;
+        // ------------------------------------------------------------------ softmax rows: set `set` owns
+        // the key tiles of its parity, with a reference maximum, a sum and an O accumulator of its own;
+        // the two partial softmaxes are merged at the end.  Nothing a set does waits on the other's tile.
+        const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
         const int t = t0 + tid;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long wq = (long long)p.n_heads * D;
         {
             const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
             const long long plane = (long long)B * p.T * wq;
-            row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
-            row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
+            if (set == 0) row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
+            else row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(&sh->a_ready);
         }
         const float cs = p.scale_log2 / (mq * mk);
+        const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int buf = j & 1;
-            const uint32_t cS = cS0 + buf * BN;
-            if (!__all_sync(0xffffffffu, fwait(&sh->s_full[buf], (uint32_t)((j >> 1) & 1), sh))) {
+        for (int j = set; j < n_tiles; j += 2) {
+            if (!__all_sync(0xffffffffu, fwait(&sh->s_full[set], (uint32_t)((j >> 1) & 1), sh))) {
                 fgive_up(sh, 45);
                 ok = false;
                 break;
@@ -197,26 +215,26 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             const int s0 = j * BN;
             const bool diag = (s0 + BN - 1 > t0);
+            uint32_t r0[32], r1[32];
+            tmem_ld32(tmem + lane_base + cS, r0);
+            tmem_ld32(tmem + lane_base + cS + 32, r1);
+            tmem_wait_ld();
             float mt = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + cS + c, r);
-                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (!diag || s0 + c + i <= t) mt = fmaxf(mt, __uint_as_float(r[i]) * cs);
+            for (int i = 0; i < 32; ++i) {
+                if (!diag || s0 + i <= t) mt = fmaxf(mt, __uint_as_float(r0[i]));
+                if (!diag || s0 + 32 + i <= t) mt = fmaxf(mt, __uint_as_float(r1[i]));
             }
+            mt *= cs;  // cs > 0
             float factor = 1.f;
             if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
                 factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
                 m_ref = mt;
             }
             l *= factor;
-            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-                // O may only be touched once P.V of tile j-1 has retired (S of tile j being complete
-                // implies only that tile j-2's has)
-                if (!__all_sync(0xffffffffu, fwait(&sh->pv_done, (uint32_t)((j - 1) & 1), sh))) {
+            if (j > 1 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // this set's O may only be touched once its previous P.V (tile j-2) has retired
+                if (!__all_sync(0xffffffffu, fwait(&sh->pv_done[set], (uint32_t)(((j >> 1) - 1) & 1), sh))) {
                     fgive_up(sh, 46);
                     ok = false;
                     break;
@@ -234,59 +252,86 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
             float psum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32], ph[16], pl[16];
-                tmem_ld32(tmem + lane_base + cS + c, r);
-                tmem_wait_ld();
+            {
+                uint32_t ph[16], pl[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float pe[2];
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        pe[e] = ex2(__uint_as_float(r[i + e]) * cs - mref_safe);
-                        if (diag && s0 + c + i + e > t) pe[e] = 0.f;
+                        pe[e] = ex2(__uint_as_float(r0[i + e]) * cs - mref_safe);
+                        if (diag && s0 + i + e > t) pe[e] = 0.f;
                         psum += pe[e];
                     }
                     split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
                 }
-                tmem_st16(tmem + lane_base + cS + c, ph);
-                tmem_st16(tmem + lane_base + cS + c + 16, pl);
+                tmem_st16(tmem + lane_base + cS, ph);
+                tmem_st16(tmem + lane_base + cS + 16, pl);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pe[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        pe[e] = ex2(__uint_as_float(r1[i + e]) * cs - mref_safe);
+                        if (diag && s0 + 32 + i + e > t) pe[e] = 0.f;
+                        psum += pe[e];
+                    }
+                    split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
+                }
+                tmem_st16(tmem + lane_base + cS + 32, ph);
+                tmem_st16(tmem + lane_base + cS + 48, pl);
             }
             l += psum;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive_warp(&sh->p_full[buf]);
+            mbar_arrive_warp(&sh->p_full[set]);
         }
+        // ---- merge the two partial softmaxes
+        sh->fin_m[set][tid] = m_ref;
+        sh->fin_l[set][tid] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the 256 softmax threads
         if (ok && !__all_sync(0xffffffffu, fwait(&sh->all_done, 0, sh))) {
             fgive_up(sh, 48);
             ok = false;
         }
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / (l * kPScale * mv);
-            float *orow = p.out + ((long long)b * p.T + t) * wq + (long long)h * D;
+            const bool two = n_tiles > 1;  // set 1 has an accumulator only then
+            const float m0 = sh->fin_m[0][tid], l0 = sh->fin_l[0][tid];
+            const float m1 = two ? sh->fin_m[1][tid] : -INFINITY, l1 = two ? sh->fin_l[1][tid] : 0.f;
+            const float mm = fmaxf(m0, m1);  // m0 is finite: key 0 is visible to every row
+            const float w0 = ex2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
+            const float lsum = w0 * l0 + w1 * l1;
+            const float inv = 1.f / (lsum * kPScale * mv);
+            const float f0 = w0 * inv, f1 = w1 * inv;
+            // set s writes columns [s D/2, (s+1) D/2) of the row
+            float *orow = p.out + ((long long)b * p.T + t) * wq + (long long)h * D + set * (D / 2);
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + cO + c, r);
+            for (int c = 0; c < D / 2; c += 32) {
+                uint32_t ra[32], rb[32];
+                tmem_ld32(tmem + lane_base + cO0 + set * (D / 2) + c, ra);
+                if (two) tmem_ld32(tmem + lane_base + cO0 + D + set * (D / 2) + c, rb);
                 tmem_wait_ld();
                 if (t < p.T) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         float4 o4;
-                        o4.x = __uint_as_float(r[i]) * inv, o4.y = __uint_as_float(r[i + 1]) * inv;
-                        o4.z = __uint_as_float(r[i + 2]) * inv, o4.w = __uint_as_float(r[i + 3]) * inv;
+                        o4.x = __uint_as_float(ra[i]) * f0, o4.y = __uint_as_float(ra[i + 1]) * f0;
+                        o4.z = __uint_as_float(ra[i + 2]) * f0, o4.w = __uint_as_float(ra[i + 3]) * f0;
+                        if (two && w1 != 0.f) {
+                            o4.x += __uint_as_float(rb[i]) * f1, o4.y += __uint_as_float(rb[i + 1]) * f1;
+                            o4.z += __uint_as_float(rb[i + 2]) * f1, o4.w += __uint_as_float(rb[i + 3]) * f1;
+                        }
                         *reinterpret_cast<float4 *>(orow + c + i) = o4;
                     }
                 }
             }
-            if (p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (m_ref + log2f(l)) * kLn2;
+            if (set == 0 && p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum)) * kLn2;
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, 512);
+    if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 struct Workspace {
