@@ -513,3 +513,24 @@ def test_tensor_core_backward_uneven_magnitudes(zt, dev, oracle):
         for kv in range(Hkv):
             a, r = got[:, kv * w:(kv + 1) * w].astype(np.float64), ref[:, kv * w:(kv + 1) * w].astype(np.float64)
             assert np.max(np.abs(a - r)) <= 1e-4 * np.max(np.abs(r)), (name, kv)
+
+
+def test_attn_pipeline_matches_batched_calls(zt, dev):
+    """AttnPipeline (copies and kernels of consecutive sequences overlapped on three streams, two buffer
+    slots) returns exactly what the batched entry points return for the same sequences: more sequences
+    than slots, so every slot is reused."""
+    B, T, H, Hkv, D = 5, 256, 8, 2, 64
+    g = torch.Generator().manual_seed(77)
+    hq, hdo = (torch.randn((B, T, H * D), generator=g).pin_memory() for _ in range(2))
+    hk, hv = (torch.randn((B, T, Hkv * D), generator=g).pin_memory() for _ in range(2))
+    hout, hdq = (torch.full((B, T, H * D), float("nan")).pin_memory() for _ in range(2))
+    hdk, hdv = (torch.full((B, T, Hkv * D), float("nan")).pin_memory() for _ in range(2))
+    hlse = torch.full((B, T, H), float("nan")).pin_memory()
+    pipe = zt.AttnPipeline(T, H, Hkv, D, slots=2, device=dev)
+    for _ in range(2):  # a second step reuses the slots' events
+        pipe.step(hq, hk, hv, hdo, hout, hdq, hdk, hdv, hlse)
+    q, k, v, do = (x.to(dev) for x in (hq, hk, hv, hdo))
+    out, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(q, k, v, out, lse, do, H, Hkv, D)
+    for name, got, want in (("out", hout, out), ("lse", hlse, lse), ("dq", hdq, dq), ("dk", hdk, dk), ("dv", hdv, dv)):
+        assert torch.equal(got, want.cpu()), name

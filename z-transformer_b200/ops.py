@@ -144,3 +144,103 @@ def decode_attention(q, k_cache, v_cache, n_keys, n_heads, n_kv_heads, head_dim,
     if rc != 0:
         raise ConfigRefused(_lib.last_error())
     return (out, lse) if want_lse else out
+
+
+class AttnPipeline:
+    """Forward + backward of a run of equally shaped sequences whose tensors live in host memory.
+
+    The reference's trainer drives device.Attn one sequence at a time: upload q, k, v (and dout),
+    launch, download (src/model.zig:481-514), each step waiting for the one before.  On a PCIe
+    link the copies take longer than the kernels, so this class runs the three stages on streams
+    of their own over `slots` sets of device buffers: while sequence b is in the kernels, b+1 is
+    on its way up and b-1 on its way down.  It calls the batched entry points (batch 1), which
+    take the forward's out and log-sum-exp, so nothing is recomputed in the backward.
+
+    Host tensors must be pinned for the copies to overlap; results are complete when step()
+    returns.
+    """
+
+    def __init__(self, t, n_heads, n_kv_heads, head_dim, slots=2, device="cuda"):
+        import torch
+        _head_config(n_heads, n_kv_heads, head_dim)
+        if slots < 1:
+            raise DimensionMismatch("slots must be at least 1")
+        self.shape = (t, n_heads, n_kv_heads, head_dim)
+        self.device = torch.device(device)
+        self.slots = slots
+        L = _lib.load()
+        self.ws_bytes = int(L.zt_attn_backward_workspace_bytes(1, t, n_heads, n_kv_heads, head_dim))
+        wq, wkv = n_heads * head_dim, n_kv_heads * head_dim
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.buf = []
+        for _ in range(slots):
+            b = {name: torch.empty((t, wq), **f32) for name in ("q", "dout", "out", "dq")}
+            b.update({name: torch.empty((t, wkv), **f32) for name in ("k", "v", "dk", "dv")})
+            b["lse"] = torch.empty((t, n_heads), **f32)
+            b["delta"] = torch.empty((t, n_heads), **f32)
+            b["ws"] = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device=self.device)
+            self.buf.append(b)
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self.ready = [torch.cuda.Event() for _ in range(slots)]   # inputs of the slot are on the device
+        self.done = [torch.cuda.Event() for _ in range(slots)]    # kernels of the slot have finished
+        self.free = [torch.cuda.Event() for _ in range(slots)]    # outputs of the slot are on the host
+
+    def step(self, q, k, v, dout, out, dq, dk, dv, lse=None):
+        """q, dout, out, dq: host [B, T, H*D]; k, v, dk, dv: host [B, T, Hkv*D]; lse: host [B, T, H] or
+        None.  Reads q, k, v, dout and fills out, dq, dk, dv (and lse)."""
+        import torch
+        t, n_heads, n_kv_heads, head_dim = self.shape
+        B = q.shape[0]
+        wq, wkv = n_heads * head_dim, n_kv_heads * head_dim
+        for x, w in ((q, wq), (dout, wq), (out, wq), (dq, wq), (k, wkv), (v, wkv), (dk, wkv), (dv, wkv)):
+            if x.is_cuda or x.dtype != torch.float32 or tuple(x.shape) != (B, t, w) or not x.is_contiguous():
+                raise DimensionMismatch("host tensors must be contiguous float32 [B, T, width]")
+        if lse is not None and tuple(lse.shape) != (B, t, n_heads):
+            raise DimensionMismatch("lse must be [B, T, H]")
+        L = _lib.load()
+        start = torch.cuda.Event()
+        start.record(torch.cuda.current_stream(self.device))
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_event(start)
+        with torch.cuda.device(self.device):
+            for b in range(B):
+                sl = b % self.slots
+                d = self.buf[sl]
+                with torch.cuda.stream(self.s_in):
+                    if b >= self.slots:
+                        self.s_in.wait_event(self.done[sl])  # the slot's inputs have been consumed
+                    d["q"].copy_(q[b], non_blocking=True)
+                    d["k"].copy_(k[b], non_blocking=True)
+                    d["v"].copy_(v[b], non_blocking=True)
+                    d["dout"].copy_(dout[b], non_blocking=True)
+                    self.ready[sl].record(self.s_in)
+                with torch.cuda.stream(self.s_run):
+                    self.s_run.wait_event(self.ready[sl])
+                    if b >= self.slots:
+                        self.s_run.wait_event(self.free[sl])  # the slot's outputs have been read
+                    st = self.s_run.cuda_stream
+                    rc = L.zt_attn_forward_batched(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+                                                   d["out"].data_ptr(), d["lse"].data_ptr(), 1, t, n_heads,
+                                                   n_kv_heads, head_dim, st)
+                    if rc == 0:
+                        rc = L.zt_attn_backward_batched(
+                            d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["out"].data_ptr(),
+                            d["lse"].data_ptr(), d["dout"].data_ptr(), d["dq"].data_ptr(), d["dk"].data_ptr(),
+                            d["dv"].data_ptr(), d["delta"].data_ptr(),
+                            d["ws"].data_ptr() if self.ws_bytes else None, self.ws_bytes, 1, t, n_heads,
+                            n_kv_heads, head_dim, st)
+                    if rc != 0:
+                        torch.cuda.synchronize(self.device)
+                        raise ConfigRefused(_lib.last_error())
+                    self.done[sl].record(self.s_run)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(self.done[sl])
+                    out[b].copy_(d["out"], non_blocking=True)
+                    dq[b].copy_(d["dq"], non_blocking=True)
+                    dk[b].copy_(d["dk"], non_blocking=True)
+                    dv[b].copy_(d["dv"], non_blocking=True)
+                    if lse is not None:
+                        lse[b].copy_(d["lse"], non_blocking=True)
+                    self.free[sl].record(self.s_out)
+        self.s_out.synchronize()
+        self.s_run.synchronize()
