@@ -17,14 +17,17 @@
 //
 // Kernels:
 //   bwd_absmax / bwd_split   per-(sequence, KV group) max |x| of q, k, v, dout; then the h and l
-//                            planes of each tensor ([2][B][T][W] halves) in the workspace.
+//                            planes of each tensor ([2][B][T][W] halves) in the workspace.  One
+//                            launch of each for all tensors.
 //   attn_bwd_dkdv_tc         one CTA per (128 keys, KV head, sequence): S^T = K Q^T and
 //                            dP^T = V dO^T per 64-row query tile of every head of the group,
 //                            P^T and dS^T written back to TMEM as packed halves,
 //                            dV += P^T dO and dK += dS^T Q accumulated in TMEM for the whole walk:
 //                            dk/dv are assigned by their one owner, no atomics.
 //   attn_bwd_dq_tc           one CTA per (128 query rows, head, sequence): S = Q K^T, dP = dO V^T,
-//                            dS, dQ += dS K over the causal key tiles; dq assigned.
+//                            dS, dQ += dS K over the causal key tiles of 64; dq assigned.
+// Both kernels issue S (and dP) one or two tiles ahead into TMEM buffers of their own and spread
+// the row work of a tile over four warp sets; see the comment above each.
 // Every wait is bounded (see tc_common.cuh); a wait that gives up raises g_tc_status.
 #pragma once
 

@@ -2,20 +2,24 @@
 // (the arithmetic of tc_bwd.cuh) and a two-deep pipeline over the key tiles.
 //
 // Same result as attn_fwd_tc (tc_fwd.cuh, 3xTF32) and the same role -- attention.forward
-// (src/attention.zig:60-153) for a batch plus each row's log-sum-exp -- at roughly twice the
-// speed: an f16 term is half a TF32 MMA, operands take half the bytes (so a key tile of both K
-// and V, hi and lo, fits three times in shared memory), and two S tiles fit in TMEM, so the
-// softmax of tile j runs while the tensor core computes S of tile j+1 and P.V of tile j-1.
+// (src/attention.zig:60-153) for a batch plus each row's log-sum-exp -- at 2.4 times the speed:
+// an f16 term is half a TF32 MMA, operands take half the bytes (three K and three V tiles, hi and
+// lo, fit in shared memory), and two S tiles and two O accumulators fit in TMEM.
 //
 //   bwd_absmax / bwd_split   (tc_bwd.cuh) q, k, v -> f16 hi/lo planes with a power-of-two scale
 //                            per (sequence, KV group), in a workspace.
-//   TMA warp        K and V hi/lo tiles of 64 keys, three stages.
-//   MMA warp        S[j+1] = Qh.Kh + Qh.Kl + Ql.Kh  (A = Q from TMEM), then, once P[j] is in TMEM,
-//                   O += Ph.Vh + Ph.Vl + Pl.Vh      (A = P from TMEM, V tile as MN-major B).
-//   softmax warps   one thread per query row, as in the TF32 kernel: lazy reference maximum
-//                   (moved only when it grows by > 2^8), P scaled by 2^7 and split into packed
-//                   f16 pairs written over S.
-// TMEM columns: [0,D/2) Qh, [D/2,D) Ql, [D,2D) O, then two S/P tiles of 64 columns.
+//   TMA warp        K and V hi/lo tiles of 64 keys, a ring of three slots each: a K tile is free
+//                   once its S has retired, two tiles before its V.
+//   MMA warp        S[j+2] = Qh.Kh + Qh.Kl + Ql.Kh  (A = Q from TMEM) into buffer j & 1 as soon as
+//                   P.V of tile j has been issued; once P[j] is in TMEM,
+//                   O[j & 1] += Ph.Vh + Ph.Vl + Pl.Vh   (A = P from TMEM, V tile as MN-major B).
+//   softmax warps   two sets of four, one thread per query row; set j & 1 owns tile j, with a
+//                   reference maximum (moved only when it grows by > 2^8), a sum and an O accumulator
+//                   of its own, so neither set waits on the other's tile.  P is scaled by 2^7 and
+//                   split into packed f16 pairs written over S.  The two partial softmaxes are merged
+//                   when the row is written.
+// TMEM columns: [0,D/2) Qh, [D/2,D) Ql, [D,2D) O of set 0, [2D,3D) O of set 1, then two S/P tiles of
+// 64 columns.
 #pragma once
 
 #include "tc_bwd.cuh"
