@@ -397,8 +397,8 @@ TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, sev
 @pytest.mark.parametrize("path", [0, 2], ids=["f16split", "3xtf32"])
 @pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
 def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, path):
-    """Both tensor-core forwards: the pipelined f16-split kernel (path 0, head_dim 64/128) and the
-    3xTF32 kernel (path 2, and head_dim 32 always)."""
+    """Both tensor-core forwards: the pipelined f16-split kernel (path 0; head_dim 32 zero-padded to its
+    64-wide tiles) and the 3xTF32 kernel (path 2)."""
     q = oracle.fill_normal((B, T, H * D), 51, 0)
     k = oracle.fill_normal((B, T, Hkv * D), 51, 1)
     v = oracle.fill_normal((B, T, Hkv * D), 51, 2)
@@ -463,6 +463,8 @@ TC_BWD_SHAPES = [  # B, T, H, Hkv, D
     # a last key tile with a single query tile: every step of its walk is a flush, handed between the two
     # row-warp sets (a hand-off that once raced)
     (1, 150, 8, 4, 64), (1, 160, 16, 4, 64), (1, 150, 8, 4, 128), (3, 133, 8, 8, 64),
+    # head_dim 32 on the 64-wide tiles (heads zero-padded in the operand planes, outputs 32 wide)
+    (1, 128, 4, 2, 32), (2, 200, 8, 2, 32), (1, 384, 4, 1, 32), (1, 513, 6, 6, 32),
 ]
 
 

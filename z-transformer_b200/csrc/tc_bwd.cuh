@@ -66,8 +66,9 @@ __host__ __device__ inline float block_mult(uint32_t bits) {
 struct PrepassTensor {
     const float *x;
     uint32_t *amax;   // [batch][width / cols_per_group] bit patterns of max |x|, zeroed by the caller
-    __half *planes;   // [2][batch][T][width]
+    __half *planes;   // [2][batch][T][width / src_head * dst_head]
     int width, cols_per_group;
+    int src_head, dst_head;  // a head's columns in x and in the planes: 32 -> 64 pads each head with zeros
 };
 struct PrepassArgs {
     PrepassTensor t[4];
@@ -107,7 +108,43 @@ constexpr int kSplitPerCta = 2048;
 __global__ void __launch_bounds__(256) bwd_split_kernel(const PrepassArgs a) {
     const PrepassTensor t = a.t[blockIdx.z];
     const int b = blockIdx.y;
-    const int w4 = t.width / 4, n_groups = t.width / t.cols_per_group;
+    const int n_groups = t.width / t.cols_per_group;
+    if (t.src_head != t.dst_head) {
+        // zero-padded heads: walk the planes' float4s, fetch the source's where there is one
+        const int w4s = t.width / 4, w4d = t.width / t.src_head * t.dst_head / 4;
+        const long long seq4d = (long long)a.T * w4d;
+        const long long first = (long long)blockIdx.x * kSplitPerCta;
+        if (first >= seq4d) return;
+        const float4 *src = reinterpret_cast<const float4 *>(t.x) + (long long)b * a.T * w4s;
+        uint2 *hp = reinterpret_cast<uint2 *>(t.planes) + b * seq4d;
+        uint2 *lp = hp + (long long)a.batch * seq4d;
+        const uint32_t *amax = t.amax + b * n_groups;
+#pragma unroll
+        for (int k = 0; k < kSplitPerCta / 256; ++k) {
+            const long long i = first + k * 256 + threadIdx.x;
+            if (i >= seq4d) break;
+            const int r = (int)(i / w4d);
+            const int cd = (int)(i - (long long)r * w4d) * 4;      // column in the planes
+            const int head = cd / t.dst_head, within = cd - head * t.dst_head;
+            uint2 hw = make_uint2(0u, 0u), lw = make_uint2(0u, 0u);
+            if (within < t.src_head) {
+                const int cs = head * t.src_head + within;          // column in x
+                const float m = block_mult(amax[cs / t.cols_per_group]);
+                const float4 v = __ldg(src + (long long)r * w4s + cs / 4);
+                const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
+                __half h[4], l[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    h[e] = __float2half_rn(s[e]);
+                    l[e] = __float2half_rn(s[e] - __half2float(h[e]));
+                }
+                hw = *reinterpret_cast<const uint2 *>(h), lw = *reinterpret_cast<const uint2 *>(l);
+            }
+            hp[i] = hw, lp[i] = lw;
+        }
+        return;
+    }
+    const int w4 = t.width / 4;
     const long long seq4 = (long long)a.T * w4;  // float4 per sequence
     const long long first = (long long)blockIdx.x * kSplitPerCta;
     if (first >= seq4) return;
@@ -138,8 +175,13 @@ __global__ void __launch_bounds__(256) bwd_split_kernel(const PrepassArgs a) {
 
 // Both passes for the tensors in `a` (amax already zeroed).
 inline int launch_prepass(const PrepassArgs &a, cudaStream_t stream) {
-    int wmax = 0;
-    for (int i = 0; i < a.n; ++i) wmax = a.t[i].width > wmax ? a.t[i].width : wmax;
+    int wmax = 0, wmax_src = 0;
+    for (int i = 0; i < a.n; ++i) {
+        const int wd = a.t[i].width / a.t[i].src_head * a.t[i].dst_head;
+        wmax = wd > wmax ? wd : wmax;
+        wmax_src = a.t[i].width > wmax_src ? a.t[i].width : wmax_src;
+    }
+    (void)wmax_src;
     const dim3 ga((unsigned)((a.T + kPrepassRows - 1) / kPrepassRows), (unsigned)a.batch, (unsigned)a.n);
     if (ZT_LAUNCH("bwd_absmax_kernel", stream, (bwd_absmax_kernel<<<ga, 256, 0, stream>>>(a)))) return 1;
     const long long seq4 = (long long)a.T * (wmax / 4);
@@ -172,6 +214,7 @@ struct BwdParams {
     const uint32_t *amax_q, *amax_k, *amax_v, *amax_do;  // [B, Hkv] bit patterns of max |x|
     float *dq, *dk, *dv;
     int batch, T, n_heads, n_kv_heads;
+    int dim_out;     // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
     float scale, scale_log2;
     float p_scale;  // P is multiplied by this power of two before its 16-bit split
     float c1;       // dP (in scaled units) is multiplied by this power of two before dS is split
@@ -641,14 +684,15 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's
                 const int c0 = (set & 1) * (D / 2);
                 const uint32_t acc = tmem + lane_base + (set < 2 ? cDV : cDK) + c0;
-                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + key) * wkv + (long long)g * D + c0;
+                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + key) * ((long long)p.n_kv_heads * p.dim_out) +
+                             (long long)g * p.dim_out + c0;
                 const float f = set < 2 ? 1.0f / (p.p_scale * mdo) : p.scale / (mdo * mv * c1 * mq);
 #pragma unroll 1
                 for (int c = 0; c < D / 2; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(acc + c, r);
                     tmem_wait_ld();
-                    if (key < p.T) {
+                    if (key < p.T && c0 + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float4 a;
@@ -921,7 +965,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             // each set writes a quarter of the row's columns
             constexpr int CW = D / 4;  // 32 or 16
             const float fq = p.scale / (mdo * mv * c1 * mk);
-            float *dqr = p.dq + ((long long)b * p.T + t) * wq + (long long)h * D + set * CW;
+            float *dqr = p.dq + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + set * CW;
             uint32_t r[32];
             if (CW == 32) {
                 tmem_ld32(tmem + lane_base + cDQ + set * CW, r);
@@ -932,7 +976,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 for (int i = 0; i < 16; ++i) r[i] = r16[i];
             }
             tmem_wait_ld();
-            if (t < p.T) {
+            if (t < p.T && set * CW < p.dim_out) {
 #pragma unroll
                 for (int i = 0; i < CW; i += 4) {
                     float4 a;
@@ -977,7 +1021,7 @@ inline BwdWorkspace bwd_workspace(void *base, int batch, int T, int n_heads, int
 
 inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const void *k, const void *v,
                              const void *dout, const void *dq, const void *dk, const void *dv) {
-    if (!(dim == 64 || dim == 128) || T < 128 || batch < 1) return false;
+    if (!(dim == 32 || dim == 64 || dim == 128) || T < 128 || batch < 1) return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(q) || !al(k) || !al(v) || !al(dout) || !al(dq) || !al(dk) || !al(dv)) return false;
     const DeviceInfo *d = device_info();
@@ -1007,8 +1051,12 @@ inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t st
 
 }  // namespace tcb
 
+// head_dim 32 runs on the 64-wide tiles: its planes carry every head zero-padded to 64 columns (the
+// MMAs would cost the same at half the width, see the clock floor above), outputs keep their 32.
+inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : dim; }
+
 inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
-    return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
+    return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).total_bytes;
 }
 
 // delta must already hold sum_j dout*out.  dq, dk, dv are assigned.
@@ -1016,29 +1064,31 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
                          const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
                          int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
     using namespace tcb;
-    const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, dim);
+    const int td = tc_tile_dim(dim);  // the kernels' D; the planes' head width
+    const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, td);
     const int group = n_heads / n_kv_heads;
-    const int wq = n_heads * dim, wkv = n_kv_heads * dim;
+    const int wq_src = n_heads * dim, wkv_src = n_kv_heads * dim;
+    const int wq = n_heads * td, wkv = n_kv_heads * td;
     if (cudaMemsetAsync(w.amax_q, 0, w.amax_bytes, stream) != cudaSuccess) {
         cudaGetLastError();
         return refuse("could not clear the backward workspace header");
     }
     PrepassArgs pa{};
     pa.n = 4, pa.batch = batch, pa.T = T;
-    pa.t[0] = {q, w.amax_q, w.q_planes, wq, group * dim};
-    pa.t[1] = {dout, w.amax_do, w.do_planes, wq, group * dim};
-    pa.t[2] = {k, w.amax_k, w.k_planes, wkv, dim};
-    pa.t[3] = {v, w.amax_v, w.v_planes, wkv, dim};
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td};
+    pa.t[1] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td};
+    pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td};
+    pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td};
     if (launch_prepass(pa, stream)) return 1;
     BwdMaps m;
-    if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&m.v128, w.v_planes, 2 * batch, T, wkv, dim, 128) ||
-        !make_half_tile_map(&m.q64, w.q_planes, 2 * batch, T, wq, dim, 64) ||
-        !make_half_tile_map(&m.g64, w.do_planes, 2 * batch, T, wq, dim, 64) ||
-        !make_half_tile_map(&m.k64, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
-        !make_half_tile_map(&m.v64, w.v_planes, 2 * batch, T, wkv, dim, 64) ||
-        !make_half_tile_map(&m.q128, w.q_planes, 2 * batch, T, wq, dim, 128) ||
-        !make_half_tile_map(&m.g128, w.do_planes, 2 * batch, T, wq, dim, 128))
+    if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, td, 128) ||
+        !make_half_tile_map(&m.v128, w.v_planes, 2 * batch, T, wkv, td, 128) ||
+        !make_half_tile_map(&m.q64, w.q_planes, 2 * batch, T, wq, td, 64) ||
+        !make_half_tile_map(&m.g64, w.do_planes, 2 * batch, T, wq, td, 64) ||
+        !make_half_tile_map(&m.k64, w.k_planes, 2 * batch, T, wkv, td, 64) ||
+        !make_half_tile_map(&m.v64, w.v_planes, 2 * batch, T, wkv, td, 64) ||
+        !make_half_tile_map(&m.q128, w.q_planes, 2 * batch, T, wq, td, 128) ||
+        !make_half_tile_map(&m.g128, w.do_planes, 2 * batch, T, wq, td, 128))
         return refuse("the TMA tensor maps for the backward could not be encoded.");
     BwdParams p{};
     p.lse = lse, p.delta = delta;
@@ -1046,16 +1096,17 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
     p.dq = dq, p.dk = dk, p.dv = dv;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.dim_out = dim;
     p.scale = 1.0f / sqrtf((float)dim), p.scale_log2 = kLog2e / sqrtf((float)dim);
     {
         int pl = 10, boost = 0;
         if (const char *e = getenv("ZT_BWD_PSCALE_LOG2")) pl = atoi(e);
         if (const char *e = getenv("ZT_BWD_DSBOOST_LOG2")) boost = atoi(e);
         p.p_scale = ldexpf(1.0f, pl);
-        p.c1 = ldexpf(1.0f, boost - 16 - (dim == 128 ? 7 : 6));
+        p.c1 = ldexpf(1.0f, boost - 16 - (td == 128 ? 7 : 6));
     }
     g_last_path = "tcgen05";
-    return dim == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
+    return td == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
 }
 
 }  // namespace zt

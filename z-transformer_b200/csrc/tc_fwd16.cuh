@@ -49,6 +49,7 @@ struct Params {
     const uint32_t *amax_q, *amax_k, *amax_v;   // [B, Hkv]
     float *out, *lse;                           // lse may be null
     int batch, T, n_heads, n_kv_heads;
+    int dim_out;  // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
     float scale_log2;
 };
 
@@ -309,14 +310,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float inv = 1.f / (lsum * kPScale * mv);
             const float f0 = w0 * inv, f1 = w1 * inv;
             // set s writes columns [s D/2, (s+1) D/2) of the row
-            float *orow = p.out + ((long long)b * p.T + t) * wq + (long long)h * D + set * (D / 2);
+            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out +
+                          set * (D / 2);
 #pragma unroll 1
             for (int c = 0; c < D / 2; c += 32) {
                 uint32_t ra[32], rb[32];
                 tmem_ld32(tmem + lane_base + cO0 + set * (D / 2) + c, ra);
                 if (two) tmem_ld32(tmem + lane_base + cO0 + D + set * (D / 2) + c, rb);
                 tmem_wait_ld();
-                if (t < p.T) {
+                if (t < p.T && set * (D / 2) + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         float4 o4;
@@ -373,12 +375,12 @@ inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Para
 }  // namespace tcf16
 
 inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
-    return tcf16::workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
+    return tcf16::workspace(nullptr, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).total_bytes;
 }
 
 inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_keys, const void *q, const void *k,
                                const void *v, const void *out) {
-    if (!(dim == 64 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
+    if (!(dim == 32 || dim == 64 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(q) || !al(k) || !al(v) || !al(out)) return false;
     const DeviceInfo *d = device_info();
@@ -388,30 +390,33 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
     using namespace tcb;
-    const tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, dim);
+    const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
+    const tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
     const int group = n_heads / n_kv_heads;
-    const int wq = n_heads * dim, wkv = n_kv_heads * dim;
+    const int wq_src = n_heads * dim, wkv_src = n_kv_heads * dim;
+    const int wkv = n_kv_heads * td;
     if (cudaMemsetAsync(w.amax_q, 0, w.amax_bytes, stream) != cudaSuccess) {
         cudaGetLastError();
         return refuse("could not clear the forward workspace header");
     }
     PrepassArgs pa{};
     pa.n = 3, pa.batch = batch, pa.T = T;
-    pa.t[0] = {q, w.amax_q, w.q_planes, wq, group * dim};
-    pa.t[1] = {k, w.amax_k, w.k_planes, wkv, dim};
-    pa.t[2] = {v, w.amax_v, w.v_planes, wkv, dim};
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td};
+    pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td};
+    pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td};
     if (launch_prepass(pa, stream)) return 1;
     CUtensorMap kmap, vmap;
-    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, dim, 64) ||
-        !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, dim, 64))
+    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, 64) ||
+        !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64))
         return refuse("the TMA tensor maps for the forward could not be encoded.");
     tcf16::Params p{};
     p.q_planes = w.q_planes, p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v;
     p.out = out, p.lse = lse;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.dim_out = dim;
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
-    return dim == 64 ? tcf16::launch_d<64>(kmap, vmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, p, stream);
+    return td == 64 ? tcf16::launch_d<64>(kmap, vmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, p, stream);
 }
 
 }  // namespace zt

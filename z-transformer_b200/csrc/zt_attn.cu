@@ -105,7 +105,7 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
 
 static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, int dim) {
 #ifndef ZT_NO_TC
-    if ((dim == 64 || dim == 128) && T >= 128) return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+    if ((dim == 32 || dim == 64 || dim == 128) && T >= 128) return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
 #endif
     (void)batch, (void)n_heads, (void)n_kv_heads;
     return 0;
