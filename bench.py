@@ -337,6 +337,17 @@ def run_ours(args):
                     "peak_source": f"{peak_kind}: TF32 dense = bf16_tflops_sustained ({peaks['bf16_tflops_sustained']}) / 2",
                     "step_frac": value / world / tf32_peak}
 
+    # MMA work issued per step by the f16-split kernels: every credited product is three kind::f16 MMAs, and
+    # the dQ kernel recomputes S and dP.  Forward 2 GEMMs, dK/dV kernel 4, dQ kernel 3, of 0.5 F each.
+    issued = None
+    if {"attn_fwd_tc16", "attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels):
+        issued_flop = 3.0 * (2 + 4 + 3) * 0.5 * F
+        issued = {"flop_per_step": issued_flop, "f16_tflops": issued_flop / (ms_step * 1e-3) / 1e12,
+                  "of_bf16_sustained_peak": issued_flop / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                  "credited_over_issued": 3.5 * F / issued_flop,
+                  "note": "kind::f16 MMA flops issued (3 per credited product, S and dP recomputed in the dQ "
+                          "kernel, masked halves of diagonal tiles not counted) against the measured bf16 GEMM peak"}
+
     # ---- end to end with host buffers (rank-local) ----------------------------------------------------
     # Every sequence's q, k, v, dout go up from pinned host memory and its out, dq, dk, dv come back,
     # inside the timed region.  Two ways:
@@ -465,6 +476,11 @@ def run_ours(args):
         cpu = {"value": flops / times[0] / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                "sample": f"every {stride}th query row of every head of the batch, fwd+bwd "
                          f"({flops / 1e9:.1f} GFLOP, exact count), one pass, {times[0]:.1f} s"}
+        # the reference's own execution model is one thread (src/README.md:59-63): a sixteenth of the sample
+        flops1, times1 = cpu_sample(1, stride * 16, 1, 0)
+        cpu["single_thread"] = {"value": flops1 / times1[0] / 1e12, "unit": "TFLOP/s",
+                                "sample": f"every {stride * 16}th query row ({flops1 / 1e9:.2f} GFLOP), "
+                                          f"{times1[0]:.1f} s"}
 
     if rank == 0:
         line = {
@@ -474,7 +490,7 @@ def run_ours(args):
             "config": {"workload": "causal GQA attention fwd+bwd, batch 8 per GPU, 32/8 heads, head_dim 128, "
                                    "T 4096, f32", **c, "l2": "inputs (1.25 GiB per step) exceed the 126 MB L2",
                        "gather": bool(args.gather and world > 1)},
-            "roofline": roofline, "kernels": klist, "cpu_baseline": cpu,
+            "roofline": roofline, "issued_mma": issued, "kernels": klist, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms,
                     "api": "zt.AttnPipeline.step: per sequence, pinned host -> device, zt_attn_forward_batched + "

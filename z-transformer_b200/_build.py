@@ -9,6 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libztattn.so")
 HOST_LIB_PATH = os.path.join(HERE, "libzthost.so")
+HARNESS_PATH = os.path.join(HERE, "zt_attn_harness")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
@@ -36,7 +37,8 @@ def _sources() -> list[str]:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    """nvcc -> libztattn.so (kernels + C ABI) and libzthost.so (C++ host mirror + its C shim)."""
+    """nvcc -> libztattn.so (kernels + C ABI), libzthost.so (C++ host mirror + its C shim, when its
+    source exists) and the zt_attn_harness program."""
     srcs = _sources()
     if force or _stale(LIB_PATH, srcs):
         cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(CSRC, "zt_attn.cu"), "-lcuda"]
@@ -48,6 +50,12 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared",
                "-o", HOST_LIB_PATH, host_src, "-L" + HERE, "-lztattn",
                "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        subprocess.check_call(cmd)
+    harness_src = os.path.join(CSRC, "zt_harness.cpp")
+    if os.path.exists(harness_src) and (force or _stale(HARNESS_PATH, srcs)):
+        # the twin-directory harness: a host program over the C ABI (csrc/zt_harness.cpp)
+        cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-Wall", "-o", HARNESS_PATH, harness_src,
+               "-L" + HERE, "-lztattn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
         subprocess.check_call(cmd)
     return LIB_PATH
 
