@@ -348,6 +348,35 @@ def run_ours(args):
                   "note": "kind::f16 MMA flops issued (3 per credited product, S and dP recomputed in the dQ "
                           "kernel, masked halves of diagonal tiles not counted) against the measured bf16 GEMM peak"}
 
+    # ---- the same step with rope.forward on q and k fused in (src/model.zig:372-375), on request -------------
+    rope = None
+    if args.rope:
+        rws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
+
+        def rope_step():
+            o, lse = zt.attention_forward_rope(q, k, v, H, Hkv, D, pos=0, workspace=rws, want_lse=True)
+            zt.attention_backward_rope(q, k, v, o, lse, do, H, Hkv, D, pos=0, workspace=rws)
+
+        for _ in range(max(args.warmup, 3)):
+            rope_step()
+        barrier()
+        zt.lib.profile(True)
+        zt.lib.profile_read()
+        e0.record()
+        for _ in range(args.steps):
+            rope_step()
+        e1.record()
+        barrier()
+        rk = zt.lib.profile_read()
+        zt.lib.profile(False)
+        rope_ms = e0.elapsed_time(e1) / args.steps
+        rope = {"ms_per_step": rope_ms, "plain_ms_per_step": ms_step, "extra_ms": rope_ms - ms_step,
+                "tflops": world * 3.5 * F / (rope_ms * 1e-3) / 1e12,
+                "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in rk.items()},
+                "note": "q, k handed over unrotated; rotation inside the pre-pass (forward and backward), R^T inside "
+                        "the dQ kernel's epilogue, one in-place pass over dk; credited FLOPs unchanged"}
+        del rws
+
     # ---- end to end with host buffers (rank-local) ----------------------------------------------------
     # Every sequence's q, k, v, dout go up from pinned host memory and its out, dq, dk, dv come back,
     # inside the timed region.  Two ways:
@@ -490,7 +519,7 @@ def run_ours(args):
             "config": {"workload": "causal GQA attention fwd+bwd, batch 8 per GPU, 32/8 heads, head_dim 128, "
                                    "T 4096, f32", **c, "l2": "inputs (1.25 GiB per step) exceed the 126 MB L2",
                        "gather": bool(args.gather and world > 1)},
-            "roofline": roofline, "issued_mma": issued, "kernels": klist, "cpu_baseline": cpu,
+            "roofline": roofline, "issued_mma": issued, "rope": rope, "kernels": klist, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms,
                     "api": "zt.AttnPipeline.step: per sequence, pinned host -> device, zt_attn_forward_batched + "
@@ -633,6 +662,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--gather", action="store_true", help="time the all-gather of sharded outputs too")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--rope", action="store_true",
+                    help="also time the step with the rotary embedding of q and k fused in (extra key `rope`)")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: batch 2 prefill and batch 8 decode (same kernels, a quarter of the work); "
                          "its line is not a benchmark result")

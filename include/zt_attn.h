@@ -121,6 +121,29 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
                              int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
 
+/* Attention with the rotary position embedding of its input side fused in: q and k are the
+ * projections BEFORE rope.forward (src/rope.zig:21-55; the reference rotates them first,
+ * src/model.zig:372-375 and src/decode.zig:244-246); row r sits at absolute position pos + r,
+ * element i of a head pairs with element i + dim/2, angle = (pos + r) / theta^(2i/dim), cosine,
+ * sine and the multiply-adds in f64.  On the tensor-core path the rotation happens while q and k are
+ * converted into the kernels' operand planes, so the rotated tensors never exist in memory.
+ *   forward:  out = attention(rope(q), rope(k), v), lse as zt_attn_forward_batched.
+ *   backward: dq, dk are the gradients of the UNROTATED q and k (ropeBackward,
+ *             src/autograd.zig:851-874, applied to the attention gradients), dv as usual; out and
+ *             lse are the rope forward's.
+ * Both take a caller workspace of zt_attn_rope_workspace_bytes(...) bytes (256-byte aligned; never
+ * 0) and allocate nothing.  Refusals: those of the batched calls, plus pos < 0, theta <= 0, and a
+ * missing, short or misaligned workspace. */
+size_t zt_attn_rope_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
+int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream);
+int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v, const float *out,
+                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                  int n_heads, int n_kv_heads, int dim, int pos, double theta,
+                                  zt_stream_t stream);
+
 /* KV-cache decode attention for a batch of sequences: decode.attnStep
  * (src/decode.zig:326-392) for every sequence at once, over device-resident
  * caches laid out as kv_cache.Layer lays them out (src/kv_cache.zig:60-95):

@@ -568,3 +568,61 @@ void zto_fill_normal(float *data, size_t n, uint64_t seed, uint64_t stream, uint
         data[ii] = (float)((i & 1) ? r * sin(th) : r * cos(th));
     }
 }
+
+/* ---- rotary position embedding -------------------------------------------------------------------
+ * rope.forward (src/rope.zig:21-55): row r carries absolute position pos + r; every head block of
+ * head_dim columns rotates on its own; element i pairs with element i + head_dim/2 of the same head
+ * (the half-split layout, not interleaved pairs); frequency, angle and both multiply-adds in f64, one
+ * narrowing at the store.  error.OddHeadDim for a zero or odd head_dim (:28), error.DimensionMismatch
+ * when the row is not a whole number of head blocks (:29). */
+#define ZTO_ODD_HEAD_DIM 7 /* rope.zig:28 error.OddHeadDim */
+
+int zto_rope_forward(const float *x, size_t rows, size_t cols, size_t pos, double theta, size_t head_dim,
+                     float *out) {
+    if (head_dim == 0 || head_dim % 2 != 0) return ZTO_ODD_HEAD_DIM;
+    if (cols % head_dim != 0) return ZTO_DIMENSION_MISMATCH;
+    const size_t half = head_dim / 2;
+    for (size_t r = 0; r < rows; ++r) {
+        const float *src = x + r * cols;
+        float *dst = out + r * cols;
+        const double t = (double)(pos + r);
+        for (size_t h = 0; h < cols / head_dim; ++h) {
+            const size_t base = h * head_dim;
+            for (size_t i = 0; i < half; ++i) {
+                const double exponent = (double)(2 * i) / (double)head_dim;
+                const double angle = t / pow(theta, exponent);
+                const double c = cos(angle), s = sin(angle);
+                const double lo = (double)src[base + i], hi = (double)src[base + i + half];
+                dst[base + i] = (float)(lo * c - hi * s);
+                dst[base + i + half] = (float)(hi * c + lo * s);
+            }
+        }
+    }
+    return ZTO_OK;
+}
+
+/* ropeBackward (src/autograd.zig:851-874): d x = R^T d y, the same two multiply-adds with the sine's
+ * sign flipped, same pairing, same f64 angle. */
+int zto_rope_backward(const float *dout, size_t rows, size_t cols, size_t pos, double theta, size_t head_dim,
+                      float *din) {
+    if (head_dim == 0 || head_dim % 2 != 0) return ZTO_ODD_HEAD_DIM;
+    if (cols % head_dim != 0) return ZTO_DIMENSION_MISMATCH;
+    const size_t half = head_dim / 2;
+    for (size_t r = 0; r < rows; ++r) {
+        const float *src = dout + r * cols;
+        float *dst = din + r * cols;
+        const double t = (double)(pos + r);
+        for (size_t h = 0; h < cols / head_dim; ++h) {
+            const size_t base = h * head_dim;
+            for (size_t i = 0; i < half; ++i) {
+                const double exponent = (double)(2 * i) / (double)head_dim;
+                const double angle = t / pow(theta, exponent);
+                const double c = cos(angle), s = sin(angle);
+                const double lo = (double)src[base + i], hi = (double)src[base + i + half];
+                dst[base + i] = (float)(lo * c + hi * s);
+                dst[base + i + half] = (float)(hi * c - lo * s);
+            }
+        }
+    }
+    return ZTO_OK;
+}

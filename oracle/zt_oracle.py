@@ -38,8 +38,12 @@ class DegenerateShape(Exception):
     pass
 
 
+class OddHeadDim(Exception):
+    """error.OddHeadDim (src/rope.zig:28)."""
+
+
 _ERR = {1: InvalidHeadConfig, 2: DimensionMismatch, 3: MemoryError, 4: Full, 5: ShapeTooLarge,
-        6: DegenerateShape}
+        6: DegenerateShape, 7: OddHeadDim}
 
 
 def build(force: bool = False) -> str:
@@ -84,6 +88,8 @@ def lib():
         _lib.zto_fill_hash.restype = C.c_float
         _lib.zto_fill_normal.argtypes = [_fp, _sz, C.c_uint64, C.c_uint64, C.c_uint64]
         _lib.zto_fill_normal.restype = None
+        _lib.zto_rope_forward.argtypes = [_fp, _sz, _sz, _sz, C.c_double, _sz, _fp]
+        _lib.zto_rope_backward.argtypes = [_fp, _sz, _sz, _sz, C.c_double, _sz, _fp]
     return _lib
 
 
@@ -267,3 +273,22 @@ def fill_normal(shape, seed: int, stream: int, first: int = 0, out: np.ndarray |
     a = out if out is not None else np.empty(n, dtype=np.float32)
     lib().zto_fill_normal(a.ctypes.data_as(_fp), n, seed, stream, first)
     return a.reshape(shape)
+
+
+ROPE_THETA = 500000.0  # model.rope_theta (src/model.zig:23)
+
+
+def rope_forward(x, pos: int, head_dim: int, theta: float = ROPE_THETA) -> np.ndarray:
+    """rope.forward (src/rope.zig:21-55): row r of x [rows, heads * head_dim] rotated to position pos + r."""
+    x = _2d(x)
+    out = np.empty_like(x)
+    _check(lib().zto_rope_forward(_p(x), x.shape[0], x.shape[1], pos, theta, head_dim, _p(out)))
+    return out
+
+
+def rope_backward(dout, pos: int, head_dim: int, theta: float = ROPE_THETA) -> np.ndarray:
+    """ropeBackward (src/autograd.zig:851-874): the gradient of rope_forward's input from that of its output."""
+    dout = _2d(dout)
+    din = np.empty_like(dout)
+    _check(lib().zto_rope_backward(_p(dout), dout.shape[0], dout.shape[1], pos, theta, head_dim, _p(din)))
+    return din

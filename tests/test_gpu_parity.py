@@ -536,3 +536,52 @@ def test_attn_pipeline_matches_batched_calls(zt, dev):
     dq, dk, dv = zt.attention_backward(q, k, v, out, lse, do, H, Hkv, D)
     for name, got, want in (("out", hout, out), ("lse", hlse, lse), ("dq", hdq, dq), ("dk", hdk, dk), ("dv", hdv, dv)):
         assert torch.equal(got, want.cpu()), name
+
+
+ROPE_SHAPES = [  # B, T, H, Hkv, D, pos -- tensor-core shapes (the rotation rides in the pre-pass) and CUDA-core ones
+    (1, 256, 8, 2, 128, 0), (2, 200, 4, 2, 64, 37), (1, 384, 4, 1, 32, 5), (1, 150, 6, 3, 128, 1000),
+    (1, 96, 4, 2, 64, 3), (1, 160, 8, 2, 96, 11),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,pos", ROPE_SHAPES)
+def test_rope_fused_forward_backward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, pos):
+    """attention over rope(q), rope(k) with q, k handed over unrotated, and the gradients of the unrotated q, k:
+    against rope.forward -> attention.forward and attentionBackward -> ropeBackward on the CPU
+    (src/model.zig:372-375, src/autograd.zig:559-569)."""
+    q = oracle.fill_normal((B, T, H * D), 71, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 71, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 71, 2)
+    do = oracle.fill_normal((B, T, H * D), 71, 3)
+    zt.lib.load().zt_attn_set_path(0)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    ws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
+    o, lse = zt.attention_forward_rope(tq, tk, tv, H, Hkv, D, pos=pos, workspace=ws, want_lse=True)
+    dq, dk, dv = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
+    torch.cuda.synchronize()
+    assert zt.lib.tc_status() == 0
+    for b in range(B):
+        qr, kr = oracle.rope_forward(q[b], pos, D), oracle.rope_forward(k[b], pos, D)
+        ro, rl = oracle.attention_forward(qr, kr, v[b], H, Hkv, D, want_lse=True, threads=4)
+        rdq, rdk, rdv = oracle.attention_backward(qr, kr, v[b], do[b], H, Hkv, D, threads=4)
+        rdq, rdk = oracle.rope_backward(rdq, pos, D), oracle.rope_backward(rdk, pos, D)
+        close(o[b].cpu().numpy(), ro, f"out[{b}]")
+        close(lse[b].cpu().numpy(), rl, f"lse[{b}]")
+        close(dq[b].cpu().numpy(), rdq, f"dq[{b}]")
+        close(dk[b].cpu().numpy(), rdk, f"dk[{b}]")
+        close(dv[b].cpu().numpy(), rdv, f"dv[{b}]")
+
+
+def test_rope_calls_refuse_bad_arguments(zt, dev):
+    B, T, H, Hkv, D = 1, 128, 4, 2, 64
+    q = torch.zeros((B, T, H * D), device=dev)
+    k = torch.zeros((B, T, Hkv * D), device=dev)
+    ws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
+    with pytest.raises(zt.device.ConfigRefused, match="negative"):
+        zt.attention_forward_rope(q, k, k, H, Hkv, D, pos=-1, workspace=ws)
+    with pytest.raises(zt.device.ConfigRefused, match="rotary base"):
+        zt.attention_forward_rope(q, k, k, H, Hkv, D, theta=0.0, workspace=ws)
+    L = zt.lib.load()
+    rc = L.zt_attn_forward_rope_batched(q.data_ptr(), k.data_ptr(), k.data_ptr(), q.data_ptr(), None,
+                                        ws.buf.data_ptr(), 16, B, T, H, Hkv, D, 0, 500000.0, None)
+    assert rc == 1 and "workspace" in zt.lib.last_error()

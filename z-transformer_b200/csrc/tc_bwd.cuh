@@ -33,6 +33,7 @@
 
 #include <cuda_fp16.h>
 
+#include "rope_kernels.cuh"
 #include "tc_common.cuh"
 #include "tc_fwd.cuh"
 #include "zt_common.cuh"
@@ -69,7 +70,25 @@ struct PrepassTensor {
     __half *planes;   // [2][batch][T][width / src_head * dst_head]
     int width, cols_per_group;
     int src_head, dst_head;  // a head's columns in x and in the planes: 32 -> 64 pads each head with zeros
+    const float2 *rope;      // null, or the (cos, sin) table [T][src_head / 2]: x is rotated on its way in
 };
+
+// Four consecutive elements of row r starting at column c of tensor t, rotated if the tensor asks for it.
+// A head's halves are multiples of four wide, so the four partners are one float4 too.
+__device__ __forceinline__ float4 prepass_load(const PrepassTensor &t, const float4 *row4, int r, int c) {
+    const float4 v = __ldg(row4 + c / 4);
+    if (t.rope == nullptr) return v;
+    const int half = t.src_head / 2;
+    const int w = c % t.src_head;
+    const bool upper = w >= half;
+    const float4 o = __ldg(row4 + (upper ? c - half : c + half) / 4);
+    const float4 *cs = reinterpret_cast<const float4 *>(t.rope + (long long)r * half + (upper ? w - half : w));
+    const float4 a = __ldg(cs), b = __ldg(cs + 1);  // four (cos, sin) pairs
+    float4 out;
+    out.x = rope_elem(v.x, o.x, make_float2(a.x, a.y), upper, false), out.y = rope_elem(v.y, o.y, make_float2(a.z, a.w), upper, false);
+    out.z = rope_elem(v.z, o.z, make_float2(b.x, b.y), upper, false), out.w = rope_elem(v.w, o.w, make_float2(b.z, b.w), upper, false);
+    return out;
+}
 struct PrepassArgs {
     PrepassTensor t[4];
     int n, batch, T;
@@ -92,6 +111,8 @@ __global__ void __launch_bounds__(256) bwd_absmax_kernel(const PrepassArgs a) {
         float m = 0.f;
 #pragma unroll 8
         for (int r = r0; r < r1; ++r) {
+            // (a tensor that will be rotated is measured unrotated: a rotated pair is at most sqrt(2) times its
+            // larger element, and the scale leaves a factor of two below the f16 range)
             const float4 v = __ldg(base + (long long)r * w4 + c4);
             m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         }
@@ -130,7 +151,7 @@ __global__ void __launch_bounds__(256) bwd_split_kernel(const PrepassArgs a) {
             if (within < t.src_head) {
                 const int cs = head * t.src_head + within;          // column in x
                 const float m = block_mult(amax[cs / t.cols_per_group]);
-                const float4 v = __ldg(src + (long long)r * w4s + cs / 4);
+                const float4 v = prepass_load(t, src + (long long)r * w4s, r, cs);
                 const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
                 __half h[4], l[4];
 #pragma unroll
@@ -160,7 +181,7 @@ __global__ void __launch_bounds__(256) bwd_split_kernel(const PrepassArgs a) {
         if (i >= seq4) break;
         const unsigned c4 = (col0 + (unsigned)o) % (unsigned)w4;
         const float m = block_mult(amax[(c4 * 4u) / (unsigned)t.cols_per_group]);
-        const float4 v = __ldg(src + i);
+        const float4 v = t.rope ? prepass_load(t, src + (i - c4), (int)((i - c4) / w4), (int)(c4 * 4u)) : __ldg(src + i);
         const float s[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
         __half h[4], l[4];
 #pragma unroll
@@ -215,6 +236,7 @@ struct BwdParams {
     float *dq, *dk, *dv;
     int batch, T, n_heads, n_kv_heads;
     int dim_out;     // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
+    const float2 *rope_t;  // null, or the (cos, sin) table transposed, [dim_out / 2][T]: dq leaves as R^T of what was computed
     float scale, scale_log2;
     float p_scale;  // P is multiplied by this power of two before its 16-bit split
     float c1;       // dP (in scaled units) is multiplied by this power of two before dS is split
@@ -966,16 +988,33 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             constexpr int CW = D / 4;  // 32 or 16
             const float fq = p.scale / (mdo * mv * c1 * mk);
             float *dqr = p.dq + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + set * CW;
-            uint32_t r[32];
+            // mine: this set's CW columns; other: their rotation partners (i +- dim_out / 2, another set's
+            // chunk of this row's accumulator), read only when dQ leaves as the gradient of the unrotated q
+            const bool rot = p.rope_t != nullptr && set * CW < p.dim_out;
+            const int half = p.dim_out / 2, col = set * CW;
+            const bool upper = col >= half;
+            const uint32_t other_at = tmem + lane_base + cDQ + (upper ? col - half : col + half);
+            uint32_t r[32], o[32];
             if (CW == 32) {
-                tmem_ld32(tmem + lane_base + cDQ + set * CW, r);
+                tmem_ld32(tmem + lane_base + cDQ + col, r);
+                if (rot) tmem_ld32(other_at, o);
+                tmem_wait_ld();
             } else {
-                uint32_t r16[16];
-                tmem_ld16(tmem + lane_base + cDQ + set * CW, r16);
+                uint32_t r16[16], o16[16];
+                tmem_ld16(tmem + lane_base + cDQ + col, r16);
+                if (rot) tmem_ld16(other_at, o16);
+                tmem_wait_ld();  // the registers hold the values only from here on
 #pragma unroll
-                for (int i = 0; i < 16; ++i) r[i] = r16[i];
+                for (int i = 0; i < 16; ++i) r[i] = r16[i], o[i] = o16[i];
             }
-            tmem_wait_ld();
+            if (rot) {
+                // the table is read transposed: the threads of a warp are consecutive rows, so entry i of 32 rows
+                // is one 256-byte run
+                const float2 *cs = p.rope_t + (long long)(upper ? col - half : col) * p.T + (t < p.T ? t : 0);
+#pragma unroll
+                for (int i = 0; i < CW; ++i)
+                    r[i] = __float_as_uint(rope_elem(__uint_as_float(r[i]), __uint_as_float(o[i]), __ldg(cs + (long long)i * p.T), upper, true));
+            }
             if (t < p.T && set * CW < p.dim_out) {
 #pragma unroll
                 for (int i = 0; i < CW; i += 4) {
@@ -1062,7 +1101,8 @@ inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_hea
 // delta must already hold sum_j dout*out.  dq, dk, dv are assigned.
 inline int launch_bwd_tc(const float *q, const float *k, const float *v, const float *dout, const float *lse,
                          const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
-                         int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+                         int n_heads, int n_kv_heads, int dim, cudaStream_t stream, const float2 *rope = nullptr,
+                         const float2 *rope_t = nullptr) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernels' D; the planes' head width
     const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, td);
@@ -1075,10 +1115,10 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     }
     PrepassArgs pa{};
     pa.n = 4, pa.batch = batch, pa.T = T;
-    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td};
-    pa.t[1] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td};
-    pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td};
-    pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td};
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td, rope};
+    pa.t[1] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td, nullptr};
+    pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
+    pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
     BwdMaps m;
     if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, td, 128) ||
@@ -1097,6 +1137,7 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     p.dq = dq, p.dk = dk, p.dv = dv;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
+    p.rope_t = rope_t;
     p.scale = 1.0f / sqrtf((float)dim), p.scale_log2 = kLog2e / sqrtf((float)dim);
     {
         int pl = 10, boost = 0;

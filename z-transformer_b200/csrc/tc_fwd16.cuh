@@ -388,7 +388,8 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 }
 
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
-                           int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+                           int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
+                           const float2 *rope = nullptr) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
     const tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
@@ -401,9 +402,9 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     }
     PrepassArgs pa{};
     pa.n = 3, pa.batch = batch, pa.T = T;
-    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td};
-    pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td};
-    pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td};
+    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td, rope};
+    pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
+    pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
     CUtensorMap kmap, vmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, 64) ||

@@ -350,6 +350,106 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
                          n_kv_heads, dim, s);
 }
 
+// ---- attention with the rotary embedding of q and k fused in ------------------------------------------
+namespace {
+struct RopeWorkspace {
+    float2 *table;         // [T][dim / 2] (cos, sin)
+    float2 *table_t;       // the same, [dim / 2][T]
+    float *q_rot, *k_rot;  // rotated copies, used only off the fused path
+    void *inner;           // the tensor-core kernels' workspace (operand planes)
+    size_t inner_bytes, total_bytes;
+};
+RopeWorkspace rope_workspace(void *base, int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    RopeWorkspace w{};
+    char *c = static_cast<char *>(base);
+    size_t off = 0;
+    w.table = reinterpret_cast<float2 *>(c + off), off += up((size_t)T * (dim / 2) * sizeof(float2));
+    w.table_t = reinterpret_cast<float2 *>(c + off), off += up((size_t)T * (dim / 2) * sizeof(float2));
+    w.q_rot = reinterpret_cast<float *>(c + off), off += up((size_t)batch * T * n_heads * dim * sizeof(float));
+    w.k_rot = reinterpret_cast<float *>(c + off), off += up((size_t)batch * T * n_kv_heads * dim * sizeof(float));
+    w.inner = c + off;
+    w.inner_bytes = backward_workspace(batch, T, n_heads, n_kv_heads, dim);  // >= the forward's planes
+    off += up(w.inner_bytes);
+    w.total_bytes = off;
+    return w;
+}
+int check_rope_call(const void *workspace, size_t workspace_bytes, size_t need, int pos, double theta) {
+    if (pos < 0) return refuse("pos %d is negative: a row cannot sit before position 0.", pos);
+    if (!(theta > 0.0)) return refuse("theta %g is not a positive rotary base.", theta);
+    if (!workspace || workspace_bytes < need)
+        return refuse("the rope calls need %zu bytes of workspace, %zu were given.", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return refuse("the rope workspace must be 256-byte aligned.");
+    return 0;
+}
+}  // namespace
+
+size_t zt_attn_rope_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    if (batch < 1 || T < 1 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || !zt_attn_dim_ok(dim))
+        return 0;
+    return rope_workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
+}
+
+int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
+    const RopeWorkspace w = rope_workspace(workspace, batch, T, n_heads, n_kv_heads, dim);
+    if (check_rope_call(workspace, workspace_bytes, w.total_bytes, pos, theta)) return 1;
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
+#ifndef ZT_NO_TC
+    if (g_path.load() == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
+        tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out) &&
+        w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim))
+        return launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table);
+#endif
+    // off the fused path: rotate into the workspace, then the ordinary forward
+    if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
+    if (launch_rope_apply(k, w.k_rot, w.table, batch, T, n_kv_heads * dim, dim, false, s)) return 1;
+    return forward_impl(w.q_rot, w.k_rot, v, out, lse, batch, T, n_heads, n_kv_heads, dim, 0, T, s);
+}
+
+int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v, const float *out,
+                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                  int n_heads, int n_kv_heads, int dim, int pos, double theta,
+                                  zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv || !delta)
+        return refuse("a null device pointer was passed.");
+    const RopeWorkspace w = rope_workspace(workspace, batch, T, n_heads, n_kv_heads, dim);
+    if (check_rope_call(workspace, workspace_bytes, w.total_bytes, pos, theta)) return 1;
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
+    if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
+    bool fused = false;
+#ifndef ZT_NO_TC
+    fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
+            tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);
+    if (fused && launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, w.inner, batch, T, n_heads, n_kv_heads, dim, s,
+                               w.table, w.table_t))
+        return 1;
+#endif
+    if (!fused) {
+        if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
+        if (launch_rope_apply(k, w.k_rot, w.table, batch, T, n_kv_heads * dim, dim, false, s)) return 1;
+        if (backward_impl(w.q_rot, w.k_rot, v, lse, delta, dout, dq, dk, dv, nullptr, 0, batch, T, n_heads, n_kv_heads, dim, s))
+            return 1;
+    }
+    // the gradients of the unrotated q and k: R^T.  The tensor-core dQ kernel applies it as it writes dq; dk
+    // (a quarter of dq's bytes here, flushed from its accumulator many times) takes a pass in place.
+    if (!fused && launch_rope_apply(dq, dq, w.table, batch, T, n_heads * dim, dim, true, s)) return 1;
+    return launch_rope_apply(dk, dk, w.table, batch, T, n_kv_heads * dim, dim, true, s);
+}
+
 size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim) {
     if (batch < 1 || n_ctx < 1 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 ||
         !zt_attn_dim_ok(dim))

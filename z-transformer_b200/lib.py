@@ -10,7 +10,7 @@ import os
 
 from ._build import LIB_PATH
 
-_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+_vp, _i, _sz, _d = C.c_void_p, C.c_int, C.c_size_t, C.c_double
 
 _SIGNATURES = {
     # name: (restype, argtypes)      -- the reference's six
@@ -32,6 +32,9 @@ _SIGNATURES = {
     "zt_attn_forward_batched": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
     "zt_attn_backward_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_backward_workspace_bytes": (_sz, [_i] * 5),
+    "zt_attn_rope_workspace_bytes": (_sz, [_i] * 5),
+    "zt_attn_forward_rope_batched": (_i, [_vp] * 6 + [_sz] + [_i] * 6 + [_d, _vp]),
+    "zt_attn_backward_rope_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 6 + [_d, _vp]),
     "zt_attn_decode": (_i, [_vp] * 7 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_decode_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_decode_static": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),

@@ -100,6 +100,75 @@ def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim):
     return dq, dk, dv
 
 
+ROPE_THETA = 500000.0  # model.rope_theta (src/model.zig:23)
+
+
+class RopeWorkspace:
+    """Caller-owned scratch of the rope calls for one (batch, T, heads, dim) shape."""
+
+    def __init__(self, batch, t, n_heads, n_kv_heads, head_dim, device="cuda"):
+        import torch
+        self.shape = (batch, t, n_heads, n_kv_heads, head_dim)
+        self.nbytes = int(_lib.load().zt_attn_rope_workspace_bytes(*self.shape))
+        if self.nbytes == 0:
+            raise ConfigRefused("the shape is not admissible")
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+
+
+def _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace):
+    _head_config(n_heads, n_kv_heads, head_dim)
+    _need_cuda_f32(q, k, v)
+    if q.dim() != 3:
+        raise DimensionMismatch("the rope calls take [B, T, width] tensors")
+    B, T = q.shape[0], q.shape[1]
+    if (k.shape[:2] != (B, T) or v.shape != k.shape or k.shape[2] != n_kv_heads * head_dim
+            or q.shape[2] != n_heads * head_dim):
+        raise DimensionMismatch("q/k/v shapes disagree with the head configuration")
+    if workspace is None:
+        workspace = RopeWorkspace(B, T, n_heads, n_kv_heads, head_dim, q.device)
+    elif workspace.shape != (B, T, n_heads, n_kv_heads, head_dim):
+        raise DimensionMismatch("the workspace was sized for another shape")
+    return B, T, workspace
+
+
+def attention_forward_rope(q, k, v, n_heads, n_kv_heads, head_dim, *, pos=0, theta=ROPE_THETA, workspace=None,
+                           want_lse=False):
+    """attention.forward over rope.forward(q), rope.forward(k) (src/model.zig:372-375): q, k are the
+    unrotated projections [B, T, width]; row r sits at position pos + r."""
+    import torch
+    B, T, workspace = _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace)
+    out = torch.empty_like(q)
+    lse = torch.empty((B, T, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_forward_rope_batched(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if want_lse else None,
+            workspace.buf.data_ptr(), workspace.nbytes, B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return (out, lse) if want_lse else out
+
+
+def attention_backward_rope(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *, pos=0, theta=ROPE_THETA,
+                            workspace=None):
+    """Gradients of the unrotated q and k (and of v): autograd.attentionBackward followed by
+    ropeBackward (src/autograd.zig:559-569,851-874)."""
+    import torch
+    B, T, workspace = _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace)
+    _need_cuda_f32(out, lse, dout)
+    if dout.shape != q.shape or out.shape != q.shape or lse.shape != (B, T, n_heads):
+        raise DimensionMismatch("dout/out/lse shapes disagree with q")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty_like(lse)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_backward_rope_batched(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), workspace.buf.data_ptr(), workspace.nbytes,
+            B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return dq, dk, dv
+
+
 class DecodeWorkspace:
     """Caller-owned scratch of zt_attn_decode for one (batch, n_ctx, heads, dim) shape."""
 
