@@ -1,0 +1,152 @@
+// zt::device::Attn (zt_host.hpp) and a C shim over it.  Links against libztattn.so and the CUDA runtime.
+#include "zt_host.hpp"
+
+#include <cuda_runtime.h>
+
+#include "../../../include/zt_attn.h"
+
+namespace zt {
+namespace device {
+
+namespace {
+Error alloc(uint64_t bytes, float **out) {  // device.zig:434-438
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess || p == nullptr) {
+        cudaGetLastError();
+        return Error::DeviceAllocFailed;
+    }
+    *out = static_cast<float *>(p);
+    return Error::Ok;
+}
+}  // namespace
+
+float *Attn::field(int i) const {
+    float *const f[N_BUFFERS] = {q, k, v, out, dout, dq, dk, dv, row_max, row_den, row_del};
+    return (i >= 0 && i < N_BUFFERS) ? f[i] : nullptr;
+}
+
+void Attn::deinitPartial(int taken) {
+    float **const f[N_BUFFERS] = {&q, &k, &v, &out, &dout, &dq, &dk, &dv, &row_max, &row_den, &row_del};
+    for (int i = 0; i < taken; ++i) {
+        if (*f[i]) cudaFree(*f[i]);
+        *f[i] = nullptr;
+    }
+}
+
+void Attn::deinit() { deinitPartial(N_BUFFERS); }
+
+Error Attn::init(uint64_t t_, uint64_t n_heads_, uint64_t n_kv_heads_, uint64_t dim_) {
+    deinit();
+    Error e;
+    int ct, ch, ckv, cd;
+    if ((e = toCInt(t_, &ct)) != Error::Ok) return e;
+    if ((e = toCInt(n_heads_, &ch)) != Error::Ok) return e;
+    if ((e = toCInt(n_kv_heads_, &ckv)) != Error::Ok) return e;
+    if ((e = toCInt(dim_, &cd)) != Error::Ok) return e;
+    // ask the C side before allocating anything (device.zig:227-241)
+    if (zt_attn_dim_ok(cd) == 0) return Error::ConfigRefused;
+    if (ch <= 0 || ckv <= 0 || ch % ckv != 0) return Error::ConfigRefused;
+    if (n_heads_ > 65535) return Error::ConfigRefused;
+    uint64_t qh, kvh, pr;
+    if ((e = bytesFor(Kind::query_headed, t_, n_heads_, n_kv_heads_, dim_, &qh)) != Error::Ok) return e;
+    if ((e = bytesFor(Kind::kv_headed, t_, n_heads_, n_kv_heads_, dim_, &kvh)) != Error::Ok) return e;
+    if ((e = bytesFor(Kind::per_row, t_, n_heads_, n_kv_heads_, dim_, &pr)) != Error::Ok) return e;
+    float **const f[N_BUFFERS] = {&q, &k, &v, &out, &dout, &dq, &dk, &dv, &row_max, &row_den, &row_del};
+    const uint64_t size[N_BUFFERS] = {qh, kvh, kvh, qh, qh, qh, kvh, kvh, pr, pr, pr};
+    for (int i = 0; i < N_BUFFERS; ++i) {
+        if ((e = alloc(size[i], f[i])) != Error::Ok) {
+            deinitPartial(i);
+            return e;
+        }
+    }
+    t = t_, n_heads = n_heads_, n_kv_heads = n_kv_heads_, dim = dim_;
+    c_t = ct, c_heads = ch, c_kv_heads = ckv, c_dim = cd;
+    return Error::Ok;
+}
+
+uint64_t Attn::totalBytes() const {  // device.zig:355-360
+    uint64_t qh = 0, kvh = 0, pr = 0;
+    if (bytesFor(Kind::query_headed, t, n_heads, n_kv_heads, dim, &qh) != Error::Ok) qh = 0;
+    if (bytesFor(Kind::kv_headed, t, n_heads, n_kv_heads, dim, &kvh) != Error::Ok) kvh = 0;
+    if (bytesFor(Kind::per_row, t, n_heads, n_kv_heads, dim, &pr) != Error::Ok) pr = 0;
+    return 4 * qh + 4 * kvh + 3 * pr;
+}
+
+Error Attn::forwardAt(int group_q, int max_tile, int q_offset, int n_keys, int t_rows) const {  // device.zig:387-398
+    const Error e = forwardBounds(c_t, q_offset, n_keys, t_rows);
+    if (e != Error::Ok) return e;
+    const int rc = zt_attn_forward(q, k, v, out, t_rows, c_heads, c_kv_heads, c_dim, group_q, max_tile, q_offset, n_keys, nullptr);
+    return rc != 0 ? Error::ConfigRefused : Error::Ok;
+}
+
+Error Attn::backward(int max_tile) const {  // device.zig:403-406
+    const int rc = zt_attn_backward(q, k, v, dout, dq, dk, dv, row_max, row_den, row_del, c_t, c_heads, c_kv_heads, c_dim,
+                                    max_tile, nullptr);
+    return rc != 0 ? Error::ConfigRefused : Error::Ok;
+}
+
+uint64_t Attn::bufferBytes(const float *target) const {  // device.zig:440-458
+    uint64_t qh = 0, kvh = 0, pr = 0;
+    if (bytesFor(Kind::query_headed, t, n_heads, n_kv_heads, dim, &qh) != Error::Ok) return 0;
+    if (bytesFor(Kind::kv_headed, t, n_heads, n_kv_heads, dim, &kvh) != Error::Ok) return 0;
+    if (bytesFor(Kind::per_row, t, n_heads, n_kv_heads, dim, &pr) != Error::Ok) return 0;
+    const uint64_t size[N_BUFFERS] = {qh, kvh, kvh, qh, qh, qh, kvh, kvh, pr, pr, pr};
+    if (target == nullptr) return 0;
+    for (int i = 0; i < N_BUFFERS; ++i)
+        if (field(i) == target) return size[i];
+    return 0;
+}
+
+// The reference maps a failed copy to DeviceAllocFailed (device.zig:418,429); kept.
+Error Attn::upload(float *dst, const float *src, uint64_t n_floats) const {  // device.zig:412-419
+    uint64_t n;
+    if (!mul_usize(n_floats, sizeof(float), &n)) return Error::ShapeTooLarge;
+    if (n > bufferBytes(dst)) return Error::ShapeTooLarge;
+    if (cudaMemcpy(dst, src, n, cudaMemcpyHostToDevice) != cudaSuccess) return Error::DeviceAllocFailed;
+    return Error::Ok;
+}
+
+Error Attn::download(float *dst, uint64_t n_floats, const float *src) const {  // device.zig:426-431
+    uint64_t n;
+    if (!mul_usize(n_floats, sizeof(float), &n)) return Error::ShapeTooLarge;
+    if (n > bufferBytes(src)) return Error::ShapeTooLarge;
+    if (cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost) != cudaSuccess) return Error::DeviceAllocFailed;
+    return Error::Ok;
+}
+
+}  // namespace device
+}  // namespace zt
+
+// ---- C shim (for tests and other foreign-function callers); error codes are Error's values -------------
+using zt::device::Attn;
+using zt::device::Error;
+using zt::device::Kind;
+
+extern "C" {
+int zth_bytes_for(int kind, uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim, uint64_t *bytes) {
+    return (int)zt::device::bytesFor((Kind)kind, t, n_heads, n_kv_heads, dim, bytes);
+}
+int zth_to_c_int(uint64_t x, int *out) { return (int)zt::device::toCInt(x, out); }
+int zth_forward_bounds(int c_t, int q_offset, int n_keys, int t) { return (int)zt::device::forwardBounds(c_t, q_offset, n_keys, t); }
+int zth_attn_init(uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim, void **handle) {
+    Attn *a = new Attn();
+    const Error e = a->init(t, n_heads, n_kv_heads, dim);
+    if (e != Error::Ok) {
+        delete a;
+        *handle = nullptr;
+        return (int)e;
+    }
+    *handle = a;
+    return 0;
+}
+void zth_attn_deinit(void *handle) { delete static_cast<Attn *>(handle); }
+uint64_t zth_attn_total_bytes(const void *handle) { return static_cast<const Attn *>(handle)->totalBytes(); }
+float *zth_attn_field(const void *handle, int i) { return static_cast<const Attn *>(handle)->field(i); }
+int zth_attn_forward(const void *handle, int group_q, int max_tile) { return (int)static_cast<const Attn *>(handle)->forward(group_q, max_tile); }
+int zth_attn_forward_at(const void *handle, int group_q, int max_tile, int q_offset, int n_keys, int t) {
+    return (int)static_cast<const Attn *>(handle)->forwardAt(group_q, max_tile, q_offset, n_keys, t);
+}
+int zth_attn_backward(const void *handle, int max_tile) { return (int)static_cast<const Attn *>(handle)->backward(max_tile); }
+int zth_attn_upload(const void *handle, float *dst, const float *src, uint64_t n) { return (int)static_cast<const Attn *>(handle)->upload(dst, src, n); }
+int zth_attn_download(const void *handle, float *dst, uint64_t n, const float *src) { return (int)static_cast<const Attn *>(handle)->download(dst, n, src); }
+}
