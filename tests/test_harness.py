@@ -85,3 +85,14 @@ def test_harness_negative_controls(twin_dir):
     assert len(set(sigs)) == 4, sigs
     assert sigs[2][2] == signature(good.stdout)[2], "dropping the Jacobian must not touch dv"
     assert run([twin_dir], ZT_HARNESS_BROKEN="7").returncode == 2
+
+
+@pytest.mark.gpu
+def test_harness_scale_relative_gate_at_training_scale(twin_dir):
+    """dout five orders of magnitude smaller, as a training step supplies it (attn.cu:103-113): the backward is
+    gated relative to max |ref| (attn_rel_tol, train.zig:706), and a defect is still caught at that scale."""
+    r = run([twin_dir], ZT_HARNESS_DOUT_SCALE="1e-5")
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "of max |ref|" in r.stdout
+    r = run([twin_dir], ZT_HARNESS_DOUT_SCALE="1e-5", ZT_HARNESS_BWD_BROKEN="3")
+    assert r.returncode == 1

@@ -24,6 +24,11 @@
 //                 3 the softmax Jacobian dropped (delta = 0: the batched backward is handed out = 0);
 //                   dv must then read exactly as in the correct run, dq and dk must not
 //                 4 the scale dropped
+//   * ZT_HARNESS_DOUT_SCALE=<x> multiplies dout (and, the backward being linear in it, the reference
+//     gradients) by x before the run and replaces the backward's absolute gate by a scale-relative one,
+//     max |got - ref| <= 1e-4 max |ref| per tensor (attn_rel_tol, src/train.zig:706).  The absolute
+//     gate is calibrated on a dout of order 0.5; a training step supplies one of order 1e-5
+//     (attn.cu:103-113), where 1e-5 absolute would pass anything.
 // `--list <dir>` parses the manifest and checks every blob's size without touching the GPU.
 // Exit status: 0 all gates passed, 1 a gate failed or a file was unreadable, 2 usage.
 #include <cuda_runtime.h>
@@ -42,6 +47,7 @@ namespace {
 
 constexpr double kFwdTol = 1e-4;  // attn.cu:51
 constexpr double kBwdTol = 1e-5;  // attn.cu:114
+constexpr double kRelTol = 1e-4;  // src/train.zig:706 attn_rel_tol
 constexpr int kTagCap = 40, kMaxShapes = 64;
 
 struct Shape {
@@ -164,7 +170,17 @@ int run(const std::string &dir) {
     int ok = 1;
 
     struct FwdRow { double max_abs, us; size_t where; const char *path; };
-    struct BwdRow { double dq, dk, dv, us; };
+    struct BwdRow { double dq, dk, dv, us, rel; };
+    double dout_scale = 1.0;
+    if (const char *e = getenv("ZT_HARNESS_DOUT_SCALE")) {
+        dout_scale = atof(e);
+        if (!(dout_scale > 0.0)) {
+            fprintf(stderr, "harness: ZT_HARNESS_DOUT_SCALE=%s is not a positive number\n", e);
+            return 2;
+        }
+        printf("harness: dout and the reference gradients scaled by %g; the backward gate is %.0e of max |ref|\n", dout_scale, kRelTol);
+    }
+    const bool relative_gate = dout_scale != 1.0;
     std::vector<FwdRow> frows(n);
     std::vector<BwdRow> brows(n);
     for (int i = 0; i < n; ++i) {
@@ -176,6 +192,13 @@ int run(const std::string &dir) {
             !read_floats(dir, s.tag, ".dk", s.kn(), &dk) || !read_floats(dir, s.tag, ".dv", s.kn(), &dv))
             return 1;
         const float root_d = sqrtf((float)s.head_dim);
+        if (dout_scale != 1.0) {
+            const float f = (float)dout_scale;
+            for (float &x : dout) x *= f;
+            for (float &x : dq) x *= f;
+            for (float &x : dk) x *= f;
+            for (float &x : dv) x *= f;
+        }
         // ---- forward ------------------------------------------------------------------------------
         {
             std::vector<float> fq = q, fk = k, fv = v;
@@ -271,7 +294,15 @@ int run(const std::string &dir) {
             brows[i].us = best;
             cudaEventDestroy(e0), cudaEventDestroy(e1);
             if (ws) cudaFree(ws);
-            if (!(brows[i].dq <= kBwdTol && brows[i].dk <= kBwdTol && brows[i].dv <= kBwdTol)) ok = 0;
+            auto max_abs = [](const std::vector<float> &x) {
+                double m = 0.0;
+                for (float f : x) m = fmax(m, fabs((double)f));
+                return m;
+            };
+            brows[i].rel = fmax(brows[i].dq / max_abs(dq), fmax(brows[i].dk / max_abs(dk), brows[i].dv / max_abs(dv)));
+            if (relative_gate ? !(brows[i].rel <= kRelTol)
+                              : !(brows[i].dq <= kBwdTol && brows[i].dk <= kBwdTol && brows[i].dv <= kBwdTol))
+                ok = 0;
         }
     }
 
@@ -286,12 +317,15 @@ int run(const std::string &dir) {
                100.0 * frows[i].max_abs / kFwdTol, frows[i].us, s.cpu_us, s.cpu_us / frows[i].us, frows[i].path,
                frows[i].max_abs <= kFwdTol ? "" : "   <-- FAIL");
     }
-    printf("\nbackward against autograd.attentionBackward (gate %.0e):\n", kBwdTol);
-    printf("  %-14s %-11s %-11s %-11s %6s  %11s\n", "shape", "max_abs_dq", "max_abs_dk", "max_abs_dv", "used", "kernel_us");
+    if (relative_gate) printf("\nbackward against autograd.attentionBackward (gate %.0e of max |ref|):\n", kRelTol);
+    else printf("\nbackward against autograd.attentionBackward (gate %.0e):\n", kBwdTol);
+    printf("  %-14s %-11s %-11s %-11s %6s  %-11s %11s\n", "shape", "max_abs_dq", "max_abs_dk", "max_abs_dv", "used", "rel_to_max", "kernel_us");
     for (int i = 0; i < n; ++i) {
         const double worst = fmax(brows[i].dq, fmax(brows[i].dk, brows[i].dv));
-        printf("  %-14s %.3e   %.3e   %.3e %5.1f%%  %11.2f%s\n", shapes[i].tag, brows[i].dq, brows[i].dk, brows[i].dv,
-               100.0 * worst / kBwdTol, brows[i].us, worst <= kBwdTol ? "" : "   <-- FAIL");
+        const bool pass = relative_gate ? brows[i].rel <= kRelTol : worst <= kBwdTol;
+        printf("  %-14s %.3e   %.3e   %.3e %5.1f%%  %.3e   %11.2f%s\n", shapes[i].tag, brows[i].dq, brows[i].dk, brows[i].dv,
+               relative_gate ? 100.0 * brows[i].rel / kRelTol : 100.0 * worst / kBwdTol, brows[i].rel, brows[i].us,
+               pass ? "" : "   <-- FAIL");
     }
 
     // ---- one launch of both entry points per shape at T = 8, on uninitialised memory ----------------
