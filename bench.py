@@ -263,8 +263,9 @@ def run_ours(args):
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
 
     def step():
-        rc = L.zt_attn_forward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                       B, T, H, Hkv, D, stream)
+        # the training pair: the forward leaves its f16 planes of q, k, v in the backward's workspace
+        rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                            ws.data_ptr(), ws_bytes, B, T, H, Hkv, D, stream)
         rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                          do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                          delta.data_ptr(), ws.data_ptr(), ws_bytes, B, T, H, Hkv, D, stream)

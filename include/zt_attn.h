@@ -121,6 +121,19 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
                              int n_heads, int n_kv_heads, int dim, zt_stream_t stream);
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
 
+/* The forward of a training step: zt_attn_forward_batched, except that the 16-bit operand planes of
+ * q, k, v it builds are written into the backward's workspace and kept there.  The next
+ * zt_attn_backward_batched on this device that is given the same workspace, the same q, k, v
+ * pointers, shape and stream then converts only dout (a quarter less pre-pass traffic per step), and
+ * this call takes nothing from the per-device arena.  The caller's promise: q, k, v are not written
+ * between the two calls.  The note is used once and dropped by any other backward; with a workspace
+ * that is NULL, short or misaligned, or a shape the tensor-core kernels do not take, this is the
+ * ordinary forward and nothing is kept.  No reference counterpart (the reference's forward keeps
+ * nothing for its backward, which recomputes the softmax statistics). */
+int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, zt_stream_t stream);
+
 /* Attention with the rotary position embedding of its input side fused in: q and k are the
  * projections BEFORE rope.forward (src/rope.zig:21-55; the reference rotates them first,
  * src/model.zig:372-375 and src/decode.zig:244-246); row r sits at absolute position pos + r,

@@ -585,3 +585,35 @@ def test_rope_calls_refuse_bad_arguments(zt, dev):
     rc = L.zt_attn_forward_rope_batched(q.data_ptr(), k.data_ptr(), k.data_ptr(), q.data_ptr(), None,
                                         ws.buf.data_ptr(), 16, B, T, H, Hkv, D, 0, 500000.0, None)
     assert rc == 1 and "workspace" in zt.lib.last_error()
+
+
+def test_forward_keep_hands_its_planes_to_the_backward(zt, dev):
+    """zt_attn_forward_batched_keep + zt_attn_backward_batched with the same workspace give bit for bit what the
+    unpaired calls give; a backward on other tensors after a keep ignores the kept planes."""
+    B, T, H, Hkv, D = 2, 300, 8, 2, 128
+    g = torch.Generator(device=dev).manual_seed(9)
+    q, do = (torch.randn((B, T, H * D), generator=g, device=dev) for _ in range(2))
+    k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
+    zt.lib.load().zt_attn_set_path(0)
+    o0, l0 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+    ref = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D)
+    ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
+    for _ in range(2):  # twice: the note is used once, the second round makes a new one
+        o1, l1 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True, keep=ws)
+        got = zt.attention_backward(q, k, v, o1, l1, do, H, Hkv, D, workspace=ws)
+        assert torch.equal(o1, o0) and torch.equal(l1, l0)
+        for a, b in zip(got, ref):
+            assert torch.equal(a, b)
+    # keep for q, then a backward for other tensors with the same workspace: must not use q's planes
+    q2 = q * 0.5
+    zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True, keep=ws)
+    o2, l2 = zt.attention_forward(q2, k, v, H, Hkv, D, want_lse=True)
+    want2 = zt.attention_backward(q2, k, v, o2, l2, do, H, Hkv, D)
+    got2 = zt.attention_backward(q2, k, v, o2, l2, do, H, Hkv, D, workspace=ws)
+    for a, b in zip(got2, want2):
+        assert torch.equal(a, b)
+    # and the note is gone: the original tensors again, without a new keep
+    got3 = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D, workspace=ws)
+    for a, b in zip(got3, ref):
+        assert torch.equal(a, b)
+    assert zt.lib.tc_status() == 0

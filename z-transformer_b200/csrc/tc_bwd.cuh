@@ -1102,23 +1102,30 @@ inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_hea
 inline int launch_bwd_tc(const float *q, const float *k, const float *v, const float *dout, const float *lse,
                          const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
                          int n_heads, int n_kv_heads, int dim, cudaStream_t stream, const float2 *rope = nullptr,
-                         const float2 *rope_t = nullptr) {
+                         const float2 *rope_t = nullptr, bool qkv_planes_kept = false) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernels' D; the planes' head width
     const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, td);
     const int group = n_heads / n_kv_heads;
     const int wq_src = n_heads * dim, wkv_src = n_kv_heads * dim;
     const int wq = n_heads * td, wkv = n_kv_heads * td;
-    if (cudaMemsetAsync(w.amax_q, 0, w.amax_bytes, stream) != cudaSuccess) {
+    // With the planes of q, k, v kept by the forward (and their maxima beside them), only dout is converted.
+    const size_t n_amax = (size_t)batch * n_kv_heads;
+    if (cudaMemsetAsync(qkv_planes_kept ? w.amax_do : w.amax_q, 0,
+                        qkv_planes_kept ? n_amax * sizeof(uint32_t) : w.amax_bytes, stream) != cudaSuccess) {
         cudaGetLastError();
         return refuse("could not clear the backward workspace header");
     }
     PrepassArgs pa{};
-    pa.n = 4, pa.batch = batch, pa.T = T;
-    pa.t[0] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td, rope};
-    pa.t[1] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td, nullptr};
-    pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
-    pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
+    pa.batch = batch, pa.T = T;
+    pa.t[0] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td, nullptr};
+    pa.n = 1;
+    if (!qkv_planes_kept) {
+        pa.t[1] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td, rope};
+        pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
+        pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
+        pa.n = 4;
+    }
     if (launch_prepass(pa, stream)) return 1;
     BwdMaps m;
     if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, td, 128) ||

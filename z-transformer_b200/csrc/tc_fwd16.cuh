@@ -387,12 +387,20 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
     return d && d->cc_major == 10 && get_encode_tiled() != nullptr;
 }
 
+// `in_backward_workspace`: lay the planes out where the backward's workspace keeps them (tc_bwd.cuh
+// bwd_workspace), so that a backward given the same workspace can use them as they are.
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
-                           const float2 *rope = nullptr) {
+                           const float2 *rope = nullptr, bool in_backward_workspace = false) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
-    const tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
+    tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
+    if (in_backward_workspace) {
+        const BwdWorkspace bw = bwd_workspace(ws, batch, T, n_heads, n_kv_heads, td);
+        w.amax_q = bw.amax_q, w.amax_k = bw.amax_k, w.amax_v = bw.amax_v;  // contiguous; amax_do follows
+        w.amax_bytes = 3 * (size_t)batch * n_kv_heads * sizeof(uint32_t);
+        w.q_planes = bw.q_planes, w.k_planes = bw.k_planes, w.v_planes = bw.v_planes;
+    }
     const int group = n_heads / n_kv_heads;
     const int wq_src = n_heads * dim, wkv_src = n_kv_heads * dim;
     const int wkv = n_kv_heads * td;

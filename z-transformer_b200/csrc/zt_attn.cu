@@ -111,6 +111,44 @@ static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, 
     return 0;
 }
 
+// The forward-for-training call (zt_attn_forward_batched_keep) leaves the f16 planes of q, k, v in the backward's
+// workspace; this is the host-side note of whose planes they are.  One note per device, used at most once, and
+// dropped by any tensor-core backward that touches a workspace.
+namespace {
+struct KeptPlanes {
+    const void *workspace = nullptr;
+    const float *q = nullptr, *k = nullptr, *v = nullptr;
+    int batch = 0, T = 0, n_heads = 0, n_kv_heads = 0, dim = 0;
+    cudaStream_t stream = nullptr;
+    bool valid = false;
+};
+KeptPlanes g_kept[64];
+std::mutex g_kept_mu;
+
+// true (and the note is consumed) when the workspace holds the planes of exactly these tensors
+bool take_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
+                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(g_kept_mu);
+    KeptPlanes &n = g_kept[dev];
+    const bool hit = n.valid && n.workspace == workspace && n.q == q && n.k == k && n.v == v && n.batch == batch &&
+                     n.T == T && n.n_heads == n_heads && n.n_kv_heads == n_kv_heads && n.dim == dim && n.stream == stream;
+    n.valid = false;
+    return hit;
+}
+void note_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
+                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    std::lock_guard<std::mutex> lock(g_kept_mu);
+    KeptPlanes &n = g_kept[dev];
+    n.workspace = workspace, n.q = q, n.k = k, n.v = v;
+    n.batch = batch, n.T = T, n.n_heads = n_heads, n.n_kv_heads = n_kv_heads, n.dim = dim, n.stream = stream;
+    n.valid = true;
+}
+}  // namespace
+
 static int backward_impl(const float *q, const float *k, const float *v, const float *lse,
                          const float *delta, const float *dout, float *dq, float *dk, float *dv,
                          void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
@@ -120,8 +158,9 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
         workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
         n_kv_heads <= tcb::kPrepassMaxGroups && tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
+        const bool kept = take_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, stream);
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
-                             dim, stream);
+                             dim, stream, nullptr, nullptr, kept);
     }
 #endif
     (void)workspace, (void)workspace_bytes;
@@ -323,6 +362,30 @@ int zt_attn_forward_batched(const float *q, const float *k, const float *v, floa
                         (cudaStream_t)stream);
 }
 
+int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
+    if (need_device()) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+#ifndef ZT_NO_TC
+    const size_t need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
+    if (g_path.load() == 0 && need > 0 && workspace && workspace_bytes >= need &&
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
+        tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
+        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true)) return 1;
+        note_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, s);
+        return 0;
+    }
+#endif
+    // shapes the f16-split kernels do not take: the ordinary forward, nothing kept
+    (void)workspace, (void)workspace_bytes;
+    return forward_impl(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, 0, T, s);
+}
+
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     if (batch < 1 || T < 1 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || !zt_attn_dim_ok(dim))
         return 0;
@@ -431,6 +494,7 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
     if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
     bool fused = false;
+    take_kept_planes(nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr);  // (drops any note: this call rewrites planes)
 #ifndef ZT_NO_TC
     fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
             tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);

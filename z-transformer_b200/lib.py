@@ -32,6 +32,7 @@ _SIGNATURES = {
     "zt_attn_forward_batched": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
     "zt_attn_backward_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_backward_workspace_bytes": (_sz, [_i] * 5),
+    "zt_attn_forward_batched_keep": (_i, [_vp] * 6 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_rope_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_forward_rope_batched": (_i, [_vp] * 6 + [_sz] + [_i] * 6 + [_d, _vp]),
     "zt_attn_backward_rope_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 6 + [_d, _vp]),

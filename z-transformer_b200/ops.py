@@ -39,8 +39,21 @@ def _head_config(n_heads, n_kv_heads, head_dim):
         raise InvalidHeadConfig(f"{n_heads}/{n_kv_heads} heads, head_dim {head_dim}")
 
 
-def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False):
-    """Batched attention.forward.  q [B, T, H*D] (or [T, H*D]); returns out (and lse [B, T, H])."""
+class BackwardWorkspace:
+    """Caller-owned scratch of the batched backward for one (batch, T, heads, dim) shape.  Handed to
+    attention_forward as `keep`, it also carries the forward's operand planes of q, k, v over to the backward."""
+
+    def __init__(self, batch, t, n_heads, n_kv_heads, head_dim, device="cuda"):
+        import torch
+        self.shape = (batch, t, n_heads, n_kv_heads, head_dim)
+        self.nbytes = int(_lib.load().zt_attn_backward_workspace_bytes(*self.shape))
+        self.buf = torch.empty(max(self.nbytes, 16), dtype=torch.uint8, device=device)
+
+
+def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False, keep=None):
+    """Batched attention.forward.  q [B, T, H*D] (or [T, H*D]); returns out (and lse [B, T, H]).
+    keep: a BackwardWorkspace of this shape; the backward that is given it next (same q, k, v, unchanged)
+    skips converting them again."""
     import torch
     _head_config(n_heads, n_kv_heads, head_dim)
     squeeze = q.dim() == 2
@@ -56,10 +69,18 @@ def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False)
     lse = torch.empty((B, T, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
     if T == 0:
         return (out[0] if squeeze else out, lse) if want_lse else (out[0] if squeeze else out)
+    if keep is not None and keep.shape != (B, T, n_heads, n_kv_heads, head_dim):
+        raise DimensionMismatch("the workspace was sized for another shape")
     with torch.cuda.device(q.device):
-        rc = _lib.load().zt_attn_forward_batched(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-            lse.data_ptr() if want_lse else None, B, T, n_heads, n_kv_heads, head_dim, _stream(q))
+        if keep is not None:
+            rc = _lib.load().zt_attn_forward_batched_keep(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if want_lse else None,
+                keep.buf.data_ptr() if keep.nbytes else None, keep.nbytes, B, T, n_heads, n_kv_heads, head_dim,
+                _stream(q))
+        else:
+            rc = _lib.load().zt_attn_forward_batched(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                lse.data_ptr() if want_lse else None, B, T, n_heads, n_kv_heads, head_dim, _stream(q))
     if rc != 0:
         raise ConfigRefused(_lib.last_error())
     if squeeze:
@@ -68,8 +89,9 @@ def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False)
     return (out, lse) if want_lse else out
 
 
-def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim):
-    """Batched autograd.attentionBackward from the forward's out and lse; returns dq, dk, dv."""
+def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *, workspace=None):
+    """Batched autograd.attentionBackward from the forward's out and lse; returns dq, dk, dv.
+    workspace: a BackwardWorkspace of this shape (one is allocated per call otherwise)."""
     import torch
     _head_config(n_heads, n_kv_heads, head_dim)
     squeeze = q.dim() == 2
@@ -85,8 +107,13 @@ def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
     L = _lib.load()
-    ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, n_heads, n_kv_heads, head_dim)
-    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device) if ws_bytes else None
+    if workspace is not None:
+        if workspace.shape != (B, T, n_heads, n_kv_heads, head_dim):
+            raise DimensionMismatch("the workspace was sized for another shape")
+        ws_bytes, ws = workspace.nbytes, (workspace.buf if workspace.nbytes else None)
+    else:
+        ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, n_heads, n_kv_heads, head_dim)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device) if ws_bytes else None
     with torch.cuda.device(q.device):
         rc = L.zt_attn_backward_batched(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
@@ -250,9 +277,10 @@ class AttnPipeline:
             b["ws"] = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device=self.device)
             self.buf.append(b)
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
-        self.ready = [torch.cuda.Event() for _ in range(slots)]   # inputs of the slot are on the device
-        self.done = [torch.cuda.Event() for _ in range(slots)]    # kernels of the slot have finished
-        self.free = [torch.cuda.Event() for _ in range(slots)]    # outputs of the slot are on the host
+        ev = lambda: [torch.cuda.Event() for _ in range(slots)]
+        self.ready_f, self.ready_b = ev(), ev()  # q, k, v of the slot are on the device; dout is
+        self.done_f, self.done = ev(), ev()      # the slot's forward has finished; its backward has
+        self.free = ev()                         # the slot's outputs are on the host
 
     def step(self, q, k, v, dout, out, dq, dk, dv, lse=None):
         """q, dout, out, dq: host [B, T, H*D]; k, v, dk, dv: host [B, T, Hkv*D]; lse: host [B, T, H] or
@@ -275,22 +303,29 @@ class AttnPipeline:
             for b in range(B):
                 sl = b % self.slots
                 d = self.buf[sl]
+                # The forward needs q, k, v only and its output can leave while the backward runs, so dout goes
+                # up behind them and out goes down ahead of the gradients: less of the first upload and of
+                # the last download is left outside the overlap.
                 with torch.cuda.stream(self.s_in):
                     if b >= self.slots:
                         self.s_in.wait_event(self.done[sl])  # the slot's inputs have been consumed
                     d["q"].copy_(q[b], non_blocking=True)
                     d["k"].copy_(k[b], non_blocking=True)
                     d["v"].copy_(v[b], non_blocking=True)
+                    self.ready_f[sl].record(self.s_in)
                     d["dout"].copy_(dout[b], non_blocking=True)
-                    self.ready[sl].record(self.s_in)
+                    self.ready_b[sl].record(self.s_in)
                 with torch.cuda.stream(self.s_run):
-                    self.s_run.wait_event(self.ready[sl])
+                    self.s_run.wait_event(self.ready_f[sl])
                     if b >= self.slots:
                         self.s_run.wait_event(self.free[sl])  # the slot's outputs have been read
                     st = self.s_run.cuda_stream
-                    rc = L.zt_attn_forward_batched(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
-                                                   d["out"].data_ptr(), d["lse"].data_ptr(), 1, t, n_heads,
-                                                   n_kv_heads, head_dim, st)
+                    rc = L.zt_attn_forward_batched_keep(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+                                                        d["out"].data_ptr(), d["lse"].data_ptr(),
+                                                        d["ws"].data_ptr() if self.ws_bytes else None, self.ws_bytes,
+                                                        1, t, n_heads, n_kv_heads, head_dim, st)
+                    self.done_f[sl].record(self.s_run)
+                    self.s_run.wait_event(self.ready_b[sl])
                     if rc == 0:
                         rc = L.zt_attn_backward_batched(
                             d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["out"].data_ptr(),
@@ -303,13 +338,14 @@ class AttnPipeline:
                         raise ConfigRefused(_lib.last_error())
                     self.done[sl].record(self.s_run)
                 with torch.cuda.stream(self.s_out):
-                    self.s_out.wait_event(self.done[sl])
+                    self.s_out.wait_event(self.done_f[sl])
                     out[b].copy_(d["out"], non_blocking=True)
+                    if lse is not None:
+                        lse[b].copy_(d["lse"], non_blocking=True)
+                    self.s_out.wait_event(self.done[sl])
                     dq[b].copy_(d["dq"], non_blocking=True)
                     dk[b].copy_(d["dk"], non_blocking=True)
                     dv[b].copy_(d["dv"], non_blocking=True)
-                    if lse is not None:
-                        lse[b].copy_(d["lse"], non_blocking=True)
                     self.free[sl].record(self.s_out)
         self.s_out.synchronize()
         self.s_run.synchronize()
