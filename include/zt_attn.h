@@ -98,7 +98,9 @@ void zt_attn_set_verbose(int on);
 
 /* Which implementation the next launches use: 0 = automatic (the fastest tensor-core
  * kernel the shape allows, CUDA-core kernels elsewhere), 1 = CUDA-core kernels only,
- * 2 = as 0 but the forward uses the 3xTF32 kernel instead of the f16-split one.  For tests
+ * 2 = as 0 but the forward uses the 3xTF32 kernel instead of the f16-split one, 3 = as 0 but
+ * the f16-split forward walks key tiles of 128 (four softmax sets sharing one accumulator;
+ * slower, experimental) instead of 64 (two sets with an accumulator each).  For tests
  * and for bisecting a parity failure; returns the previous value. */
 int zt_attn_set_path(int path);
 

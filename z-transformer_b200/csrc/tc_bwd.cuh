@@ -214,12 +214,12 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t *>(&h);
 }
-// (a, b) -> packed h pair and packed l pair
+// (a, b) -> packed h pair and packed l pair: one paired conversion each way instead of two single ones
 __device__ __forceinline__ void split_pack(float a, float b, uint32_t &hw, uint32_t &lw) {
-    const __half ha = __float2half_rn(a), hb = __float2half_rn(b);
-    const __half2 hh = __halves2half2(ha, hb);
+    const __half2 hh = __floats2half2_rn(a, b);
+    const float2 back = __half22float2(hh);
     hw = *reinterpret_cast<const uint32_t *>(&hh);
-    lw = pack_half2(a - __half2float(ha), b - __half2float(hb));
+    lw = pack_half2(a - back.x, b - back.y);
 }
 
 __device__ __forceinline__ void red_add_v4(float *addr, float4 v) {

@@ -340,6 +340,329 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The same forward on key tiles of 128: every MMA is N = 128 (S) or N = D (P.V), none pays the
+// ~50-clock floor of a narrower instruction.  One O accumulator and one softmax state per row, so the
+// four softmax sets (32 key columns of the tile each) agree on the tile's row maximum through shared
+// memory before anyone exponentiates.  grid as attn_fwd_tc16; 576 threads: 16 softmax warps, TMA, MMA.
+// Measured 20 % slower than the 64-key kernel at head_dim 128, T = 4096 (3.69 ms against 3.08): with one
+// softmax state the row work of a tile (as many instructions per key as before, now with an exchange
+// between the sets in the middle) is a single stage beside the tensor core's 3072 clocks, not two
+// independent ones.  Kept selectable (zt_attn_set_path(3)) as the starting point for a version with
+// two query tiles per CTA; not the default.
+// TMEM: [0,D/2) Qh, [D/2,D) Ql, [D,2D) O, then two S/P tiles of 128 columns.  Shared memory: two K
+// tiles of 128 keys, two V half-tiles of 64 keys (a half is free as soon as its four MMA steps retire).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kWideSoftmaxWarps = 16;
+constexpr int kWideThreads = (kWideSoftmaxWarps + 2) * 32;
+
+struct WideShared {
+    uint64_t full_k[2], free_k[2], full_v[2], free_v[2];
+    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], all_done;
+    uint64_t x_ready[2], sum_ready;  // the sets' exchanges: mbarriers, so that a set that gave up cannot strand the others
+    uint32_t tmem_base;
+    volatile int abort;
+    float xmax[2][4][128];  // [tile parity][set][row]: the sets' maxima over their columns of the tile
+    float xsum[4][128];     // the sets' sums, exchanged once at the end
+};
+__device__ __forceinline__ bool wwait(uint64_t *bar, uint32_t parity, WideShared *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void wgive_up(WideShared *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+template <int D>
+__host__ __device__ constexpr size_t wide_smem_bytes() {
+    return 2 * 2 * (size_t)(128 * D * 2) + 2 * 2 * (size_t)(64 * D * 2) + sizeof(WideShared) + 1024;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWideThreads, 1)
+    attn_fwd_tc16w(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
+    constexpr int NB = D / 64, W2 = D / 2, BN = 128;
+    constexpr int KP = BN * D * 2;   // bytes of one plane of a 128-key K tile
+    constexpr int VP = 64 * D * 2;   // bytes of one plane of a 64-key V half-tile
+    constexpr int cQh = 0, cQl = W2, cO = D, cS0 = 2 * D;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sK = smem;               // slot s: Kh, Kl at sK + s * 2 KP + {0, 1} KP
+    uint8_t *sV = smem + 4 * KP;      // half-slot s: Vh, Vl at sV + s * 2 VP + {0, 1} VP
+    WideShared *sh = reinterpret_cast<WideShared *>(sV + 4 * VP);
+
+    const int warp = threadIdx.x >> 5;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (p.n_heads / p.n_kv_heads);
+    const int t0 = qt * 128;
+    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
+    const int n_tiles = (rows_end + BN - 1) / BN;
+    const int B = p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
+            mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
+            mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], kWideSoftmaxWarps), mbar_init(&sh->pv_done[i], 1);
+            mbar_init(&sh->x_ready[i], kWideSoftmaxWarps);
+        }
+        mbar_init(&sh->a_ready, kWideSoftmaxWarps);
+        mbar_init(&sh->all_done, 1);
+        mbar_init(&sh->sum_ready, kWideSoftmaxWarps);
+        sh->abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == kWideSoftmaxWarps + 1) tmem_alloc(&sh->tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
+    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
+
+    if (warp == kWideSoftmaxWarps) {
+        // ------------------------------------------------------------------ TMA producer: K(j), then the two
+        // halves of V(j).  K(j) goes into the slot S(j-2) has released; V half c into the one half c-2 has.
+        if (elect_one()) {
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
+            int k_issued = 0, v_issued = 0;
+            bool ok = true;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2 && !wwait(&sh->free_k[s], (uint32_t)(((j >> 1) & 1) ^ 1), sh)) { wgive_up(sh, 51); break; }
+                mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
+                tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
+                tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
+                ++k_issued;
+                for (int half = 0; half < 2; ++half) {
+                    const int c = 2 * j + half, vs = c & 1;
+                    if (c >= 2 && !wwait(&sh->free_v[vs], (uint32_t)(((c >> 1) & 1) ^ 1), sh)) { wgive_up(sh, 51); ok = false; break; }
+                    mbar_arrive_expect_tx(&sh->full_v[vs], 2 * VP);
+                    tma_load_4d(sV + vs * 2 * VP, &vmap, &sh->full_v[vs], 0, c * 64, g * NB, b);
+                    tma_load_4d(sV + vs * 2 * VP + VP, &vmap, &sh->full_v[vs], 0, c * 64, g * NB, B + b);
+                    ++v_issued;
+                }
+            }
+            if (sh->abort) {
+                // let the copies in flight land before the CTA's shared memory goes away
+                for (int j = (k_issued > 2 ? k_issued - 2 : 0); j < k_issued; ++j) mbar_wait(&sh->full_k[j & 1], (uint32_t)((j >> 1) & 1));
+                for (int c = (v_issued > 2 ? v_issued - 2 : 0); c < v_issued; ++c) mbar_wait(&sh->full_v[c & 1], (uint32_t)((c >> 1) & 1));
+            }
+        }
+        __syncwarp();
+    } else if (warp == kWideSoftmaxWarps + 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
+            constexpr uint32_t id_o = idesc_f16(128, D, false, true);
+            bool ok = wwait(&sh->a_ready, 0, sh);
+            if (!ok) wgive_up(sh, 52);
+            tc_fence_after();
+            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
+            auto issue_qk = [&](int j) -> bool {  // S of tile j into buffer j & 1
+                const int s = j & 1;
+                if (!wwait(&sh->full_k[s], (uint32_t)((j >> 1) & 1), sh)) return false;
+                tc_fence_after();
+                const uint32_t kh = k_u32 + (uint32_t)(s * 2 * KP);
+                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
+                const uint32_t cS = cS0 + s * BN;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
+                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
+                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                }
+                mma_commit(&sh->free_k[s]);
+                mma_commit(&sh->s_full[s]);
+                return true;
+            };
+            if (ok && !issue_qk(0)) { wgive_up(sh, 53); ok = false; }
+            if (ok && n_tiles > 1 && !issue_qk(1)) { wgive_up(sh, 53); ok = false; }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int buf = j & 1;
+                if (!wwait(&sh->p_full[buf], (uint32_t)((j >> 1) & 1), sh)) { wgive_up(sh, 54); break; }
+                tc_fence_after();
+                const uint32_t cS = cS0 + buf * BN;
+                // P: the set of key columns [32 c, 32 c + 32) left its hi halves in the first 16 columns of its
+                // 32-column window and its lo halves in the last 16; a V half-tile serves four MMA steps
+                for (int half = 0; ok && half < 2; ++half) {
+                    const int c = 2 * j + half, vs = c & 1;
+                    if (!wwait(&sh->full_v[vs], (uint32_t)((c >> 1) & 1), sh)) { wgive_up(sh, 54); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t vh = v_u32 + (uint32_t)(vs * 2 * VP);
+                    const uint64_t mvh = desc_mnmajor_16b(vh, 64 * 128), mvl = desc_mnmajor_16b(vh + VP, 64 * 128);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int kk = half * 4 + k4;
+                        const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                        const uint64_t dvh = desc_advance(mvh, k4 * 2048), dvl = desc_advance(mvl, k4 * 2048);
+                        mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 0 || kk > 0) ? 1 : 0);
+                        mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
+                        mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
+                    }
+                    mma_commit(&sh->free_v[vs]);
+                }
+                if (!ok) break;
+                mma_commit(&sh->pv_done[buf]);
+                if (j == n_tiles - 1) mma_commit(&sh->all_done);  // completes once, after the last P.V
+                // S(j+2) overwrites the P tile this P.V has just read
+                if (j + 2 < n_tiles && !issue_qk(j + 2)) { wgive_up(sh, 53); break; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ softmax: one thread per query row
+        // and 32 of the tile's 128 key columns (set `set`)
+        const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
+        const int t = t0 + tid;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const long long wq = (long long)p.n_heads * D;
+        {
+            // Q's planes -> TMEM: 16 words of each plane's row per set at head_dim 128, sets 0 and 1 at 64
+            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
+            const long long plane = (long long)B * p.T * wq;
+            if (set * 16 < W2) {
+                tcb::row_to_tmem16(p.q_planes + off + set * 32, t < p.T, tmem + lane_base + cQh + set * 16);
+                tcb::row_to_tmem16(p.q_planes + plane + off + set * 32, t < p.T, tmem + lane_base + cQl + set * 16);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->a_ready);
+        }
+        const float cs = p.scale_log2 / (mq * mk);
+        float m_ref = -INFINITY, l = 0.f;  // l: this thread's columns only
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int buf = j & 1;
+            if (!__all_sync(0xffffffffu, wwait(&sh->s_full[buf], (uint32_t)((j >> 1) & 1), sh))) {
+                wgive_up(sh, 55);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t wS = tmem + lane_base + cS0 + buf * BN + set * 32;
+            const int s0 = j * BN + set * 32;
+            const bool diag = (j * BN + BN - 1 > t0);
+            uint32_t r[32];
+            tmem_ld32(wS, r);
+            tmem_wait_ld();
+            float mine = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (!diag || s0 + i <= t) mine = fmaxf(mine, __uint_as_float(r[i]));
+            // the row's maximum over the whole tile: every set posts its own, all read all four
+            // (an arrival for tile j+2 needs S(j+2), hence P.V(j), hence every warp past this wait for tile j:
+            // the barrier of a parity is never more than one phase ahead of a waiter)
+            sh->xmax[buf][set][tid] = mine;
+            mbar_arrive_warp(&sh->x_ready[buf]);
+            if (!__all_sync(0xffffffffu, wwait(&sh->x_ready[buf], (uint32_t)((j >> 1) & 1), sh))) {
+                wgive_up(sh, 57);
+                ok = false;
+                break;
+            }
+            float mt = fmaxf(fmaxf(sh->xmax[buf][0][tid], sh->xmax[buf][1][tid]), fmaxf(sh->xmax[buf][2][tid], sh->xmax[buf][3][tid]));
+            mt *= cs;  // cs > 0
+            float factor = 1.f;
+            if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
+                factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
+                m_ref = mt;
+            }
+            l *= factor;
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O may only be touched once P.V of tile j-1 has retired; the four sets share the row's
+                // factor and take a quarter of its O columns each
+                if (!__all_sync(0xffffffffu, wwait(&sh->pv_done[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), sh))) {
+                    wgive_up(sh, 56);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                constexpr int CW = D / 4;  // 32 or 16
+                if (CW == 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_base + cO + set * CW, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tmem + lane_base + cO + set * CW, o);
+                } else {
+                    uint32_t o[16];
+                    tmem_ld16(tmem + lane_base + cO + set * CW, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st16(tmem + lane_base + cO + set * CW, o);
+                }
+            }
+            const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float psum = 0.f;
+            uint32_t ph[16], pl[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float pe[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    pe[e] = ex2(__uint_as_float(r[i + e]) * cs - mref_safe);
+                    if (diag && s0 + i + e > t) pe[e] = 0.f;
+                    psum += pe[e];
+                }
+                split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
+            }
+            tmem_st16(wS, ph);
+            tmem_st16(wS + 16, pl);
+            l += psum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->p_full[buf]);
+        }
+        // ---- the row's sum over all four sets, then a quarter of its O columns each
+        sh->xsum[set][tid] = l;
+        mbar_arrive_warp(&sh->sum_ready);
+        if (ok && !__all_sync(0xffffffffu, wwait(&sh->sum_ready, 0, sh) && wwait(&sh->all_done, 0, sh))) {
+            wgive_up(sh, 58);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const float lsum = sh->xsum[0][tid] + sh->xsum[1][tid] + sh->xsum[2][tid] + sh->xsum[3][tid];
+            const float inv = 1.f / (lsum * kPScale * mv);
+            constexpr int CW = D / 4;
+            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + set * CW;
+            uint32_t o[32];
+            if (CW == 32) {
+                tmem_ld32(tmem + lane_base + cO + set * CW, o);
+                tmem_wait_ld();
+            } else {
+                uint32_t o16[16];
+                tmem_ld16(tmem + lane_base + cO + set * CW, o16);
+                tmem_wait_ld();  // the registers hold the values only from here on
+#pragma unroll
+                for (int i = 0; i < 16; ++i) o[i] = o16[i];
+            }
+            if (t < p.T && set * CW < p.dim_out) {
+#pragma unroll
+                for (int i = 0; i < CW; i += 4) {
+                    float4 o4;
+                    o4.x = __uint_as_float(o[i]) * inv, o4.y = __uint_as_float(o[i + 1]) * inv;
+                    o4.z = __uint_as_float(o[i + 2]) * inv, o4.w = __uint_as_float(o[i + 3]) * inv;
+                    *reinterpret_cast<float4 *>(orow + i) = o4;
+                }
+            }
+            if (set == 0 && p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (m_ref + log2f(lsum)) * kLn2;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kWideSoftmaxWarps + 1) tmem_dealloc(tmem, 512);
+}
+
 struct Workspace {
     uint32_t *amax_q, *amax_k, *amax_v;
     __half *q_planes, *k_planes, *v_planes;
@@ -372,6 +695,15 @@ inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Para
     return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, p)));
 }
 
+template <int D>
+inline int launch_wide_d(const CUtensorMap &kmap128, const CUtensorMap &vmap64, const Params &p, cudaStream_t stream) {
+    size_t smem = wide_smem_bytes<D>();
+    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
+    if (optin_smem((const void *)attn_fwd_tc16w<D>, smem)) return 1;
+    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
+    return ZT_LAUNCH("attn_fwd_tc16w", stream, (attn_fwd_tc16w<D><<<grid, kWideThreads, smem, stream>>>(kmap128, vmap64, p)));
+}
+
 }  // namespace tcf16
 
 inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
@@ -391,7 +723,7 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 // bwd_workspace), so that a backward given the same workspace can use them as they are.
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
-                           const float2 *rope = nullptr, bool in_backward_workspace = false) {
+                           const float2 *rope = nullptr, bool in_backward_workspace = false, bool wide = false) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
     tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
@@ -415,7 +747,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
     CUtensorMap kmap, vmap;
-    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, 64) ||
+    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
         !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64))
         return refuse("the TMA tensor maps for the forward could not be encoded.");
     tcf16::Params p{};
@@ -425,6 +757,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.dim_out = dim;
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
+    if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
     return td == 64 ? tcf16::launch_d<64>(kmap, vmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, p, stream);
 }
 
