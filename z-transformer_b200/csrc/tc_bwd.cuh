@@ -654,16 +654,29 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 tmem_ld16(wS, rs);
                 tmem_wait_ld();
                 uint32_t ph[8], pl[8];
+                // a step whose 64 query rows all lie past the tile's last key and inside the sequence needs no
+                // mask (most steps of a long sequence); the test is the same for every thread of the CTA
+                const int q_first = walk.qi * BQ;
+                if (q_first >= s0 + 127 && q_first + BQ <= p.T && s0 + 128 <= p.T) {
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
+                    for (int i = 0; i < 16; i += 2) {
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int t = t0 + i + e;
-                        const bool vis = (key <= t) && (t < p.T) && (key < p.T);
-                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
-                        pr[i + e] = vis ? pe : 0.f;
+                        for (int e = 0; e < 2; ++e)
+                            pr[i + e] = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
+                        split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
                     }
-                    split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int t = t0 + i + e;
+                            const bool vis = (key <= t) && (t < p.T) && (key < p.T);
+                            const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
+                            pr[i + e] = vis ? pe : 0.f;
+                        }
+                        split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
+                    }
                 }
                 tmem_st8(wS, ph);
                 tmem_st8(wS + 8, pl);
@@ -960,17 +973,31 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             tmem_wait_ld();
             uint32_t dh[8], dl[8];
             const int key0 = j * BN + set * 16;
+            // a key tile that ends before the query tile begins needs no mask; the same test for the whole CTA
+            if (j * BN + BN - 1 <= t0 && j * BN + BN <= p.T) {
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                float dv[2];
+                for (int i = 0; i < 16; i += 2) {
+                    float dv[2];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = key0 + i + e;
-                    const bool vis = (key <= t) && (key < p.T);
-                    const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
-                    dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
+                    for (int e = 0; e < 2; ++e) {
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
+                        dv[e] = fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f);
+                    }
+                    split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
-                split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float dv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = key0 + i + e;
+                        const bool vis = (key <= t) && (key < p.T);
+                        const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
+                        dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
+                    }
+                    split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
+                }
             }
             tmem_st8(wP, dh);
             tmem_st8(wP + 8, dl);
