@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
     KvShared *sh = reinterpret_cast<KvShared *>(smem + 3 * KP + NS * 4 * QP);
 
     const int warp = threadIdx.x >> 5;
-    const int kt = (int)gridDim.x - 1 - (int)blockIdx.x;  // early key tiles see the most query rows
+    const int kt = (int)blockIdx.x;  // early key tiles see the most query rows: the longest walks start first
     const int g = blockIdx.y, b = blockIdx.z;
     const int group = p.n_heads / p.n_kv_heads;
     const int s0 = kt * 128;
