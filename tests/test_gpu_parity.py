@@ -558,8 +558,12 @@ def test_rope_fused_forward_backward_matches_oracle(zt, dev, oracle, B, T, H, Hk
     ws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
     o, lse = zt.attention_forward_rope(tq, tk, tv, H, Hkv, D, pos=pos, workspace=ws, want_lse=True)
     dq, dk, dv = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
+    # the first backward used the planes the forward left in the workspace; a second one converts q, k, v itself
+    again = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
     torch.cuda.synchronize()
     assert zt.lib.tc_status() == 0
+    for a, b_ in zip((dq, dk, dv), again):
+        assert torch.equal(a, b_)
     for b in range(B):
         qr, kr = oracle.rope_forward(q[b], pos, D), oracle.rope_forward(k[b], pos, D)
         ro, rl = oracle.attention_forward(qr, kr, v[b], H, Hkv, D, want_lse=True, threads=4)

@@ -121,6 +121,9 @@ struct KeptPlanes {
     const float *q = nullptr, *k = nullptr, *v = nullptr;
     int batch = 0, T = 0, n_heads = 0, n_kv_heads = 0, dim = 0;
     cudaStream_t stream = nullptr;
+    bool rope = false;  // the planes of q and k are rotated ones, for (pos, theta)
+    int pos = 0;
+    double theta = 0.0;
     bool valid = false;
 };
 KeptPlanes g_kept[64];
@@ -128,24 +131,28 @@ std::mutex g_kept_mu;
 
 // true (and the note is consumed) when the workspace holds the planes of exactly these tensors
 bool take_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
-                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream, bool rope = false, int pos = 0,
+                      double theta = 0.0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     std::lock_guard<std::mutex> lock(g_kept_mu);
     KeptPlanes &n = g_kept[dev];
     const bool hit = n.valid && n.workspace == workspace && n.q == q && n.k == k && n.v == v && n.batch == batch &&
-                     n.T == T && n.n_heads == n_heads && n.n_kv_heads == n_kv_heads && n.dim == dim && n.stream == stream;
+                     n.T == T && n.n_heads == n_heads && n.n_kv_heads == n_kv_heads && n.dim == dim && n.stream == stream &&
+                     n.rope == rope && (!rope || (n.pos == pos && n.theta == theta));
     n.valid = false;
     return hit;
 }
 void note_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
-                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream) {
+                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream, bool rope = false, int pos = 0,
+                      double theta = 0.0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
     std::lock_guard<std::mutex> lock(g_kept_mu);
     KeptPlanes &n = g_kept[dev];
     n.workspace = workspace, n.q = q, n.k = k, n.v = v;
     n.batch = batch, n.T = T, n.n_heads = n_heads, n.n_kv_heads = n_kv_heads, n.dim = dim, n.stream = stream;
+    n.rope = rope, n.pos = pos, n.theta = theta;
     n.valid = true;
 }
 }  // namespace
@@ -471,8 +478,13 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
 #ifndef ZT_NO_TC
     if ((g_path.load() == 0) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out) &&
-        w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim))
-        return launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, false, false);
+        w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim)) {
+        // the planes (rotated q and k among them) go where the backward keeps its own: the rope backward that
+        // follows with the same workspace, tensors, pos and theta converts only dout
+        if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, false)) return 1;
+        note_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
+        return 0;
+    }
 #endif
     // off the fused path: rotate into the workspace, then the ordinary forward
     if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
@@ -497,12 +509,13 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
     if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
     bool fused = false;
-    take_kept_planes(nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr);  // (drops any note: this call rewrites planes)
+    // (any note is consumed here: this call rewrites or reuses the planes)
+    const bool kept = take_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
 #ifndef ZT_NO_TC
     fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
             tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);
     if (fused && launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, w.inner, batch, T, n_heads, n_kv_heads, dim, s,
-                               w.table, w.table_t))
+                               w.table, w.table_t, kept))
         return 1;
 #endif
     if (!fused) {
