@@ -113,3 +113,37 @@ def test_holder_forward_and_backward_against_the_oracle(host, oracle):
     rdq, rdk, rdv = oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=4)
     for got, ref in ((out, ro), (dq, rdq), (dk, rdk), (dv, rdv)):
         assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-5 + 1e-4 * np.abs(ref))
+
+
+@pytest.mark.gpu
+def test_cpp_pipeline_matches_the_batched_calls(host, zt):
+    """zt::device::AttnPipeline (three streams, two slots, more sequences than slots) against the batched entry
+    points on the same sequences, bit for bit."""
+    import torch
+    host.zth_pipeline_init.argtypes = [U64, U64, U64, U64, C.c_int, C.POINTER(C.c_void_p)]
+    host.zth_pipeline_deinit.argtypes = [C.c_void_p]
+    host.zth_pipeline_step.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 9
+    B, T, H, Hkv, D = 5, 256, 8, 2, 64
+    g = torch.Generator().manual_seed(91)
+    hq, hdo = (torch.randn((B, T, H * D), generator=g).pin_memory() for _ in range(2))
+    hk, hv = (torch.randn((B, T, Hkv * D), generator=g).pin_memory() for _ in range(2))
+    hout, hdq = (torch.full((B, T, H * D), float("nan")).pin_memory() for _ in range(2))
+    hdk, hdv = (torch.full((B, T, Hkv * D), float("nan")).pin_memory() for _ in range(2))
+    hlse = torch.full((B, T, H), float("nan")).pin_memory()
+    h = C.c_void_p()
+    assert host.zth_pipeline_init(T, H, Hkv, D, 0, C.byref(h)) == DEGENERATE
+    assert host.zth_pipeline_init(T, 5, 2, D, 2, C.byref(h)) == REFUSED
+    assert host.zth_pipeline_init(T, H, Hkv, D, 2, C.byref(h)) == OK
+    try:
+        for _ in range(2):
+            rc = host.zth_pipeline_step(h, B, hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), hdo.data_ptr(), hout.data_ptr(),
+                                        hdq.data_ptr(), hdk.data_ptr(), hdv.data_ptr(), hlse.data_ptr())
+            assert rc == OK
+    finally:
+        host.zth_pipeline_deinit(h)
+    dev = torch.device("cuda:0")
+    q, k, v, do = (x.to(dev) for x in (hq, hk, hv, hdo))
+    out, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(q, k, v, out, lse, do, H, Hkv, D)
+    for name, got, want in (("out", hout, out), ("lse", hlse, lse), ("dq", hdq, dq), ("dk", hdk, dk), ("dv", hdv, dv)):
+        assert torch.equal(got, want.cpu()), name

@@ -114,6 +114,138 @@ Error Attn::download(float *dst, uint64_t n_floats, const float *src) const {  /
     return Error::Ok;
 }
 
+// ---- AttnPipeline ----------------------------------------------------------------------------------------
+struct AttnPipeline::Slot {
+    float *q = nullptr, *k = nullptr, *v = nullptr, *dout = nullptr, *out = nullptr, *lse = nullptr;
+    float *dq = nullptr, *dk = nullptr, *dv = nullptr, *delta = nullptr;
+    void *ws = nullptr;
+    cudaEvent_t ready_f = nullptr, ready_b = nullptr, done_f = nullptr, done = nullptr, free_ = nullptr;
+};
+
+void AttnPipeline::deinit() {
+    if (slot_) {
+        for (int i = 0; i < slots_; ++i) {
+            Slot &s = slot_[i];
+            float *bufs[] = {s.q, s.k, s.v, s.dout, s.out, s.lse, s.dq, s.dk, s.dv, s.delta};
+            for (float *b : bufs)
+                if (b) cudaFree(b);
+            if (s.ws) cudaFree(s.ws);
+            cudaEvent_t evs[] = {s.ready_f, s.ready_b, s.done_f, s.done, s.free_};
+            for (cudaEvent_t e : evs)
+                if (e) cudaEventDestroy(e);
+        }
+        delete[] slot_;
+        slot_ = nullptr;
+    }
+    void **streams[] = {&s_in_, &s_run_, &s_out_};
+    for (void **st : streams) {
+        if (*st) cudaStreamDestroy(static_cast<cudaStream_t>(*st));
+        *st = nullptr;
+    }
+    slots_ = 0;
+}
+
+Error AttnPipeline::init(uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim, int slots) {
+    deinit();
+    Error e;
+    if (slots < 1) return Error::DegenerateShape;
+    if ((e = toCInt(t, &c_t)) != Error::Ok || (e = toCInt(n_heads, &c_heads)) != Error::Ok ||
+        (e = toCInt(n_kv_heads, &c_kv_heads)) != Error::Ok || (e = toCInt(dim, &c_dim)) != Error::Ok)
+        return e;
+    if (zt_attn_dim_ok(c_dim) == 0) return Error::ConfigRefused;
+    if (c_heads <= 0 || c_kv_heads <= 0 || c_heads % c_kv_heads != 0 || n_heads > 65535) return Error::ConfigRefused;
+    if ((e = bytesFor(Kind::query_headed, t, n_heads, n_kv_heads, dim, &qh_)) != Error::Ok) return e;
+    if ((e = bytesFor(Kind::kv_headed, t, n_heads, n_kv_heads, dim, &kvh_)) != Error::Ok) return e;
+    if ((e = bytesFor(Kind::per_row, t, n_heads, n_kv_heads, dim, &pr_)) != Error::Ok) return e;
+    ws_bytes_ = zt_attn_backward_workspace_bytes(1, c_t, c_heads, c_kv_heads, c_dim);
+    slot_ = new Slot[slots];
+    slots_ = slots;
+    cudaStream_t st[3];
+    for (int i = 0; i < 3; ++i)
+        if (cudaStreamCreateWithFlags(&st[i], cudaStreamNonBlocking) != cudaSuccess) {
+            for (int j = 0; j < i; ++j) cudaStreamDestroy(st[j]);
+            deinit();
+            return Error::DeviceAllocFailed;
+        }
+    s_in_ = st[0], s_run_ = st[1], s_out_ = st[2];
+    for (int i = 0; i < slots; ++i) {
+        Slot &s = slot_[i];
+        float **bufs[] = {&s.q, &s.dout, &s.out, &s.dq, &s.k, &s.v, &s.dk, &s.dv, &s.lse, &s.delta};
+        const uint64_t size[] = {qh_, qh_, qh_, qh_, kvh_, kvh_, kvh_, kvh_, pr_, pr_};
+        for (int b = 0; b < 10; ++b)
+            if (alloc(size[b], bufs[b]) != Error::Ok) {
+                deinit();
+                return Error::DeviceAllocFailed;
+            }
+        if (ws_bytes_ && cudaMalloc(&s.ws, ws_bytes_) != cudaSuccess) {
+            deinit();
+            return Error::DeviceAllocFailed;
+        }
+        cudaEvent_t *evs[] = {&s.ready_f, &s.ready_b, &s.done_f, &s.done, &s.free_};
+        for (cudaEvent_t *ev : evs)
+            if (cudaEventCreateWithFlags(ev, cudaEventDisableTiming) != cudaSuccess) {
+                deinit();
+                return Error::DeviceAllocFailed;
+            }
+    }
+    return Error::Ok;
+}
+
+Error AttnPipeline::step(int batch, const float *q, const float *k, const float *v, const float *dout, float *out,
+                         float *dq, float *dk, float *dv, float *lse) {
+    if (!slot_ || batch < 1) return Error::DegenerateShape;
+    cudaStream_t s_in = static_cast<cudaStream_t>(s_in_), s_run = static_cast<cudaStream_t>(s_run_),
+                 s_out = static_cast<cudaStream_t>(s_out_);
+    const uint64_t qf = qh_ / sizeof(float), kf = kvh_ / sizeof(float), pf = pr_ / sizeof(float);
+    bool failed = false, refused = false;
+    auto copy = [&](void *dst, const void *src, uint64_t bytes, cudaMemcpyKind kind, cudaStream_t st) {
+        if (cudaMemcpyAsync(dst, src, bytes, kind, st) != cudaSuccess) failed = true;
+    };
+    for (int b = 0; b < batch && !failed && !refused; ++b) {
+        Slot &s = slot_[b % slots_];
+        const bool reused = b >= slots_;
+        // The forward needs q, k, v only and its output can leave while the backward runs: dout goes up behind
+        // them and out goes down ahead of the gradients.
+        if (reused) cudaStreamWaitEvent(s_in, s.done, 0);  // the slot's inputs have been consumed
+        copy(s.q, q + b * qf, qh_, cudaMemcpyHostToDevice, s_in);
+        copy(s.k, k + b * kf, kvh_, cudaMemcpyHostToDevice, s_in);
+        copy(s.v, v + b * kf, kvh_, cudaMemcpyHostToDevice, s_in);
+        cudaEventRecord(s.ready_f, s_in);
+        copy(s.dout, dout + b * qf, qh_, cudaMemcpyHostToDevice, s_in);
+        cudaEventRecord(s.ready_b, s_in);
+
+        cudaStreamWaitEvent(s_run, s.ready_f, 0);
+        if (reused) cudaStreamWaitEvent(s_run, s.free_, 0);  // the slot's outputs have been read
+        if (zt_attn_forward_batched_keep(s.q, s.k, s.v, s.out, s.lse, s.ws, ws_bytes_, 1, c_t, c_heads, c_kv_heads, c_dim,
+                                         reinterpret_cast<zt_stream_t>(s_run)))
+            refused = true;
+        cudaEventRecord(s.done_f, s_run);
+        cudaStreamWaitEvent(s_run, s.ready_b, 0);
+        if (!refused && zt_attn_backward_batched(s.q, s.k, s.v, s.out, s.lse, s.dout, s.dq, s.dk, s.dv, s.delta, s.ws,
+                                                 ws_bytes_, 1, c_t, c_heads, c_kv_heads, c_dim,
+                                                 reinterpret_cast<zt_stream_t>(s_run)))
+            refused = true;
+        cudaEventRecord(s.done, s_run);
+
+        cudaStreamWaitEvent(s_out, s.done_f, 0);
+        copy(out + b * qf, s.out, qh_, cudaMemcpyDeviceToHost, s_out);
+        if (lse) copy(lse + b * pf, s.lse, pr_, cudaMemcpyDeviceToHost, s_out);
+        cudaStreamWaitEvent(s_out, s.done, 0);
+        copy(dq + b * qf, s.dq, qh_, cudaMemcpyDeviceToHost, s_out);
+        copy(dk + b * kf, s.dk, kvh_, cudaMemcpyDeviceToHost, s_out);
+        copy(dv + b * kf, s.dv, kvh_, cudaMemcpyDeviceToHost, s_out);
+        cudaEventRecord(s.free_, s_out);
+    }
+    const bool sync_ok = cudaStreamSynchronize(s_in) == cudaSuccess && cudaStreamSynchronize(s_run) == cudaSuccess &&
+                         cudaStreamSynchronize(s_out) == cudaSuccess;
+    if (refused) return Error::ConfigRefused;
+    if (failed || !sync_ok) {
+        cudaGetLastError();
+        return Error::DeviceTransferFailed;
+    }
+    return Error::Ok;
+}
+
 }  // namespace device
 }  // namespace zt
 
@@ -149,4 +281,21 @@ int zth_attn_forward_at(const void *handle, int group_q, int max_tile, int q_off
 int zth_attn_backward(const void *handle, int max_tile) { return (int)static_cast<const Attn *>(handle)->backward(max_tile); }
 int zth_attn_upload(const void *handle, float *dst, const float *src, uint64_t n) { return (int)static_cast<const Attn *>(handle)->upload(dst, src, n); }
 int zth_attn_download(const void *handle, float *dst, uint64_t n, const float *src) { return (int)static_cast<const Attn *>(handle)->download(dst, n, src); }
+
+int zth_pipeline_init(uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim, int slots, void **handle) {
+    zt::device::AttnPipeline *p = new zt::device::AttnPipeline();
+    const Error e = p->init(t, n_heads, n_kv_heads, dim, slots);
+    if (e != Error::Ok) {
+        delete p;
+        *handle = nullptr;
+        return (int)e;
+    }
+    *handle = p;
+    return 0;
+}
+void zth_pipeline_deinit(void *handle) { delete static_cast<zt::device::AttnPipeline *>(handle); }
+int zth_pipeline_step(void *handle, int batch, const float *q, const float *k, const float *v, const float *dout,
+                      float *out, float *dq, float *dk, float *dv, float *lse) {
+    return (int)static_cast<zt::device::AttnPipeline *>(handle)->step(batch, q, k, v, dout, out, dq, dk, dv, lse);
+}
 }

@@ -82,5 +82,34 @@ private:
     void deinitPartial(int taken);
 };
 
+// Forward + backward of a run of equally shaped sequences whose tensors live in (pinned) host memory, with the
+// upload of sequence b+1, the kernels of b and the download of b-1 overlapped on three streams over `slots`
+// sets of device buffers.  The reference's trainer drives device.Attn one sequence at a time, each step waiting
+// for the one before (src/model.zig:481-514); over PCIe the copies take longer than the kernels.  Uses the
+// batched entry points (batch 1): the forward keeps its operand planes for the backward and nothing is
+// recomputed.  No reference counterpart.
+class AttnPipeline {
+public:
+    AttnPipeline() = default;
+    AttnPipeline(const AttnPipeline &) = delete;
+    AttnPipeline &operator=(const AttnPipeline &) = delete;
+    ~AttnPipeline() { deinit(); }
+
+    Error init(uint64_t t, uint64_t n_heads, uint64_t n_kv_heads, uint64_t dim, int slots);
+    void deinit();
+    // q, dout, out, dq: host [batch][t][n_heads * dim]; k, v, dk, dv: host [batch][t][n_kv_heads * dim];
+    // lse: host [batch][t][n_heads] or null.  Returns when every result is in host memory.
+    Error step(int batch, const float *q, const float *k, const float *v, const float *dout, float *out, float *dq,
+               float *dk, float *dv, float *lse);
+
+private:
+    struct Slot;
+    Slot *slot_ = nullptr;
+    int slots_ = 0;
+    int c_t = 0, c_heads = 0, c_kv_heads = 0, c_dim = 0;
+    uint64_t qh_ = 0, kvh_ = 0, pr_ = 0, ws_bytes_ = 0;
+    void *s_in_ = nullptr, *s_run_ = nullptr, *s_out_ = nullptr;  // cudaStream_t
+};
+
 }  // namespace device
 }  // namespace zt
