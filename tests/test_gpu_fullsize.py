@@ -42,7 +42,9 @@ def randn(shape, seed, dev):
 
 
 @pytest.mark.parametrize("B,T,H,Hkv,D", [(8, 2048, 32, 8, 128), (8, 4096, 32, 8, 32), (8, 512, 32, 8, 256),
-                                         (8, 1024, 32, 8, 64)])
+                                         (8, 1024, 32, 8, 64),
+                                         (8, 4096, 32, 8, 128),     # the headline point of the sweep
+                                         (1, 32768, 32, 8, 128)])   # the long-context prefill
 def test_prefill_sweep_point(zt, dev, oracle, B, T, H, Hkv, D):
     q, k, v, do = (randn((B, T, n * D), s, dev) for n, s in ((H, 1), (Hkv, 2), (Hkv, 3), (H, 4)))
     o, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
