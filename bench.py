@@ -598,12 +598,43 @@ def run_all_configs(args):
                "fwd_ms": ms_f, "fwd_tflops": F / ms_f / 1e9, "fwd_frac_tf32_peak": F / ms_f / 1e9 / tf32_peak,
                "fwd_path": path_f}
         if backward:
+            bws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
+
             def bwd():
-                zt.attention_backward(q, k, v, state["o"], state["lse"], do, H, Hkv, D)
+                zt.attention_backward(q, k, v, state["o"], state["lse"], do, H, Hkv, D, workspace=bws)
             ms_b = timed(bwd, reps)
             out.update({"bwd_ms": ms_b, "bwd_tflops": 2.5 * F / ms_b / 1e9, "bwd_path": zt.lib.last_path(),
                         "fwd_bwd_tflops": 3.5 * F / (ms_f + ms_b) / 1e9,
                         "fwd_bwd_frac_tf32_peak": 3.5 * F / (ms_f + ms_b) / 1e9 / tf32_peak})
+            # The step as a trainer issues it: the forward keeps its operand planes for the backward, and the
+            # eight launches are captured once into a CUDA graph (all scratch is the caller's workspace).
+            L = zt.lib.load()
+            o_, dq_ = torch.empty_like(q), torch.empty_like(q)
+            dk_, dv_ = torch.empty_like(k), torch.empty_like(v)
+            lse_, delta_ = (torch.empty((B, T, H), device=dev) for _ in range(2))
+
+            def pair(stream):
+                rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), o_.data_ptr(),
+                                                    lse_.data_ptr(), bws.buf.data_ptr() if bws.nbytes else None,
+                                                    bws.nbytes, B, T, H, Hkv, D, stream)
+                rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), o_.data_ptr(),
+                                                 lse_.data_ptr(), do.data_ptr(), dq_.data_ptr(), dk_.data_ptr(),
+                                                 dv_.data_ptr(), delta_.data_ptr(),
+                                                 bws.buf.data_ptr() if bws.nbytes else None, bws.nbytes, B, T, H, Hkv, D,
+                                                 stream)
+                if rc != 0:
+                    raise RuntimeError(zt.lib.last_error())
+
+            if out["bwd_path"] == "tcgen05":
+                pair(torch.cuda.current_stream(dev).cuda_stream)
+                torch.cuda.synchronize(dev)
+                graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream(dev)
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(graph, stream=side):
+                        pair(torch.cuda.current_stream(dev).cuda_stream)
+                ms_g = timed(graph.replay, max(reps, 20))
+                out.update({"step_graph_ms": ms_g, "step_graph_tflops": 3.5 * F / ms_g / 1e9,
+                            "step_graph_frac_tf32_peak": 3.5 * F / ms_g / 1e9 / tf32_peak})
         return out
 
     # 1. GPT-mini forward (replicated on every rank: it does not shard)
@@ -613,8 +644,9 @@ def run_all_configs(args):
     for D in (32, 64, 128, 256):
         for T in (512, 1024, 2048, 4096):
             r = prefill(f"2 sweep D{D} T{T}", Bs, T, 32, 8, D, True, 5 if D < 256 else 2)
-            for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops"):
-                r[key + "_job"] = r[key] * world
+            for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops", "step_graph_tflops"):
+                if key in r:
+                    r[key + "_job"] = r[key] * world
             emit(**r, scaling="strong (batch 8 split over ranks)")
     # 3. Llama-3 decode, sequences split over the ranks
     def decode(tag, B, n_ctx, nk_host):
@@ -643,8 +675,9 @@ def run_all_configs(args):
     # 4. 32k prefill, KV heads split over the ranks
     sh = zt.sharding.shard_kv_heads(32, 8, world, rank)
     r = prefill("4 prefill T32768 (KV heads sharded)", 1, 32768, sh.n_heads, sh.n_kv_heads, 128, True, 2)
-    for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops"):
-        r[key + "_job"] = r[key] * world
+    for key in ("fwd_tflops", "bwd_tflops", "fwd_bwd_tflops", "step_graph_tflops"):
+        if key in r:
+            r[key + "_job"] = r[key] * world
     emit(**r, scaling="strong (8 KV heads split over ranks)")
     # 5. ragged decode: lengths uniform in [1, 16384], longest-first balanced over the ranks
     rng = np.random.default_rng(0)

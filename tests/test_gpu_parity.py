@@ -621,3 +621,44 @@ def test_forward_keep_hands_its_planes_to_the_backward(zt, dev):
     for a, b in zip(got3, ref):
         assert torch.equal(a, b)
     assert zt.lib.tc_status() == 0
+
+
+def test_training_pair_is_capturable_in_a_cuda_graph(zt, dev):
+    """zt_attn_forward_batched_keep + zt_attn_backward_batched take all their scratch from the caller's workspace and
+    only enqueue on the caller's stream, so a step can be captured once and replayed: short sequences are bound by
+    the eight launches of a step, not by the kernels."""
+    B, T, H, Hkv, D = 2, 512, 8, 2, 128
+    g = torch.Generator(device=dev).manual_seed(13)
+    q, do = (torch.randn((B, T, H * D), generator=g, device=dev) for _ in range(2))
+    k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
+    L = zt.lib.load()
+    L.zt_attn_set_path(0)
+    ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
+    out, dq = torch.empty_like(q), torch.empty_like(q)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    lse, delta = (torch.empty((B, T, H), device=dev) for _ in range(2))
+
+    def step(stream):
+        rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                            ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream)
+        rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                         do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+                                         ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream)
+        assert rc == 0, zt.lib.last_error()
+
+    step(torch.cuda.current_stream(dev).cuda_stream)  # eager: also sets the kernels' shared-memory attributes
+    torch.cuda.synchronize()
+    want = [x.clone() for x in (out, lse, dq, dk, dv)]
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            step(torch.cuda.current_stream(dev).cuda_stream)
+    for x in (out, lse, dq, dk, dv):
+        x.fill_(float("nan"))
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for got, ref in zip((out, lse, dq, dk, dv), want):
+        assert torch.equal(got, ref)
+    assert zt.lib.tc_status() == 0
