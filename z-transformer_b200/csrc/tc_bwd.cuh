@@ -1087,7 +1087,7 @@ inline BwdWorkspace bwd_workspace(void *base, int batch, int T, int n_heads, int
 
 inline bool tc_bwd_supported(int batch, int T, int dim, const void *q, const void *k, const void *v,
                              const void *dout, const void *dq, const void *dk, const void *dv) {
-    if (!(dim == 32 || dim == 64 || dim == 128) || T < 128 || batch < 1) return false;
+    if (!(dim == 32 || dim == 64 || dim == 96 || dim == 128) || T < 128 || batch < 1) return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(q) || !al(k) || !al(v) || !al(dout) || !al(dq) || !al(dk) || !al(dv)) return false;
     const DeviceInfo *d = device_info();
@@ -1117,9 +1117,11 @@ inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t st
 
 }  // namespace tcb
 
-// head_dim 32 runs on the 64-wide tiles: its planes carry every head zero-padded to 64 columns (the
-// MMAs would cost the same at half the width, see the clock floor above), outputs keep their 32.
-inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : dim; }
+// head_dim 32 runs on the 64-wide tiles and head_dim 96 on the 128-wide ones: the planes carry every head
+// zero-padded to the tile's width (at 32 the MMAs would cost the same at half the width, see the clock floor
+// above; at 96 a quarter of the tensor work is padding), outputs keep their own width.  The kernels write
+// their outputs in 32-column (128-wide tiles) or 16/32-column (64-wide) pieces, which is why only these two.
+inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : (dim == 96 ? 128 : dim); }
 
 inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).total_bytes;

@@ -712,7 +712,7 @@ inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_h
 
 inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_keys, const void *q, const void *k,
                                const void *v, const void *out) {
-    if (!(dim == 32 || dim == 64 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
+    if (!(dim == 32 || dim == 64 || dim == 96 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(q) || !al(k) || !al(v) || !al(out)) return false;
     const DeviceInfo *d = device_info();

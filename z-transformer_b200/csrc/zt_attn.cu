@@ -106,7 +106,8 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
 
 static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, int dim) {
 #ifndef ZT_NO_TC
-    if ((dim == 32 || dim == 64 || dim == 128) && T >= 128) return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+    if ((dim == 32 || dim == 64 || dim == 96 || dim == 128) && T >= 128)
+        return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
 #endif
     (void)batch, (void)n_heads, (void)n_kv_heads;
     return 0;
@@ -508,14 +509,16 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     cudaStream_t s = (cudaStream_t)stream;
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
     if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
-    bool fused = false;
+    bool fused = false, dq_in_kernel = false;
     // (any note is consumed here: this call rewrites or reuses the planes)
     const bool kept = take_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
 #ifndef ZT_NO_TC
     fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
             tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);
+    // the dQ kernel's epilogue rotates whole 16- or 32-column pieces: not at head_dim 96, whose halves are 48 wide
+    dq_in_kernel = fused && dim != 96;
     if (fused && launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, w.inner, batch, T, n_heads, n_kv_heads, dim, s,
-                               w.table, w.table_t, kept))
+                               w.table, dq_in_kernel ? w.table_t : nullptr, kept))
         return 1;
 #endif
     if (!fused) {
@@ -526,7 +529,7 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     }
     // the gradients of the unrotated q and k: R^T.  The tensor-core dQ kernel applies it as it writes dq; dk
     // (a quarter of dq's bytes here, flushed from its accumulator many times) takes a pass in place.
-    if (!fused && launch_rope_apply(dq, dq, w.table, batch, T, n_heads * dim, dim, true, s)) return 1;
+    if (!dq_in_kernel && launch_rope_apply(dq, dq, w.table, batch, T, n_heads * dim, dim, true, s)) return 1;
     return launch_rope_apply(dk, dk, w.table, batch, T, n_kv_heads * dim, dim, true, s);
 }
 
