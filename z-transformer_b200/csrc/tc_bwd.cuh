@@ -617,7 +617,11 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             mbar_arrive_warp(&sh->a_ready);
         }
         const float cs = p.scale_log2 / (mq * mk);
-        const float dfac = mdo * mv * c1;
+        // P is wanted times p_scale (for its 16-bit split) and dS without it: the scale rides in the exponent
+        // (lse minus log2 p_scale) and leaves through dP's and delta's factors
+        const float lse_shift = log2f(p.p_scale);
+        const float c1p = c1 / p.p_scale;
+        const float dfac = mdo * mv * c1p;
         // lse (set 0's first 64 threads) and delta (set 1's) of a step's 64 query rows, fetched one step
         // ahead into a register and published through shared memory
         auto fetch = [&](const Walk &w, int it) -> float {
@@ -625,7 +629,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             const int t = w.qi * BQ + tid;
             if (t >= p.T) return 0.f;
             const long long idx = ((long long)b * p.T + t) * p.n_heads + g * group + w.hh;
-            return set == 0 ? __ldg(p.lse + idx) * kLog2e : __ldg(p.delta + idx) * dfac;
+            return set == 0 ? __ldg(p.lse + idx) * kLog2e - lse_shift : __ldg(p.delta + idx) * dfac;
         };
         auto publish = [&](int it, float v) {
             if (threadIdx.x < 256 && tid < 64) (set == 0 ? sh->lse2 : sh->dels)[it & 1][tid] = v;
@@ -663,7 +667,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
                             pr[i + e] = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
-                        split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
+                        split_pack(pr[i], pr[i + 1], ph[i >> 1], pl[i >> 1]);
                     }
                 } else {
 #pragma unroll
@@ -675,7 +679,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                             const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
                             pr[i + e] = vis ? pe : 0.f;
                         }
-                        split_pack(pr[i] * p.p_scale, pr[i + 1] * p.p_scale, ph[i >> 1], pl[i >> 1]);
+                        split_pack(pr[i], pr[i + 1], ph[i >> 1], pl[i >> 1]);
                     }
                 }
                 tmem_st8(wS, ph);
@@ -700,7 +704,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                     float dv[2];
 #pragma unroll
                     for (int e = 0; e < 2; ++e)
-                        dv[e] = fminf(fmaxf(pr[i + e] * (__uint_as_float(rd[i + e]) * c1 - sh->dels[it & 1][set * 16 + i + e]), -65000.f), 65000.f);
+                        dv[e] = fminf(fmaxf(pr[i + e] * (__uint_as_float(rd[i + e]) * c1p - sh->dels[it & 1][set * 16 + i + e]), -65000.f), 65000.f);
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
                 tmem_st8(wP, dh);

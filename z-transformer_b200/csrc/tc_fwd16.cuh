@@ -33,7 +33,7 @@ using tcb::row_to_tmem;
 using tcb::split_pack;
 
 constexpr int kThreads = 320;  // 8 softmax warps (two sets of four), 1 TMA warp, 1 MMA warp
-constexpr float kPScale = 128.0f;
+constexpr float kPScale = 128.0f;  // 2^7: P is multiplied by it before its 16-bit split (the 7.0f in the kernels)
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Shared {
@@ -63,6 +63,34 @@ __device__ __forceinline__ bool fwait(uint64_t *bar, uint32_t parity, Shared *sh
 __device__ __forceinline__ void fgive_up(Shared *sh, int code) {
     sh->abort = code;
     atomicMax(&g_tc_status, code);
+}
+
+// The row work on 32 score columns, in two forms chosen per tile (the same for every thread of the CTA): a tile
+// that ends before the query tile begins needs no mask.  P comes out already multiplied by kPScale (the scale
+// rides in the exponent: `off` is the reference maximum minus log2 kPScale), split into packed f16 pairs.
+template <bool MASK>
+__device__ __forceinline__ float row_max32(const uint32_t (&r)[32], int key0, int t, float m) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        if (!MASK || key0 + i <= t) m = fmaxf(m, __uint_as_float(r[i]));
+    return m;
+}
+template <bool MASK>
+__device__ __forceinline__ float row_exp32(const uint32_t (&r)[32], int key0, int t, float cs, float off,
+                                           uint32_t (&ph)[16], uint32_t (&pl)[16]) {
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float pe[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            pe[e] = ex2(__uint_as_float(r[i + e]) * cs - off);
+            if (MASK && key0 + i + e > t) pe[e] = 0.f;
+            sum += pe[e];
+        }
+        split_pack(pe[0], pe[1], ph[i >> 1], pl[i >> 1]);
+    }
+    return sum;
 }
 
 template <int D>
@@ -225,11 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             tmem_ld32(tmem + lane_base + cS + 32, r1);
             tmem_wait_ld();
             float mt = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                if (!diag || s0 + i <= t) mt = fmaxf(mt, __uint_as_float(r0[i]));
-                if (!diag || s0 + 32 + i <= t) mt = fmaxf(mt, __uint_as_float(r1[i]));
-            }
+            if (diag) mt = row_max32<true>(r1, s0 + 32, t, row_max32<true>(r0, s0, t, mt));
+            else mt = row_max32<false>(r1, s0 + 32, t, row_max32<false>(r0, s0, t, mt));
             mt *= cs;  // cs > 0
             float factor = 1.f;
             if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
@@ -255,34 +280,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tmem_st32(tmem + lane_base + cO + c, r);
                 }
             }
-            const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float psum = 0.f;
+            // l is kept in P's units (times kPScale), like O
+            const float off = ((m_ref == -INFINITY) ? 0.f : m_ref) - 7.0f;  // log2 kPScale
+            float psum;
             {
                 uint32_t ph[16], pl[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pe[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        pe[e] = ex2(__uint_as_float(r0[i + e]) * cs - mref_safe);
-                        if (diag && s0 + i + e > t) pe[e] = 0.f;
-                        psum += pe[e];
-                    }
-                    split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
-                }
+                psum = diag ? row_exp32<true>(r0, s0, t, cs, off, ph, pl) : row_exp32<false>(r0, s0, t, cs, off, ph, pl);
                 tmem_st16(tmem + lane_base + cS, ph);
                 tmem_st16(tmem + lane_base + cS + 16, pl);
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pe[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        pe[e] = ex2(__uint_as_float(r1[i + e]) * cs - mref_safe);
-                        if (diag && s0 + 32 + i + e > t) pe[e] = 0.f;
-                        psum += pe[e];
-                    }
-                    split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
-                }
+                psum += diag ? row_exp32<true>(r1, s0 + 32, t, cs, off, ph, pl) : row_exp32<false>(r1, s0 + 32, t, cs, off, ph, pl);
                 tmem_st16(tmem + lane_base + cS + 32, ph);
                 tmem_st16(tmem + lane_base + cS + 48, pl);
             }
@@ -307,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float mm = fmaxf(m0, m1);  // m0 is finite: key 0 is visible to every row
             const float w0 = ex2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
             const float lsum = w0 * l0 + w1 * l1;
-            const float inv = 1.f / (lsum * kPScale * mv);
+            const float inv = 1.f / (lsum * mv);  // lsum, like O, carries kPScale
             const float f0 = w0 * inv, f1 = w1 * inv;
             // set s writes columns [s D/2, (s+1) D/2) of the row
             float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out +
@@ -332,7 +338,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
             }
-            if (set == 0 && p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum)) * kLn2;
+            if (set == 0 && p.lse && t < p.T)
+                p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum) - 7.0f) * kLn2;
         }
     }
     tc_fence_before();
