@@ -166,6 +166,35 @@ def dist_env():
     return rank, world, local
 
 
+def bind_near_gpu(local: int, world: int) -> str:
+    """With several ranks on one host, run this rank on the CPUs NVML names as the GPU's own (its NUMA node), so
+    that the pinned host buffers it allocates afterwards are first touched there and its copies do not cross the
+    socket interconnect.  Returns a note for the JSON line.  Single-rank runs keep every CPU (the CPU baseline
+    wants them)."""
+    if world <= 1:
+        return "unbound"
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = local
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if local < len(ids) and ids[local].isdigit():
+                idx = int(ids[local])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        n_words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, n_words)
+        cpus = {w * 64 + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if not cpus:
+            return "unbound (no overlap with the allowed CPUs)"
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} CPUs of the GPU's NUMA node"
+    except Exception as e:  # NVML binding absent, or the call is not supported here
+        return f"unbound ({type(e).__name__})"
+
+
 # ------------------------------------------------------------------------------------------------
 # reference arm: the CPU port on a bounded sample
 # ------------------------------------------------------------------------------------------------
@@ -241,6 +270,7 @@ def run_ours(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    cpu_binding = bind_near_gpu(local, world)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     zt = importlib.import_module("z-transformer_b200")
@@ -522,7 +552,7 @@ def run_ours(args):
                        "gather": bool(args.gather and world > 1)},
             "roofline": roofline, "issued_mma": issued, "rope": rope, "kernels": klist, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms,
+                    "ms_per_step": e2e_ms, "host_cpus": cpu_binding,
                     "api": "zt.AttnPipeline.step: per sequence, pinned host -> device, zt_attn_forward_batched + "
                            "zt_attn_backward_batched, device -> pinned host; three streams, three buffer slots"},
             "e2e_sync": {"value": e2e_sync_value, "unit": "TFLOP/s", "ms_per_step": e2e_sync_ms,
