@@ -38,7 +38,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 struct Shared {
     uint64_t full_k[3], free_k[3], full_v[3], free_v[3];
-    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], all_done;
+    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], all_done, q_full;
     uint32_t tmem_base;
     volatile int abort;
     float fin_m[2][128], fin_l[2][128];  // each set's reference maximum and sum, for the final merge
@@ -95,7 +95,8 @@ __device__ __forceinline__ float row_exp32(const uint32_t (&r)[32], int key0, in
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-    attn_fwd_tc16(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
+    attn_fwd_tc16(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const __grid_constant__ CUtensorMap qmap, const Params p) {
     constexpr int NB = D / 64, W2 = D / 2, BN = 64;
     constexpr int KP = BN * D * 2;  // bytes of one plane of a key tile
     constexpr int cQh = 0, cQl = W2, cO0 = D, cS0 = 3 * D;  // O of set s at cO0 + s D, S/P of buffer i at cS0 + 64 i
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init(&sh->a_ready, 8);
         for (int i = 0; i < 2; ++i) mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 4), mbar_init(&sh->pv_done[i], 1);
         mbar_init(&sh->all_done, 1);
+        mbar_init(&sh->q_full, 1);
         sh->abort = 0;
         mbar_fence_init();
     }
@@ -137,25 +139,42 @@ __global__ void __launch_bounds__(kThreads, 1)
         // ------------------------------------------------------------------ TMA producer
         // K of tile j is free again once S(j) has retired, two tiles before its V: rings of their own
         if (elect_one()) {
-            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
-            int issued = 0;  // half-steps: K of tile issued / 2, then its V
-            for (int j = 0; j < n_tiles; ++j) {
+            tma_prefetch_desc(&qmap), tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
+            // the query tile's two planes, staged in V's first two slots until the row threads have moved
+            // them into TMEM: one bulk copy each instead of a strided read per thread
+            mbar_arrive_expect_tx(&sh->q_full, 4 * KP);
+            tma_load_4d(sV, &qmap, &sh->q_full, 0, t0, h * NB, b);
+            tma_load_4d(sV + 2 * KP, &qmap, &sh->q_full, 0, t0, h * NB, B + b);
+            int n_k = 0, n_v = 0;  // tiles issued
+            bool live = true;
+            auto load_k = [&](int j) {
                 const int s = j % 3;
-                const uint32_t free_par = (uint32_t)(((j / 3) & 1) ^ 1);
-                if (j >= 3 && !fwait(&sh->free_k[s], free_par, sh)) { fgive_up(sh, 41); break; }
+                if (j >= 3 && !fwait(&sh->free_k[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { fgive_up(sh, 41), live = false; return; }
                 mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
                 tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
                 tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
-                ++issued;
-                if (j >= 3 && !fwait(&sh->free_v[s], free_par, sh)) { fgive_up(sh, 41); break; }
+                ++n_k;
+            };
+            auto load_v = [&](int j) {
+                const int s = j % 3;
+                if (j >= 3 && !fwait(&sh->free_v[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { fgive_up(sh, 41), live = false; return; }
                 mbar_arrive_expect_tx(&sh->full_v[s], 2 * KP);
                 tma_load_4d(sV + s * 2 * KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, b);
                 tma_load_4d(sV + s * 2 * KP + KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, B + b);
-                ++issued;
+                ++n_v;
+            };
+            const int first = n_tiles < 3 ? n_tiles : 3;
+            for (int j = 0; j < first; ++j) load_k(j);
+            // V's slots are the query tile's until every row thread has its row in TMEM
+            if (!fwait(&sh->a_ready, 0, sh)) fgive_up(sh, 41), live = false;
+            for (int j = 0; live && j < first; ++j) load_v(j);
+            for (int j = 3; live && j < n_tiles; ++j) {
+                load_k(j);
+                if (live) load_v(j);
             }
             if (sh->abort) {
                 // let the copies in flight land before the CTA's shared memory goes away
-                const int n_k = (issued + 1) / 2, n_v = issued / 2;
+                mbar_wait(&sh->q_full, 0);
                 for (int j = (n_k > 3 ? n_k - 3 : 0); j < n_k; ++j) mbar_wait(&sh->full_k[j % 3], (uint32_t)((j / 3) & 1));
                 for (int j = (n_v > 3 ? n_v - 3 : 0); j < n_v; ++j) mbar_wait(&sh->full_v[j % 3], (uint32_t)((j / 3) & 1));
             }
@@ -225,12 +244,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
         const int t = t0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const long long wq = (long long)p.n_heads * D;
+        bool ok = true;
         {
-            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
-            const long long plane = (long long)B * p.T * wq;
-            if (set == 0) row_to_tmem<W2>(p.q_planes + off, t < p.T, tmem + lane_base + cQh);
-            else row_to_tmem<W2>(p.q_planes + plane + off, t < p.T, tmem + lane_base + cQl);
+            // this thread's row of Q's hi (set 0) or lo (set 1) plane, out of the 128-byte-swizzled staging tile
+            if (!__all_sync(0xffffffffu, fwait(&sh->q_full, 0, sh))) fgive_up(sh, 49), ok = false;
+            const uint8_t *src = sV + set * 2 * KP + tid * 128;
+#pragma unroll
+            for (int kb = 0; kb < NB; ++kb) {
+                uint32_t r[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v4 = *reinterpret_cast<const uint4 *>(src + kb * (128 * 128) + ((c ^ (tid & 7)) << 4));
+                    r[4 * c] = v4.x, r[4 * c + 1] = v4.y, r[4 * c + 2] = v4.z, r[4 * c + 3] = v4.w;
+                }
+                tmem_st32(tmem + lane_base + (set == 0 ? cQh : cQl) + kb * 32, r);
+            }
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(&sh->a_ready);
@@ -238,8 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float cs = p.scale_log2 / (mq * mk);
         const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
         float m_ref = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = set; j < n_tiles; j += 2) {
+        for (int j = set; ok && j < n_tiles; j += 2) {
             if (!__all_sync(0xffffffffu, fwait(&sh->s_full[set], (uint32_t)((j >> 1) & 1), sh))) {
                 fgive_up(sh, 45);
                 ok = false;
@@ -305,6 +332,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             fgive_up(sh, 48);
             ok = false;
         }
+        // The merged rows go to global memory through shared memory (K's slots: every tile has been consumed
+        // once all_done completes): a thread owns a row in TMEM, and 32 rows per store instruction would cost
+        // 32 memory transactions each; written back a row (or two) per instruction they cost four.
+        constexpr int CH = D / 4;  // 16-byte chunks per row; chunk c of row r sits at chunk c ^ (r & (CH - 1))
         if (ok) {
             tc_fence_after();
             const bool two = n_tiles > 1;  // set 1 has an accumulator only then
@@ -315,37 +346,350 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float lsum = w0 * l0 + w1 * l1;
             const float inv = 1.f / (lsum * mv);  // lsum, like O, carries kPScale
             const float f0 = w0 * inv, f1 = w1 * inv;
-            // set s writes columns [s D/2, (s+1) D/2) of the row
-            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out +
-                          set * (D / 2);
+            // set s merges columns [s D/2, (s+1) D/2) of the row
+            uint8_t *srow = sK + tid * (D * 4);
 #pragma unroll 1
             for (int c = 0; c < D / 2; c += 32) {
                 uint32_t ra[32], rb[32];
                 tmem_ld32(tmem + lane_base + cO0 + set * (D / 2) + c, ra);
                 if (two) tmem_ld32(tmem + lane_base + cO0 + D + set * (D / 2) + c, rb);
                 tmem_wait_ld();
-                if (t < p.T && set * (D / 2) + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        float4 o4;
-                        o4.x = __uint_as_float(ra[i]) * f0, o4.y = __uint_as_float(ra[i + 1]) * f0;
-                        o4.z = __uint_as_float(ra[i + 2]) * f0, o4.w = __uint_as_float(ra[i + 3]) * f0;
-                        if (two && w1 != 0.f) {
-                            o4.x += __uint_as_float(rb[i]) * f1, o4.y += __uint_as_float(rb[i + 1]) * f1;
-                            o4.z += __uint_as_float(rb[i + 2]) * f1, o4.w += __uint_as_float(rb[i + 3]) * f1;
-                        }
-                        *reinterpret_cast<float4 *>(orow + c + i) = o4;
+                for (int i = 0; i < 32; i += 4) {
+                    float4 o4;
+                    o4.x = __uint_as_float(ra[i]) * f0, o4.y = __uint_as_float(ra[i + 1]) * f0;
+                    o4.z = __uint_as_float(ra[i + 2]) * f0, o4.w = __uint_as_float(ra[i + 3]) * f0;
+                    if (two && w1 != 0.f) {
+                        o4.x += __uint_as_float(rb[i]) * f1, o4.y += __uint_as_float(rb[i + 1]) * f1;
+                        o4.z += __uint_as_float(rb[i + 2]) * f1, o4.w += __uint_as_float(rb[i + 3]) * f1;
                     }
+                    const int ch = (set * (D / 2) + c + i) >> 2;
+                    *reinterpret_cast<float4 *>(srow + ((ch ^ (tid & (CH - 1))) << 4)) = o4;
                 }
             }
             if (set == 0 && p.lse && t < p.T)
                 p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum) - 7.0f) * kLn2;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (!sh->abort) {
+            constexpr int RPI = 32 / CH;  // rows per store instruction
+            const int lane = threadIdx.x & 31;
+            const int ch = lane & (CH - 1);
+            const long long wo = (long long)p.n_heads * p.dim_out;
+#pragma unroll 4
+            for (int i = 0; i < 16; i += RPI) {
+                const int r = warp * 16 + i + lane / CH;
+                const float4 o4 = *reinterpret_cast<const float4 *>(sK + r * (D * 4) + ((ch ^ (r & (CH - 1))) << 4));
+                if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
+                    *reinterpret_cast<float4 *>(p.out + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = o4;
+            }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 9) tmem_dealloc(tmem, 512);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same kernel with eight softmax warps per set instead of four: two threads share a query row, 32 of the
+// tile's 64 key columns each, and agree on the tile's row maximum through shared memory.  576 threads.
+// Measured no faster than the four-warp form (3.03 ms against 2.99 at head_dim 128, T = 4096): halving a
+// thread's share of the row work does not shorten the step, so that work is not what bounds it.  Selectable
+// (zt_attn_set_path(4)), not the default.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kThreadsH = 18 * 32;
+
+struct SharedH {
+    uint64_t full_k[3], free_k[3], full_v[3], free_v[3];
+    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], x_ready[2], all_done;
+    uint32_t tmem_base;
+    volatile int abort;
+    float xmax[2][2][128];               // [set][column half][row]: the halves' maxima over the current tile
+    float fin_m[2][128], fin_l[2][2][128];
+};
+__device__ __forceinline__ bool hwait(uint64_t *bar, uint32_t parity, SharedH *sh) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && sh->abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void hgive_up(SharedH *sh, int code) {
+    sh->abort = code;
+    atomicMax(&g_tc_status, code);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreadsH, 1)
+    attn_fwd_tc16h(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
+    constexpr int NB = D / 64, W2 = D / 2, BN = 64;
+    constexpr int KP = BN * D * 2;  // bytes of one plane of a key tile
+    constexpr int cQh = 0, cQl = W2, cO0 = D, cS0 = 3 * D;  // O of set s at cO0 + s D, S/P of buffer i at cS0 + 64 i
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sK = smem, *sV = smem + 6 * KP;  // three slots of (hi, lo) each
+    SharedH *sh = reinterpret_cast<SharedH *>(smem + 12 * KP);
+
+    const int warp = threadIdx.x >> 5;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (p.n_heads / p.n_kv_heads);
+    const int t0 = qt * 128;
+    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
+    const int n_tiles = (rows_end + BN - 1) / BN;
+    const int B = p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
+            mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
+        }
+        mbar_init(&sh->a_ready, 16);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 8), mbar_init(&sh->pv_done[i], 1);
+            mbar_init(&sh->x_ready[i], 8);
+        }
+        mbar_init(&sh->all_done, 1);
+        sh->abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 17) tmem_alloc(&sh->tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
+    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
+
+    if (warp == 16) {
+        // ------------------------------------------------------------------ TMA producer
+        // K of tile j is free again once S(j) has retired, two tiles before its V: rings of their own
+        if (elect_one()) {
+            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
+            int issued = 0;  // half-steps: K of tile issued / 2, then its V
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % 3;
+                const uint32_t free_par = (uint32_t)(((j / 3) & 1) ^ 1);
+                if (j >= 3 && !hwait(&sh->free_k[s], free_par, sh)) { hgive_up(sh, 41); break; }
+                mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
+                tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
+                tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
+                ++issued;
+                if (j >= 3 && !hwait(&sh->free_v[s], free_par, sh)) { hgive_up(sh, 41); break; }
+                mbar_arrive_expect_tx(&sh->full_v[s], 2 * KP);
+                tma_load_4d(sV + s * 2 * KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, b);
+                tma_load_4d(sV + s * 2 * KP + KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, B + b);
+                ++issued;
+            }
+            if (sh->abort) {
+                // let the copies in flight land before the CTA's shared memory goes away
+                const int n_k = (issued + 1) / 2, n_v = issued / 2;
+                for (int j = (n_k > 3 ? n_k - 3 : 0); j < n_k; ++j) mbar_wait(&sh->full_k[j % 3], (uint32_t)((j / 3) & 1));
+                for (int j = (n_v > 3 ? n_v - 3 : 0); j < n_v; ++j) mbar_wait(&sh->full_v[j % 3], (uint32_t)((j / 3) & 1));
+            }
+        }
+        __syncwarp();
+    } else if (warp == 17) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
+            constexpr uint32_t id_o = idesc_f16(128, D, false, true);
+            bool ok = hwait(&sh->a_ready, 0, sh);
+            if (!ok) hgive_up(sh, 42);
+            tc_fence_after();
+            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
+            // S of tile j into buffer j & 1
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % 3;
+                if (!hwait(&sh->full_k[s], (uint32_t)((j / 3) & 1), sh)) return false;
+                tc_fence_after();
+                const uint32_t kh = k_u32 + (uint32_t)(s * 2 * KP);
+                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
+                const uint32_t cS = cS0 + (j & 1) * BN;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
+                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
+                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
+                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
+                }
+                mma_commit(&sh->free_k[s]);
+                mma_commit(&sh->s_full[j & 1]);
+                return true;
+            };
+            if (ok && !issue_qk(0)) { hgive_up(sh, 43); ok = false; }
+            if (ok && n_tiles > 1 && !issue_qk(1)) { hgive_up(sh, 43); ok = false; }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int s = j % 3, set = j & 1;
+                if (!hwait(&sh->p_full[set], (uint32_t)((j >> 1) & 1), sh) ||
+                    !hwait(&sh->full_v[s], (uint32_t)((j / 3) & 1), sh)) { hgive_up(sh, 44); break; }
+                tc_fence_after();
+                const uint32_t vh = v_u32 + (uint32_t)(s * 2 * KP);
+                const uint64_t mvh = desc_mnmajor_16b(vh, BN * 128), mvl = desc_mnmajor_16b(vh + KP, BN * 128);
+                const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
+                    const uint64_t dvh = desc_advance(mvh, kk * 2048), dvl = desc_advance(mvl, kk * 2048);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 1 || kk > 0) ? 1 : 0);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
+                    mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
+                }
+                mma_commit(&sh->free_v[s]);
+                mma_commit(&sh->pv_done[set]);
+                // completes once, after the last P.V: a barrier that counts tiles may be two phases ahead
+                // of a row thread by the time it gets there, which a parity wait cannot tell apart
+                if (j == n_tiles - 1) mma_commit(&sh->all_done);
+                // S(j+2) overwrites the P tile this P.V has just read
+                if (j + 2 < n_tiles && !issue_qk(j + 2)) { hgive_up(sh, 43); break; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ softmax rows: set `set` (eight warps)
+        // owns the key tiles of its parity, with a reference maximum, a sum and an O accumulator of its own; two
+        // threads share a row, 32 of the tile's 64 key columns each, and agree on the tile's row maximum through
+        // shared memory.  Nothing a set does waits on the other set's tile.
+        const int set = warp >> 3, hf = (warp >> 2) & 1;
+        const int tid = (warp & 3) * 32 + (threadIdx.x & 31);
+        const int t = t0 + tid;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const long long wq = (long long)p.n_heads * D;
+        {
+            // set 0 loads Q's hi plane, set 1 its lo plane; each thread half of the row's words
+            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
+            const long long plane = (long long)B * p.T * wq;
+            const __half *src = p.q_planes + (set ? plane : 0) + off;
+            const uint32_t dst = tmem + lane_base + (set ? cQl : cQh);
+#pragma unroll
+            for (int c = hf * (W2 / 2); c < (hf + 1) * (W2 / 2); c += 16) tcb::row_to_tmem16(src + 2 * c, t < p.T, dst + c);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->a_ready);
+        }
+        const float cs = p.scale_log2 / (mq * mk);
+        const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
+        const uint32_t wS = tmem + lane_base + cS + hf * 32;
+        float m_ref = -INFINITY, l = 0.f;  // l: this thread's columns only
+        bool ok = true;
+        for (int j = set; j < n_tiles; j += 2) {
+            if (!__all_sync(0xffffffffu, hwait(&sh->s_full[set], (uint32_t)((j >> 1) & 1), sh))) {
+                hgive_up(sh, 45);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int s0 = j * BN + hf * 32;
+            const bool diag = (j * BN + BN - 1 > t0);
+            uint32_t r[32];
+            tmem_ld32(wS, r);
+            tmem_wait_ld();
+            const float mine = diag ? row_max32<true>(r, s0, t, -INFINITY) : row_max32<false>(r, s0, t, -INFINITY);
+            // the row's maximum over the tile: both halves post theirs, both read both.  (An arrival for the
+            // set's next tile needs its S, hence P.V of this one, hence every warp past this wait.)
+            sh->xmax[set][hf][tid] = mine;
+            mbar_arrive_warp(&sh->x_ready[set]);
+            if (!__all_sync(0xffffffffu, hwait(&sh->x_ready[set], (uint32_t)((j >> 1) & 1), sh))) {
+                hgive_up(sh, 47);
+                ok = false;
+                break;
+            }
+            float mt = fmaxf(sh->xmax[set][0][tid], sh->xmax[set][1][tid]);
+            mt *= cs;  // cs > 0
+            float factor = 1.f;
+            if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
+                factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
+                m_ref = mt;
+            }
+            l *= factor;
+            if (j > 1 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // this set's O may only be touched once its previous P.V (tile j-2) has retired; the two threads
+                // of a row share its factor and take half of its O columns each
+                if (!__all_sync(0xffffffffu, hwait(&sh->pv_done[set], (uint32_t)(((j >> 1) - 1) & 1), sh))) {
+                    hgive_up(sh, 46);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = hf * (D / 2); c < (hf + 1) * (D / 2); c += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_base + cO + c, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tmem + lane_base + cO + c, o);
+                }
+            }
+            // l is kept in P's units (times kPScale), like O
+            const float off = ((m_ref == -INFINITY) ? 0.f : m_ref) - 7.0f;  // log2 kPScale
+            uint32_t ph[16], pl[16];
+            l += diag ? row_exp32<true>(r, s0, t, cs, off, ph, pl) : row_exp32<false>(r, s0, t, cs, off, ph, pl);
+            tmem_st16(wS, ph);
+            tmem_st16(wS + 16, pl);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive_warp(&sh->p_full[set]);
+        }
+        // ---- merge: the two halves' sums, then the two sets' partial softmaxes
+        if (hf == 0) sh->fin_m[set][tid] = m_ref;
+        sh->fin_l[set][hf][tid] = l;
+        asm volatile("bar.sync 1, 512;" ::: "memory");  // the 512 softmax threads, once, after the loop
+        if (ok && !__all_sync(0xffffffffu, hwait(&sh->all_done, 0, sh))) {
+            hgive_up(sh, 48);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            const bool two = n_tiles > 1;  // set 1 has an accumulator only then
+            const float m0 = sh->fin_m[0][tid], l0 = sh->fin_l[0][0][tid] + sh->fin_l[0][1][tid];
+            const float m1 = two ? sh->fin_m[1][tid] : -INFINITY, l1 = two ? sh->fin_l[1][0][tid] + sh->fin_l[1][1][tid] : 0.f;
+            const float mm = fmaxf(m0, m1);  // m0 is finite: key 0 is visible to every row
+            const float w0 = ex2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
+            const float lsum = w0 * l0 + w1 * l1;
+            const float inv = 1.f / (lsum * mv);  // lsum, like O, carries kPScale
+            const float f0 = w0 * inv, f1 = w1 * inv;
+            // each of the row's four threads writes a quarter of its columns
+            constexpr int CW = D / 4;  // 32 or 16
+            const int col = (set * 2 + hf) * CW;
+            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + col;
+            uint32_t ra[32], rb[32];
+            if (CW == 32) {
+                tmem_ld32(tmem + lane_base + cO0 + col, ra);
+                if (two) tmem_ld32(tmem + lane_base + cO0 + D + col, rb);
+                tmem_wait_ld();
+            } else {
+                uint32_t a16[16], b16[16];
+                tmem_ld16(tmem + lane_base + cO0 + col, a16);
+                if (two) tmem_ld16(tmem + lane_base + cO0 + D + col, b16);
+                tmem_wait_ld();  // the registers hold the values only from here on
+#pragma unroll
+                for (int i = 0; i < 16; ++i) ra[i] = a16[i], rb[i] = b16[i];
+            }
+            if (t < p.T && col < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
+#pragma unroll
+                for (int i = 0; i < CW; i += 4) {
+                    float4 o4;
+                    o4.x = __uint_as_float(ra[i]) * f0, o4.y = __uint_as_float(ra[i + 1]) * f0;
+                    o4.z = __uint_as_float(ra[i + 2]) * f0, o4.w = __uint_as_float(ra[i + 3]) * f0;
+                    if (two && w1 != 0.f) {
+                        o4.x += __uint_as_float(rb[i]) * f1, o4.y += __uint_as_float(rb[i + 1]) * f1;
+                        o4.z += __uint_as_float(rb[i + 2]) * f1, o4.w += __uint_as_float(rb[i + 3]) * f1;
+                    }
+                    *reinterpret_cast<float4 *>(orow + i) = o4;
+                }
+            }
+            if (set == 0 && hf == 0 && p.lse && t < p.T)
+                p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum) - 7.0f) * kLn2;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 17) tmem_dealloc(tmem, 512);
+}
+
 
 // ---------------------------------------------------------------------------------------------------
 // The same forward on key tiles of 128: every MMA is N = 128 (S) or N = D (P.V), none pays the
@@ -694,12 +1038,13 @@ inline Workspace workspace(void *base, int batch, int T, int n_heads, int n_kv_h
 }
 
 template <int D>
-inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Params &p, cudaStream_t stream) {
+inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
+                    cudaStream_t stream) {
     size_t smem = 12 * (size_t)(64 * D * 2) + sizeof(Shared) + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
     if (optin_smem((const void *)attn_fwd_tc16<D>, smem)) return 1;
     const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
-    return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, p)));
+    return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, qmap, p)));
 }
 
 template <int D>
@@ -709,6 +1054,15 @@ inline int launch_wide_d(const CUtensorMap &kmap128, const CUtensorMap &vmap64, 
     if (optin_smem((const void *)attn_fwd_tc16w<D>, smem)) return 1;
     const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
     return ZT_LAUNCH("attn_fwd_tc16w", stream, (attn_fwd_tc16w<D><<<grid, kWideThreads, smem, stream>>>(kmap128, vmap64, p)));
+}
+
+template <int D>
+inline int launch_h_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Params &p, cudaStream_t stream) {
+    size_t smem = 12 * (size_t)(64 * D * 2) + sizeof(SharedH) + 1024;
+    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
+    if (optin_smem((const void *)attn_fwd_tc16h<D>, smem)) return 1;
+    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
+    return ZT_LAUNCH("attn_fwd_tc16h", stream, (attn_fwd_tc16h<D><<<grid, kThreadsH, smem, stream>>>(kmap, vmap, p)));
 }
 
 }  // namespace tcf16
@@ -730,7 +1084,7 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 // bwd_workspace), so that a backward given the same workspace can use them as they are.
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
-                           const float2 *rope = nullptr, bool in_backward_workspace = false, bool wide = false) {
+                           const float2 *rope = nullptr, bool in_backward_workspace = false, int variant = 0) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
     tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
@@ -753,9 +1107,12 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
-    CUtensorMap kmap, vmap;
+    // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set
+    const bool wide = variant == 1;
+    CUtensorMap kmap, vmap, qmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
-        !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64))
+        !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64) ||
+        !make_half_tile_map(&qmap, w.q_planes, 2 * batch, T, n_heads * td, td, 128))
         return refuse("the TMA tensor maps for the forward could not be encoded.");
     tcf16::Params p{};
     p.q_planes = w.q_planes, p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v;
@@ -765,7 +1122,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
     if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
-    return td == 64 ? tcf16::launch_d<64>(kmap, vmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, p, stream);
+    if (variant == 2) return td == 64 ? tcf16::launch_h_d<64>(kmap, vmap, p, stream) : tcf16::launch_h_d<128>(kmap, vmap, p, stream);
+    return td == 64 ? tcf16::launch_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, qmap, p, stream);
 }
 
 }  // namespace zt

@@ -80,16 +80,16 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
     const int path = g_path.load();
-    if ((path == 0 || path == 3) && n_kv_heads <= tcb::kPrepassMaxGroups &&
+    if ((path == 0 || path == 3 || path == 4) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
         // The f16-split forward keeps its operand planes in the per-device arena (no entry point
         // of the forward takes a workspace); see device_arena for when that allocates.
         const size_t need = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
         if (void *arena = device_arena(need))
             return launch_fwd_tc16(q, k, v, out, lse, arena, batch, T, n_heads, n_kv_heads, dim, stream, nullptr, false,
-                                   path == 3);
+                                   path == 3 ? 1 : (path == 4 ? 2 : 0));
     }
-    if ((path == 0 || path == 2 || path == 3) &&
+    if ((path == 0 || path == 2 || path == 3 || path == 4) &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
     }
@@ -241,7 +241,7 @@ size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float)
 const char *zt_attn_last_error(void) { return g_last_error; }
 const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
-int zt_attn_set_path(int path) { return g_path.exchange((path >= 1 && path <= 3) ? path : 0); }
+int zt_attn_set_path(int path) { return g_path.exchange((path >= 1 && path <= 4) ? path : 0); }
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
 
 int zt_attn_tc_status(int *host_status) {
@@ -383,10 +383,10 @@ int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v,
 #ifndef ZT_NO_TC
     const size_t need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
     const int keep_path = g_path.load();
-    if ((keep_path == 0 || keep_path == 3) && need > 0 && workspace && workspace_bytes >= need &&
+    if ((keep_path == 0 || keep_path == 3 || keep_path == 4) && need > 0 && workspace && workspace_bytes >= need &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
-        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 3))
+        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 3 ? 1 : (keep_path == 4 ? 2 : 0)))
             return 1;
         note_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, s);
         return 0;
@@ -482,7 +482,7 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
         w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim)) {
         // the planes (rotated q and k among them) go where the backward keeps its own: the rope backward that
         // follows with the same workspace, tensors, pos and theta converts only dout
-        if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, false)) return 1;
+        if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, 0)) return 1;
         note_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
         return 0;
     }
