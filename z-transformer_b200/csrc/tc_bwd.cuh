@@ -771,7 +771,7 @@ constexpr int kDqKSlots = 3, kDqVSlots = 2;
 
 struct DqShared {
     uint64_t full_k[kDqKSlots], free_k[kDqKSlots], full_v[kDqVSlots], free_v[kDqVSlots];
-    uint64_t ql_full, a_ready, sdp_full[2], p_full[2], all_done;
+    uint64_t ql_full, qh_full, a_ready, sdp_full[2], p_full[2], all_done;
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -820,6 +820,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         for (int i = 0; i < kDqKSlots; ++i) mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
         for (int i = 0; i < kDqVSlots; ++i) mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
         mbar_init(&sh->ql_full, 1);
+        mbar_init(&sh->qh_full, 1);
         mbar_init(&sh->a_ready, kKvRowWarps);
         for (int i = 0; i < 2; ++i) mbar_init(&sh->sdp_full[i], 1), mbar_init(&sh->p_full[i], kKvRowWarps);
         mbar_init(&sh->all_done, 1);
@@ -843,24 +844,43 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             mbar_arrive_expect_tx(&sh->ql_full, 2 * QP);
             tma_load_4d(sQl, &qmap, &sh->ql_full, 0, t0, h * NB, B + b);
             tma_load_4d(sGl, &gmap, &sh->ql_full, 0, t0, h * NB, B + b);
-            int issued = 0;  // half-steps: K of tile issued / 2, then V
-            for (int j = 0; j < n_tiles; ++j) {
-                const int ks = j % kDqKSlots, vs = j % kDqVSlots;
-                if (j >= kDqKSlots && !dwait(&sh->free_k[ks], (uint32_t)(((j / kDqKSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
+            // the hi planes, bound for TMEM, are staged in K's slots 1 and 2 until the row threads have moved them:
+            // one bulk copy each instead of a strided read per thread
+            mbar_arrive_expect_tx(&sh->qh_full, 2 * QP);
+            tma_load_4d(sK + 2 * KP, &qmap, &sh->qh_full, 0, t0, h * NB, b);
+            tma_load_4d(sK + 4 * KP, &gmap, &sh->qh_full, 0, t0, h * NB, b);
+            int n_k = 0, n_v = 0;  // tiles issued
+            bool live = true;
+            auto load_k = [&](int j) {
+                const int ks = j % kDqKSlots;
+                if (j >= kDqKSlots && !dwait(&sh->free_k[ks], (uint32_t)(((j / kDqKSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31), live = false; return; }
                 mbar_arrive_expect_tx(&sh->full_k[ks], 2 * KP);
                 tma_load_4d(sK + ks * 2 * KP, &kmap, &sh->full_k[ks], 0, j * BN, g * NB, b);
                 tma_load_4d(sK + ks * 2 * KP + KP, &kmap, &sh->full_k[ks], 0, j * BN, g * NB, B + b);
-                ++issued;
-                if (j >= kDqVSlots && !dwait(&sh->free_v[vs], (uint32_t)(((j / kDqVSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31); break; }
+                ++n_k;
+            };
+            auto load_v = [&](int j) {
+                const int vs = j % kDqVSlots;
+                if (j >= kDqVSlots && !dwait(&sh->free_v[vs], (uint32_t)(((j / kDqVSlots) & 1) ^ 1), sh)) { dgive_up(sh, 31), live = false; return; }
                 mbar_arrive_expect_tx(&sh->full_v[vs], 2 * KP);
                 tma_load_4d(sV + vs * 2 * KP, &vmap, &sh->full_v[vs], 0, j * BN, g * NB, b);
                 tma_load_4d(sV + vs * 2 * KP + KP, &vmap, &sh->full_v[vs], 0, j * BN, g * NB, B + b);
-                ++issued;
+                ++n_v;
+            };
+            load_k(0), load_v(0);
+            if (n_tiles > 1) load_v(1);
+            // K's slots 1 and 2 are the hi planes' until every row thread has its part of them in TMEM
+            if (!dwait(&sh->a_ready, 0, sh)) dgive_up(sh, 31), live = false;
+            if (live && n_tiles > 1) load_k(1);
+            if (live && n_tiles > 2) load_k(2);
+            for (int j = 2; live && j < n_tiles; ++j) {
+                if (j >= kDqKSlots) load_k(j);
+                if (live) load_v(j);
             }
             if (sh->abort) {
                 // let the copies in flight land before the CTA's shared memory goes away
                 mbar_wait(&sh->ql_full, 0);
-                const int n_k = (issued + 1) / 2, n_v = issued / 2;
+                mbar_wait(&sh->qh_full, 0);
                 for (int j = (n_k > kDqKSlots ? n_k - kDqKSlots : 0); j < n_k; ++j)
                     mbar_wait(&sh->full_k[j % kDqKSlots], (uint32_t)((j / kDqKSlots) & 1));
                 for (int j = (n_v > kDqVSlots ? n_v - kDqVSlots : 0); j < n_v; ++j)
@@ -945,13 +965,24 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
         const int t = t0 + tid;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const long long wq = (long long)p.n_heads * D;
+        bool ok = true;
         {
-            // the hi planes of the Q and dO rows -> TMEM, 16 words of each per set
-            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
+            // the hi planes of the Q and dO rows -> TMEM, 16 words (four 16-byte chunks of the 128-byte-swizzled
+            // staging tiles) of each per set
+            if (!__all_sync(0xffffffffu, dwait(&sh->qh_full, 0, sh))) dgive_up(sh, 37), ok = false;
             if (set * 16 < W2) {
-                row_to_tmem16(p.q_planes + off + set * 32, t < p.T, tmem + lane_base + cQh + set * 16);
-                row_to_tmem16(p.do_planes + off + set * 32, t < p.T, tmem + lane_base + cGh + set * 16);
+                const uint8_t *src = sK + 2 * KP + (set >> 1) * (128 * 128) + tid * 128;
+                uint32_t rq[16], rg[16];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int at = (((set & 1) * 4 + c) ^ (tid & 7)) << 4;
+                    const uint4 a = *reinterpret_cast<const uint4 *>(src + at);
+                    const uint4 g4 = *reinterpret_cast<const uint4 *>(src + 2 * KP + at);
+                    rq[4 * c] = a.x, rq[4 * c + 1] = a.y, rq[4 * c + 2] = a.z, rq[4 * c + 3] = a.w;
+                    rg[4 * c] = g4.x, rg[4 * c + 1] = g4.y, rg[4 * c + 2] = g4.z, rg[4 * c + 3] = g4.w;
+                }
+                tmem_st16(tmem + lane_base + cQh + set * 16, rq);
+                tmem_st16(tmem + lane_base + cGh + set * 16, rg);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -961,8 +992,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         const long long ridx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
         const float lse2 = (t < p.T) ? __ldg(p.lse + ridx) * kLog2e : 0.f;
         const float dels = (t < p.T) ? __ldg(p.delta + ridx) * (mdo * mv * c1) : 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
+        for (int j = 0; ok && j < n_tiles; ++j) {
             if (!__all_sync(0xffffffffu, dwait(&sh->sdp_full[j & 1], (uint32_t)((j >> 1) & 1), sh))) {
                 dgive_up(sh, 35);
                 ok = false;
@@ -1018,7 +1048,6 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             // each set writes a quarter of the row's columns
             constexpr int CW = D / 4;  // 32 or 16
             const float fq = p.scale / (mdo * mv * c1 * mk);
-            float *dqr = p.dq + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + set * CW;
             // mine: this set's CW columns; other: their rotation partners (i +- dim_out / 2, another set's
             // chunk of this row's accumulator), read only when dQ leaves as the gradient of the unrotated q
             const bool rot = p.rope_t != nullptr && set * CW < p.dim_out;
@@ -1046,14 +1075,30 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 for (int i = 0; i < CW; ++i)
                     r[i] = __float_as_uint(rope_elem(__uint_as_float(r[i]), __uint_as_float(o[i]), __ldg(cs + (long long)i * p.T), upper, true));
             }
-            if (t < p.T && set * CW < p.dim_out) {
+            // to global memory through shared memory (K's slots, free once all_done completes): a thread owns a
+            // row in TMEM, and a store of 32 rows costs 32 memory transactions; a row per instruction costs four
+            uint8_t *srow = sK + tid * (D * 4);
 #pragma unroll
-                for (int i = 0; i < CW; i += 4) {
-                    float4 a;
-                    a.x = __uint_as_float(r[i]) * fq, a.y = __uint_as_float(r[i + 1]) * fq;
-                    a.z = __uint_as_float(r[i + 2]) * fq, a.w = __uint_as_float(r[i + 3]) * fq;
-                    *reinterpret_cast<float4 *>(dqr + i) = a;
-                }
+            for (int i = 0; i < CW; i += 4) {
+                float4 a;
+                a.x = __uint_as_float(r[i]) * fq, a.y = __uint_as_float(r[i + 1]) * fq;
+                a.z = __uint_as_float(r[i + 2]) * fq, a.w = __uint_as_float(r[i + 3]) * fq;
+                const int ch = (col + i) >> 2;  // chunk c of row r sits at chunk c ^ (r & (CW - 1)): D / 4 chunks a row
+                *reinterpret_cast<float4 *>(srow + ((ch ^ (tid & (CW - 1))) << 4)) = a;
+            }
+        }
+        asm volatile("bar.sync 1, 512;" ::: "memory");  // the 512 row threads
+        if (!sh->abort) {
+            constexpr int CH = D / 4, RPI = 32 / CH;  // 16-byte chunks per row, rows per store instruction
+            const int lane = threadIdx.x & 31;
+            const int ch = lane & (CH - 1);
+            const long long wo = (long long)p.n_heads * p.dim_out;
+#pragma unroll
+            for (int i = 0; i < 8; i += RPI) {
+                const int r = warp * 8 + i + lane / CH;
+                const float4 a = *reinterpret_cast<const float4 *>(sK + r * (D * 4) + ((ch ^ (r & (CH - 1))) << 4));
+                if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
+                    *reinterpret_cast<float4 *>(p.dq + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = a;
             }
         }
     }
