@@ -380,8 +380,10 @@ __global__ void __launch_bounds__(kKvThreads, 1)
     KvShared *sh = reinterpret_cast<KvShared *>(smem + 3 * KP + NS * 4 * QP);
 
     const int warp = threadIdx.x >> 5;
-    const int kt = (int)blockIdx.x;  // early key tiles see the most query rows: the longest walks start first
-    const int g = blockIdx.y, b = blockIdx.z;
+    // Launch order (x fastest): the KV groups of one sequence, key tile by key tile.  Early key tiles see the
+    // most query rows, so within a sequence the longest walks start first and the shortest last, which keeps
+    // the kernel's tail (SMs idle while the last long CTA finishes) to a fraction of one walk.
+    const int g = blockIdx.x, kt = (int)blockIdx.y, b = blockIdx.z;
     const int group = p.n_heads / p.n_kv_heads;
     const int s0 = kt * 128;
     const int n_q = (p.T + BQ - 1) / BQ, qi0 = s0 / BQ;
@@ -720,32 +722,52 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                     break;
                 }
                 tc_fence_after();
-                // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's
+                // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's.  A thread owns a key
+                // row; written as they are, the 32 rows of a warp would cost 32 memory transactions per
+                // instruction.  Eight lanes first transpose their 8 x 8 blocks of float4 among themselves, so that
+                // lane j holds the j-th float4 of eight rows and an instruction covers four rows' 128-byte runs.
                 const int c0 = (set & 1) * (D / 2);
                 const uint32_t acc = tmem + lane_base + (set < 2 ? cDV : cDK) + c0;
-                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + key) * ((long long)p.n_kv_heads * p.dim_out) +
-                             (long long)g * p.dim_out + c0;
+                const int lane = threadIdx.x & 31, j8 = lane & 7;
+                const long long wo = (long long)p.n_kv_heads * p.dim_out;
+                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + (key - j8)) * wo + (long long)g * p.dim_out + c0 + 4 * j8;
                 const float f = set < 2 ? 1.0f / (p.p_scale * mdo) : p.scale / (mdo * mv * c1 * mq);
 #pragma unroll 1
                 for (int c = 0; c < D / 2; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(acc + c, r);
                     tmem_wait_ld();
-                    if (key < p.T && c0 + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
+                    for (int M = 4; M >= 1; M >>= 1) {
+                        const bool up = (lane & M) != 0;
+#pragma unroll
+                        for (int m = 0; m < 8; ++m) {
+                            if (m & M) continue;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t send = up ? r[4 * m + e] : r[4 * (m ^ M) + e];
+                                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, M);
+                                if (up) r[4 * m + e] = recv;
+                                else r[4 * (m ^ M) + e] = recv;
+                            }
+                        }
+                    }
+                    if (c0 + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (key - j8 + i >= p.T) continue;
                             float4 a;
-                            a.x = __uint_as_float(r[i]) * f, a.y = __uint_as_float(r[i + 1]) * f;
-                            a.z = __uint_as_float(r[i + 2]) * f, a.w = __uint_as_float(r[i + 3]) * f;
+                            a.x = __uint_as_float(r[4 * i]) * f, a.y = __uint_as_float(r[4 * i + 1]) * f;
+                            a.z = __uint_as_float(r[4 * i + 2]) * f, a.w = __uint_as_float(r[4 * i + 3]) * f;
                             // the first flush assigns (dk/dv need no zeroing by the caller); later ones
                             // add in memory: a rounded f32 add with no reply to wait for
-                            if (n_flush == 0) *reinterpret_cast<float4 *>(dst + c + i) = a;
-                            else red_add_v4(dst + c + i, a);
+                            if (n_flush == 0) *reinterpret_cast<float4 *>(dst + i * wo + c) = a;
+                            else red_add_v4(dst + i * wo + c, a);
                         }
                     }
                 }
                 ++n_flush;
-                __threadfence();
+                // (no fence: the tensor core only needs the accumulators read, and nobody else adds to these rows)
                 tc_fence_before();
                 mbar_arrive_warp(&sh->flush_done);
             }
@@ -808,6 +830,8 @@ __global__ void __launch_bounds__(kKvThreads, 1)
     DqShared *sh = reinterpret_cast<DqShared *>(sV + kDqVSlots * 2 * KP);
 
     const int warp = threadIdx.x >> 5;
+    // launch order (x fastest): a head's query tiles, late (long) ones first.  (Starting the heads of a sequence
+    // tile by tile instead, which would shorten the tail, measured 1 % slower.)
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     const int g = h / (p.n_heads / p.n_kv_heads);
@@ -1155,7 +1179,7 @@ inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t st
     const size_t sb = dq_smem_bytes<D>() > floor_ ? dq_smem_bytes<D>() : floor_;
     if (optin_smem((const void *)attn_bwd_dkdv_tc<D>, sa)) return 1;
     if (optin_smem((const void *)attn_bwd_dq_tc<D>, sb)) return 1;
-    const dim3 grid_a((unsigned)((p.T + 127) / 128), (unsigned)p.n_kv_heads, (unsigned)p.batch);
+    const dim3 grid_a((unsigned)p.n_kv_heads, (unsigned)((p.T + 127) / 128), (unsigned)p.batch);
     const dim3 grid_b((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
     if (ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
                   (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(m.k128, m.v128, m.q64, m.g64, p))))

@@ -106,7 +106,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     Shared *sh = reinterpret_cast<Shared *>(smem + 12 * KP);
 
     const int warp = threadIdx.x >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
+    // launch order (x fastest): a head's query tiles, late (long) ones first.  (Starting the heads of a sequence
+    // tile by tile instead, which would shorten the tail, measured 3 % slower.)
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     const int g = h / (p.n_heads / p.n_kv_heads);
     const int t0 = qt * 128;
