@@ -642,6 +642,66 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         ahead.next();
         int n_flush = 0;
         bool ok = true;
+        // The accumulators go to memory one step late: after a flush step's dS the row threads would only wait
+        // for its dV and dK to retire, and the next step's exp and dS need neither the accumulators nor that
+        // wait, so they come first and the tensor core finds them done when the flush ends.
+        auto flush_now = [&]() -> bool {
+            if (!__all_sync(0xffffffffu, kwait(&sh->flush_ready, (uint32_t)(n_flush & 1), sh))) {
+                kgive_up(sh, 26);
+                return false;
+            }
+            tc_fence_after();
+            // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's.  A thread owns a key
+            // row; written as they are, the 32 rows of a warp would cost 32 memory transactions per
+            // instruction.  Eight lanes first transpose their 8 x 8 blocks of float4 among themselves, so that
+            // lane j holds the j-th float4 of eight rows and an instruction covers four rows' 128-byte runs.
+            const int c0 = (set & 1) * (D / 2);
+            const uint32_t acc = tmem + lane_base + (set < 2 ? cDV : cDK) + c0;
+            const int lane = threadIdx.x & 31, j8 = lane & 7;
+            const long long wo = (long long)p.n_kv_heads * p.dim_out;
+            float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + (key - j8)) * wo + (long long)g * p.dim_out + c0 + 4 * j8;
+            const float f = set < 2 ? 1.0f / (p.p_scale * mdo) : p.scale / (mdo * mv * c1 * mq);
+#pragma unroll 1
+            for (int c = 0; c < D / 2; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(acc + c, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int M = 4; M >= 1; M >>= 1) {
+                    const bool up = (lane & M) != 0;
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        if (m & M) continue;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t send = up ? r[4 * m + e] : r[4 * (m ^ M) + e];
+                            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, M);
+                            if (up) r[4 * m + e] = recv;
+                            else r[4 * (m ^ M) + e] = recv;
+                        }
+                    }
+                }
+                if (c0 + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (key - j8 + i >= p.T) continue;
+                        float4 a;
+                        a.x = __uint_as_float(r[4 * i]) * f, a.y = __uint_as_float(r[4 * i + 1]) * f;
+                        a.z = __uint_as_float(r[4 * i + 2]) * f, a.w = __uint_as_float(r[4 * i + 3]) * f;
+                        // the first flush assigns (dk/dv need no zeroing by the caller); later ones
+                        // add in memory: a rounded f32 add with no reply to wait for
+                        if (n_flush == 0) *reinterpret_cast<float4 *>(dst + i * wo + c) = a;
+                        else red_add_v4(dst + i * wo + c, a);
+                    }
+                }
+            }
+            ++n_flush;
+            // (no fence: the tensor core only needs the accumulators read, and nobody else adds to these rows)
+            tc_fence_before();
+            mbar_arrive_warp(&sh->flush_done);
+            return true;
+        };
+        bool flush_pending = false;
         for (int it = 0; it < n_it; ++it, walk.next(), ahead.next()) {
             const int t0 = walk.qi * BQ + set * 16;
             const uint32_t par = (uint32_t)(it & 1);
@@ -715,61 +775,13 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(&sh->p_full);
+            if (flush_pending) {
+                flush_pending = false;
+                if (!flush_now()) { ok = false; break; }
+            }
             if (walk.flush) {
-                if (!__all_sync(0xffffffffu, kwait(&sh->flush_ready, (uint32_t)(n_flush & 1), sh))) {
-                    kgive_up(sh, 26);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                // sets 0, 1 add the halves of dV's columns to memory, sets 2, 3 those of dK's.  A thread owns a key
-                // row; written as they are, the 32 rows of a warp would cost 32 memory transactions per
-                // instruction.  Eight lanes first transpose their 8 x 8 blocks of float4 among themselves, so that
-                // lane j holds the j-th float4 of eight rows and an instruction covers four rows' 128-byte runs.
-                const int c0 = (set & 1) * (D / 2);
-                const uint32_t acc = tmem + lane_base + (set < 2 ? cDV : cDK) + c0;
-                const int lane = threadIdx.x & 31, j8 = lane & 7;
-                const long long wo = (long long)p.n_kv_heads * p.dim_out;
-                float *dst = (set < 2 ? p.dv : p.dk) + ((long long)b * p.T + (key - j8)) * wo + (long long)g * p.dim_out + c0 + 4 * j8;
-                const float f = set < 2 ? 1.0f / (p.p_scale * mdo) : p.scale / (mdo * mv * c1 * mq);
-#pragma unroll 1
-                for (int c = 0; c < D / 2; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(acc + c, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int M = 4; M >= 1; M >>= 1) {
-                        const bool up = (lane & M) != 0;
-#pragma unroll
-                        for (int m = 0; m < 8; ++m) {
-                            if (m & M) continue;
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const uint32_t send = up ? r[4 * m + e] : r[4 * (m ^ M) + e];
-                                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, M);
-                                if (up) r[4 * m + e] = recv;
-                                else r[4 * (m ^ M) + e] = recv;
-                            }
-                        }
-                    }
-                    if (c0 + c < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            if (key - j8 + i >= p.T) continue;
-                            float4 a;
-                            a.x = __uint_as_float(r[4 * i]) * f, a.y = __uint_as_float(r[4 * i + 1]) * f;
-                            a.z = __uint_as_float(r[4 * i + 2]) * f, a.w = __uint_as_float(r[4 * i + 3]) * f;
-                            // the first flush assigns (dk/dv need no zeroing by the caller); later ones
-                            // add in memory: a rounded f32 add with no reply to wait for
-                            if (n_flush == 0) *reinterpret_cast<float4 *>(dst + i * wo + c) = a;
-                            else red_add_v4(dst + i * wo + c, a);
-                        }
-                    }
-                }
-                ++n_flush;
-                // (no fence: the tensor core only needs the accumulators read, and nobody else adds to these rows)
-                tc_fence_before();
-                mbar_arrive_warp(&sh->flush_done);
+                if (it + 1 < n_it) flush_pending = true;
+                else if (!flush_now()) { ok = false; break; }
             }
         }
         (void)ok;
