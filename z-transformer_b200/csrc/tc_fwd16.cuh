@@ -50,6 +50,7 @@ struct Params {
     float *out, *lse;                           // lse may be null
     int batch, T, n_heads, n_kv_heads;
     int dim_out;  // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
+    int ahead;    // attn_fwd_tc16 prefetches the query tile of the block this many places on in launch order; 0: none
     float scale_log2;
 };
 
@@ -149,6 +150,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_4d(sV + 2 * KP, &qmap, &sh->q_full, 0, t0, h * NB, B + b);
             int n_k = 0, n_v = 0;  // tiles issued
             bool live = true;
+            const auto prefetch_next_q = [&]() {
+                // The query tile of the CTA that will start when one of the running ones ends (`ahead` blocks on in
+                // launch order, about the number of SMs), into L2: its planes were written once by the pre-pass and
+                // would otherwise come from DRAM, under load, before that CTA's first MMA can go out.
+                const long long gx = gridDim.x, gy = gridDim.y;
+                const long long lin = blockIdx.x + gx * (blockIdx.y + gy * blockIdx.z) + p.ahead;
+                if (p.ahead <= 0 || lin >= gx * gy * gridDim.z) return;
+                const int nx = (int)(lin % gx), ny = (int)((lin / gx) % gy), nz = (int)(lin / (gx * gy));
+                const int nt0 = ((int)gx - 1 - nx) * 128;
+                tma_prefetch_l2_4d(&qmap, 0, nt0, ny * NB, nz);
+                tma_prefetch_l2_4d(&qmap, 0, nt0, ny * NB, B + nz);
+            };
             auto load_k = [&](int j) {
                 const int s = j % 3;
                 if (j >= 3 && !fwait(&sh->free_k[s], (uint32_t)(((j / 3) & 1) ^ 1), sh)) { fgive_up(sh, 41), live = false; return; }
@@ -170,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             // V's slots are the query tile's until every row thread has its row in TMEM
             if (!fwait(&sh->a_ready, 0, sh)) fgive_up(sh, 41), live = false;
             for (int j = 0; live && j < first; ++j) load_v(j);
+            prefetch_next_q();
             for (int j = 3; live && j < n_tiles; ++j) {
                 load_k(j);
                 if (live) load_v(j);
@@ -1121,6 +1135,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.out = out, p.lse = lse;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
+    p.ahead = device_info() ? device_info()->sm_count : 0;  // one CTA per SM
+    if (const char *e = getenv("ZT_FWD_AHEAD")) p.ahead = atoi(e);
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
     if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
