@@ -101,7 +101,9 @@ void zt_attn_set_verbose(int on);
  * 2 = as 0 but the forward uses the 3xTF32 kernel instead of the f16-split one, 3 = as 0 but
  * the f16-split forward walks key tiles of 128 (four softmax sets sharing one accumulator;
  * slower, experimental) instead of 64 (two sets with an accumulator each), 4 = as 0 but the
- * two sets have eight softmax warps each (two threads per row) instead of four.  For tests
+ * two sets have eight softmax warps each (two threads per row) instead of four, 5 = as 0 but
+ * one CTA per SM walks a list of query tiles, with the next tile's Q fetched a tile ahead and
+ * the K/V rings streaming across tiles (0.8 % faster at the headline shape).  For tests
  * and for bisecting a parity failure; returns the previous value. */
 int zt_attn_set_path(int path);
 

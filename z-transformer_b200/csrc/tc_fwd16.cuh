@@ -50,6 +50,7 @@ struct Params {
     float *out, *lse;                           // lse may be null
     int batch, T, n_heads, n_kv_heads;
     int dim_out;  // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
+    int n_items;  // attn_fwd_tc16p: pairs of query tiles over all heads and sequences
     int ahead;    // attn_fwd_tc16 prefetches the query tile of the block this many places on in launch order; 0: none
     float scale_log2;
 };
@@ -1081,6 +1082,11 @@ inline int launch_h_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Pa
     return ZT_LAUNCH("attn_fwd_tc16h", stream, (attn_fwd_tc16h<D><<<grid, kThreadsH, smem, stream>>>(kmap, vmap, p)));
 }
 
+// (tc_fwd16p.cuh)
+template <int D>
+inline int launch_p_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
+                      cudaStream_t stream);
+
 }  // namespace tcf16
 
 inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
@@ -1123,7 +1129,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
-    // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set
+    // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set;
+    // 3: variant 0 with CTAs that walk several query tiles
     const bool wide = variant == 1;
     CUtensorMap kmap, vmap, qmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
@@ -1140,6 +1147,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
     if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
+    p.n_items = (((T + 127) / 128 + 1) / 2) * n_heads * batch;
+    if (variant == 3) return td == 64 ? tcf16::launch_p_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_p_d<128>(kmap, vmap, qmap, p, stream);
     if (variant == 2) return td == 64 ? tcf16::launch_h_d<64>(kmap, vmap, p, stream) : tcf16::launch_h_d<128>(kmap, vmap, p, stream);
     return td == 64 ? tcf16::launch_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, qmap, p, stream);
 }
