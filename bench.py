@@ -343,11 +343,11 @@ def run_ours(args):
     # Algorithmic operations credited per launch: forward 2 GEMMs = F; key-outer backward kernel
     # S, dP, dV, dK = 2 F; query-outer backward kernel dQ = 0.5 F (its recomputed S and dP are
     # overhead, not credited); together the backward's 2.5 F.
-    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_fwd_tc16": F, "attn_fwd_tc16w": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
+    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_fwd_tc16": F, "attn_fwd_tc16g": F, "attn_fwd_tc16p": F, "attn_fwd_tc16w": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
               "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
     # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the B=2 case
     # (profiles/prefill_tensor_core_kernels_small_case.md), scaled by the batch: traffic is per sequence.
-    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_fwd_tc16": 304.6e6, "attn_bwd_dkdv_tc": 590.7e6,
+    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_fwd_tc16": 304.6e6, "attn_fwd_tc16g": 304.6e6, "attn_bwd_dkdv_tc": 590.7e6,
                   "attn_bwd_dq_tc": 448.7e6}
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
     total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
@@ -371,7 +371,7 @@ def run_ours(args):
     # MMA work issued per step by the f16-split kernels: every credited product is three kind::f16 MMAs, and
     # the dQ kernel recomputes S and dP.  Forward 2 GEMMs, dK/dV kernel 4, dQ kernel 3, of 0.5 F each.
     issued = None
-    if {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels) and ({"attn_fwd_tc16", "attn_fwd_tc16w"} & set(kernels)):
+    if {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels) and ({"attn_fwd_tc16", "attn_fwd_tc16g", "attn_fwd_tc16p", "attn_fwd_tc16w"} & set(kernels)):
         issued_flop = 3.0 * (2 + 4 + 3) * 0.5 * F
         issued = {"flop_per_step": issued_flop, "f16_tflops": issued_flop / (ms_step * 1e-3) / 1e12,
                   "of_bf16_sustained_peak": issued_flop / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],

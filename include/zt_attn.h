@@ -97,14 +97,16 @@ const char *zt_attn_last_error(void);
 void zt_attn_set_verbose(int on);
 
 /* Which implementation the next launches use: 0 = automatic (the fastest tensor-core
- * kernel the shape allows, CUDA-core kernels elsewhere), 1 = CUDA-core kernels only,
- * 2 = as 0 but the forward uses the 3xTF32 kernel instead of the f16-split one, 3 = as 0 but
- * the f16-split forward walks key tiles of 128 (four softmax sets sharing one accumulator;
- * slower, experimental) instead of 64 (two sets with an accumulator each), 4 = as 0 but the
- * two sets have eight softmax warps each (two threads per row) instead of four, 5 = as 0 but
- * one CTA per SM walks a list of query tiles, with the next tile's Q fetched a tile ahead and
- * the K/V rings streaming across tiles (0.8 % faster at the headline shape).  For tests
- * and for bisecting a parity failure; returns the previous value. */
+ * kernel the shape allows, CUDA-core kernels elsewhere: the f16-split forward takes the same
+ * query rows of two heads of a KV group per CTA when the group has an even number of query
+ * heads, one head per CTA otherwise), 1 = CUDA-core kernels only, 2 = as 0 but the forward
+ * uses the 3xTF32 kernel instead of the f16-split one.  The others are forms of the f16-split
+ * forward with one head per CTA: 6 = the plain one (key tiles of 64, two softmax sets of four
+ * warps splitting the key tiles by parity), 3 = key tiles of 128 (four softmax sets sharing
+ * one accumulator; slower), 4 = eight softmax warps per set (two threads per row), 5 = one
+ * CTA per SM walking a list of query tiles, the next tile's Q fetched a tile ahead and the
+ * K/V rings streaming across tiles.  For tests and for bisecting a parity failure; returns
+ * the previous value. */
 int zt_attn_set_path(int path);
 
 /* Batched training-shaped forward: `batch` independent sequences of T rows,

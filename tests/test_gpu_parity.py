@@ -394,11 +394,11 @@ TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, sev
 ]
 
 
-@pytest.mark.parametrize("path", [0, 5, 4, 3, 2], ids=["f16split-64x4", "f16split-walk", "f16split-64x8", "f16split-128", "3xtf32"])
+@pytest.mark.parametrize("path", [0, 6, 5, 4, 3, 2], ids=["f16split-auto", "f16split-1head", "f16split-walk", "f16split-64x8", "f16split-128", "3xtf32"])
 @pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
 def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, path):
     """The tensor-core forwards: the f16-split kernel on key tiles of 64 with four softmax warps per set (path 0) or
-    eight (path 4), with CTAs that walk several query tiles (path 5) and on key tiles of 128 (path 3), head_dim
+    eight (path 4), with CTAs that walk several query tiles (path 5); path 0 takes two heads of a KV group per CTA where the group is even, path 6 never does and on key tiles of 128 (path 3), head_dim
     32 zero-padded to their 64-wide tiles, and the 3xTF32 kernel (path 2)."""
     q = oracle.fill_normal((B, T, H * D), 51, 0)
     k = oracle.fill_normal((B, T, Hkv * D), 51, 1)

@@ -1082,6 +1082,10 @@ inline int launch_h_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Pa
     return ZT_LAUNCH("attn_fwd_tc16h", stream, (attn_fwd_tc16h<D><<<grid, kThreadsH, smem, stream>>>(kmap, vmap, p)));
 }
 
+// (tc_fwd16g.cuh)
+template <int D>
+inline int launch_g_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
+                      cudaStream_t stream);
 // (tc_fwd16p.cuh)
 template <int D>
 inline int launch_p_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
@@ -1130,7 +1134,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
     // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set;
-    // 3: variant 0 with CTAs that walk several query tiles
+    // 3: as 4 with CTAs that walk several query tiles; 4: one head per CTA.  Variant 0 takes two heads of a KV group
+    // per CTA (attn_fwd_tc16g) when the group has an even number of query heads, and is variant 4 otherwise.
     const bool wide = variant == 1;
     CUtensorMap kmap, vmap, qmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
@@ -1148,6 +1153,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     g_last_path = "tcgen05";
     if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
     p.n_items = (((T + 127) / 128 + 1) / 2) * n_heads * batch;
+    if (variant == 0 && (n_heads / n_kv_heads) % 2 == 0)
+        return td == 64 ? tcf16::launch_g_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_g_d<128>(kmap, vmap, qmap, p, stream);
     if (variant == 3) return td == 64 ? tcf16::launch_p_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_p_d<128>(kmap, vmap, qmap, p, stream);
     if (variant == 2) return td == 64 ? tcf16::launch_h_d<64>(kmap, vmap, p, stream) : tcf16::launch_h_d<128>(kmap, vmap, p, stream);
     return td == 64 ? tcf16::launch_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, qmap, p, stream);
