@@ -347,7 +347,7 @@ def run_ours(args):
               "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
     # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the B=2 case
     # (profiles/prefill_tensor_core_kernels_small_case.md), scaled by the batch: traffic is per sequence.
-    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_fwd_tc16": 304.6e6, "attn_fwd_tc16g": 304.6e6, "attn_bwd_dkdv_tc": 590.7e6,
+    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_fwd_tc16": 304.6e6, "attn_fwd_tc16g": 300.1e6, "attn_bwd_dkdv_tc": 590.7e6,
                   "attn_bwd_dq_tc": 448.7e6}
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
     total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0

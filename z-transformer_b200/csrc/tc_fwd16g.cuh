@@ -49,8 +49,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     SharedG *sh = reinterpret_cast<SharedG *>(sQl + 4 * KP);
 
     const int warp = threadIdx.x >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
-    const int h0 = 2 * (int)blockIdx.y, b = blockIdx.z;
+    // launch order (x fastest): the head pairs of a sequence, query tile by query tile, late (long) tiles first, so
+    // that the last CTAs to start are the shortest (1.5 % faster than a head pair's tiles together)
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int h0 = 2 * (int)blockIdx.x, b = blockIdx.z;
     const int g = h0 / (p.n_heads / p.n_kv_heads);
     const int t0 = qt * 128;
     const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
@@ -332,7 +334,7 @@ inline int launch_g_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CU
     size_t smem = 14 * (size_t)(64 * D * 2) + sizeof(SharedG);
     if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
     if (optin_smem((const void *)attn_fwd_tc16g<D>, smem)) return 1;
-    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)(p.n_heads / 2), (unsigned)p.batch);
+    const dim3 grid((unsigned)(p.n_heads / 2), (unsigned)((p.T + 127) / 128), (unsigned)p.batch);
     return ZT_LAUNCH("attn_fwd_tc16g", stream, (attn_fwd_tc16g<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, qmap, p)));
 }
 
