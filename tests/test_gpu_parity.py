@@ -595,14 +595,16 @@ def test_rope_calls_refuse_bad_arguments(zt, dev):
     assert rc == 1 and "workspace" in zt.lib.last_error()
 
 
-def test_forward_keep_hands_its_planes_to_the_backward(zt, dev):
+@pytest.mark.parametrize("path", [0, 6, 5], ids=["auto", "1head", "walk"])
+def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
     """zt_attn_forward_batched_keep + zt_attn_backward_batched with the same workspace give bit for bit what the
-    unpaired calls give; a backward on other tensors after a keep ignores the kept planes."""
+    unpaired calls give; a backward on other tensors after a keep ignores the kept planes.  For each form of the
+    f16-split forward that a training loop may be set to."""
     B, T, H, Hkv, D = 2, 300, 8, 2, 128
     g = torch.Generator(device=dev).manual_seed(9)
     q, do = (torch.randn((B, T, H * D), generator=g, device=dev) for _ in range(2))
     k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
-    zt.lib.load().zt_attn_set_path(0)
+    zt.lib.load().zt_attn_set_path(path)
     o0, l0 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
     ref = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D)
     ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
@@ -624,6 +626,32 @@ def test_forward_keep_hands_its_planes_to_the_backward(zt, dev):
     got3 = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D, workspace=ws)
     for a, b in zip(got3, ref):
         assert torch.equal(a, b)
+    zt.lib.load().zt_attn_set_path(0)
+    assert zt.lib.tc_status() == 0
+
+
+def test_forward_forms_agree_bit_for_bit(zt, dev):
+    """One head per CTA, two heads per CTA and the walking CTAs run the same arithmetic in the same order per row:
+    their outputs and log-sum-exps are identical, at a shape with tails and a padded head."""
+    for (B, T, H, Hkv, D) in [(2, 1000, 8, 2, 128), (1, 777, 8, 4, 64), (1, 500, 4, 1, 96)]:
+        g = torch.Generator(device=dev).manual_seed(21)
+        q = torch.randn((B, T, H * D), generator=g, device=dev)
+        k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
+        res = []
+        for path in (6, 0, 5):
+            zt.lib.load().zt_attn_set_path(path)
+            try:
+                res.append(zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True))
+            finally:
+                zt.lib.load().zt_attn_set_path(0)
+            assert zt.lib.last_path() == "tcgen05"
+        torch.cuda.synchronize()
+        # the walking CTAs are the one-head kernel tile for tile
+        assert torch.equal(res[0][0], res[2][0]) and torch.equal(res[0][1], res[2][1])
+        # two heads per CTA: a head's key tiles all go through one softmax state instead of two merged ones, so
+        # rounding differs; the parity bound of the forward (1e-5 + 1e-4 |ref|) holds between them with room
+        err = (res[0][0] - res[1][0]).abs()
+        assert bool((err <= 2e-6 + 2e-5 * res[0][0].abs()).all())
     assert zt.lib.tc_status() == 0
 
 
