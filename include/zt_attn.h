@@ -99,7 +99,8 @@ void zt_attn_set_verbose(int on);
 /* Which implementation the next launches use: 0 = automatic (the fastest tensor-core
  * kernel the shape allows, CUDA-core kernels elsewhere: the f16-split forward takes the same
  * query rows of two heads of a KV group per CTA when the group has an even number of query
- * heads, one head per CTA otherwise), 1 = CUDA-core kernels only, 2 = as 0 but the forward
+ * heads and that still gives every SM a CTA, one head per CTA otherwise; 7 = two heads per CTA
+ * whatever the number of CTAs), 1 = CUDA-core kernels only, 2 = as 0 but the forward
  * uses the 3xTF32 kernel instead of the f16-split one.  The others are forms of the f16-split
  * forward with one head per CTA: 6 = the plain one (key tiles of 64, two softmax sets of four
  * warps splitting the key tiles by parity), 3 = key tiles of 128 (four softmax sets sharing

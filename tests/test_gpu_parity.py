@@ -394,11 +394,11 @@ TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, sev
 ]
 
 
-@pytest.mark.parametrize("path", [0, 6, 5, 4, 3, 2], ids=["f16split-auto", "f16split-1head", "f16split-walk", "f16split-64x8", "f16split-128", "3xtf32"])
+@pytest.mark.parametrize("path", [0, 7, 6, 5, 4, 3, 2], ids=["f16split-auto", "f16split-2heads", "f16split-1head", "f16split-walk", "f16split-64x8", "f16split-128", "3xtf32"])
 @pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
 def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, path):
     """The tensor-core forwards: the f16-split kernel on key tiles of 64 with four softmax warps per set (path 0) or
-    eight (path 4), with CTAs that walk several query tiles (path 5); path 0 takes two heads of a KV group per CTA where the group is even, path 6 never does and on key tiles of 128 (path 3), head_dim
+    eight (path 4), with CTAs that walk several query tiles (path 5); path 0 takes two heads of a KV group per CTA where the group is even and the launch is large enough, path 7 wherever the group is even, path 6 never and on key tiles of 128 (path 3), head_dim
     32 zero-padded to their 64-wide tiles, and the 3xTF32 kernel (path 2)."""
     q = oracle.fill_normal((B, T, H * D), 51, 0)
     k = oracle.fill_normal((B, T, Hkv * D), 51, 1)
@@ -595,7 +595,7 @@ def test_rope_calls_refuse_bad_arguments(zt, dev):
     assert rc == 1 and "workspace" in zt.lib.last_error()
 
 
-@pytest.mark.parametrize("path", [0, 6, 5], ids=["auto", "1head", "walk"])
+@pytest.mark.parametrize("path", [0, 7, 6, 5], ids=["auto", "2heads", "1head", "walk"])
 def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
     """zt_attn_forward_batched_keep + zt_attn_backward_batched with the same workspace give bit for bit what the
     unpaired calls give; a backward on other tensors after a keep ignores the kept planes.  For each form of the
@@ -638,7 +638,7 @@ def test_forward_forms_agree_bit_for_bit(zt, dev):
         q = torch.randn((B, T, H * D), generator=g, device=dev)
         k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
         res = []
-        for path in (6, 0, 5):
+        for path in (6, 7, 5):
             zt.lib.load().zt_attn_set_path(path)
             try:
                 res.append(zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True))

@@ -1135,7 +1135,8 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     if (launch_prepass(pa, stream)) return 1;
     // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set;
     // 3: as 4 with CTAs that walk several query tiles; 4: one head per CTA.  Variant 0 takes two heads of a KV group
-    // per CTA (attn_fwd_tc16g) when the group has an even number of query heads, and is variant 4 otherwise.
+    // per CTA (attn_fwd_tc16g) when the group has an even number of query heads and that still gives every SM a CTA,
+    // and is variant 4 otherwise; variant 5 takes two heads whatever the number of CTAs.
     const bool wide = variant == 1;
     CUtensorMap kmap, vmap, qmap;
     if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
@@ -1153,7 +1154,10 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     g_last_path = "tcgen05";
     if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
     p.n_items = (((T + 127) / 128 + 1) / 2) * n_heads * batch;
-    if (variant == 0 && (n_heads / n_kv_heads) % 2 == 0)
+    // two heads per CTA halve the number of CTAs: not when that leaves SMs without one
+    const long long pair_ctas = (long long)((T + 127) / 128) * (n_heads / 2) * batch;
+    if ((variant == 0 || variant == 5) && (n_heads / n_kv_heads) % 2 == 0 &&
+        (variant == 5 || (device_info() && pair_ctas >= device_info()->sm_count)))
         return td == 64 ? tcf16::launch_g_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_g_d<128>(kmap, vmap, qmap, p, stream);
     if (variant == 3) return td == 64 ? tcf16::launch_p_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_p_d<128>(kmap, vmap, qmap, p, stream);
     if (variant == 2) return td == 64 ? tcf16::launch_h_d<64>(kmap, vmap, p, stream) : tcf16::launch_h_d<128>(kmap, vmap, p, stream);

@@ -82,16 +82,16 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
     const int path = g_path.load();
-    if ((path == 0 || path == 3 || path == 4 || path == 5 || path == 6) && n_kv_heads <= tcb::kPrepassMaxGroups &&
+    if ((path == 0 || path == 3 || path == 4 || path == 5 || path == 6 || path == 7) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
         // The f16-split forward keeps its operand planes in the per-device arena (no entry point
         // of the forward takes a workspace); see device_arena for when that allocates.
         const size_t need = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
         if (void *arena = device_arena(need))
             return launch_fwd_tc16(q, k, v, out, lse, arena, batch, T, n_heads, n_kv_heads, dim, stream, nullptr, false,
-                                   path == 3 ? 1 : (path == 4 ? 2 : (path == 5 ? 3 : (path == 6 ? 4 : 0))));
+                                   path == 3 ? 1 : (path == 4 ? 2 : (path == 5 ? 3 : (path == 6 ? 4 : (path == 7 ? 5 : 0)))));
     }
-    if ((path == 0 || path == 2 || path == 3 || path == 4 || path == 5 || path == 6) &&
+    if ((path == 0 || path == 2 || path == 3 || path == 4 || path == 5 || path == 6 || path == 7) &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
     }
@@ -243,7 +243,7 @@ size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float)
 const char *zt_attn_last_error(void) { return g_last_error; }
 const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
-int zt_attn_set_path(int path) { return g_path.exchange((path >= 1 && path <= 6) ? path : 0); }
+int zt_attn_set_path(int path) { return g_path.exchange((path >= 1 && path <= 7) ? path : 0); }
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
 
 int zt_attn_tc_status(int *host_status) {
@@ -385,10 +385,10 @@ int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v,
 #ifndef ZT_NO_TC
     const size_t need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
     const int keep_path = g_path.load();
-    if ((keep_path == 0 || keep_path == 3 || keep_path == 4 || keep_path == 5 || keep_path == 6) && need > 0 && workspace && workspace_bytes >= need &&
+    if ((keep_path == 0 || keep_path == 3 || keep_path == 4 || keep_path == 5 || keep_path == 6 || keep_path == 7) && need > 0 && workspace && workspace_bytes >= need &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
-        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 3 ? 1 : (keep_path == 4 ? 2 : (keep_path == 5 ? 3 : (keep_path == 6 ? 4 : 0)))))
+        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 3 ? 1 : (keep_path == 4 ? 2 : (keep_path == 5 ? 3 : (keep_path == 6 ? 4 : (keep_path == 7 ? 5 : 0))))))
             return 1;
         note_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, s);
         return 0;
