@@ -21,14 +21,20 @@
  * narrowing per term (autograd.zig:829-836); that order (head outer, query row,
  * then key ascending) is kept so the roundings land where the reference's do.
  *
- * Parity status: the forward is pinned by the reference's own known-answer
- * tests (src/attention_test.zig), restated in tests/test_oracle_kat.py.  The
- * backward has no literal vectors anywhere in the reference (it is pinned there
- * only by whole-model finite differences), so here it is pinned by central
- * differences against the forward above and by an independent float64 autograd.
- * The reference itself needs Zig 0.16 and cannot be built beside this file, so
- * there is no oracle/_ref binary: backward parity is "pinned by derivation, not
- * by reference-run vectors".
+ * Parity status: pinned.  The forward is pinned by the reference's own
+ * known-answer tests (src/attention_test.zig), restated in
+ * tests/test_oracle_kat.py.  The backward has no literal vectors anywhere in the
+ * reference; it is pinned by outputs of the reference's own CUDA kernels
+ * (src/cuda/attn_kernels.cu:402-634), which the reference graded against its Zig
+ * CPU code at <= 8.4e-7 (outputs/bench/run-attn.log:36-46) and which, unlike the
+ * Zig code (Zig 0.16 is needed), compile here: oracle/zt_ref.py builds them in
+ * place into oracle/_ref/, tests/golden/make_ref_fixtures.py ran them on a B200
+ * and tests/test_ref_cuda_fixtures.py holds this file to their dq, dk, dv (and
+ * forward and decode outputs) under the reference's own gates.  Central
+ * differences and an independent float64 autograd check it as well
+ * (tests/test_oracle_backward.py).  The log-sum-exp the reference never emits
+ * is defined here as row max + ln(denominator) in f64; it is pinned through the
+ * backward, whose P = exp(S - lse) consumes it.
  *
  * The reference's Zig uses @exp/@sqrt on f64; glibc exp/sqrt in double are used
  * here.  A last-ulp difference in exp() disappears under the f32 store.
