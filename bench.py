@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gather]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one causal GQA forward + backward pass over one batch of the sweep
 configuration (batch 8, 32 query heads over 8 KV heads, head_dim 128, T 4096, f32,
@@ -12,10 +12,14 @@ context 8192, Llama-3-8B heads) in GB/s, the roofline of the dominant kernel, th
 baseline (the oracle port timed on a bounded sample) and the end-to-end figure through
 the reference-facing C ABI with host buffers.
 
-With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU
-workload on its own batch -- sequences are independent, so there is no data-path
-collective -- and the value is the whole job's rate over the slowest rank's time.
-`--gather` adds the NCCL all-gather that returns the sharded outputs to every rank.
+With N > 1 (launched by torchrun, one rank per GPU) the same job -- batch 8 -- is SHARDED: every
+rank runs 8 / N of the sequences (sequences are independent, so there is no data-path collective)
+and the NCCL all-gather that returns out, dq, dk, dv to every rank is inside the timed region, on
+a second stream so that it overlaps the next step's kernels.  `value` is the whole job's rate over
+the slowest rank's time ("scaling": "strong"); the line also carries the phases by themselves
+(`phases`: compute only, gather only), the replica run of the same per-GPU workload on every rank
+(`weak`), the 32k prefill with its KV heads sharded (`long_context`) and the ragged decode with its
+sequences balanced over the ranks (`ragged_decode`), both with their all-gathers timed.
 
 `--impl reference` times the reference's CPU implementation of the same step (the C
 restatement under oracle/, the reference itself being Zig and not buildable here) on the
@@ -42,8 +46,28 @@ DECODE = dict(batch=64, n_ctx=8192, n_heads=32, n_kv_heads=8, head_dim=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+WORKLOAD = "causal GQA attention fwd+bwd, batch 8, 32/8 heads, head_dim 128, T 4096, f32"
+
+
+def headline_config():
+    """The `config` object, the same in both arms."""
+    return {"workload": WORKLOAD, **PREFILL,
+            "l2": "inputs (1.25 GiB per step) exceed the 126 MB L2; nothing is flushed between steps"}
+
+
 def fwd_flops(batch, T, n_heads, head_dim):
     return 2.0 * batch * n_heads * head_dim * T * (T + 1)
+
+
+def load_traffic():
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the captured kernels, from the file
+    written beside the ncu summaries: {kernel: {"bytes": ..., "units": sequences in the captured launch, ...}}.
+    Traffic is per sequence, so a launch of B sequences moves bytes * B / units.  None when the file is absent."""
+    path = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f)
 
 
 def load_peaks():
@@ -237,14 +261,12 @@ def run_reference(args):
     flops, times = cpu_sample(threads, stride, args.steps, min(args.warmup, 1))
     sec = sum(times) / len(times)
     value = flops / sec / 1e12
-    c = PREFILL
     line = {
         "impl": "reference", "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64-accumulate/f32-store",
         "data": "synthetic",
-        "config": {"workload": "causal GQA attention fwd+bwd, batch 8, 32/8 heads, head_dim 128, T 4096, f32",
-                   **c},
+        "config": headline_config(),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": f"every {stride}th query row of every head of the batch "
                                    f"({flops / 1e9:.2f} GFLOP per step, exact count), OpenMP over (item, KV head)"},
@@ -260,6 +282,7 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 
 def run_ours(args):
+    import ctypes
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -276,6 +299,8 @@ def run_ours(args):
     zt = importlib.import_module("z-transformer_b200")
     L = zt.lib.load()
     peaks, peak_kind = load_peaks()
+    traffic = load_traffic()
+    tf32_sust, tf32_burst = peaks["bf16_tflops_sustained"] / 2.0, peaks["bf16_tflops"] / 2.0
 
     c = dict(PREFILL)
     if args.small:  # profiling case: same kernels and tile walk, a quarter of the batch
@@ -283,110 +308,209 @@ def run_ours(args):
     B, T, H, Hkv, D = c["batch"], c["T"], c["n_heads"], c["n_kv_heads"], c["head_dim"]
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
-    q, do = (torch.randn((B, T, H * D), generator=gen, device=dev) for _ in range(2))
-    k, v = (torch.randn((B, T, Hkv * D), generator=gen, device=dev) for _ in range(2))
-    out, dq = torch.empty_like(q), torch.empty_like(q)
-    dk, dv = torch.empty_like(k), torch.empty_like(v)
-    lse, delta = (torch.empty((B, T, H), device=dev) for _ in range(2))
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, H, Hkv, D)
-    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-
-    def step():
-        # the training pair: the forward leaves its f16 planes of q, k, v in the backward's workspace
-        rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                            ws.data_ptr(), ws_bytes, B, T, H, Hkv, D, stream)
-        rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                         do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                         delta.data_ptr(), ws.data_ptr(), ws_bytes, B, T, H, Hkv, D, stream)
-        if rc != 0:
-            raise RuntimeError("libztattn refused the step: " + zt.lib.last_error())
-        if args.gather and world > 1:
-            for x in (out, dq, dk, dv):
-                zt.sharding.gather_batch(x, world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    main_stream = torch.cuda.current_stream(dev)
+    comm_stream = torch.cuda.Stream(dev)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    zt.lib.profile(True)
-    zt.lib.profile_read()
-    launches0 = zt.lib.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    launches = zt.lib.launch_count() - launches0
-    kernels = zt.lib.profile_read()
-    zt.lib.profile(False)
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    F = fwd_flops(B, T, H, D)
-    value = world * 3.5 * F / (ms_step * 1e-3) / 1e12
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def prefill_run(Bl, Hl, Hkvl, Tl, steps, warmup, gather, sample_clocks=False):
+        """`steps` forward+backward passes over this rank's Bl sequences of Hl/Hkvl heads (device-resident inputs).
+        gather: None, or "batch" / "heads": the all-gather that returns out, dq, dk, dv to every rank is part of
+        every step, issued on a second stream so that it overlaps the kernels that follow (the outputs are
+        double-buffered: a step's kernels never write what an earlier step's gather still reads)."""
+        q, do = (torch.randn((Bl, Tl, Hl * D), generator=gen, device=dev) for _ in range(2))
+        k, v = (torch.randn((Bl, Tl, Hkvl * D), generator=gen, device=dev) for _ in range(2))
+        n_sets = 2 if gather else 1
+        outs = [dict(out=torch.empty_like(q), dq=torch.empty_like(q), dk=torch.empty_like(k), dv=torch.empty_like(v))
+                for _ in range(n_sets)]
+        lse, delta = (torch.empty((Bl, Tl, Hl), device=dev) for _ in range(2))
+        ws_bytes = L.zt_attn_backward_workspace_bytes(Bl, Tl, Hl, Hkvl, D)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        gathered = None
+        if gather:
+            gathered = {n: torch.empty((world,) + tuple(x.shape), device=dev) for n, x in outs[0].items()}
+        comm_done = [torch.cuda.Event() for _ in range(n_sets)]
+        ev_out, ev_grad = torch.cuda.Event(), torch.cuda.Event()
+        stream = main_stream.cuda_stream
+        token = ctypes.c_ulonglong(0)
+
+        def step(i, with_gather=True):
+            o = outs[i % n_sets]
+            if gather and with_gather and i >= n_sets:
+                main_stream.wait_event(comm_done[i % n_sets])
+            # the training pair: the forward leaves its f16 planes of q, k, v in the backward's workspace
+            rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
+                                                lse.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D, stream,
+                                                ctypes.byref(token))
+            if gather and with_gather:
+                ev_out.record(main_stream)
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(ev_out)
+                    dist.all_gather_into_tensor(gathered["out"], o["out"])
+            rc |= L.zt_attn_backward_batched_kept(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
+                                                  lse.data_ptr(), do.data_ptr(), o["dq"].data_ptr(), o["dk"].data_ptr(),
+                                                  o["dv"].data_ptr(), delta.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl,
+                                                  Hl, Hkvl, D, stream, token.value)
+            if rc != 0:
+                raise RuntimeError("libztattn refused the step: " + zt.lib.last_error())
+            if gather and with_gather:
+                ev_grad.record(main_stream)
+                with torch.cuda.stream(comm_stream):
+                    comm_stream.wait_event(ev_grad)
+                    for n in ("dq", "dk", "dv"):
+                        dist.all_gather_into_tensor(gathered[n], o[n])
+                    if gather == "heads":  # [G, T, Hs D] -> [T, H D]: the ranks' column slices side by side
+                        for n in ("out", "dq", "dk", "dv"):
+                            g = gathered[n]
+                            g.movedim(0, -2).reshape(*g.shape[1:-1], world * g.shape[-1]).contiguous()
+                    comm_done[i % n_sets].record(comm_stream)
+
+        def drain():
+            if gather:
+                for ev in comm_done:
+                    main_stream.wait_event(ev)
+
+        for i in range(warmup):
+            step(i)
+        drain()
+        barrier()
+        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        if sampler:
+            sampler.start()
+        zt.lib.profile(True)
+        zt.lib.profile_read()
+        launches0 = zt.lib.launch_count()
+        barrier()
+        e0.record()
+        for i in range(steps):
+            step(i)
+        drain()
+        e1.record()
+        barrier()
+        launches = zt.lib.launch_count() - launches0
+        kernels = zt.lib.profile_read()
+        zt.lib.profile(False)
+        clocks = sampler.stop() if sampler else None
+        res = {"ms_per_step": max_over_ranks(e0.elapsed_time(e1) / steps), "kernels": kernels, "launches": int(launches),
+               "clocks": clocks}
+        if gather:
+            # the phases by themselves: the kernels with no gather, and the four gathers with nothing beside them
+            nph = max(3, min(steps, 5))
+            barrier()
+            e0.record()
+            for i in range(nph):
+                step(i, with_gather=False)
+            e1.record()
+            barrier()
+            res["compute_ms"] = max_over_ranks(e0.elapsed_time(e1) / nph)
+            o = outs[0]
+            barrier()
+            e0.record()
+            for _ in range(nph):
+                for n in ("out", "dq", "dk", "dv"):
+                    dist.all_gather_into_tensor(gathered[n], o[n])
+            e1.record()
+            barrier()
+            res["gather_ms"] = max_over_ranks(e0.elapsed_time(e1) / nph)
+            res["gather_bytes_per_rank"] = int(sum(x.numel() for x in o.values()) * 4 * (world - 1))
+        return res
+
+    # ---- the headline step ------------------------------------------------------------------------------------
+    F = fwd_flops(B, T, H, D)   # of the whole job: batch 8 (the replica run does it on every rank)
+    strong = world > 1 and B % world == 0 and not args.small
+    weak_res = None
+    if strong:
+        # the job's 8 sequences split over the ranks, outputs gathered; then the replica run for comparison
+        main = prefill_run(B // world, H, Hkv, T, args.steps, args.warmup, "batch", sample_clocks=True)
+        weak_res = prefill_run(B, H, Hkv, T, max(3, args.steps // 2), args.warmup, None)
+        Bl = B // world
+        value = 3.5 * F / (main["ms_per_step"] * 1e-3) / 1e12
+    else:
+        main = prefill_run(B, H, Hkv, T, args.steps, args.warmup, None, sample_clocks=True)
+        Bl = B
+        value = world * 3.5 * F / (main["ms_per_step"] * 1e-3) / 1e12
+    ms_step, kernels, launches, clocks = main["ms_per_step"], main["kernels"], main["launches"], main["clocks"]
+    Fl = fwd_flops(Bl, T, H, D)  # of one rank's launch
 
     # ---- roofline of the dominant kernel (by summed device time over the timed region) ----------
     # Algorithmic operations credited per launch: forward 2 GEMMs = F; key-outer backward kernel
     # S, dP, dV, dK = 2 F; query-outer backward kernel dQ = 0.5 F (its recomputed S and dP are
     # overhead, not credited); together the backward's 2.5 F.
-    credit = {"attn_fwd_simt": F, "attn_fwd_tc": F, "attn_fwd_tc16": F, "attn_fwd_tc16g": F, "attn_fwd_tc16p": F, "attn_fwd_tc16w": F, "attn_bwd_dkdv_simt": 2.0 * F, "attn_bwd_dq_simt": 0.5 * F,
-              "attn_bwd_tc": 2.5 * F, "attn_bwd_dkdv_tc": 2.0 * F, "attn_bwd_dq_tc": 0.5 * F}
-    # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the B=2 case
-    # (profiles/prefill_tensor_core_kernels_small_case.md), scaled by the batch: traffic is per sequence.
-    traffic_b2 = {"attn_fwd_tc": 305.3e6, "attn_fwd_tc16": 304.6e6, "attn_fwd_tc16g": 300.1e6, "attn_bwd_dkdv_tc": 590.7e6,
-                  "attn_bwd_dq_tc": 448.7e6}
-    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+    credit = {"attn_fwd_simt": Fl, "attn_fwd_tc": Fl, "attn_fwd_tc16": Fl, "attn_fwd_tc16g": Fl, "attn_fwd_tc16x": Fl,
+              "attn_bwd_dkdv_simt": 2.0 * Fl, "attn_bwd_dq_simt": 0.5 * Fl, "attn_bwd_dkdv_tc": 2.0 * Fl,
+              "attn_bwd_dq_tc": 0.5 * Fl}
     total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
     klist = []
     for name, (n, ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
         entry = {"kernel": name, "launches": n, "ms_per_launch": ms / n, "share": ms / total_kernel_ms}
         if name in credit:
             entry["tflops"] = credit[name] / (ms / n * 1e-3) / 1e12
-            entry["frac_of_tf32_peak"] = entry["tflops"] / tf32_peak
+            entry["frac_of_tf32_peak"] = entry["tflops"] / tf32_sust
+            entry["frac_of_tf32_peak_burst"] = entry["tflops"] / tf32_burst
         klist.append(entry)
     dom = klist[0] if klist else None
     roofline = None
     if dom and "tflops" in dom:
-        roofline = {"bound": "tensor", "kernel": dom["kernel"], "achieved": dom["tflops"], "peak": tf32_peak,
-                    "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_peak,
-                    "traffic": traffic_b2[dom["kernel"]] * B / 2 if dom["kernel"] in traffic_b2 else None,
-                    "traffic_source": "ncu capture at batch 2, scaled by batch",
-                    "peak_source": f"{peak_kind}: TF32 dense = bf16_tflops_sustained ({peaks['bf16_tflops_sustained']}) / 2",
-                    "step_frac": value / world / tf32_peak}
+        tr = (traffic or {}).get(dom["kernel"])
+        step_tflops = 3.5 * Fl / ((main.get("compute_ms") or ms_step) * 1e-3) / 1e12  # one GPU's kernels
+        roofline = {"bound": "tensor", "kernel": dom["kernel"], "achieved": dom["tflops"], "peak": tf32_sust,
+                    "unit": "TFLOP/s", "frac": dom["tflops"] / tf32_sust,
+                    "traffic": tr["bytes"] * Bl / tr["units"] if tr else None,
+                    "traffic_source": (f"profiles/ncu_dram_traffic.json ({tr['source']}), scaled by sequences per launch"
+                                       if tr else None),
+                    "peak_source": f"{peak_kind}: TF32 dense = bf16_tflops_sustained ({peaks['bf16_tflops_sustained']}) / 2 "
+                                   "(no TF32 figure is measured; a TF32 MMA is half the rate of a bf16 one)",
+                    "frac_of_burst_peak": dom["tflops"] / tf32_burst,
+                    "burst_peak": tf32_burst,
+                    "step_frac": step_tflops / tf32_sust, "step_frac_of_burst_peak": step_tflops / tf32_burst}
 
     # MMA work issued per step by the f16-split kernels: every credited product is three kind::f16 MMAs, and
     # the dQ kernel recomputes S and dP.  Forward 2 GEMMs, dK/dV kernel 4, dQ kernel 3, of 0.5 F each.
     issued = None
-    if {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels) and ({"attn_fwd_tc16", "attn_fwd_tc16g", "attn_fwd_tc16p", "attn_fwd_tc16w"} & set(kernels)):
-        issued_flop = 3.0 * (2 + 4 + 3) * 0.5 * F
-        issued = {"flop_per_step": issued_flop, "f16_tflops": issued_flop / (ms_step * 1e-3) / 1e12,
-                  "of_bf16_sustained_peak": issued_flop / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
-                  "credited_over_issued": 3.5 * F / issued_flop,
+    if {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels) and ({"attn_fwd_tc16", "attn_fwd_tc16g"} & set(kernels)):
+        issued_flop = 3.0 * (2 + 4 + 3) * 0.5 * Fl
+        t_s = (main.get("compute_ms") or ms_step) * 1e-3
+        issued = {"flop_per_step": issued_flop, "f16_tflops": issued_flop / t_s / 1e12,
+                  "of_bf16_sustained_peak": issued_flop / t_s / 1e12 / peaks["bf16_tflops_sustained"],
+                  "credited_over_issued": 3.5 * Fl / issued_flop,
                   "note": "kind::f16 MMA flops issued (3 per credited product, S and dP recomputed in the dQ "
                           "kernel, masked halves of diagonal tiles not counted) against the measured bf16 GEMM peak"}
 
+    phases = None
+    if strong:
+        phases = {"compute_ms": main["compute_ms"], "gather_ms_alone": main["gather_ms"],
+                  "step_ms_overlapped": ms_step, "gather_bytes_received_per_rank": main["gather_bytes_per_rank"],
+                  "gather_busbw_gbs": main["gather_bytes_per_rank"] / (main["gather_ms"] * 1e-3) / 1e9,
+                  "limiter": "gather" if main["gather_ms"] > main["compute_ms"] else "compute",
+                  "note": "NCCL all_gather_into_tensor of out, dq, dk, dv (f32) to every rank; in the step it runs on "
+                          "a second stream beside the next kernels, outputs double-buffered"}
+    weak = None
+    if weak_res:
+        weak = {"value": world * 3.5 * F / (weak_res["ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": weak_res["ms_per_step"], "scaling": "weak",
+                "note": "every rank runs the whole batch of 8 on its own data, no gather (replicas)"}
+
     # ---- the same step with rope.forward on q and k fused in (src/model.zig:372-375), on request -------------
     rope = None
-    if args.rope:
+    if args.rope and not strong:
+        q, do = (torch.randn((B, T, H * D), generator=gen, device=dev) for _ in range(2))
+        k, v = (torch.randn((B, T, Hkv * D), generator=gen, device=dev) for _ in range(2))
         rws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
 
         def rope_step():
-            o, lse = zt.attention_forward_rope(q, k, v, H, Hkv, D, pos=0, workspace=rws, want_lse=True)
-            zt.attention_backward_rope(q, k, v, o, lse, do, H, Hkv, D, pos=0, workspace=rws)
+            o, lse_ = zt.attention_forward_rope(q, k, v, H, Hkv, D, pos=0, workspace=rws, want_lse=True)
+            zt.attention_backward_rope(q, k, v, o, lse_, do, H, Hkv, D, pos=0, workspace=rws, kept=True)
 
         for _ in range(max(args.warmup, 3)):
             rope_step()
@@ -406,7 +530,7 @@ def run_ours(args):
                 "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in rk.items()},
                 "note": "q, k handed over unrotated; rotation inside the pre-pass (forward and backward), R^T inside "
                         "the dQ kernel's epilogue, one in-place pass over dk; credited FLOPs unchanged"}
-        del rws
+        del rws, q, k, v, do
 
     # ---- end to end with host buffers (rank-local) ----------------------------------------------------
     # Every sequence's q, k, v, dout go up from pinned host memory and its out, dq, dk, dv come back,
@@ -417,12 +541,13 @@ def run_ours(args):
     #    (src/model.zig:481-514): upload, zt_attn_forward, zt_attn_backward, download, one sequence
     #    after the other on one stream.  The reference ABI's backward is given neither out nor the
     #    log-sum-exp, so it recomputes the forward; the credited work is 3.5 F either way.
+    # With N ranks the job's 8 sequences are split: every rank moves and computes its own 8 / N.
     e2e_steps = max(1, min(args.steps, 3))
-    e2e_B = 1 if args.small else B
-    hq, hdo = (torch.randn((B, T, H * D)).pin_memory() for _ in range(2))
-    hk, hv = (torch.randn((B, T, Hkv * D)).pin_memory() for _ in range(2))
-    hout, hdq = (torch.empty((B, T, H * D)).pin_memory() for _ in range(2))
-    hdk, hdv = (torch.empty((B, T, Hkv * D)).pin_memory() for _ in range(2))
+    e2e_B = 1 if args.small else Bl
+    hq, hdo = (torch.randn((e2e_B, T, H * D)).pin_memory() for _ in range(2))
+    hk, hv = (torch.randn((e2e_B, T, Hkv * D)).pin_memory() for _ in range(2))
+    hout, hdq = (torch.empty((e2e_B, T, H * D)).pin_memory() for _ in range(2))
+    hdk, hdv = (torch.empty((e2e_B, T, Hkv * D)).pin_memory() for _ in range(2))
     holder = zt.Attn(T, H, Hkv, D, device=dev)
     pipe = zt.AttnPipeline(T, H, Hkv, D, slots=3, device=dev)
 
@@ -440,48 +565,71 @@ def run_ours(args):
             hdv[b].view(-1).copy_(holder.dv, non_blocking=True)
 
     def e2e_step():
-        pipe.step(hq[:e2e_B], hk[:e2e_B], hv[:e2e_B], hdo[:e2e_B], hout[:e2e_B], hdq[:e2e_B], hdk[:e2e_B],
-                  hdv[:e2e_B])
+        pipe.step(hq, hk, hv, hdo, hout, hdq, hdk, hdv)
 
-    def timed(fn):
+    def timed(fn, reps=e2e_steps):
         fn()
         barrier()
         e0.record()
-        for _ in range(e2e_steps):
+        for _ in range(reps):
             fn()
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1) / e2e_steps
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(e0.elapsed_time(e1) / reps)
 
     e2e_sync_ms = timed(e2e_sync_step)
     e2e_ms = timed(e2e_step)
-    e2e_value = world * 3.5 * F * (e2e_B / B) / (e2e_ms * 1e-3) / 1e12
-    e2e_sync_value = world * 3.5 * F * (e2e_B / B) / (e2e_sync_ms * 1e-3) / 1e12
+    job_share = world * e2e_B / B  # batch-8 jobs' worth of flops that one e2e step does, all ranks together
+    e2e_value = job_share * 3.5 * F / (e2e_ms * 1e-3) / 1e12
+    e2e_sync_value = job_share * 3.5 * F / (e2e_sync_ms * 1e-3) / 1e12
     h2d = (2 * hq[0].numel() + 2 * hk[0].numel()) * 4 * e2e_B
     d2h = h2d
+    # What the host's copy engines give this rank, measured beside the figure they bound: one direction at a
+    # time and both at once (PCIe is full duplex), 256 MiB pinned buffers, all ranks copying together.
+    n_copy = hq[0].numel() if hq[0].numel() * 4 <= (256 << 20) else (256 << 20) // 4
+    src_h, dst_h = hq.view(-1)[:n_copy], hout.view(-1)[:n_copy]
+    dbuf_up, dbuf_dn = torch.empty(n_copy, device=dev), torch.randn(n_copy, device=dev)
+    up = lambda: dbuf_up.copy_(src_h, non_blocking=True)
+
+    def down():
+        with torch.cuda.stream(comm_stream):
+            dst_h.copy_(dbuf_dn, non_blocking=True)
+
+    def both():
+        up()
+        down()
+
+    def timed_copy(fn):
+        ms = timed(lambda: (fn(), comm_stream.synchronize()), 5)
+        return n_copy * 4 / (ms * 1e-3) / 1e9
+    h2d_gbs, d2h_gbs, duplex_gbs = timed_copy(up), timed_copy(down), timed_copy(both)
+    copy_bound_ms = max(h2d, d2h) / (duplex_gbs * 1e9) * 1e3
+    pcie = {"h2d_gbs": h2d_gbs, "d2h_gbs": d2h_gbs, "each_way_when_both_run_gbs": duplex_gbs,
+            "copy_bound_ms_per_step": copy_bound_ms, "e2e_over_copy_bound": copy_bound_ms / e2e_ms,
+            "note": "pinned host <-> device cudaMemcpyAsync of 256 MiB per direction, every rank at once, max over "
+                    "ranks; the copy bound of a step is its bytes one way over the duplex rate"}
     del pipe
-    del hq, hdo, hk, hv, hout, hdq, hdk, hdv, holder
+    del hq, hdo, hk, hv, hout, hdq, hdk, hdv, holder, dbuf_up, dbuf_dn
 
     # ---- decode configuration -------------------------------------------------------------------
     d = dict(DECODE)
     if args.small:
         d["batch"] = 8
     Bd, n_ctx = d["batch"], d["n_ctx"]
-    kc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
-    vc = torch.randn((Bd, n_ctx, Hkv * D), generator=gen, device=dev)
-    qd = torch.randn((Bd, H * D), generator=gen, device=dev)
-    n_keys = torch.full((Bd,), n_ctx, dtype=torch.int32, device=dev)
-    wsd = zt.DecodeWorkspace(Bd, n_ctx, H, Hkv, D, dev)
+    Bd_l = Bd // world if (strong and Bd % world == 0) else Bd  # the job's 64 sequences split over the ranks
+    kc = torch.randn((Bd_l, n_ctx, Hkv * D), generator=gen, device=dev)
+    vc = torch.randn((Bd_l, n_ctx, Hkv * D), generator=gen, device=dev)
+    qd = torch.randn((Bd_l, H * D), generator=gen, device=dev)
+    n_keys = torch.full((Bd_l,), n_ctx, dtype=torch.int32, device=dev)
+    wsd = zt.DecodeWorkspace(Bd_l, n_ctx, H, Hkv, D, dev)
     outd = torch.empty_like(qd)
+    outd_all = torch.empty((world,) + tuple(outd.shape), device=dev) if strong else None
     dsteps = max(args.steps, 10)
 
     def dstep():
         zt.decode_attention(qd, kc, vc, n_keys, H, Hkv, D, workspace=wsd, out=outd)
+        if strong:
+            dist.all_gather_into_tensor(outd_all, outd)
 
     for _ in range(max(args.warmup, 3)):
         dstep()
@@ -495,26 +643,27 @@ def run_ours(args):
     barrier()
     dk_prof = zt.lib.profile_read()
     zt.lib.profile(False)
-    d_ms = e0.elapsed_time(e1) / dsteps
-    if world > 1:
-        t = torch.tensor([d_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        d_ms = float(t.item())
-    d_bytes = float(Bd) * n_ctx * 2 * Hkv * D * 4 + 2.0 * Bd * H * D * 4
-    d_gbs = world * d_bytes / (d_ms * 1e-3) / 1e9
+    d_ms = max_over_ranks(e0.elapsed_time(e1) / dsteps)
+    d_bytes_l = float(Bd_l) * n_ctx * 2 * Hkv * D * 4 + 2.0 * Bd_l * H * D * 4
+    d_gbs = world * d_bytes_l / (d_ms * 1e-3) / 1e9
     dn, dms = dk_prof.get("decode_splitk_kernel", (1, d_ms))
-    d_kernel_gbs = d_bytes / (dms / dn * 1e-3) / 1e9
+    d_kernel_gbs = d_bytes_l / (dms / dn * 1e-3) / 1e9
+    dtr = (traffic or {}).get("decode_splitk_kernel")
     decode = {"metric": "decode_attn_hbm_gbs", "value": d_gbs, "unit": "GB/s", "ms_per_step": d_ms,
+              "scaling": "strong (the 64 sequences split over the ranks, outputs all-gathered inside the step)" if strong
+                         else "weak",
               "config": {"workload": "KV-cache decode attention, batch 64, context 8192 (new token's row included), "
-                                     "32/8 heads, head_dim 128, f32", **d},
-              "bytes_per_step": d_bytes,
+                                     "32/8 heads, head_dim 128, f32", **d, "batch_per_gpu": Bd_l},
+              "bytes_per_step": world * d_bytes_l,
               "roofline": {"bound": "hbm", "kernel": "decode_splitk_kernel", "achieved": d_kernel_gbs,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": d_kernel_gbs / peaks["hbm_gbs"],
-                           "traffic": 541.2e6 * Bd / 8, "traffic_source": "ncu capture at batch 8, scaled by batch",
+                           "traffic": dtr["bytes"] * Bd_l / dtr["units"] if dtr else None,
+                           "traffic_source": (f"profiles/ncu_dram_traffic.json ({dtr['source']}), scaled by sequences "
+                                              "per launch") if dtr else None,
                            "peak_source": f"{peak_kind}: hbm_gbs"},
               "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in dk_prof.items()}}
     # decode end to end with host buffers: q up, out down; the cache stays resident in HBM
-    hqd, houtd = torch.randn((Bd, H * D)).pin_memory(), torch.empty((Bd, H * D)).pin_memory()
+    hqd, houtd = torch.randn((Bd_l, H * D)).pin_memory(), torch.empty((Bd_l, H * D)).pin_memory()
     barrier()
     e0.record()
     for _ in range(dsteps):
@@ -523,9 +672,62 @@ def run_ours(args):
         houtd.copy_(outd, non_blocking=True)
     e1.record()
     barrier()
-    decode["e2e"] = {"value": world * d_bytes / (e0.elapsed_time(e1) / dsteps * 1e-3) / 1e9, "unit": "GB/s",
-                     "h2d_bytes_per_step": hqd.numel() * 4, "d2h_bytes_per_step": houtd.numel() * 4}
+    decode["e2e"] = {"value": world * d_bytes_l / (max_over_ranks(e0.elapsed_time(e1) / dsteps) * 1e-3) / 1e9,
+                     "unit": "GB/s", "h2d_bytes_per_step": hqd.numel() * 4, "d2h_bytes_per_step": houtd.numel() * 4}
     del kc, vc
+
+    # ---- the two sharded configurations of the benchmark definition, with their gathers --------------------------
+    long_context = ragged = None
+    if not args.small and not args.no_extras and Hkv % world == 0 and 256 % world == 0:
+        # 32k prefill: the 8 KV heads (and their query heads) split over the ranks; outputs are column slices,
+        # all-gathered and laid side by side
+        sh = zt.sharding.shard_kv_heads(H, Hkv, world, rank)
+        T4 = 32768
+        r4 = prefill_run(1, sh.n_heads, sh.n_kv_heads, T4, 3, 3, "heads" if world > 1 else None)
+        F4 = fwd_flops(1, T4, H, D)
+        long_context = {"config": "T 32768, batch 1, 32/8 heads, head_dim 128, fwd+bwd; KV heads sharded over the ranks",
+                        "ms_per_step": r4["ms_per_step"], "tflops": 3.5 * F4 / (r4["ms_per_step"] * 1e-3) / 1e12,
+                        "frac_of_tf32_peak_per_gpu": 3.5 * F4 / (r4["ms_per_step"] * 1e-3) / 1e12 / world / tf32_sust,
+                        "scaling": "strong", "kv_heads_per_gpu": sh.n_kv_heads}
+        if world > 1:
+            long_context.update({"compute_ms": r4["compute_ms"], "gather_ms_alone": r4["gather_ms"],
+                                 "gather_bytes_received_per_rank": r4["gather_bytes_per_rank"]})
+        # ragged decode: 256 sequences, lengths uniform in [1, 16384], balanced longest-first over the ranks
+        rng = np.random.default_rng(0)
+        lengths = rng.integers(1, 16385, size=256)
+        assignment, inverse = zt.sharding.balance_sequences(lengths, world)
+        mine = lengths[np.array(assignment[rank])].astype(np.int32)
+        B5, ctx5 = 256 // world, 16384
+        kc5 = torch.empty((B5, ctx5, Hkv * D), device=dev)
+        vc5 = torch.empty_like(kc5)
+        for i in range(0, B5, 16):
+            kc5[i:i + 16].normal_(generator=gen)
+            vc5[i:i + 16].normal_(generator=gen)
+        q5 = torch.randn((B5, H * D), generator=gen, device=dev)
+        nk5 = torch.from_numpy(mine).to(dev)
+        ws5 = zt.DecodeWorkspace(B5, ctx5, H, Hkv, D, dev)
+        out5 = torch.empty_like(q5)
+        all5 = torch.empty((world,) + tuple(out5.shape), device=dev)
+        inv5 = torch.as_tensor(inverse, dtype=torch.long, device=dev)
+
+        def step5(with_gather=True):
+            zt.decode_attention(q5, kc5, vc5, nk5, H, Hkv, D, workspace=ws5, out=out5)
+            if world > 1 and with_gather:
+                dist.all_gather_into_tensor(all5, out5)
+                all5.view(256, H * D).index_select(0, inv5)  # back into the caller's order
+
+        ms5 = timed(step5, 10)
+        ms5_compute = timed(lambda: step5(False), 10)
+        bytes5 = float(lengths.sum()) * 2 * Hkv * D * 4 + 2.0 * 256 * H * D * 4
+        loads = [int(lengths[np.array(a)].sum()) for a in assignment]
+        ragged = {"config": "ragged decode, 256 sequences, context U[1, 16384] (seed 0), 32/8 heads, head_dim 128; "
+                            "sequences balanced longest-first over the ranks",
+                  "ms_per_step": ms5, "compute_ms": ms5_compute, "gbs": bytes5 / (ms5 * 1e-3) / 1e9,
+                  "gbs_per_gpu": bytes5 / (ms5 * 1e-3) / 1e9 / world,
+                  "frac_of_hbm_peak_per_gpu": bytes5 / (ms5 * 1e-3) / 1e9 / world / peaks["hbm_gbs"],
+                  "bytes_per_step": bytes5, "keys_per_rank_max_over_mean": max(loads) / (sum(loads) / world),
+                  "scaling": "strong"}
+        del kc5, vc5
 
     # ---- CPU baseline on rank 0 at N = 1 --------------------------------------------------------
     cpu = None
@@ -543,22 +745,29 @@ def run_ours(args):
                                           f"{times1[0]:.1f} s"}
 
     if rank == 0:
+        cfg = headline_config()
+        if args.small:
+            cfg["batch"] = B
         line = {
             "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "causal GQA attention fwd+bwd, batch 8 per GPU, 32/8 heads, head_dim 128, "
-                                   "T 4096, f32", **c, "l2": "inputs (1.25 GiB per step) exceed the 126 MB L2",
-                       "gather": bool(args.gather and world > 1)},
-            "roofline": roofline, "issued_mma": issued, "rope": rope, "kernels": klist, "cpu_baseline": cpu,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": cfg,
+            "sharding": (f"the batch of 8 split over {world} ranks ({Bl} per GPU); NCCL all-gather of out, dq, dk, dv "
+                         "to every rank inside the step, overlapped with the next kernels") if strong else
+                        ("one GPU" if world == 1 else "replicas"),
+            "roofline": roofline, "issued_mma": issued, "phases": phases, "weak": weak, "rope": rope, "kernels": klist,
+            "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "host_cpus": cpu_binding,
-                    "api": "zt.AttnPipeline.step: per sequence, pinned host -> device, zt_attn_forward_batched + "
-                           "zt_attn_backward_batched, device -> pinned host; three streams, three buffer slots"},
+                    "ms_per_step": e2e_ms, "host_cpus": cpu_binding, "pcie": pcie,
+                    "api": "zt.AttnPipeline.step: per sequence, pinned host -> device, zt_attn_forward_batched_keep + "
+                           "zt_attn_backward_batched_kept, device -> pinned host; three streams, three buffer slots"
+                           + (f"; each rank moves and computes its {Bl} of the job's 8 sequences" if strong else "")},
             "e2e_sync": {"value": e2e_sync_value, "unit": "TFLOP/s", "ms_per_step": e2e_sync_ms,
                          "api": "device.Attn pattern: upload, zt_attn_forward, zt_attn_backward, download, one "
                                 "sequence after the other on one stream"},
-            "gpu_launches": int(launches), "clocks": clocks, "decode": decode, "small": bool(args.small),
+            "gpu_launches": int(launches), "clocks": clocks, "decode": decode, "long_context": long_context,
+            "ragged_decode": ragged, "small": bool(args.small),
             "paths": {"prefill": [k_["kernel"] for k_ in klist]},
         }
         print(json.dumps(line), flush=True)
@@ -644,14 +853,16 @@ def run_all_configs(args):
             lse_, delta_ = (torch.empty((B, T, H), device=dev) for _ in range(2))
 
             def pair(stream):
+                import ctypes
+                token = ctypes.c_ulonglong(0)
                 rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), o_.data_ptr(),
                                                     lse_.data_ptr(), bws.buf.data_ptr() if bws.nbytes else None,
-                                                    bws.nbytes, B, T, H, Hkv, D, stream)
-                rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), o_.data_ptr(),
-                                                 lse_.data_ptr(), do.data_ptr(), dq_.data_ptr(), dk_.data_ptr(),
-                                                 dv_.data_ptr(), delta_.data_ptr(),
-                                                 bws.buf.data_ptr() if bws.nbytes else None, bws.nbytes, B, T, H, Hkv, D,
-                                                 stream)
+                                                    bws.nbytes, B, T, H, Hkv, D, stream, ctypes.byref(token))
+                rc |= L.zt_attn_backward_batched_kept(q.data_ptr(), k.data_ptr(), v.data_ptr(), o_.data_ptr(),
+                                                      lse_.data_ptr(), do.data_ptr(), dq_.data_ptr(), dk_.data_ptr(),
+                                                      dv_.data_ptr(), delta_.data_ptr(),
+                                                      bws.buf.data_ptr() if bws.nbytes else None, bws.nbytes, B, T, H,
+                                                      Hkv, D, stream, token.value)
                 if rc != 0:
                     raise RuntimeError(zt.lib.last_error())
 
@@ -724,7 +935,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--gather", action="store_true", help="time the all-gather of sharded outputs too")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the 32k prefill and the ragged decode (extra keys `long_context`, `ragged_decode`)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--rope", action="store_true",
                     help="also time the step with the rotary embedding of q and k fused in (extra key `rope`)")

@@ -12,9 +12,13 @@
  * Conventions (from src/cuda/attn_kernels.cu:21-54, kept):
  *   - every pointer is a DEVICE pointer unless its name starts with `host_`;
  *   - the caller owns all buffers; entry points taking a `workspace` argument
- *     never allocate.  The six reference entry points take no workspace; the
- *     only memory they may create is one small per-device arena, made once on
- *     first use (see zt_attn_forward below);
+ *     never allocate.  The reference's two launching entry points and
+ *     zt_attn_forward_batched take no workspace; their scratch (the 16-bit
+ *     operand planes of q, k, v, dout: up to 4 bytes per element of those
+ *     tensors, or 16 MiB for a decode-shaped call) lives in one per-device
+ *     arena.  See "The per-device arena" below for when it allocates, how to
+ *     make that never happen mid-run (zt_attn_reserve) and what calls that
+ *     share it must not do;
  *   - return 0: the work was enqueued on `stream` (no synchronisation);
  *     return 1: refused, with the reason on stderr and in zt_attn_last_error();
  *     nothing was launched and no buffer was touched;
@@ -87,6 +91,27 @@ int zt_attn_backward(const float *q, const float *k, const float *v, const float
 /* Extensions                                                                 */
 /* ------------------------------------------------------------------------- */
 
+/* The per-device arena.  zt_attn_forward, zt_attn_backward and zt_attn_forward_batched have no
+ * workspace argument (the reference's signatures have none, src/cuda/device.zig:69-105), so their
+ * scratch comes from an arena this library keeps per device.  Rules:
+ *  - it is allocated (cudaMalloc) by the first call on a device that needs it and grows when a
+ *    later call needs more; it never shrinks, and an outgrown arena is kept until the process ends
+ *    (work queued earlier may still be using it), so growth costs memory, never correctness;
+ *  - zt_attn_reserve sizes it for a shape up front -- the place for it is where the reference's
+ *    holder sizes its own eleven buffers (device.Attn.init, src/cuda/device.zig:221-299; that
+ *    function already calls zt_attn_dim_ok).  After zt_attn_reserve(batch, T, ...) no call of
+ *    that shape or a smaller one allocates.  (No counterpart in the reference, whose kernels need
+ *    no scratch.)
+ *  - while `stream` is being captured into a CUDA graph a call that would have to grow the arena
+ *    is refused (return 1) instead of allocating inside the capture: reserve first;
+ *  - every call on a device shares the arena: two calls that use it must not overlap on the GPU
+ *    (different streams or host threads without an ordering between them) -- the second would
+ *    overwrite the first one's operand planes.  Calls queued on one stream are safe.  The batched
+ *    calls that take a caller workspace (_keep, backward_batched, _rope_, decode) do not touch it. */
+int zt_attn_reserve(int batch, int T, int n_heads, int n_kv_heads, int dim);
+/* Bytes the current device's arena holds now (0 before its first use). */
+size_t zt_attn_arena_bytes(void);
+
 /* The reason of the calling thread's most recent refusal ("" if none).  The
  * reference only prints to stderr (src/cuda/attn_kernels.cu:21-37); bindings
  * that cannot capture stderr read it here. */
@@ -96,18 +121,13 @@ const char *zt_attn_last_error(void);
  * (the return code and zt_attn_last_error() still report them). */
 void zt_attn_set_verbose(int on);
 
-/* Which implementation the next launches use: 0 = automatic (the fastest tensor-core
- * kernel the shape allows, CUDA-core kernels elsewhere: the f16-split forward takes the same
- * query rows of two heads of a KV group per CTA when the group has an even number of query
- * heads and that still gives every SM a CTA, one head per CTA otherwise; 7 = two heads per CTA
- * whatever the number of CTAs), 1 = CUDA-core kernels only, 2 = as 0 but the forward
- * uses the 3xTF32 kernel instead of the f16-split one.  The others are forms of the f16-split
- * forward with one head per CTA: 6 = the plain one (key tiles of 64, two softmax sets of four
- * warps splitting the key tiles by parity), 3 = key tiles of 128 (four softmax sets sharing
- * one accumulator; slower), 4 = eight softmax warps per set (two threads per row), 5 = one
- * CTA per SM walking a list of query tiles, the next tile's Q fetched a tile ahead and the
- * K/V rings streaming across tiles.  For tests and for bisecting a parity failure; returns
- * the previous value. */
+/* Which implementation the next launches use: 0 = automatic (the fastest tensor-core kernel the
+ * shape allows, CUDA-core kernels elsewhere; the f16-split forward takes the same query rows of two
+ * heads of a KV group per CTA when the group has an even number of query heads and that still gives
+ * every SM a CTA, one head per CTA otherwise), 1 = CUDA-core kernels only, 2 = as 0 but the forward
+ * uses the 3xTF32 kernel instead of the f16-split one, 6 = the f16-split forward with one head per
+ * CTA, 7 = with two heads per CTA whatever the number of CTAs.  Any other value selects 0.  For
+ * tests and for bisecting a parity failure; returns the previous value. */
 int zt_attn_set_path(int path);
 
 /* Batched training-shaped forward: `batch` independent sequences of T rows,
@@ -130,17 +150,27 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
 
 /* The forward of a training step: zt_attn_forward_batched, except that the 16-bit operand planes of
- * q, k, v it builds are written into the backward's workspace and kept there.  The next
- * zt_attn_backward_batched on this device that is given the same workspace, the same q, k, v
- * pointers, shape and stream then converts only dout (a quarter less pre-pass traffic per step), and
- * this call takes nothing from the per-device arena.  The caller's promise: q, k, v are not written
- * between the two calls.  The note is used once and dropped by any other backward; with a workspace
- * that is NULL, short or misaligned, or a shape the tensor-core kernels do not take, this is the
- * ordinary forward and nothing is kept.  No reference counterpart (the reference's forward keeps
- * nothing for its backward, which recomputes the softmax statistics). */
+ * q, k, v it builds are written into the backward's workspace and kept there, and *host_token
+ * (a host pointer, may be NULL) receives a token for them: non-zero when planes were kept, 0 when not
+ * (a workspace that is NULL, short or misaligned, or a shape the tensor-core kernels do not take:
+ * this is then the ordinary forward).  This call takes nothing from the per-device arena.
+ * zt_attn_backward_batched_kept, given the same workspace, shape and that token, converts only dout
+ * (a quarter less pre-pass traffic per step).  The token is the caller's statement that q, k, v have
+ * not been written since the forward; the library never infers that from pointer values.  A token is
+ * good for one backward; any other call that writes the workspace (another forward_keep, a plain
+ * backward) retires it, and a retired or mismatched token is refused (return 1), never silently
+ * honoured.  With token 0 the _kept call is zt_attn_backward_batched.  Tokens are checked on the
+ * host when the call is made: when a CUDA graph is captured, capture the forward and its backward
+ * together.  No reference counterpart (the reference's forward keeps nothing for its backward, which
+ * recomputes the softmax statistics). */
 int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
                                  void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, zt_stream_t stream);
+                                 int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token);
+int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v, const float *out,
+                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                  int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                                  unsigned long long token);
 
 /* Attention with the rotary position embedding of its input side fused in: q and k are the
  * projections BEFORE rope.forward (src/rope.zig:21-55; the reference rotates them first,
@@ -153,17 +183,21 @@ int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v,
  *             src/autograd.zig:851-874, applied to the attention gradients), dv as usual; out and
  *             lse are the rope forward's.
  * Both take a caller workspace of zt_attn_rope_workspace_bytes(...) bytes (256-byte aligned; never
- * 0) and allocate nothing.  Refusals: those of the batched calls, plus pos < 0, theta <= 0, and a
- * missing, short or misaligned workspace. */
+ * 0) and allocate nothing.  The forward keeps its operand planes (rotated q and k among them) in that
+ * workspace and reports a token through *host_token (may be NULL) exactly as
+ * zt_attn_forward_batched_keep does; the backward takes it back (`token`; 0 converts everything
+ * again) under the same rules, pos and theta included.  Refusals: those of the batched calls, plus
+ * pos < 0, theta <= 0, a missing, short or misaligned workspace, and a stale token. */
 size_t zt_attn_rope_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim);
 int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
                                  void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream);
+                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream,
+                                 unsigned long long *host_token);
 int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v, const float *out,
                                   const float *lse, const float *dout, float *dq, float *dk, float *dv,
                                   float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
                                   int n_heads, int n_kv_heads, int dim, int pos, double theta,
-                                  zt_stream_t stream);
+                                  zt_stream_t stream, unsigned long long token);
 
 /* KV-cache decode attention for a batch of sequences: decode.attnStep
  * (src/decode.zig:326-392) for every sequence at once, over device-resident
@@ -203,7 +237,9 @@ size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_k
  *
  * Rules that come with a shared, permanent scratch:
  *  - the first call made with a given device current looks up the array's address on that
- *    device; make that first call before starting any stream capture;
+ *    device (and, where the CUDA runtime loads modules lazily, is what makes the array exist there):
+ *    make that first call at start-up -- before any stream capture, and before a memory pool of the
+ *    caller's takes the rest of the device;
  *  - all calls on a device use the same array, which still holds the previous call's partial
  *    results: two calls may not overlap on the GPU (different streams, or threads, without an
  *    ordering between them race on it).  Calls queued on one stream are safe. */
@@ -213,7 +249,8 @@ int zt_attn_decode_static(const float *q, const float *k_cache, const float *v_c
 size_t zt_attn_decode_static_capacity(void);
 
 /* After synchronising: number of sequences the last zt_attn_decode that used
- * `workspace` skipped for a bad n_keys (the count is kept inside the workspace). */
+ * `workspace` skipped for a bad n_keys (the count is kept inside the workspace).
+ * A NULL workspace reads the count of the last zt_attn_decode_static on the current device. */
 int zt_attn_decode_status(const void *workspace, int *host_bad_sequences);
 
 /* kv_cache.Layer.append for a batch of device-resident caches
@@ -233,6 +270,13 @@ unsigned long long zt_attn_launch_count(void);
  * of its bounded internal waits, else the code of the wait that did (its outputs are then
  * invalid).  A correct run never sets it; tests assert 0. */
 int zt_attn_tc_status(int *host_status);
+
+/* After synchronising: how many thread blocks of the tensor-core backward met the bound on dS since
+ * the last call of this function (which clears the count).  The backward hands dS to the tensor core
+ * as 16-bit pieces, scaled so that its worst case stays inside their range; a value that reaches the
+ * bound all the same (only an Inf or NaN arriving in dout or delta can) is clamped and counted here
+ * instead of passing unnoticed.  A correct run reads 0; tests assert it. */
+int zt_attn_tc_saturated(unsigned int *host_count);
 
 /* Per-kernel device timing for benchmarks.  zt_attn_profile(1) makes every later launch
  * record a pair of CUDA events on its stream; zt_attn_profile_read waits for them, writes one

@@ -450,6 +450,128 @@ int zto_sampled_step(const float *q, const float *k, const float *v, const float
     return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
 }
 
+/*
+ * The backward of one KV group restricted to what a long-context check can afford:
+ *   - dq of the query rows listed in `rows` (n_rows of them), every head of the group:
+ *     dq_rows[(i * group + hh) * dim + j];
+ *   - dk, dv of the LAST `window` keys (keys s >= T - window): dk_win[(s - s_lo) * dim + j].
+ * A key's dk/dv receive terms only from query rows t >= s, so the window needs the rows
+ * t >= s_lo of the group's heads and nothing else; each of those rows still needs its whole
+ * softmax (keys 0..t), which is where the time goes.
+ *
+ * Arithmetic and order are exactly zto_backward_row's (autograd.zig:735-838): per row the
+ * f64 score, max, exp, denominator, probability, d_probs and their dot; per key f32
+ * accumulators that receive one f32-narrowed term per (head of the group -- outer --, query
+ * row ascending).  Rows are independent, so the per-row statistics are computed in parallel
+ * first; then every key of the window (independent of the other keys) replays its own
+ * accumulation in the reference's order from those statistics.
+ */
+int zto_backward_window(const float *q, const float *k, const float *v, const float *dout, size_t T,
+                        size_t n_heads, size_t n_kv_heads, size_t dim, size_t kv, const size_t *rows,
+                        size_t n_rows, size_t window, float *dq_rows, float *dk_win, float *dv_win,
+                        int threads) {
+    if (n_kv_heads == 0 || dim == 0 || n_heads % n_kv_heads != 0) return ZTO_INVALID_HEAD_CONFIG;
+    if (kv >= n_kv_heads || window > T) return ZTO_DIMENSION_MISMATCH;
+    for (size_t i = 0; i < n_rows; ++i)
+        if (rows[i] >= T) return ZTO_DIMENSION_MISMATCH;
+    const size_t group = n_heads / n_kv_heads;
+    const size_t q_cols = n_heads * dim, k_cols = n_kv_heads * dim;
+    const double scale = 1.0 / sqrt((double)dim);
+    const size_t s_lo = T - window;
+    if (threads < 1) threads = 1;
+    int failed = 0;
+    /* per (head of the group, row t >= s_lo): row max, denominator, dot_pp */
+    double *stats = (double *)malloc(sizeof(double) * 3 * (group * window > 0 ? group * window : 1));
+    if (!stats) return ZTO_OUT_OF_MEMORY;
+#pragma omp parallel num_threads(threads)
+    {
+        double *probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+        double *d_probs = (double *)malloc(sizeof(double) * (T ? T : 1));
+        double *p_ds = (double *)malloc(sizeof(double) * (T ? T : 1));
+        float *dk_dummy = (float *)malloc(sizeof(float) * (T ? T : 1) * k_cols);
+        float *dq_dummy = (float *)malloc(sizeof(float) * q_cols);
+        const int ok = probs && d_probs && p_ds && dk_dummy && dq_dummy;
+        if (!ok) {
+#pragma omp atomic write
+            failed = 1;
+        }
+        /* dq of the listed rows: the reference's row body, its dk/dv side effects discarded */
+#pragma omp for schedule(dynamic, 1)
+        for (long u = 0; u < (long)(n_rows * group); ++u) {
+            if (!ok) continue;
+            const size_t i = (size_t)u / group, hh = (size_t)u % group, h = kv * group + hh, t = rows[i];
+            /* zto_backward_row writes dq[t * q_cols + h * dim + j]: aim that at dq_dummy */
+            zto_backward_row(q, k, v, dout, q_cols, k_cols, dim, h, kv, t, scale, probs, d_probs, p_ds,
+                             dq_dummy - t * q_cols, dk_dummy, dk_dummy);
+            memcpy(dq_rows + (i * group + hh) * dim, dq_dummy + h * dim, sizeof(float) * dim);
+        }
+        /* statistics of the rows that reach the window */
+#pragma omp for schedule(dynamic, 4)
+        for (long u = 0; u < (long)(group * window); ++u) {
+            if (!ok) continue;
+            const size_t hh = (size_t)u / window, t = s_lo + (size_t)u % window, h = kv * group + hh;
+            const float *q_head = q + t * q_cols + h * dim;
+            const float *dh = dout + t * q_cols + h * dim;
+            double row_max = -INFINITY;
+            for (size_t s = 0; s <= t; ++s) {
+                const float *k_head = k + s * k_cols + kv * dim;
+                double dot = 0.0;
+                for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
+                probs[s] = dot * scale;
+                if (probs[s] > row_max) row_max = probs[s];
+            }
+            double denom = 0.0;
+            for (size_t s = 0; s <= t; ++s) {
+                probs[s] = exp(probs[s] - row_max);
+                denom += probs[s];
+            }
+            for (size_t s = 0; s <= t; ++s) probs[s] /= denom;
+            double dot_pp = 0.0;
+            for (size_t s = 0; s <= t; ++s) {
+                const float *v_head = v + s * k_cols + kv * dim;
+                double acc = 0.0;
+                for (size_t j = 0; j < dim; ++j) acc += (double)dh[j] * (double)v_head[j];
+                dot_pp += probs[s] * acc;
+            }
+            stats[3 * u] = row_max, stats[3 * u + 1] = denom, stats[3 * u + 2] = dot_pp;
+        }
+        /* every key of the window replays its accumulation: heads outer, rows ascending */
+#pragma omp for schedule(dynamic, 4)
+        for (long w = 0; w < (long)window; ++w) {
+            if (!ok) continue;
+            const size_t s = s_lo + (size_t)w;
+            const float *k_head = k + s * k_cols + kv * dim;
+            const float *v_head = v + s * k_cols + kv * dim;
+            float *dk_row = dk_win + (size_t)w * dim, *dv_row = dv_win + (size_t)w * dim;
+            for (size_t j = 0; j < dim; ++j) dk_row[j] = 0.0f, dv_row[j] = 0.0f;
+            for (size_t hh = 0; hh < group; ++hh) {
+                const size_t h = kv * group + hh;
+                for (size_t t = s; t < T; ++t) {
+                    const double *st = stats + 3 * (hh * window + (t - s_lo));
+                    const float *q_head = q + t * q_cols + h * dim;
+                    const float *dh = dout + t * q_cols + h * dim;
+                    double dot = 0.0, acc = 0.0;
+                    for (size_t j = 0; j < dim; ++j) dot += (double)q_head[j] * (double)k_head[j];
+                    for (size_t j = 0; j < dim; ++j) acc += (double)dh[j] * (double)v_head[j];
+                    const double probs_s = exp(dot * scale - st[0]) / st[1];
+                    const double p_ds_s = probs_s * (acc - st[2]);
+                    for (size_t j = 0; j < dim; ++j) {
+                        dk_row[j] += (float)(p_ds_s * (double)q_head[j] * scale);
+                        dv_row[j] += (float)(probs_s * (double)dh[j]);
+                    }
+                }
+            }
+        }
+        free(probs);
+        free(d_probs);
+        free(p_ds);
+        free(dk_dummy);
+        free(dq_dummy);
+    }
+    free(stats);
+    return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
 /* ---- kv_cache.Layer (src/kv_cache.zig:60-135), storage semantics only ------ */
 
 typedef struct {

@@ -75,6 +75,8 @@ def lib():
                                                 _sz, _sz, _sz, _sz, _fp, _fp, _fp, C.c_int]
         _lib.zto_attention_backward_kv_group.argtypes = [_fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
                                                          _fp, _fp, _fp]
+        _lib.zto_backward_window.argtypes = [_fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, C.POINTER(_sz), _sz, _sz,
+                                             _fp, _fp, _fp, C.c_int]
         _lib.zto_attention_forward_rows.argtypes = [_fp, _fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
                                                     _sz, _sz]
         _lib.zto_sampled_step.argtypes = [_fp] * 8 + [_sz] * 7 + [C.c_int, C.c_int,
@@ -161,6 +163,21 @@ def attention_backward_kv_group(q, k, v, dout, n_heads, n_kv_heads, head_dim, kv
     _check(lib().zto_attention_backward_kv_group(_p(q), _p(k), _p(v), _p(dout), q.shape[0], n_heads,
                                                  n_kv_heads, head_dim, kv, _p(dq), _p(dk), _p(dv)))
     return dq, dk, dv
+
+
+def backward_window(q, k, v, dout, n_heads, n_kv_heads, head_dim, kv, rows, window, *, threads=1):
+    """attentionBackward of KV head `kv` where a long sequence can afford it: dq of the query rows in
+    `rows` for the group's heads ([len(rows), group, D]) and dk, dv of the last `window` keys
+    ([window, D] each), in the reference's arithmetic and accumulation order."""
+    q, k, v, dout = _2d(q), _2d(k), _2d(v), _2d(dout)
+    group = n_heads // n_kv_heads
+    rows_a = (_sz * len(rows))(*[int(r) for r in rows])
+    dq_rows = np.zeros((len(rows), group, head_dim), dtype=np.float32)
+    dk_win = np.zeros((window, head_dim), dtype=np.float32)
+    dv_win = np.zeros((window, head_dim), dtype=np.float32)
+    _check(lib().zto_backward_window(_p(q), _p(k), _p(v), _p(dout), q.shape[0], n_heads, n_kv_heads, head_dim, kv,
+                                     rows_a, len(rows), window, _p(dq_rows), _p(dk_win), _p(dv_win), threads))
+    return dq_rows, dk_win, dv_win
 
 
 def attention_forward_rows(q, k, v, n_heads, n_kv_heads, head_dim, h, t0, t1):

@@ -84,6 +84,54 @@ def test_prefill_backward_one_kv_group_exact(zt, dev, oracle):
     close(dv[b, :, cols_k].cpu().numpy(), rdv[:, cols_k], "dv group")
 
 
+def _host_threads():
+    import os
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def test_headline_backward_one_kv_group_every_element(zt, dev, oracle):
+    """The benchmark's own point (batch 8, T 4096, 32/8 heads, head_dim 128): every element of dq (four heads)
+    and of dk, dv of one KV group of one sequence against the oracle, element-wise at the stated bar.  The dK/dV
+    kernel's accumulators take terms from all 4 x 64 query tiles here, the walk and the flush schedule that keep
+    the tensor core's truncating accumulation in check are exercised at their full depth, and a tile flushed to
+    the wrong rows could not hide behind a sum."""
+    B, T, H, Hkv, D = 8, 4096, 32, 8, 128
+    q, k, v, do = (randn((B, T, n * D), s, dev) for n, s in ((H, 21), (Hkv, 22), (Hkv, 23), (H, 24)))
+    o, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(q, k, v, o, lse, do, H, Hkv, D)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    b, kv, g = 5, 3, H // Hkv
+    rdq, rdk, rdv = oracle.backward_window(*(x[b].cpu().numpy() for x in (q, k, v, do)), H, Hkv, D, kv,
+                                           list(range(T)), T, threads=_host_threads())
+    close(dq[b].view(T, H, D)[:, kv * g:(kv + 1) * g].cpu().numpy(), rdq, "dq of the group")
+    close(dk[b, :, kv * D:(kv + 1) * D].cpu().numpy(), rdk, "dk of the group")
+    close(dv[b, :, kv * D:(kv + 1) * D].cpu().numpy(), rdv, "dv of the group")
+
+
+def test_long_context_backward_sampled_rows_and_last_keys(zt, dev, oracle):
+    """T 32768 (the long-context prefill): dq of sampled query rows of one KV group and dk, dv of its last 2048
+    keys (a key needs only the query rows at or after it, so the tail is what the oracle can afford), element-wise
+    at the stated bar.  The earliest key tiles, whose accumulators see all 512 query tiles, are covered by the
+    identities of test_prefill_sweep_point and, exactly, at T 4096 above."""
+    B, T, H, Hkv, D = 1, 32768, 32, 8, 128
+    q, k, v, do = (randn((B, T, n * D), s, dev) for n, s in ((H, 31), (Hkv, 32), (Hkv, 33), (H, 34)))
+    o, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+    dq, dk, dv = zt.attention_backward(q, k, v, o, lse, do, H, Hkv, D)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    kv, g, window = 6, H // Hkv, 2048
+    rows = [0, 1, 127, 128, 4095, 16383, 16384, 30000, 32767]
+    rdq, rdk, rdv = oracle.backward_window(*(x[0].cpu().numpy() for x in (q, k, v, do)), H, Hkv, D, kv, rows, window,
+                                           threads=_host_threads())
+    close(dq[0].view(T, H, D)[rows][:, kv * g:(kv + 1) * g].cpu().numpy(), rdq, "dq of sampled rows")
+    close(dk[0, T - window:, kv * D:(kv + 1) * D].cpu().numpy(), rdk, "dk of the last keys")
+    close(dv[0, T - window:, kv * D:(kv + 1) * D].cpu().numpy(), rdv, "dv of the last keys")
+
+
 def test_llama3_decode_full_size(zt, dev, oracle):
     """B 64, context 8192 (the new token's row included), 32/8 heads, head_dim 128: 4 GiB of cache."""
     B, n_ctx, H, Hkv, D = 64, 8192, 32, 8, 128

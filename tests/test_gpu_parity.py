@@ -394,12 +394,12 @@ TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, sev
 ]
 
 
-@pytest.mark.parametrize("path", [0, 7, 6, 5, 4, 3, 2], ids=["f16split-auto", "f16split-2heads", "f16split-1head", "f16split-walk", "f16split-64x8", "f16split-128", "3xtf32"])
+@pytest.mark.parametrize("path", [0, 7, 6, 2], ids=["f16split-auto", "f16split-2heads", "f16split-1head", "3xtf32"])
 @pytest.mark.parametrize("B,T,H,Hkv,D", TC_SHAPES)
 def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, path):
-    """The tensor-core forwards: the f16-split kernel on key tiles of 64 with four softmax warps per set (path 0) or
-    eight (path 4), with CTAs that walk several query tiles (path 5); path 0 takes two heads of a KV group per CTA where the group is even and the launch is large enough, path 7 wherever the group is even, path 6 never and on key tiles of 128 (path 3), head_dim
-    32 zero-padded to their 64-wide tiles, and the 3xTF32 kernel (path 2)."""
+    """The tensor-core forwards: the f16-split kernel (key tiles of 64; path 0 takes two heads of a KV group per CTA
+    where the group is even and the launch is large enough, path 7 wherever the group is even, path 6 never), head_dim
+    32 and 96 zero-padded to their 64- and 128-wide tiles, and the 3xTF32 kernel (path 2)."""
     q = oracle.fill_normal((B, T, H * D), 51, 0)
     k = oracle.fill_normal((B, T, Hkv * D), 51, 1)
     v = oracle.fill_normal((B, T, Hkv * D), 51, 2)
@@ -561,7 +561,7 @@ def test_rope_fused_forward_backward_matches_oracle(zt, dev, oracle, B, T, H, Hk
     tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
     ws = zt.RopeWorkspace(B, T, H, Hkv, D, dev)
     o, lse = zt.attention_forward_rope(tq, tk, tv, H, Hkv, D, pos=pos, workspace=ws, want_lse=True)
-    dq, dk, dv = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
+    dq, dk, dv = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws, kept=True)
     # the first backward used the planes the forward left in the workspace; a second one converts q, k, v itself
     again = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
     torch.cuda.synchronize()
@@ -591,54 +591,69 @@ def test_rope_calls_refuse_bad_arguments(zt, dev):
         zt.attention_forward_rope(q, k, k, H, Hkv, D, theta=0.0, workspace=ws)
     L = zt.lib.load()
     rc = L.zt_attn_forward_rope_batched(q.data_ptr(), k.data_ptr(), k.data_ptr(), q.data_ptr(), None,
-                                        ws.buf.data_ptr(), 16, B, T, H, Hkv, D, 0, 500000.0, None)
+                                        ws.buf.data_ptr(), 16, B, T, H, Hkv, D, 0, 500000.0, None, None)
     assert rc == 1 and "workspace" in zt.lib.last_error()
 
 
-@pytest.mark.parametrize("path", [0, 7, 6, 5], ids=["auto", "2heads", "1head", "walk"])
+@pytest.mark.parametrize("path", [0, 7, 6], ids=["auto", "2heads", "1head"])
 def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
-    """zt_attn_forward_batched_keep + zt_attn_backward_batched with the same workspace give bit for bit what the
-    unpaired calls give; a backward on other tensors after a keep ignores the kept planes.  For each form of the
-    f16-split forward that a training loop may be set to."""
+    """zt_attn_forward_batched_keep + zt_attn_backward_batched_kept (same workspace, the forward's token) give bit
+    for bit what the unpaired calls give.  Reuse happens only on the caller's word: a plain backward with that
+    workspace converts everything again, whatever the pointers are; a spent or stale token is refused."""
     B, T, H, Hkv, D = 2, 300, 8, 2, 128
     g = torch.Generator(device=dev).manual_seed(9)
     q, do = (torch.randn((B, T, H * D), generator=g, device=dev) for _ in range(2))
     k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
     zt.lib.load().zt_attn_set_path(path)
-    o0, l0 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
-    ref = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D)
-    ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
-    for _ in range(2):  # twice: the note is used once, the second round makes a new one
-        o1, l1 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True, keep=ws)
-        got = zt.attention_backward(q, k, v, o1, l1, do, H, Hkv, D, workspace=ws)
-        assert torch.equal(o1, o0) and torch.equal(l1, l0)
-        for a, b in zip(got, ref):
+    try:
+        o0, l0 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+        ref = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D)
+        ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
+        for _ in range(2):  # twice: a token is good for one backward, the second round gets a new one
+            o1, l1 = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True, keep=ws)
+            assert ws.token != 0
+            got = zt.attention_backward(q, k, v, o1, l1, do, H, Hkv, D, workspace=ws, kept=True)
+            assert ws.token == 0
+            assert torch.equal(o1, o0) and torch.equal(l1, l0)
+            for a, b in zip(got, ref):
+                assert torch.equal(a, b)
+        # q is rewritten IN PLACE between the keep and a plain backward (same pointers, same workspace): the
+        # plain backward never looks at kept planes, so the gradients are those of the new q
+        qm = q.clone()
+        zt.attention_forward(qm, k, v, H, Hkv, D, want_lse=True, keep=ws)
+        qm.mul_(0.5)
+        o2, l2 = zt.attention_forward(qm, k, v, H, Hkv, D, want_lse=True)
+        want2 = zt.attention_backward(qm, k, v, o2, l2, do, H, Hkv, D)
+        got2 = zt.attention_backward(qm, k, v, o2, l2, do, H, Hkv, D, workspace=ws)
+        for a, b in zip(got2, want2):
             assert torch.equal(a, b)
-    # keep for q, then a backward for other tensors with the same workspace: must not use q's planes
-    q2 = q * 0.5
-    zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True, keep=ws)
-    o2, l2 = zt.attention_forward(q2, k, v, H, Hkv, D, want_lse=True)
-    want2 = zt.attention_backward(q2, k, v, o2, l2, do, H, Hkv, D)
-    got2 = zt.attention_backward(q2, k, v, o2, l2, do, H, Hkv, D, workspace=ws)
-    for a, b in zip(got2, want2):
-        assert torch.equal(a, b)
-    # and the note is gone: the original tensors again, without a new keep
-    got3 = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D, workspace=ws)
-    for a, b in zip(got3, ref):
-        assert torch.equal(a, b)
-    zt.lib.load().zt_attn_set_path(0)
-    assert zt.lib.tc_status() == 0
+        # that backward rewrote the workspace: the token of the keep before it is stale now, and is refused
+        stale = ws.token
+        assert stale != 0
+        zt.lib.load().zt_attn_set_verbose(0)
+        with pytest.raises(zt.device.ConfigRefused):
+            zt.attention_backward(qm, k, v, o2, l2, do, H, Hkv, D, workspace=ws, kept=True)
+        zt.lib.load().zt_attn_set_verbose(1)
+        # and without a token the original tensors give the original gradients
+        got3 = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D, workspace=ws)
+        for a, b in zip(got3, ref):
+            assert torch.equal(a, b)
+    finally:
+        zt.lib.load().zt_attn_set_path(0)
+        zt.lib.load().zt_attn_set_verbose(1)
+    assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
 
 
-def test_forward_forms_agree_bit_for_bit(zt, dev):
-    """One head per CTA, two heads per CTA and the walking CTAs run the same arithmetic in the same order per row:
-    their outputs and log-sum-exps are identical, at a shape with tails and a padded head."""
+def test_forward_forms_agree(zt, dev):
+    """One head per CTA and two heads per CTA: a head's key tiles go through one softmax state instead of two
+    merged ones, so rounding differs; the two agree far inside the forward's parity bound, at shapes with tails
+    and a padded head."""
     for (B, T, H, Hkv, D) in [(2, 1000, 8, 2, 128), (1, 777, 8, 4, 64), (1, 500, 4, 1, 96)]:
         g = torch.Generator(device=dev).manual_seed(21)
         q = torch.randn((B, T, H * D), generator=g, device=dev)
         k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
         res = []
-        for path in (6, 7, 5):
+        for path in (6, 7):
             zt.lib.load().zt_attn_set_path(path)
             try:
                 res.append(zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True))
@@ -646,17 +661,13 @@ def test_forward_forms_agree_bit_for_bit(zt, dev):
                 zt.lib.load().zt_attn_set_path(0)
             assert zt.lib.last_path() == "tcgen05"
         torch.cuda.synchronize()
-        # the walking CTAs are the one-head kernel tile for tile
-        assert torch.equal(res[0][0], res[2][0]) and torch.equal(res[0][1], res[2][1])
-        # two heads per CTA: a head's key tiles all go through one softmax state instead of two merged ones, so
-        # rounding differs; the parity bound of the forward (1e-5 + 1e-4 |ref|) holds between them with room
         err = (res[0][0] - res[1][0]).abs()
         assert bool((err <= 2e-6 + 2e-5 * res[0][0].abs()).all())
     assert zt.lib.tc_status() == 0
 
 
 def test_training_pair_is_capturable_in_a_cuda_graph(zt, dev):
-    """zt_attn_forward_batched_keep + zt_attn_backward_batched take all their scratch from the caller's workspace and
+    """zt_attn_forward_batched_keep + zt_attn_backward_batched_kept take all their scratch from the caller's workspace and
     only enqueue on the caller's stream, so a step can be captured once and replayed: short sequences are bound by
     the eight launches of a step, not by the kernels."""
     B, T, H, Hkv, D = 2, 512, 8, 2, 128
@@ -671,11 +682,13 @@ def test_training_pair_is_capturable_in_a_cuda_graph(zt, dev):
     lse, delta = (torch.empty((B, T, H), device=dev) for _ in range(2))
 
     def step(stream):
+        token = ctypes.c_ulonglong(0)
         rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                            ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream)
-        rc |= L.zt_attn_backward_batched(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                         do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
-                                         ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream)
+                                            ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream, ctypes.byref(token))
+        assert rc == 0 and token.value != 0, zt.lib.last_error()
+        rc = L.zt_attn_backward_batched_kept(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                             do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+                                             ws.buf.data_ptr(), ws.nbytes, B, T, H, Hkv, D, stream, token.value)
         assert rc == 0, zt.lib.last_error()
 
     step(torch.cuda.current_stream(dev).cuda_stream)  # eager: also sets the kernels' shared-memory attributes
@@ -694,3 +707,59 @@ def test_training_pair_is_capturable_in_a_cuda_graph(zt, dev):
     for got, ref in zip((out, lse, dq, dk, dv), want):
         assert torch.equal(got, ref)
     assert zt.lib.tc_status() == 0
+
+
+# ---- dynamic range inside one (sequence, KV group) -------------------------------------------------------------
+
+def _outlier_inputs(T, H, Hkv, D, which, mag, frac=1e-3, seed=5):
+    """N(0,1) everywhere, with a fraction `frac` of the elements of the tensors named in `which` multiplied by mag."""
+    rng = np.random.default_rng(seed)
+    ts = {}
+    for name, w in (("q", H * D), ("k", Hkv * D), ("v", Hkv * D), ("do", H * D)):
+        x = rng.standard_normal((T, w)).astype(np.float32)
+        if name in which:
+            x[rng.random((T, w)) < frac] *= np.float32(mag)
+        ts[name] = x
+    return ts["q"], ts["k"], ts["v"], ts["do"]
+
+
+def _violations(got, ref):
+    g, r = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return int((~(np.abs(g - r) <= ATOL + RTOL * np.abs(r))).sum())
+
+
+@pytest.mark.parametrize("which,mag", [(("do",), 1e2), (("v",), 1e2), (("v", "do"), 1e2), (("v",), 1e3), (("do",), 1e3),
+                                       (("v", "do"), 1e3)],
+                         ids=["dout-x100", "v-x100", "v+dout-x100", "v-x1000", "dout-x1000", "v+dout-x1000"])
+def test_tensor_core_backward_outliers_inside_a_kv_group(zt, dev, oracle, which, mag):
+    """The operand planes carry one power-of-two scale per (sequence, KV group), so what stresses the f16 split is a
+    wide range INSIDE a group: here one element in a thousand of v and/or dout is 100 or 1000 times the rest (all
+    in one KV group).  dS is scaled per query row in the dQ kernel and from the group's measured maximum in the
+    dK/dV kernel, so the bulk rows keep their precision.  At a hundred times the bulk everything meets the stated
+    bar (a handful of dk elements apart, as on the CUDA-core path, whose f32 sums meet the same rounding); at a
+    thousand times, a few elements in ten thousand miss it (counts pinned below, a regression guard: before the
+    per-row scale a quarter of dq and a third of dk missed it at a HUNDRED times).  Outliers in q and k are a
+    different matter: scores of 10^3 and more lose |score| 2^-23 in any f32 accumulation, on the CUDA-core path
+    and in the reference's own kernels alike, and are not this library's to fix."""
+    T, H, Hkv, D = 512, 4, 1, 128
+    q, k, v, do = _outlier_inputs(T, H, Hkv, D, which, mag)
+    ref_o, ref_lse = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
+    ref = dict(zip(("dq", "dk", "dv"), oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)))
+    counts = {}
+    for path in (0, 1):
+        zt.lib.load().zt_attn_set_path(path)
+        try:
+            o, lse, dq, dk, dv = run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D)
+        finally:
+            zt.lib.load().zt_attn_set_path(0)
+        assert zt.lib.last_path() == ("tcgen05" if path == 0 else "simt")
+        close(o, ref_o, "out")
+        close(lse, ref_lse, "lse")
+        counts[path] = {n: _violations(x, ref[n]) for n, x in (("dq", dq), ("dk", dk), ("dv", dv))}
+    assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    n_q, n_k = T * H * D, T * Hkv * D
+    if mag <= 1e2:
+        assert counts[0]["dq"] == 0 and counts[0]["dv"] <= 2 and counts[0]["dk"] <= 8, counts
+    else:
+        # measured: dq 1..64, dk 40..335, dv 0..33 of 262144 / 65536 elements (CUDA cores: 0..2, 6..33, 0)
+        assert counts[0]["dq"] <= n_q // 2000 and counts[0]["dk"] <= n_k // 100 and counts[0]["dv"] <= n_k // 1000, counts

@@ -59,10 +59,26 @@ def test_static_scratch_decode_matches_workspace_decode_twice(zt):
             assert L.zt_attn_decode_workspace_bytes(B, n_ctx, H, Hkv, D) <= L.zt_attn_decode_static_capacity()
             out = torch.full_like(q, 123.0)
             lse = torch.full((B, H), 123.0, device=dev)
+            if round_ == 0 and seed == 101:
+                # the very first call on the device may have to find the built-in array (and, with lazy module
+                # loading, make it exist): done once, here, before the calls whose memory use is measured
+                assert call_static(L, q, kc, vc, n_keys, out, lse, B, n_ctx, H, Hkv, D) == 0, zt.lib.last_error()
+            # the property the entry point is named for: the device's free memory is the same before and after
+            # the call -- nothing was allocated (or freed) on the way, by the library or by torch on its behalf
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info(dev)
+            reserved_before = torch.cuda.memory_reserved(dev)
             assert call_static(L, q, kc, vc, n_keys, out, lse, B, n_ctx, H, Hkv, D) == 0, zt.lib.last_error()
             torch.cuda.synchronize()
+            free_after, _ = torch.cuda.mem_get_info(dev)
+            assert free_after == free_before and torch.cuda.memory_reserved(dev) == reserved_before
             close(out.cpu().numpy(), ref.cpu().numpy(), f"out round {round_} {B}x{n_ctx}")
             close(lse.cpu().numpy(), ref_lse.cpu().numpy(), f"lse round {round_} {B}x{n_ctx}")
+            # the count of refused sequences sits in the built-in scratch; a NULL workspace reads it
+            import ctypes
+            bad = ctypes.c_int(-1)
+            assert L.zt_attn_decode_status(None, ctypes.byref(bad)) == 0, zt.lib.last_error()
+            assert bad.value == (1 if round_ == 1 else 0)
 
 
 def test_static_scratch_refuses_what_does_not_fit(zt):

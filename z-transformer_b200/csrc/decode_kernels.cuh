@@ -303,9 +303,11 @@ struct DecodePlan {
     size_t ml_bytes, acc_bytes, total_bytes;
 };
 
-// The split is a pure function of the shape, so the workspace-size query and the
-// launch agree.  The chunk is as large as keeps roughly four waves of blocks in
-// flight (two blocks per SM on 148 SMs), between 128 and 1024 keys.
+// The split is a pure function of the shape and of the current device's SM count, so the
+// workspace-size query and the launch agree (both made with the same device current).  The
+// chunk is as large as keeps roughly four waves of blocks in flight (two blocks per SM),
+// between 128 and 1024 keys.  Without a device (a size query on a machine with none) the
+// count of a B200, 148, stands in.
 inline DecodePlan decode_plan(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim) {
     DecodePlan pl{};
     const int group = n_heads / n_kv_heads;
@@ -315,7 +317,8 @@ inline DecodePlan decode_plan(int batch, int n_ctx, int n_heads, int n_kv_heads,
     pl.lpk = chunks4 <= 8 ? 8 : 16;
     pl.nch = (chunks4 + pl.lpk - 1) / pl.lpk;
     const long long units = (long long)batch * n_kv_heads * pl.n_sub;
-    const long long target_blocks = 4LL * 2 * 148;
+    const DeviceInfo *di = device_info();
+    const long long target_blocks = 4LL * 2 * (di && di->sm_count > 0 ? di->sm_count : 148);
     long long want = (target_blocks + units - 1) / units;
     if (want < 1) want = 1;
     long long chunk = (n_ctx + want - 1) / want;

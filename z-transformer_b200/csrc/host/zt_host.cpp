@@ -216,14 +216,16 @@ Error AttnPipeline::step(int batch, const float *q, const float *k, const float 
 
         cudaStreamWaitEvent(s_run, s.ready_f, 0);
         if (reused) cudaStreamWaitEvent(s_run, s.free_, 0);  // the slot's outputs have been read
+        // q, k, v of the slot are not written between its forward and its backward, which is what the token says
+        unsigned long long token = 0;
         if (zt_attn_forward_batched_keep(s.q, s.k, s.v, s.out, s.lse, s.ws, ws_bytes_, 1, c_t, c_heads, c_kv_heads, c_dim,
-                                         reinterpret_cast<zt_stream_t>(s_run)))
+                                         reinterpret_cast<zt_stream_t>(s_run), &token))
             refused = true;
         cudaEventRecord(s.done_f, s_run);
         cudaStreamWaitEvent(s_run, s.ready_b, 0);
-        if (!refused && zt_attn_backward_batched(s.q, s.k, s.v, s.out, s.lse, s.dout, s.dq, s.dk, s.dv, s.delta, s.ws,
-                                                 ws_bytes_, 1, c_t, c_heads, c_kv_heads, c_dim,
-                                                 reinterpret_cast<zt_stream_t>(s_run)))
+        if (!refused && zt_attn_backward_batched_kept(s.q, s.k, s.v, s.out, s.lse, s.dout, s.dq, s.dk, s.dv, s.delta,
+                                                      s.ws, ws_bytes_, 1, c_t, c_heads, c_kv_heads, c_dim,
+                                                      reinterpret_cast<zt_stream_t>(s_run), token))
             refused = true;
         cudaEventRecord(s.done, s_run);
 

@@ -204,16 +204,28 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt(const SimtFwdParam
 __global__ void __launch_bounds__(256) attn_delta_kernel(const float *__restrict__ out,
                                                          const float *__restrict__ dout,
                                                          float *__restrict__ delta,
+                                                         float *__restrict__ rnorm,
                                                          long long n_rows, int dim) {
     const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     const int lane = threadIdx.x & 31;
     const float *o = out + row * dim, *g = dout + row * dim;
-    float acc = 0.f;
-    for (int j = lane; j < dim; j += 32) acc = fmaf(__ldg(o + j), __ldg(g + j), acc);
+    float acc = 0.f, sq = 0.f;
+    for (int j = lane; j < dim; j += 32) {
+        const float gj = __ldg(g + j);
+        acc = fmaf(__ldg(o + j), gj, acc);
+        sq = fmaf(gj, gj, sq);
+    }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) delta[row] = acc;
+    for (int off = 16; off > 0; off >>= 1) {
+        acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        sq += __shfl_xor_sync(0xffffffffu, sq, off);
+    }
+    if (lane == 0) {
+        delta[row] = acc;
+        // |dout row| for the tensor-core backward's per-row scale of dS (null when nobody wants it)
+        if (rnorm) rnorm[row] = sqrtf(sq);
+    }
 }
 
 // Fill a float buffer (row_den of the reference ABI is documented as 1).
@@ -397,11 +409,11 @@ inline int launch_fwd_simt(const SimtFwdParams &p, int batch, cudaStream_t strea
     return ZT_LAUNCH("attn_fwd_simt", stream, attn_fwd_simt<<<grid, kSimtThreads, smem, stream>>>(p));
 }
 
-inline int launch_delta(const float *out, const float *dout, float *delta, long long n_rows,
+inline int launch_delta(const float *out, const float *dout, float *delta, float *rnorm, long long n_rows,
                         int dim, cudaStream_t stream) {
     const long long blocks = (n_rows + 7) / 8;
     return ZT_LAUNCH("attn_delta_kernel", stream,
-                     attn_delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>(out, dout, delta, n_rows, dim));
+                     attn_delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>(out, dout, delta, rnorm, n_rows, dim));
 }
 
 inline int launch_bwd_simt(const SimtBwdParams &p, int batch, cudaStream_t stream) {

@@ -210,6 +210,37 @@ inline int launch_prepass(const PrepassArgs &a, cudaStream_t stream) {
     return ZT_LAUNCH("bwd_split_kernel", stream, (bwd_split_kernel<<<gs, 256, 0, stream>>>(a)));
 }
 
+// max over the rows s of |v[b, s, kv, :]| (Euclidean), per (sequence, KV head).  grid (ceil(T / 256), n_kv_heads,
+// batch), 8 warps; a warp walks 32 rows of the block's 256 and keeps a running maximum, the block then makes ONE
+// atomic: thousands of atomics on the same word serialise in L2 (a warp per row took 0.2 ms at the headline shape).
+// vnmax holds f32 bit patterns (non-negative, so they order like integers), zeroed by the caller.
+__global__ void __launch_bounds__(256) bwd_vnorm_kernel(const float *__restrict__ v, uint32_t *__restrict__ vnmax,
+                                                        int T, int n_kv_heads, int dim) {
+    __shared__ float wmax[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kv = blockIdx.y, b = blockIdx.z;
+    const int r0 = blockIdx.x * 256 + warp * 32;
+    float best = 0.f;
+    for (int r = r0; r < r0 + 32 && r < T; ++r) {
+        const float *x = v + (((long long)b * T + r) * n_kv_heads + kv) * dim;
+        float acc = 0.f;
+        for (int j = lane; j < dim; j += 32) {
+            const float e = __ldg(x + j);
+            acc = fmaf(e, e, acc);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        best = fmaxf(best, acc);
+    }
+    if (lane == 0) wmax[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = wmax[0];
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, wmax[i]);
+        // (an Inf or NaN row: sqrt keeps it, and the scale built from it falls back to 1)
+        atomicMax(vnmax + b * n_kv_heads + kv, __float_as_uint(sqrtf(m)));
+    }
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t *>(&h);
@@ -233,14 +264,40 @@ struct BwdParams {
     const __half *k_planes, *v_planes;   // dkdv kernel: the hi planes of K and V are read straight into TMEM
     const __half *q_planes, *do_planes;  // dq kernel: Q, dO planes read straight into TMEM
     const uint32_t *amax_q, *amax_k, *amax_v, *amax_do;  // [B, Hkv] bit patterns of max |x|
+    const float *rnorm;      // [B, T, H] Euclidean norm of each row of dout (bwd_rownorm_kernel)
+    const uint32_t *vnmax;   // [B, Hkv] bit pattern of the largest Euclidean norm of a row of v
+    uint32_t *dsmax;         // [B, Hkv] bit pattern of max |dS| (true units): written by the dQ kernel, read by dK/dV
     float *dq, *dk, *dv;
     int batch, T, n_heads, n_kv_heads;
     int dim_out;     // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
     const float2 *rope_t;  // null, or the (cos, sin) table transposed, [dim_out / 2][T]: dq leaves as R^T of what was computed
     float scale, scale_log2;
     float p_scale;  // P is multiplied by this power of two before its 16-bit split
-    float c1;       // dP (in scaled units) is multiplied by this power of two before dS is split
 };
+
+// The scale of dS.  dS = P (dP - delta) leaves the row threads as a pair of f16 pieces, so it must sit inside the
+// f16 range, and as high in it as possible: a value 2^11 below the top of the range still has both pieces as
+// normal numbers, one 2^26 below it has lost its low piece and half of the high one.  A single worst-case scale
+// for a whole (sequence, KV group) -- |dP| <= head_dim max|dout| max|v| -- wastes the width of the head, the
+// flatness of P and, worst, every outlier: with 0.1 % of dout and v a hundred times the rest, most of dq and a
+// third of dk fell outside the tolerance.  So each kernel scales by what it can know:
+//  * the dQ kernel owns whole rows of dS, so every query row has a scale of its own, from a bound that holds for
+//    that row alone: |dP[t, s]| <= |dout[t]| |v[s]| (Euclidean norms), |delta[t]| is at most the largest |dP| of
+//    its row and P <= 1, so |dS[t, s]| <= 2 |dout[t]| max_s |v[s]|.  Rows are independent of each other's
+//    magnitude, and the scale only moves the accumulator of its own row, which is divided by it on the way out;
+//  * the dK/dV kernel sums dS over query rows, so there one scale must serve a CTA.  It is calibrated, not
+//    bounded: the dQ kernel, which runs first, records the largest |dS| it formed in each (sequence, KV group),
+//    and the dK/dV kernel places that value an eighth below the top of the range (its own dS differs from the
+//    dQ kernel's by rounding only).
+// pow2_below_top(x, top): the power of two c with x c in [2^(top-1), 2^top); 1 when x is zero or not finite.
+__device__ __forceinline__ float pow2_for(float x, int top) {
+    if (!(x > 0.f) || !(x < 3.0e38f)) return 1.0f;
+    int e;
+    frexpf(x, &e);  // x = m 2^e, m in [0.5, 1)
+    int k = top - e;
+    k = k > 120 ? 120 : (k < -120 ? -120 : k);
+    return __uint_as_float((uint32_t)(k + 127) << 23);
+}
 
 // The dK/dV kernel's walk over (query tile, head of the group), and where its TMEM accumulators
 // are flushed to memory.
@@ -258,6 +315,12 @@ struct BwdParams {
 //    kFlushTiles query tiles for the same reason, which keeps the error flat in T.
 //    (Before the periodic flushes, with a flush only per head: 12-26 of 524288 dk/dv elements
 //    outside the tolerance at T = 4096; with them: none.)
+// The bound on dS.  dS leaves the row threads as a pair of f16 pieces, so it must stay inside the f16 range;
+// the scale c1 (launch_bwd_tc) is chosen from the worst case so that it does, with a factor of two to spare.
+// Values are clamped to the bound all the same -- it costs two instructions and keeps an Inf or NaN that
+// arrived in dout from spreading through the accumulators of a whole CTA -- and a clamp that fires is counted
+// in g_tc_saturated (zt_attn_tc_saturated), which every test asserts to be zero.
+constexpr float kDsBound = 65000.f;
 constexpr int kFlushTiles = 8;  // query tiles of 64 rows between flushes (512 rows)
 constexpr int kDiagTiles = 2;   // query tiles that overlap a 128-key tile
 // An iterator: step `it` is (head hh of the group, query tile qi); `flush` says the accumulators are
@@ -417,7 +480,9 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 
     const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
-    const float c1 = p.c1;
+    // dS in this CTA's units: the largest |dS| of the (sequence, KV group), as the dQ kernel met it, goes to
+    // [2^12, 2^13); c1 turns dP of the scaled planes into those units
+    const float c1 = pow2_for(__uint_as_float(p.dsmax[b * p.n_kv_heads + g]), 13) / (mdo * mv);
 
     if (warp == kKvRowWarps) {
         // ------------------------------------------------------------------ TMA producer
@@ -642,6 +707,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         ahead.next();
         int n_flush = 0;
         bool ok = true;
+        bool saturated = false;  // a dS value of this thread met kDsBound (or was not a number)
         // The accumulators go to memory one step late: after a flush step's dS the row threads would only wait
         // for its dV and dK to retire, and the next step's exp and dS need neither the accumulators nor that
         // wait, so they come first and the tensor core finds them done when the flush ends.
@@ -765,8 +831,11 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 for (int i = 0; i < 16; i += 2) {
                     float dv[2];
 #pragma unroll
-                    for (int e = 0; e < 2; ++e)
-                        dv[e] = fminf(fmaxf(pr[i + e] * (__uint_as_float(rd[i + e]) * c1p - sh->dels[it & 1][set * 16 + i + e]), -65000.f), 65000.f);
+                    for (int e = 0; e < 2; ++e) {
+                        const float x = pr[i + e] * (__uint_as_float(rd[i + e]) * c1p - sh->dels[it & 1][set * 16 + i + e]);
+                        saturated |= !(fabsf(x) <= kDsBound);
+                        dv[e] = fminf(fmaxf(x, -kDsBound), kDsBound);
+                    }
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
                 tmem_st8(wP, dh);
@@ -785,6 +854,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             }
         }
         (void)ok;
+        if (__any_sync(0xffffffffu, saturated) && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_saturated, 1u);
     }
     tc_fence_before();
     __syncthreads();
@@ -871,7 +941,6 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 
     const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
     const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]), mdo = block_mult(p.amax_do[b * p.n_kv_heads + g]);
-    const float c1 = p.c1;
 
     if (warp == kKvRowWarps) {
         // ------------------------------------------------------------------ TMA producer
@@ -1027,7 +1096,12 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         const float cs = p.scale_log2 / (mq * mk);
         const long long ridx = ((long long)b * p.T + (t < p.T ? t : 0)) * p.n_heads + h;
         const float lse2 = (t < p.T) ? __ldg(p.lse + ridx) * kLog2e : 0.f;
-        const float dels = (t < p.T) ? __ldg(p.delta + ridx) * (mdo * mv * c1) : 0.f;
+        // this row's scale: |dS| <= 2 |dout[t]| max |v[s]| (a shade more: P may round to just above 1) goes below 2^14
+        const float cq = (t < p.T) ? pow2_for(2.02f * __ldg(p.rnorm + ridx) * __uint_as_float(p.vnmax[b * p.n_kv_heads + g]), 14) : 1.0f;
+        const float c1 = cq / (mdo * mv);
+        const float dels = (t < p.T) ? __ldg(p.delta + ridx) * cq : 0.f;
+        float ds_top = 0.f;  // largest |dS| of this thread, in the row's units
+        bool saturated = false;  // a dS value of this thread met kDsBound (or was not a number)
         for (int j = 0; ok && j < n_tiles; ++j) {
             if (!__all_sync(0xffffffffu, dwait(&sh->sdp_full[j & 1], (uint32_t)((j >> 1) & 1), sh))) {
                 dgive_up(sh, 35);
@@ -1051,7 +1125,11 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
-                        dv[e] = fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f);
+                        const float x = pe * (__uint_as_float(rd[i + e]) * c1 - dels);
+                        const float ax = fabsf(x);
+                        saturated |= !(ax <= kDsBound);
+                        ds_top = fmaxf(ds_top, ax);
+                        dv[e] = fminf(fmaxf(x, -kDsBound), kDsBound);
                     }
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
@@ -1064,7 +1142,11 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                         const int key = key0 + i + e;
                         const bool vis = (key <= t) && (key < p.T);
                         const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
-                        dv[e] = vis ? fminf(fmaxf(pe * (__uint_as_float(rd[i + e]) * c1 - dels), -65000.f), 65000.f) : 0.f;
+                        const float x = vis ? pe * (__uint_as_float(rd[i + e]) * c1 - dels) : 0.f;
+                        const float ax = fabsf(x);
+                        saturated |= !(ax <= kDsBound);
+                        ds_top = fmaxf(ds_top, ax);
+                        dv[e] = fminf(fmaxf(x, -kDsBound), kDsBound);
                     }
                     split_pack(dv[0], dv[1], dh[i >> 1], dl[i >> 1]);
                 }
@@ -1075,6 +1157,18 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             tc_fence_before();
             mbar_arrive_warp(&sh->p_full[j & 1]);
         }
+        if (__any_sync(0xffffffffu, saturated) && (threadIdx.x & 31) == 0) atomicAdd(&g_tc_saturated, 1u);
+        {
+            // the largest |dS| of the (sequence, KV group), in true units, for the dK/dV kernel's scale (a clamped or
+            // non-finite value counts as the bound: the flag above has already reported it)
+            float top = fminf(ds_top, kDsBound) / cq;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+            // (most warps find a larger value already there and make no atomic)
+            uint32_t *cell = p.dsmax + b * p.n_kv_heads + g;
+            if ((threadIdx.x & 31) == 0 && __float_as_uint(top) > *reinterpret_cast<volatile uint32_t *>(cell))
+                atomicMax(cell, __float_as_uint(top));
+        }
         if (ok && !__all_sync(0xffffffffu, dwait(&sh->all_done, 0, sh))) {
             dgive_up(sh, 36);
             ok = false;
@@ -1083,7 +1177,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             tc_fence_after();
             // each set writes a quarter of the row's columns
             constexpr int CW = D / 4;  // 32 or 16
-            const float fq = p.scale / (mdo * mv * c1 * mk);
+            const float fq = p.scale / (cq * mk);
             // mine: this set's CW columns; other: their rotation partners (i +- dim_out / 2, another set's
             // chunk of this row's accumulator), read only when dQ leaves as the gradient of the unrotated q
             const bool rot = p.rope_t != nullptr && set * CW < p.dim_out;
@@ -1146,26 +1240,29 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 // ---- host side ----------------------------------------------------------------------------------------
 
 struct BwdWorkspace {
-    uint32_t *amax_q, *amax_k, *amax_v, *amax_do;
+    uint32_t *amax_q, *amax_k, *amax_v, *amax_do, *vnmax, *dsmax;  // six [batch, n_kv_heads] arrays, in this order
     __half *q_planes, *do_planes, *k_planes, *v_planes;
+    float *rnorm;  // [batch, T, n_heads]
     size_t total_bytes, amax_bytes;
 };
 
 inline BwdWorkspace bwd_workspace(void *base, int batch, int T, int n_heads, int n_kv_heads, int dim) {
     BwdWorkspace w{};
     const size_t n_amax = (size_t)batch * n_kv_heads;
-    w.amax_bytes = (4 * n_amax * sizeof(uint32_t) + 1023) / 1024 * 1024;
+    w.amax_bytes = (6 * n_amax * sizeof(uint32_t) + 1023) / 1024 * 1024;
     const size_t qh = (size_t)2 * batch * T * n_heads * dim * sizeof(__half);
     const size_t kh = (size_t)2 * batch * T * n_kv_heads * dim * sizeof(__half);
     auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
     char *c = static_cast<char *>(base);
     w.amax_q = reinterpret_cast<uint32_t *>(c);
     w.amax_k = w.amax_q + n_amax, w.amax_v = w.amax_k + n_amax, w.amax_do = w.amax_v + n_amax;
+    w.vnmax = w.amax_do + n_amax, w.dsmax = w.vnmax + n_amax;
     size_t off = w.amax_bytes;
     w.q_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
     w.do_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
     w.k_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
     w.v_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
+    w.rnorm = reinterpret_cast<float *>(c + off), off += up((size_t)batch * T * n_heads * sizeof(float));
     w.total_bytes = off;
     return w;
 }
@@ -1193,11 +1290,12 @@ inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t st
     if (optin_smem((const void *)attn_bwd_dq_tc<D>, sb)) return 1;
     const dim3 grid_a((unsigned)p.n_kv_heads, (unsigned)((p.T + 127) / 128), (unsigned)p.batch);
     const dim3 grid_b((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
-    if (ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
-                  (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(m.k128, m.v128, m.q64, m.g64, p))))
+    // dQ first: it records the largest |dS| of every (sequence, KV group), which scales dS in the dK/dV kernel
+    if (ZT_LAUNCH("attn_bwd_dq_tc", stream,
+                  (attn_bwd_dq_tc<D><<<grid_b, kKvThreads, sb, stream>>>(m.k64, m.v64, m.q128, m.g128, p))))
         return 1;
-    return ZT_LAUNCH("attn_bwd_dq_tc", stream,
-                     (attn_bwd_dq_tc<D><<<grid_b, kKvThreads, sb, stream>>>(m.k64, m.v64, m.q128, m.g128, p)));
+    return ZT_LAUNCH("attn_bwd_dkdv_tc", stream,
+                     (attn_bwd_dkdv_tc<D><<<grid_a, kKvThreads, sa, stream>>>(m.k128, m.v128, m.q64, m.g64, p)));
 }
 
 }  // namespace tcb
@@ -1225,8 +1323,9 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     const int wq = n_heads * td, wkv = n_kv_heads * td;
     // With the planes of q, k, v kept by the forward (and their maxima beside them), only dout is converted.
     const size_t n_amax = (size_t)batch * n_kv_heads;
+    // (with kept planes the maxima of q, k, v stay; those of dout, the row norms of v and max |dS| start from zero)
     if (cudaMemsetAsync(qkv_planes_kept ? w.amax_do : w.amax_q, 0,
-                        qkv_planes_kept ? n_amax * sizeof(uint32_t) : w.amax_bytes, stream) != cudaSuccess) {
+                        qkv_planes_kept ? 3 * n_amax * sizeof(uint32_t) : w.amax_bytes, stream) != cudaSuccess) {
         cudaGetLastError();
         return refuse("could not clear the backward workspace header");
     }
@@ -1241,6 +1340,11 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
         pa.n = 4;
     }
     if (launch_prepass(pa, stream)) return 1;
+    {
+        const dim3 gv((unsigned)((T + 255) / 256), (unsigned)n_kv_heads, (unsigned)batch);
+        if (ZT_LAUNCH("bwd_vnorm_kernel", stream, (bwd_vnorm_kernel<<<gv, 256, 0, stream>>>(v, w.vnmax, T, n_kv_heads, dim))))
+            return 1;
+    }
     BwdMaps m;
     if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, td, 128) ||
         !make_half_tile_map(&m.v128, w.v_planes, 2 * batch, T, wkv, td, 128) ||
@@ -1255,18 +1359,15 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     p.lse = lse, p.delta = delta;
     p.k_planes = w.k_planes, p.v_planes = w.v_planes, p.q_planes = w.q_planes, p.do_planes = w.do_planes;
     p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
+    p.rnorm = w.rnorm, p.vnmax = w.vnmax, p.dsmax = w.dsmax;
     p.dq = dq, p.dk = dk, p.dv = dv;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
     p.rope_t = rope_t;
     p.scale = 1.0f / sqrtf((float)dim), p.scale_log2 = kLog2e / sqrtf((float)dim);
-    {
-        int pl = 10, boost = 0;
-        if (const char *e = getenv("ZT_BWD_PSCALE_LOG2")) pl = atoi(e);
-        if (const char *e = getenv("ZT_BWD_DSBOOST_LOG2")) boost = atoi(e);
-        p.p_scale = ldexpf(1.0f, pl);
-        p.c1 = ldexpf(1.0f, boost - 16 - (td == 128 ? 7 : 6));
-    }
+    // P in [0, 1] is split after a multiplication by 2^10 (its low piece then stays a normal f16 down to p ~ 2^-14).
+    // dS is scaled inside the kernels (see "The scale of dS" above).
+    p.p_scale = ldexpf(1.0f, 10);
     g_last_path = "tcgen05";
     return td == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
 }

@@ -35,6 +35,9 @@ namespace zt {
 // Non-zero after a tensor-core kernel gave up on a wait (code = which one).  Read by
 // zt_attn_tc_status(); never set in a correct run.
 static __device__ int g_tc_status;
+// Number of CTAs of the backward kernels in which a dS value met the bound of its 16-bit split (see
+// tc_bwd.cuh, "the bound on dS"); read and cleared by zt_attn_tc_saturated.  A correct run never raises it.
+static __device__ unsigned int g_tc_saturated;
 
 namespace tcf {
 
@@ -438,6 +441,12 @@ inline int launch_fwd_tc(const float *q, const float *k, const float *v, float *
 // 0 when no tensor-core kernel has ever given up on a wait on the current device.
 inline int tc_status_read(int *host_value) {
     return cudaMemcpyFromSymbol(host_value, g_tc_status, sizeof(int)) == cudaSuccess ? 0 : 1;
+}
+// The count of backward CTAs that saturated a dS value since the last read; cleared by the read.
+inline int tc_saturated_read(unsigned int *host_value) {
+    if (cudaMemcpyFromSymbol(host_value, g_tc_saturated, sizeof(unsigned int)) != cudaSuccess) return 1;
+    const unsigned int zero = 0;
+    return cudaMemcpyToSymbol(g_tc_saturated, &zero, sizeof(unsigned int)) == cudaSuccess ? 0 : 1;
 }
 
 }  // namespace zt

@@ -50,7 +50,6 @@ struct Params {
     float *out, *lse;                           // lse may be null
     int batch, T, n_heads, n_kv_heads;
     int dim_out;  // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
-    int n_items;  // attn_fwd_tc16p: pairs of query tiles over all heads and sequences
     int ahead;    // attn_fwd_tc16 prefetches the query tile of the block this many places on in launch order; 0: none
     float scale_log2;
 };
@@ -407,629 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
-// ---------------------------------------------------------------------------------------------------
-// The same kernel with eight softmax warps per set instead of four: two threads share a query row, 32 of the
-// tile's 64 key columns each, and agree on the tile's row maximum through shared memory.  576 threads.
-// Measured no faster than the four-warp form (3.03 ms against 2.99 at head_dim 128, T = 4096): halving a
-// thread's share of the row work does not shorten the step, so that work is not what bounds it.  Selectable
-// (zt_attn_set_path(4)), not the default.
-// ---------------------------------------------------------------------------------------------------
-constexpr int kThreadsH = 18 * 32;
-
-struct SharedH {
-    uint64_t full_k[3], free_k[3], full_v[3], free_v[3];
-    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], x_ready[2], all_done;
-    uint32_t tmem_base;
-    volatile int abort;
-    float xmax[2][2][128];               // [set][column half][row]: the halves' maxima over the current tile
-    float fin_m[2][128], fin_l[2][2][128];
-};
-__device__ __forceinline__ bool hwait(uint64_t *bar, uint32_t parity, SharedH *sh) {
-    for (uint32_t i = 0; i < (1u << 20); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && sh->abort) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void hgive_up(SharedH *sh, int code) {
-    sh->abort = code;
-    atomicMax(&g_tc_status, code);
-}
-
-template <int D>
-__global__ void __launch_bounds__(kThreadsH, 1)
-    attn_fwd_tc16h(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
-    constexpr int NB = D / 64, W2 = D / 2, BN = 64;
-    constexpr int KP = BN * D * 2;  // bytes of one plane of a key tile
-    constexpr int cQh = 0, cQl = W2, cO0 = D, cS0 = 3 * D;  // O of set s at cO0 + s D, S/P of buffer i at cS0 + 64 i
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sK = smem, *sV = smem + 6 * KP;  // three slots of (hi, lo) each
-    SharedH *sh = reinterpret_cast<SharedH *>(smem + 12 * KP);
-
-    const int warp = threadIdx.x >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int g = h / (p.n_heads / p.n_kv_heads);
-    const int t0 = qt * 128;
-    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
-    const int n_tiles = (rows_end + BN - 1) / BN;
-    const int B = p.batch;
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < 3; ++i) {
-            mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
-            mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
-        }
-        mbar_init(&sh->a_ready, 16);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], 8), mbar_init(&sh->pv_done[i], 1);
-            mbar_init(&sh->x_ready[i], 8);
-        }
-        mbar_init(&sh->all_done, 1);
-        sh->abort = 0;
-        mbar_fence_init();
-    }
-    if (warp == 17) tmem_alloc(&sh->tmem_base, 512);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh->tmem_base;
-
-    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
-    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
-
-    if (warp == 16) {
-        // ------------------------------------------------------------------ TMA producer
-        // K of tile j is free again once S(j) has retired, two tiles before its V: rings of their own
-        if (elect_one()) {
-            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
-            int issued = 0;  // half-steps: K of tile issued / 2, then its V
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % 3;
-                const uint32_t free_par = (uint32_t)(((j / 3) & 1) ^ 1);
-                if (j >= 3 && !hwait(&sh->free_k[s], free_par, sh)) { hgive_up(sh, 41); break; }
-                mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
-                tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
-                tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
-                ++issued;
-                if (j >= 3 && !hwait(&sh->free_v[s], free_par, sh)) { hgive_up(sh, 41); break; }
-                mbar_arrive_expect_tx(&sh->full_v[s], 2 * KP);
-                tma_load_4d(sV + s * 2 * KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, b);
-                tma_load_4d(sV + s * 2 * KP + KP, &vmap, &sh->full_v[s], 0, j * BN, g * NB, B + b);
-                ++issued;
-            }
-            if (sh->abort) {
-                // let the copies in flight land before the CTA's shared memory goes away
-                const int n_k = (issued + 1) / 2, n_v = issued / 2;
-                for (int j = (n_k > 3 ? n_k - 3 : 0); j < n_k; ++j) mbar_wait(&sh->full_k[j % 3], (uint32_t)((j / 3) & 1));
-                for (int j = (n_v > 3 ? n_v - 3 : 0); j < n_v; ++j) mbar_wait(&sh->full_v[j % 3], (uint32_t)((j / 3) & 1));
-            }
-        }
-        __syncwarp();
-    } else if (warp == 17) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
-            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
-            constexpr uint32_t id_o = idesc_f16(128, D, false, true);
-            bool ok = hwait(&sh->a_ready, 0, sh);
-            if (!ok) hgive_up(sh, 42);
-            tc_fence_after();
-            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
-            // S of tile j into buffer j & 1
-            auto issue_qk = [&](int j) -> bool {
-                const int s = j % 3;
-                if (!hwait(&sh->full_k[s], (uint32_t)((j / 3) & 1), sh)) return false;
-                tc_fence_after();
-                const uint32_t kh = k_u32 + (uint32_t)(s * 2 * KP);
-                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
-                const uint32_t cS = cS0 + (j & 1) * BN;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
-                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
-                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
-                }
-                mma_commit(&sh->free_k[s]);
-                mma_commit(&sh->s_full[j & 1]);
-                return true;
-            };
-            if (ok && !issue_qk(0)) { hgive_up(sh, 43); ok = false; }
-            if (ok && n_tiles > 1 && !issue_qk(1)) { hgive_up(sh, 43); ok = false; }
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int s = j % 3, set = j & 1;
-                if (!hwait(&sh->p_full[set], (uint32_t)((j >> 1) & 1), sh) ||
-                    !hwait(&sh->full_v[s], (uint32_t)((j / 3) & 1), sh)) { hgive_up(sh, 44); break; }
-                tc_fence_after();
-                const uint32_t vh = v_u32 + (uint32_t)(s * 2 * KP);
-                const uint64_t mvh = desc_mnmajor_16b(vh, BN * 128), mvl = desc_mnmajor_16b(vh + KP, BN * 128);
-                const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
-                    const uint64_t dvh = desc_advance(mvh, kk * 2048), dvl = desc_advance(mvl, kk * 2048);
-                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 1 || kk > 0) ? 1 : 0);
-                    mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
-                    mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
-                }
-                mma_commit(&sh->free_v[s]);
-                mma_commit(&sh->pv_done[set]);
-                // completes once, after the last P.V: a barrier that counts tiles may be two phases ahead
-                // of a row thread by the time it gets there, which a parity wait cannot tell apart
-                if (j == n_tiles - 1) mma_commit(&sh->all_done);
-                // S(j+2) overwrites the P tile this P.V has just read
-                if (j + 2 < n_tiles && !issue_qk(j + 2)) { hgive_up(sh, 43); break; }
-            }
-        }
-        __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ softmax rows: set `set` (eight warps)
-        // owns the key tiles of its parity, with a reference maximum, a sum and an O accumulator of its own; two
-        // threads share a row, 32 of the tile's 64 key columns each, and agree on the tile's row maximum through
-        // shared memory.  Nothing a set does waits on the other set's tile.
-        const int set = warp >> 3, hf = (warp >> 2) & 1;
-        const int tid = (warp & 3) * 32 + (threadIdx.x & 31);
-        const int t = t0 + tid;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const long long wq = (long long)p.n_heads * D;
-        {
-            // set 0 loads Q's hi plane, set 1 its lo plane; each thread half of the row's words
-            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
-            const long long plane = (long long)B * p.T * wq;
-            const __half *src = p.q_planes + (set ? plane : 0) + off;
-            const uint32_t dst = tmem + lane_base + (set ? cQl : cQh);
-#pragma unroll
-            for (int c = hf * (W2 / 2); c < (hf + 1) * (W2 / 2); c += 16) tcb::row_to_tmem16(src + 2 * c, t < p.T, dst + c);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive_warp(&sh->a_ready);
-        }
-        const float cs = p.scale_log2 / (mq * mk);
-        const uint32_t cS = cS0 + set * BN, cO = cO0 + set * D;
-        const uint32_t wS = tmem + lane_base + cS + hf * 32;
-        float m_ref = -INFINITY, l = 0.f;  // l: this thread's columns only
-        bool ok = true;
-        for (int j = set; j < n_tiles; j += 2) {
-            if (!__all_sync(0xffffffffu, hwait(&sh->s_full[set], (uint32_t)((j >> 1) & 1), sh))) {
-                hgive_up(sh, 45);
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            const int s0 = j * BN + hf * 32;
-            const bool diag = (j * BN + BN - 1 > t0);
-            uint32_t r[32];
-            tmem_ld32(wS, r);
-            tmem_wait_ld();
-            const float mine = diag ? row_max32<true>(r, s0, t, -INFINITY) : row_max32<false>(r, s0, t, -INFINITY);
-            // the row's maximum over the tile: both halves post theirs, both read both.  (An arrival for the
-            // set's next tile needs its S, hence P.V of this one, hence every warp past this wait.)
-            sh->xmax[set][hf][tid] = mine;
-            mbar_arrive_warp(&sh->x_ready[set]);
-            if (!__all_sync(0xffffffffu, hwait(&sh->x_ready[set], (uint32_t)((j >> 1) & 1), sh))) {
-                hgive_up(sh, 47);
-                ok = false;
-                break;
-            }
-            float mt = fmaxf(sh->xmax[set][0][tid], sh->xmax[set][1][tid]);
-            mt *= cs;  // cs > 0
-            float factor = 1.f;
-            if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
-                factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
-                m_ref = mt;
-            }
-            l *= factor;
-            if (j > 1 && __any_sync(0xffffffffu, factor != 1.f)) {
-                // this set's O may only be touched once its previous P.V (tile j-2) has retired; the two threads
-                // of a row share its factor and take half of its O columns each
-                if (!__all_sync(0xffffffffu, hwait(&sh->pv_done[set], (uint32_t)(((j >> 1) - 1) & 1), sh))) {
-                    hgive_up(sh, 46);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-#pragma unroll 1
-                for (int c = hf * (D / 2); c < (hf + 1) * (D / 2); c += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem + lane_base + cO + c, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                    tmem_st32(tmem + lane_base + cO + c, o);
-                }
-            }
-            // l is kept in P's units (times kPScale), like O
-            const float off = ((m_ref == -INFINITY) ? 0.f : m_ref) - 7.0f;  // log2 kPScale
-            uint32_t ph[16], pl[16];
-            l += diag ? row_exp32<true>(r, s0, t, cs, off, ph, pl) : row_exp32<false>(r, s0, t, cs, off, ph, pl);
-            tmem_st16(wS, ph);
-            tmem_st16(wS + 16, pl);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive_warp(&sh->p_full[set]);
-        }
-        // ---- merge: the two halves' sums, then the two sets' partial softmaxes
-        if (hf == 0) sh->fin_m[set][tid] = m_ref;
-        sh->fin_l[set][hf][tid] = l;
-        asm volatile("bar.sync 1, 512;" ::: "memory");  // the 512 softmax threads, once, after the loop
-        if (ok && !__all_sync(0xffffffffu, hwait(&sh->all_done, 0, sh))) {
-            hgive_up(sh, 48);
-            ok = false;
-        }
-        if (ok) {
-            tc_fence_after();
-            const bool two = n_tiles > 1;  // set 1 has an accumulator only then
-            const float m0 = sh->fin_m[0][tid], l0 = sh->fin_l[0][0][tid] + sh->fin_l[0][1][tid];
-            const float m1 = two ? sh->fin_m[1][tid] : -INFINITY, l1 = two ? sh->fin_l[1][0][tid] + sh->fin_l[1][1][tid] : 0.f;
-            const float mm = fmaxf(m0, m1);  // m0 is finite: key 0 is visible to every row
-            const float w0 = ex2(m0 - mm), w1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - mm);
-            const float lsum = w0 * l0 + w1 * l1;
-            const float inv = 1.f / (lsum * mv);  // lsum, like O, carries kPScale
-            const float f0 = w0 * inv, f1 = w1 * inv;
-            // each of the row's four threads writes a quarter of its columns
-            constexpr int CW = D / 4;  // 32 or 16
-            const int col = (set * 2 + hf) * CW;
-            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + col;
-            uint32_t ra[32], rb[32];
-            if (CW == 32) {
-                tmem_ld32(tmem + lane_base + cO0 + col, ra);
-                if (two) tmem_ld32(tmem + lane_base + cO0 + D + col, rb);
-                tmem_wait_ld();
-            } else {
-                uint32_t a16[16], b16[16];
-                tmem_ld16(tmem + lane_base + cO0 + col, a16);
-                if (two) tmem_ld16(tmem + lane_base + cO0 + D + col, b16);
-                tmem_wait_ld();  // the registers hold the values only from here on
-#pragma unroll
-                for (int i = 0; i < 16; ++i) ra[i] = a16[i], rb[i] = b16[i];
-            }
-            if (t < p.T && col < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
-#pragma unroll
-                for (int i = 0; i < CW; i += 4) {
-                    float4 o4;
-                    o4.x = __uint_as_float(ra[i]) * f0, o4.y = __uint_as_float(ra[i + 1]) * f0;
-                    o4.z = __uint_as_float(ra[i + 2]) * f0, o4.w = __uint_as_float(ra[i + 3]) * f0;
-                    if (two && w1 != 0.f) {
-                        o4.x += __uint_as_float(rb[i]) * f1, o4.y += __uint_as_float(rb[i + 1]) * f1;
-                        o4.z += __uint_as_float(rb[i + 2]) * f1, o4.w += __uint_as_float(rb[i + 3]) * f1;
-                    }
-                    *reinterpret_cast<float4 *>(orow + i) = o4;
-                }
-            }
-            if (set == 0 && hf == 0 && p.lse && t < p.T)
-                p.lse[((long long)b * p.T + t) * p.n_heads + h] = (mm + log2f(lsum) - 7.0f) * kLn2;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 17) tmem_dealloc(tmem, 512);
-}
-
-
-// ---------------------------------------------------------------------------------------------------
-// The same forward on key tiles of 128: every MMA is N = 128 (S) or N = D (P.V), none pays the
-// ~50-clock floor of a narrower instruction.  One O accumulator and one softmax state per row, so the
-// four softmax sets (32 key columns of the tile each) agree on the tile's row maximum through shared
-// memory before anyone exponentiates.  grid as attn_fwd_tc16; 576 threads: 16 softmax warps, TMA, MMA.
-// Measured 20 % slower than the 64-key kernel at head_dim 128, T = 4096 (3.69 ms against 3.08): with one
-// softmax state the row work of a tile (as many instructions per key as before, now with an exchange
-// between the sets in the middle) is a single stage beside the tensor core's 3072 clocks, not two
-// independent ones.  Kept selectable (zt_attn_set_path(3)) as the starting point for a version with
-// two query tiles per CTA; not the default.
-// TMEM: [0,D/2) Qh, [D/2,D) Ql, [D,2D) O, then two S/P tiles of 128 columns.  Shared memory: two K
-// tiles of 128 keys, two V half-tiles of 64 keys (a half is free as soon as its four MMA steps retire).
-// ---------------------------------------------------------------------------------------------------
-constexpr int kWideSoftmaxWarps = 16;
-constexpr int kWideThreads = (kWideSoftmaxWarps + 2) * 32;
-
-struct WideShared {
-    uint64_t full_k[2], free_k[2], full_v[2], free_v[2];
-    uint64_t a_ready, s_full[2], p_full[2], pv_done[2], all_done;
-    uint64_t x_ready[2], sum_ready;  // the sets' exchanges: mbarriers, so that a set that gave up cannot strand the others
-    uint32_t tmem_base;
-    volatile int abort;
-    float xmax[2][4][128];  // [tile parity][set][row]: the sets' maxima over their columns of the tile
-    float xsum[4][128];     // the sets' sums, exchanged once at the end
-};
-__device__ __forceinline__ bool wwait(uint64_t *bar, uint32_t parity, WideShared *sh) {
-    for (uint32_t i = 0; i < (1u << 20); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && sh->abort) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void wgive_up(WideShared *sh, int code) {
-    sh->abort = code;
-    atomicMax(&g_tc_status, code);
-}
-template <int D>
-__host__ __device__ constexpr size_t wide_smem_bytes() {
-    return 2 * 2 * (size_t)(128 * D * 2) + 2 * 2 * (size_t)(64 * D * 2) + sizeof(WideShared) + 1024;
-}
-
-template <int D>
-__global__ void __launch_bounds__(kWideThreads, 1)
-    attn_fwd_tc16w(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
-    constexpr int NB = D / 64, W2 = D / 2, BN = 128;
-    constexpr int KP = BN * D * 2;   // bytes of one plane of a 128-key K tile
-    constexpr int VP = 64 * D * 2;   // bytes of one plane of a 64-key V half-tile
-    constexpr int cQh = 0, cQl = W2, cO = D, cS0 = 2 * D;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sK = smem;               // slot s: Kh, Kl at sK + s * 2 KP + {0, 1} KP
-    uint8_t *sV = smem + 4 * KP;      // half-slot s: Vh, Vl at sV + s * 2 VP + {0, 1} VP
-    WideShared *sh = reinterpret_cast<WideShared *>(sV + 4 * VP);
-
-    const int warp = threadIdx.x >> 5;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int g = h / (p.n_heads / p.n_kv_heads);
-    const int t0 = qt * 128;
-    const int rows_end = (t0 + 128 < p.T) ? t0 + 128 : p.T;
-    const int n_tiles = (rows_end + BN - 1) / BN;
-    const int B = p.batch;
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&sh->full_k[i], 1), mbar_init(&sh->free_k[i], 1);
-            mbar_init(&sh->full_v[i], 1), mbar_init(&sh->free_v[i], 1);
-            mbar_init(&sh->s_full[i], 1), mbar_init(&sh->p_full[i], kWideSoftmaxWarps), mbar_init(&sh->pv_done[i], 1);
-            mbar_init(&sh->x_ready[i], kWideSoftmaxWarps);
-        }
-        mbar_init(&sh->a_ready, kWideSoftmaxWarps);
-        mbar_init(&sh->all_done, 1);
-        mbar_init(&sh->sum_ready, kWideSoftmaxWarps);
-        sh->abort = 0;
-        mbar_fence_init();
-    }
-    if (warp == kWideSoftmaxWarps + 1) tmem_alloc(&sh->tmem_base, 512);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh->tmem_base;
-
-    const float mq = block_mult(p.amax_q[b * p.n_kv_heads + g]), mk = block_mult(p.amax_k[b * p.n_kv_heads + g]);
-    const float mv = block_mult(p.amax_v[b * p.n_kv_heads + g]);
-
-    if (warp == kWideSoftmaxWarps) {
-        // ------------------------------------------------------------------ TMA producer: K(j), then the two
-        // halves of V(j).  K(j) goes into the slot S(j-2) has released; V half c into the one half c-2 has.
-        if (elect_one()) {
-            tma_prefetch_desc(&kmap), tma_prefetch_desc(&vmap);
-            int k_issued = 0, v_issued = 0;
-            bool ok = true;
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int s = j & 1;
-                if (j >= 2 && !wwait(&sh->free_k[s], (uint32_t)(((j >> 1) & 1) ^ 1), sh)) { wgive_up(sh, 51); break; }
-                mbar_arrive_expect_tx(&sh->full_k[s], 2 * KP);
-                tma_load_4d(sK + s * 2 * KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, b);
-                tma_load_4d(sK + s * 2 * KP + KP, &kmap, &sh->full_k[s], 0, j * BN, g * NB, B + b);
-                ++k_issued;
-                for (int half = 0; half < 2; ++half) {
-                    const int c = 2 * j + half, vs = c & 1;
-                    if (c >= 2 && !wwait(&sh->free_v[vs], (uint32_t)(((c >> 1) & 1) ^ 1), sh)) { wgive_up(sh, 51); ok = false; break; }
-                    mbar_arrive_expect_tx(&sh->full_v[vs], 2 * VP);
-                    tma_load_4d(sV + vs * 2 * VP, &vmap, &sh->full_v[vs], 0, c * 64, g * NB, b);
-                    tma_load_4d(sV + vs * 2 * VP + VP, &vmap, &sh->full_v[vs], 0, c * 64, g * NB, B + b);
-                    ++v_issued;
-                }
-            }
-            if (sh->abort) {
-                // let the copies in flight land before the CTA's shared memory goes away
-                for (int j = (k_issued > 2 ? k_issued - 2 : 0); j < k_issued; ++j) mbar_wait(&sh->full_k[j & 1], (uint32_t)((j >> 1) & 1));
-                for (int c = (v_issued > 2 ? v_issued - 2 : 0); c < v_issued; ++c) mbar_wait(&sh->full_v[c & 1], (uint32_t)((c >> 1) & 1));
-            }
-        }
-        __syncwarp();
-    } else if (warp == kWideSoftmaxWarps + 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
-            constexpr uint32_t id_s = idesc_f16(128, BN, false, false);
-            constexpr uint32_t id_o = idesc_f16(128, D, false, true);
-            bool ok = wwait(&sh->a_ready, 0, sh);
-            if (!ok) wgive_up(sh, 52);
-            tc_fence_after();
-            const uint32_t k_u32 = smem_u32(sK), v_u32 = smem_u32(sV);
-            auto issue_qk = [&](int j) -> bool {  // S of tile j into buffer j & 1
-                const int s = j & 1;
-                if (!wwait(&sh->full_k[s], (uint32_t)((j >> 1) & 1), sh)) return false;
-                tc_fence_after();
-                const uint32_t kh = k_u32 + (uint32_t)(s * 2 * KP);
-                const uint64_t bkh = desc_kmajor(kh), bkl = desc_kmajor(kh + KP);
-                const uint32_t cS = cS0 + s * BN;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t bo = (uint32_t)((kk >> 2) * (BN * 128) + (kk & 3) * 32);
-                    const uint64_t dkh = desc_advance(bkh, bo), dkl = desc_advance(bkl, bo);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkh, id_s, kk > 0);
-                    mma_ts_f16(tmem + cS, tmem + cQh + kk * 8, dkl, id_s, 1);
-                    mma_ts_f16(tmem + cS, tmem + cQl + kk * 8, dkh, id_s, 1);
-                }
-                mma_commit(&sh->free_k[s]);
-                mma_commit(&sh->s_full[s]);
-                return true;
-            };
-            if (ok && !issue_qk(0)) { wgive_up(sh, 53); ok = false; }
-            if (ok && n_tiles > 1 && !issue_qk(1)) { wgive_up(sh, 53); ok = false; }
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int buf = j & 1;
-                if (!wwait(&sh->p_full[buf], (uint32_t)((j >> 1) & 1), sh)) { wgive_up(sh, 54); break; }
-                tc_fence_after();
-                const uint32_t cS = cS0 + buf * BN;
-                // P: the set of key columns [32 c, 32 c + 32) left its hi halves in the first 16 columns of its
-                // 32-column window and its lo halves in the last 16; a V half-tile serves four MMA steps
-                for (int half = 0; ok && half < 2; ++half) {
-                    const int c = 2 * j + half, vs = c & 1;
-                    if (!wwait(&sh->full_v[vs], (uint32_t)((c >> 1) & 1), sh)) { wgive_up(sh, 54); ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t vh = v_u32 + (uint32_t)(vs * 2 * VP);
-                    const uint64_t mvh = desc_mnmajor_16b(vh, 64 * 128), mvl = desc_mnmajor_16b(vh + VP, 64 * 128);
-#pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) {
-                        const int kk = half * 4 + k4;
-                        const uint32_t ac = (uint32_t)(32 * (kk >> 1) + (kk & 1) * 8);
-                        const uint64_t dvh = desc_advance(mvh, k4 * 2048), dvl = desc_advance(mvl, k4 * 2048);
-                        mma_ts_f16(tmem + cO, tmem + cS + ac, dvh, id_o, (j > 0 || kk > 0) ? 1 : 0);
-                        mma_ts_f16(tmem + cO, tmem + cS + ac, dvl, id_o, 1);
-                        mma_ts_f16(tmem + cO, tmem + cS + ac + 16, dvh, id_o, 1);
-                    }
-                    mma_commit(&sh->free_v[vs]);
-                }
-                if (!ok) break;
-                mma_commit(&sh->pv_done[buf]);
-                if (j == n_tiles - 1) mma_commit(&sh->all_done);  // completes once, after the last P.V
-                // S(j+2) overwrites the P tile this P.V has just read
-                if (j + 2 < n_tiles && !issue_qk(j + 2)) { wgive_up(sh, 53); break; }
-            }
-        }
-        __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ softmax: one thread per query row
-        // and 32 of the tile's 128 key columns (set `set`)
-        const int tid = threadIdx.x & 127, set = threadIdx.x >> 7;
-        const int t = t0 + tid;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const long long wq = (long long)p.n_heads * D;
-        {
-            // Q's planes -> TMEM: 16 words of each plane's row per set at head_dim 128, sets 0 and 1 at 64
-            const long long off = ((long long)b * p.T + (t < p.T ? t : 0)) * wq + (long long)h * D;
-            const long long plane = (long long)B * p.T * wq;
-            if (set * 16 < W2) {
-                tcb::row_to_tmem16(p.q_planes + off + set * 32, t < p.T, tmem + lane_base + cQh + set * 16);
-                tcb::row_to_tmem16(p.q_planes + plane + off + set * 32, t < p.T, tmem + lane_base + cQl + set * 16);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive_warp(&sh->a_ready);
-        }
-        const float cs = p.scale_log2 / (mq * mk);
-        float m_ref = -INFINITY, l = 0.f;  // l: this thread's columns only
-        bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int buf = j & 1;
-            if (!__all_sync(0xffffffffu, wwait(&sh->s_full[buf], (uint32_t)((j >> 1) & 1), sh))) {
-                wgive_up(sh, 55);
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            const uint32_t wS = tmem + lane_base + cS0 + buf * BN + set * 32;
-            const int s0 = j * BN + set * 32;
-            const bool diag = (j * BN + BN - 1 > t0);
-            uint32_t r[32];
-            tmem_ld32(wS, r);
-            tmem_wait_ld();
-            float mine = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (!diag || s0 + i <= t) mine = fmaxf(mine, __uint_as_float(r[i]));
-            // the row's maximum over the whole tile: every set posts its own, all read all four
-            // (an arrival for tile j+2 needs S(j+2), hence P.V(j), hence every warp past this wait for tile j:
-            // the barrier of a parity is never more than one phase ahead of a waiter)
-            sh->xmax[buf][set][tid] = mine;
-            mbar_arrive_warp(&sh->x_ready[buf]);
-            if (!__all_sync(0xffffffffu, wwait(&sh->x_ready[buf], (uint32_t)((j >> 1) & 1), sh))) {
-                wgive_up(sh, 57);
-                ok = false;
-                break;
-            }
-            float mt = fmaxf(fmaxf(sh->xmax[buf][0][tid], sh->xmax[buf][1][tid]), fmaxf(sh->xmax[buf][2][tid], sh->xmax[buf][3][tid]));
-            mt *= cs;  // cs > 0
-            float factor = 1.f;
-            if ((mt > m_ref + kRescaleThreshold || m_ref == -INFINITY) && mt != -INFINITY) {
-                factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
-                m_ref = mt;
-            }
-            l *= factor;
-            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-                // O may only be touched once P.V of tile j-1 has retired; the four sets share the row's
-                // factor and take a quarter of its O columns each
-                if (!__all_sync(0xffffffffu, wwait(&sh->pv_done[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), sh))) {
-                    wgive_up(sh, 56);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                constexpr int CW = D / 4;  // 32 or 16
-                if (CW == 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem + lane_base + cO + set * CW, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                    tmem_st32(tmem + lane_base + cO + set * CW, o);
-                } else {
-                    uint32_t o[16];
-                    tmem_ld16(tmem + lane_base + cO + set * CW, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                    tmem_st16(tmem + lane_base + cO + set * CW, o);
-                }
-            }
-            const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float psum = 0.f;
-            uint32_t ph[16], pl[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float pe[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    pe[e] = ex2(__uint_as_float(r[i + e]) * cs - mref_safe);
-                    if (diag && s0 + i + e > t) pe[e] = 0.f;
-                    psum += pe[e];
-                }
-                split_pack(pe[0] * kPScale, pe[1] * kPScale, ph[i >> 1], pl[i >> 1]);
-            }
-            tmem_st16(wS, ph);
-            tmem_st16(wS + 16, pl);
-            l += psum;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive_warp(&sh->p_full[buf]);
-        }
-        // ---- the row's sum over all four sets, then a quarter of its O columns each
-        sh->xsum[set][tid] = l;
-        mbar_arrive_warp(&sh->sum_ready);
-        if (ok && !__all_sync(0xffffffffu, wwait(&sh->sum_ready, 0, sh) && wwait(&sh->all_done, 0, sh))) {
-            wgive_up(sh, 58);
-            ok = false;
-        }
-        if (ok) {
-            tc_fence_after();
-            const float lsum = sh->xsum[0][tid] + sh->xsum[1][tid] + sh->xsum[2][tid] + sh->xsum[3][tid];
-            const float inv = 1.f / (lsum * kPScale * mv);
-            constexpr int CW = D / 4;
-            float *orow = p.out + ((long long)b * p.T + t) * ((long long)p.n_heads * p.dim_out) + (long long)h * p.dim_out + set * CW;
-            uint32_t o[32];
-            if (CW == 32) {
-                tmem_ld32(tmem + lane_base + cO + set * CW, o);
-                tmem_wait_ld();
-            } else {
-                uint32_t o16[16];
-                tmem_ld16(tmem + lane_base + cO + set * CW, o16);
-                tmem_wait_ld();  // the registers hold the values only from here on
-#pragma unroll
-                for (int i = 0; i < 16; ++i) o[i] = o16[i];
-            }
-            if (t < p.T && set * CW < p.dim_out) {
-#pragma unroll
-                for (int i = 0; i < CW; i += 4) {
-                    float4 o4;
-                    o4.x = __uint_as_float(o[i]) * inv, o4.y = __uint_as_float(o[i + 1]) * inv;
-                    o4.z = __uint_as_float(o[i + 2]) * inv, o4.w = __uint_as_float(o[i + 3]) * inv;
-                    *reinterpret_cast<float4 *>(orow + i) = o4;
-                }
-            }
-            if (set == 0 && p.lse && t < p.T) p.lse[((long long)b * p.T + t) * p.n_heads + h] = (m_ref + log2f(lsum)) * kLn2;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == kWideSoftmaxWarps + 1) tmem_dealloc(tmem, 512);
-}
 
 struct Workspace {
     uint32_t *amax_q, *amax_k, *amax_v;
@@ -1064,31 +440,9 @@ inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUte
     return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, qmap, p)));
 }
 
-template <int D>
-inline int launch_wide_d(const CUtensorMap &kmap128, const CUtensorMap &vmap64, const Params &p, cudaStream_t stream) {
-    size_t smem = wide_smem_bytes<D>();
-    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
-    if (optin_smem((const void *)attn_fwd_tc16w<D>, smem)) return 1;
-    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
-    return ZT_LAUNCH("attn_fwd_tc16w", stream, (attn_fwd_tc16w<D><<<grid, kWideThreads, smem, stream>>>(kmap128, vmap64, p)));
-}
-
-template <int D>
-inline int launch_h_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const Params &p, cudaStream_t stream) {
-    size_t smem = 12 * (size_t)(64 * D * 2) + sizeof(SharedH) + 1024;
-    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
-    if (optin_smem((const void *)attn_fwd_tc16h<D>, smem)) return 1;
-    const dim3 grid((unsigned)((p.T + 127) / 128), (unsigned)p.n_heads, (unsigned)p.batch);
-    return ZT_LAUNCH("attn_fwd_tc16h", stream, (attn_fwd_tc16h<D><<<grid, kThreadsH, smem, stream>>>(kmap, vmap, p)));
-}
-
 // (tc_fwd16g.cuh)
 template <int D>
 inline int launch_g_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
-                      cudaStream_t stream);
-// (tc_fwd16p.cuh)
-template <int D>
-inline int launch_p_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
                       cudaStream_t stream);
 
 }  // namespace tcf16
@@ -1133,13 +487,11 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
-    // variant 0: key tiles of 64, four softmax warps per set; 1: key tiles of 128; 2: key tiles of 64, eight warps per set;
-    // 3: as 4 with CTAs that walk several query tiles; 4: one head per CTA.  Variant 0 takes two heads of a KV group
-    // per CTA (attn_fwd_tc16g) when the group has an even number of query heads and that still gives every SM a CTA,
-    // and is variant 4 otherwise; variant 5 takes two heads whatever the number of CTAs.
-    const bool wide = variant == 1;
+    // variant 0: two heads of a KV group per CTA (attn_fwd_tc16g) when the group has an even number of query heads
+    // and that still gives every SM a CTA, one head per CTA (attn_fwd_tc16) otherwise; 1: one head per CTA;
+    // 2: two heads per CTA whatever the number of CTAs (the group must be even).
     CUtensorMap kmap, vmap, qmap;
-    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, wide ? 128 : 64) ||
+    if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, td, 64) ||
         !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64) ||
         !make_half_tile_map(&qmap, w.q_planes, 2 * batch, T, n_heads * td, td, 128))
         return refuse("the TMA tensor maps for the forward could not be encoded.");
@@ -1149,18 +501,13 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
     p.ahead = device_info() ? device_info()->sm_count : 0;  // one CTA per SM
-    if (const char *e = getenv("ZT_FWD_AHEAD")) p.ahead = atoi(e);
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";
-    if (wide) return td == 64 ? tcf16::launch_wide_d<64>(kmap, vmap, p, stream) : tcf16::launch_wide_d<128>(kmap, vmap, p, stream);
-    p.n_items = (((T + 127) / 128 + 1) / 2) * n_heads * batch;
     // two heads per CTA halve the number of CTAs: not when that leaves SMs without one
     const long long pair_ctas = (long long)((T + 127) / 128) * (n_heads / 2) * batch;
-    if ((variant == 0 || variant == 5) && (n_heads / n_kv_heads) % 2 == 0 &&
-        (variant == 5 || (device_info() && pair_ctas >= device_info()->sm_count)))
+    if ((variant == 0 || variant == 2) && (n_heads / n_kv_heads) % 2 == 0 &&
+        (variant == 2 || (device_info() && pair_ctas >= device_info()->sm_count)))
         return td == 64 ? tcf16::launch_g_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_g_d<128>(kmap, vmap, qmap, p, stream);
-    if (variant == 3) return td == 64 ? tcf16::launch_p_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_p_d<128>(kmap, vmap, qmap, p, stream);
-    if (variant == 2) return td == 64 ? tcf16::launch_h_d<64>(kmap, vmap, p, stream) : tcf16::launch_h_d<128>(kmap, vmap, p, stream);
     return td == 64 ? tcf16::launch_d<64>(kmap, vmap, qmap, p, stream) : tcf16::launch_d<128>(kmap, vmap, qmap, p, stream);
 }
 

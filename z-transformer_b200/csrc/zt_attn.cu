@@ -17,7 +17,6 @@
 #include "tc_bwd.cuh"
 #include "tc_fwd.cuh"
 #include "tc_fwd16.cuh"
-#include "tc_fwd16p.cuh"
 #include "tc_fwd16g.cuh"
 #endif
 
@@ -28,28 +27,43 @@ namespace zt {
 constexpr int kMinDim = 32, kMaxDim = 256;  // src/cuda/attn_kernels.cu:147-148
 constexpr size_t kArenaBytes = 16u << 20;
 
-// One arena per device for the reference's entry points, which take no workspace argument:
-// created on the first call that needs scratch on that device, kept until the process ends,
-// and replaced by a larger one only when a call needs more than it holds (cudaFree waits for
-// the device, so work still using the old arena has finished).  A steady-state caller -- same
-// shapes step after step -- therefore never allocates after its first step.
-static void *device_arena(size_t need = kArenaBytes) {
+// One arena per device for the entry points that take no workspace argument (the reference's own two, and
+// the batched forward): created on the first call that needs scratch on that device, or by zt_attn_reserve.
+// It only ever grows, and an arena that has been outgrown is retired, not freed: a launch queued earlier, or a
+// thread that read the old pointer a moment ago, may still be using it, and cudaFree would also stall the
+// device.  Retired arenas are released when the process ends.  A steady-state caller -- same shapes step after
+// step -- allocates on its first step (or in zt_attn_reserve) and never again.
+// Growth is refused (nullptr, with the reason recorded) while `stream` is being captured into a CUDA graph:
+// an allocation inside a capture would break it, and the caller can size the arena beforehand.
+// Every call on a device shares the arena: calls that use it must not overlap on the GPU (see zt_attn.h).
+static void *device_arena(size_t need, cudaStream_t stream, bool *refused_in_capture = nullptr,
+                          size_t *held_now = nullptr) {
     static void *arena[64] = {};
     static size_t held[64] = {};
     static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (need < kArenaBytes) need = kArenaBytes;
     std::lock_guard<std::mutex> lock(mu);
+    if (held_now) {  // a query: how large is the current device's arena
+        *held_now = held[dev];
+        return arena[dev];
+    }
+    if (need < kArenaBytes) need = kArenaBytes;
     if (held[dev] < need) {
-        if (arena[dev]) cudaFree(arena[dev]);
-        arena[dev] = nullptr, held[dev] = 0;
-        if (cudaMalloc(&arena[dev], need) != cudaSuccess) {
-            cudaGetLastError();
-            arena[dev] = nullptr;
-        } else {
-            held[dev] = need;
+        // (the legacy default stream cannot be captured, and asking about it would itself disturb a capture
+        // running on another stream)
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (stream != nullptr && cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+        if (cap != cudaStreamCaptureStatusNone) {
+            if (refused_in_capture) *refused_in_capture = true;
+            return nullptr;
         }
+        void *fresh = nullptr;
+        if (cudaMalloc(&fresh, need) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        arena[dev] = fresh, held[dev] = need;  // the old arena, if any, stays allocated until exit
     }
     return arena[dev];
 }
@@ -82,16 +96,21 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
     const int path = g_path.load();
-    if ((path == 0 || path == 3 || path == 4 || path == 5 || path == 6 || path == 7) && n_kv_heads <= tcb::kPrepassMaxGroups &&
+    if ((path == 0 || path == 6 || path == 7) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
         // The f16-split forward keeps its operand planes in the per-device arena (no entry point
         // of the forward takes a workspace); see device_arena for when that allocates.
         const size_t need = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
-        if (void *arena = device_arena(need))
+        bool in_capture = false;
+        void *arena = device_arena(need, stream, &in_capture);
+        if (in_capture)
+            return refuse("this shape needs %zu bytes of the per-device arena, which would have to grow while the "
+                          "stream is being captured: call zt_attn_reserve for the shape before the capture.", need);
+        if (arena)
             return launch_fwd_tc16(q, k, v, out, lse, arena, batch, T, n_heads, n_kv_heads, dim, stream, nullptr, false,
-                                   path == 3 ? 1 : (path == 4 ? 2 : (path == 5 ? 3 : (path == 6 ? 4 : (path == 7 ? 5 : 0)))));
+                                   path == 6 ? 1 : (path == 7 ? 2 : 0));
     }
-    if ((path == 0 || path == 2 || path == 3 || path == 4 || path == 5 || path == 6 || path == 7) &&
+    if ((path == 0 || path == 2 || path == 6 || path == 7) &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
     }
@@ -116,65 +135,89 @@ static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, 
 }
 
 // The forward-for-training call (zt_attn_forward_batched_keep) leaves the f16 planes of q, k, v in the backward's
-// workspace; this is the host-side note of whose planes they are.  One note per device, used at most once, and
-// dropped by any tensor-core backward that touches a workspace.
+// workspace and hands the caller a token; a backward that is given the token back (zt_attn_backward_batched_kept)
+// converts only dout.  The library keeps one record per (device, workspace) of which token is current, for which
+// shape; a token is good for one backward, and any other call that writes the workspace retires it.  Nothing is
+// ever inferred from pointer values of q, k, v: reuse happens only when the caller asks for it.
 namespace {
 struct KeptPlanes {
     const void *workspace = nullptr;
-    const float *q = nullptr, *k = nullptr, *v = nullptr;
     int batch = 0, T = 0, n_heads = 0, n_kv_heads = 0, dim = 0;
-    cudaStream_t stream = nullptr;
     bool rope = false;  // the planes of q and k are rotated ones, for (pos, theta)
     int pos = 0;
     double theta = 0.0;
-    bool valid = false;
+    unsigned long long token = 0;  // 0: no planes kept
 };
-KeptPlanes g_kept[64];
+constexpr int kKeptSlots = 8;
+KeptPlanes g_kept[64][kKeptSlots];
+unsigned long long g_next_token = 1;
 std::mutex g_kept_mu;
 
-// true (and the note is consumed) when the workspace holds the planes of exactly these tensors
-bool take_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
-                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream, bool rope = false, int pos = 0,
-                      double theta = 0.0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    std::lock_guard<std::mutex> lock(g_kept_mu);
-    KeptPlanes &n = g_kept[dev];
-    const bool hit = n.valid && n.workspace == workspace && n.q == q && n.k == k && n.v == v && n.batch == batch &&
-                     n.T == T && n.n_heads == n_heads && n.n_kv_heads == n_kv_heads && n.dim == dim && n.stream == stream &&
-                     n.rope == rope && (!rope || (n.pos == pos && n.theta == theta));
-    n.valid = false;
-    return hit;
-}
-void note_kept_planes(const void *workspace, const float *q, const float *k, const float *v, int batch, int T,
-                      int n_heads, int n_kv_heads, int dim, cudaStream_t stream, bool rope = false, int pos = 0,
-                      double theta = 0.0) {
+// Forget whatever was kept in `workspace` (the caller is about to overwrite it).
+void drop_kept_planes(const void *workspace) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
     std::lock_guard<std::mutex> lock(g_kept_mu);
-    KeptPlanes &n = g_kept[dev];
-    n.workspace = workspace, n.q = q, n.k = k, n.v = v;
-    n.batch = batch, n.T = T, n.n_heads = n_heads, n.n_kv_heads = n_kv_heads, n.dim = dim, n.stream = stream;
-    n.rope = rope, n.pos = pos, n.theta = theta;
-    n.valid = true;
+    for (KeptPlanes &n : g_kept[dev])
+        if (n.workspace == workspace) n = KeptPlanes{};
+}
+// Record that `workspace` now holds the planes of a forward of this shape; returns the token for them.
+unsigned long long note_kept_planes(const void *workspace, int batch, int T, int n_heads, int n_kv_heads, int dim,
+                                    bool rope = false, int pos = 0, double theta = 0.0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(g_kept_mu);
+    KeptPlanes *slot = nullptr;
+    for (KeptPlanes &n : g_kept[dev])
+        if (n.workspace == workspace) slot = &n;
+    if (!slot)
+        for (KeptPlanes &n : g_kept[dev])
+            if (n.token == 0) { slot = &n; break; }
+    if (!slot) {  // every slot holds a live token: the oldest one goes
+        slot = &g_kept[dev][0];
+        for (KeptPlanes &n : g_kept[dev])
+            if (n.token < slot->token) slot = &n;
+    }
+    *slot = KeptPlanes{workspace, batch, T, n_heads, n_kv_heads, dim, rope, pos, theta, g_next_token++};
+    return slot->token;
+}
+// true (and the token is spent) when `token` is the current one of `workspace`, for exactly this shape.
+bool take_kept_planes(const void *workspace, unsigned long long token, int batch, int T, int n_heads, int n_kv_heads,
+                      int dim, bool rope = false, int pos = 0, double theta = 0.0) {
+    int dev = 0;
+    if (token == 0 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(g_kept_mu);
+    for (KeptPlanes &n : g_kept[dev]) {
+        if (n.workspace != workspace || n.token != token) continue;
+        const bool hit = n.batch == batch && n.T == T && n.n_heads == n_heads && n.n_kv_heads == n_kv_heads &&
+                         n.dim == dim && n.rope == rope && (!rope || (n.pos == pos && n.theta == theta));
+        n = KeptPlanes{};
+        return hit;
+    }
+    return false;
 }
 }  // namespace
 
-static int backward_impl(const float *q, const float *k, const float *v, const float *lse,
-                         const float *delta, const float *dout, float *dq, float *dk, float *dv,
+// delta = sum_j dout * out is formed here (into the caller's `delta`), then the gradients.  `out` may alias dq
+// (the reference ABI's backward rebuilds the forward's output there): it is read before dq is written.
+static int backward_impl(const float *q, const float *k, const float *v, const float *out, const float *lse,
+                         float *delta, const float *dout, float *dq, float *dk, float *dv,
                          void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                         int n_kv_heads, int dim, cudaStream_t stream) {
+                         int n_kv_heads, int dim, cudaStream_t stream, bool kept = false) {
 #ifndef ZT_NO_TC
     if (g_path.load() != 1 && workspace &&
         workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
         n_kv_heads <= tcb::kPrepassMaxGroups && tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv)) {
-        const bool kept = take_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, stream);
+        // the tensor-core kernels also want each row's |dout| (their scale of dS): the same pass writes it
+        float *rnorm = tcb::bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).rnorm;
+        if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
                              dim, stream, nullptr, nullptr, kept);
     }
 #endif
-    (void)workspace, (void)workspace_bytes;
+    (void)workspace, (void)workspace_bytes, (void)kept;
+    if (launch_delta(out, dout, delta, nullptr, (long long)batch * T * n_heads, dim, stream)) return 1;
     SimtBwdParams p{};
     p.q = q, p.k = k, p.v = v, p.dout = dout, p.lse = lse, p.delta = delta;
     p.dq = dq, p.dk = dk, p.dv = dv;
@@ -243,7 +286,7 @@ size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float)
 const char *zt_attn_last_error(void) { return g_last_error; }
 const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
-int zt_attn_set_path(int path) { return g_path.exchange((path >= 1 && path <= 7) ? path : 0); }
+int zt_attn_set_path(int path) { return g_path.exchange((path == 1 || path == 2 || path == 6 || path == 7) ? path : 0); }
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
 
 int zt_attn_tc_status(int *host_status) {
@@ -258,6 +301,46 @@ int zt_attn_tc_status(int *host_status) {
     *host_status = 0;
 #endif
     return 0;
+}
+
+int zt_attn_tc_saturated(unsigned int *host_count) {
+    if (!host_count) return refuse("a null pointer was passed.");
+#ifndef ZT_NO_TC
+    if (need_device()) return 1;
+    if (tc_saturated_read(host_count)) {
+        const cudaError_t e = cudaGetLastError();
+        return refuse("reading the saturation count failed: %s", cudaGetErrorString(e));
+    }
+#else
+    *host_count = 0;
+#endif
+    return 0;
+}
+
+int zt_attn_reserve(int batch, int T, int n_heads, int n_kv_heads, int dim) {
+    g_last_error[0] = 0;
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    if (need_device()) return 1;
+    size_t need = kArenaBytes;  // the decode-shaped forward's partial results
+#ifndef ZT_NO_TC
+    if (n_kv_heads <= tcb::kPrepassMaxGroups && (dim == 32 || dim == 64 || dim == 96 || dim == 128) && T >= 128) {
+        const size_t f = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+        const size_t b = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
+        need = f > need ? f : need;
+        need = b > need ? b : need;
+    }
+#endif
+    bool in_capture = false;
+    if (!device_arena(need, nullptr, &in_capture))
+        return refuse("the per-device arena of %zu bytes could not be allocated.", need);
+    return 0;
+}
+
+size_t zt_attn_arena_bytes(void) {
+    size_t held = 0;
+    device_arena(0, nullptr, nullptr, &held);
+    return held;
 }
 
 void zt_attn_profile(int on) { g_profile.store(on ? 1 : 0); }
@@ -320,7 +403,11 @@ int zt_attn_forward(const float *q, const float *k, const float *v, float *out, 
         // q_offset and sees keys 0 .. q_offset (q_offset <= n_keys - 1 was checked above).
         n_keys = q_offset + 1;
         const DecodePlan pl = decode_plan(1, n_keys, n_heads, n_kv_heads, dim);
-        void *arena = pl.total_bytes <= kArenaBytes ? device_arena() : nullptr;
+        bool in_capture = false;
+        void *arena = pl.total_bytes <= kArenaBytes ? device_arena(kArenaBytes, (cudaStream_t)stream, &in_capture) : nullptr;
+        if (in_capture)
+            return refuse("the per-device arena does not exist yet and the stream is being captured: call "
+                          "zt_attn_reserve before the capture.");
         if (arena) {
             DecodeParams p{};
             p.q = q, p.k_cache = k, p.v_cache = v, p.n_keys = nullptr, p.n_keys_all = n_keys;
@@ -347,17 +434,21 @@ int zt_attn_backward(const float *q, const float *k, const float *v, const float
         return refuse("a null device pointer was passed.");
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
+    // the arena must hold the backward's planes (at least the forward's): grown, if at all, before any launch
+    const size_t need = backward_workspace(1, T, n_heads, n_kv_heads, dim);
+    bool in_capture = false;
+    void *arena = need ? device_arena(need, s, &in_capture) : nullptr;
+    if (in_capture)
+        return refuse("this shape needs %zu bytes of the per-device arena, which would have to grow while the "
+                      "stream is being captured: call zt_attn_reserve for the shape before the capture.", need);
     // The reference's backward sees neither the forward's output nor its log-sum-exp, so
     // both are rebuilt here: the forward runs into dq (same shape as out, assigned later)
     // with the log-sum-exp into row_max, then row_del = sum_j dout * out.
     if (forward_impl(q, k, v, dq, row_max, 1, T, n_heads, n_kv_heads, dim, 0, T, s)) return 1;
-    if (launch_delta(dq, dout, row_del, (long long)T * n_heads, dim, s)) return 1;
     const long long n = (long long)T * n_heads;
     if (ZT_LAUNCH("fill_kernel", s, fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(row_den, n, 1.0f)))
         return 1;
-    const size_t need = backward_workspace(1, T, n_heads, n_kv_heads, dim);
-    void *arena = need ? device_arena(need) : nullptr;
-    return backward_impl(q, k, v, row_max, row_del, dout, dq, dk, dv, arena, arena ? need : 0, 1, T, n_heads,
+    return backward_impl(q, k, v, dq, row_max, row_del, dout, dq, dk, dv, arena, arena ? need : 0, 1, T, n_heads,
                          n_kv_heads, dim, s);
 }
 
@@ -375,22 +466,25 @@ int zt_attn_forward_batched(const float *q, const float *k, const float *v, floa
 
 int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
                                  void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, zt_stream_t stream) {
+                                 int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token) {
     g_last_error[0] = 0;
+    if (host_token) *host_token = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
     if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
+    if (workspace) drop_kept_planes(workspace);
 #ifndef ZT_NO_TC
     const size_t need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
     const int keep_path = g_path.load();
-    if ((keep_path == 0 || keep_path == 3 || keep_path == 4 || keep_path == 5 || keep_path == 6 || keep_path == 7) && need > 0 && workspace && workspace_bytes >= need &&
+    if ((keep_path == 0 || keep_path == 6 || keep_path == 7) && need > 0 && workspace && workspace_bytes >= need &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
-        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 3 ? 1 : (keep_path == 4 ? 2 : (keep_path == 5 ? 3 : (keep_path == 6 ? 4 : (keep_path == 7 ? 5 : 0))))))
+        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 6 ? 1 : (keep_path == 7 ? 2 : 0)))
             return 1;
-        note_kept_planes(workspace, q, k, v, batch, T, n_heads, n_kv_heads, dim, s);
+        const unsigned long long token = note_kept_planes(workspace, batch, T, n_heads, n_kv_heads, dim);
+        if (host_token) *host_token = token;
         return 0;
     }
 #endif
@@ -405,10 +499,11 @@ size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_
     return backward_workspace(batch, T, n_heads, n_kv_heads, dim);
 }
 
-int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
-                             const float *lse, const float *dout, float *dq, float *dk, float *dv,
-                             float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
-                             int n_heads, int n_kv_heads, int dim, zt_stream_t stream) {
+int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v, const float *out,
+                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                  int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                                  unsigned long long token) {
     g_last_error[0] = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
@@ -421,9 +516,22 @@ int zt_attn_backward_batched(const float *q, const float *k, const float *v, con
         return refuse("the backward workspace must be 256-byte aligned.");
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
-    if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
-    return backward_impl(q, k, v, lse, delta, dout, dq, dk, dv, workspace, workspace_bytes, batch, T, n_heads,
-                         n_kv_heads, dim, s);
+    // spent or not, a token does not outlive a backward that rewrites the workspace
+    const bool kept = take_kept_planes(workspace, token, batch, T, n_heads, n_kv_heads, dim);
+    if (token != 0 && !kept)
+        return refuse("token %llu is not the current one of this workspace for this shape: the planes it stood for "
+                      "are gone (pass 0 to convert q, k, v again).", token);
+    if (workspace) drop_kept_planes(workspace);
+    return backward_impl(q, k, v, out, lse, delta, dout, dq, dk, dv, workspace, workspace_bytes, batch, T, n_heads,
+                         n_kv_heads, dim, s, kept);
+}
+
+int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
+                             const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                             float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                             int n_heads, int n_kv_heads, int dim, zt_stream_t stream) {
+    return zt_attn_backward_batched_kept(q, k, v, out, lse, dout, dq, dk, dv, delta, workspace, workspace_bytes, batch,
+                                         T, n_heads, n_kv_heads, dim, stream, 0ull);
 }
 
 // ---- attention with the rotary embedding of q and k fused in ------------------------------------------
@@ -468,8 +576,10 @@ size_t zt_attn_rope_workspace_bytes(int batch, int T, int n_heads, int n_kv_head
 
 int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
                                  void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream) {
+                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream,
+                                 unsigned long long *host_token) {
     g_last_error[0] = 0;
+    if (host_token) *host_token = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
     if (!q || !k || !v || !out) return refuse("a null device pointer was passed.");
@@ -477,6 +587,7 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
     if (check_rope_call(workspace, workspace_bytes, w.total_bytes, pos, theta)) return 1;
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
+    drop_kept_planes(w.inner);
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
 #ifndef ZT_NO_TC
     if ((g_path.load() == 0) && n_kv_heads <= tcb::kPrepassMaxGroups &&
@@ -485,7 +596,8 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
         // the planes (rotated q and k among them) go where the backward keeps its own: the rope backward that
         // follows with the same workspace, tensors, pos and theta converts only dout
         if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, 0)) return 1;
-        note_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
+        const unsigned long long token = note_kept_planes(w.inner, batch, T, n_heads, n_kv_heads, dim, true, pos, theta);
+        if (host_token) *host_token = token;
         return 0;
     }
 #endif
@@ -499,7 +611,7 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
                                   const float *lse, const float *dout, float *dq, float *dk, float *dv,
                                   float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
                                   int n_heads, int n_kv_heads, int dim, int pos, double theta,
-                                  zt_stream_t stream) {
+                                  zt_stream_t stream, unsigned long long token) {
     g_last_error[0] = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
@@ -509,16 +621,21 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     if (check_rope_call(workspace, workspace_bytes, w.total_bytes, pos, theta)) return 1;
     if (need_device()) return 1;
     cudaStream_t s = (cudaStream_t)stream;
+    const bool kept = take_kept_planes(w.inner, token, batch, T, n_heads, n_kv_heads, dim, true, pos, theta);
+    if (token != 0 && !kept)
+        return refuse("token %llu is not the current one of this workspace for this shape, pos and theta: the planes "
+                      "it stood for are gone (pass 0 to convert q, k, v again).", token);
+    drop_kept_planes(w.inner);
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
-    if (launch_delta(out, dout, delta, (long long)batch * T * n_heads, dim, s)) return 1;
     bool fused = false, dq_in_kernel = false;
-    // (any note is consumed here: this call rewrites or reuses the planes)
-    const bool kept = take_kept_planes(w.inner, q, k, v, batch, T, n_heads, n_kv_heads, dim, s, true, pos, theta);
 #ifndef ZT_NO_TC
     fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
             tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);
     // the dQ kernel's epilogue rotates whole 16- or 32-column pieces: not at head_dim 96, whose halves are 48 wide
     dq_in_kernel = fused && dim != 96;
+    if (fused && launch_delta(out, dout, delta, tcb::bwd_workspace(w.inner, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).rnorm,
+                              (long long)batch * T * n_heads, dim, s))
+        return 1;
     if (fused && launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, w.inner, batch, T, n_heads, n_kv_heads, dim, s,
                                w.table, dq_in_kernel ? w.table_t : nullptr, kept))
         return 1;
@@ -526,7 +643,7 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     if (!fused) {
         if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
         if (launch_rope_apply(k, w.k_rot, w.table, batch, T, n_kv_heads * dim, dim, false, s)) return 1;
-        if (backward_impl(w.q_rot, w.k_rot, v, lse, delta, dout, dq, dk, dv, nullptr, 0, batch, T, n_heads, n_kv_heads, dim, s))
+        if (backward_impl(w.q_rot, w.k_rot, v, out, lse, delta, dout, dq, dk, dv, nullptr, 0, batch, T, n_heads, n_kv_heads, dim, s))
             return 1;
     }
     // the gradients of the unrotated q and k: R^T.  The tensor-core dQ kernel applies it as it writes dq; dk
@@ -618,7 +735,10 @@ int zt_attn_decode_static(const float *q, const float *k_cache, const float *v_c
 }
 
 int zt_attn_decode_status(const void *workspace, int *host_bad_sequences) {
-    if (!workspace || !host_bad_sequences) return refuse("a null pointer was passed.");
+    if (!host_bad_sequences) return refuse("a null pointer was passed.");
+    // a null workspace asks for the built-in scratch of zt_attn_decode_static on the current device
+    if (!workspace) workspace = static_scratch_address();
+    if (!workspace) return 1;
     if (cudaMemcpy(host_bad_sequences, workspace, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
         const cudaError_t e = cudaGetLastError();
         return refuse("reading the decode status failed: %s", cudaGetErrorString(e));

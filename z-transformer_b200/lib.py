@@ -32,10 +32,14 @@ _SIGNATURES = {
     "zt_attn_forward_batched": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
     "zt_attn_backward_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_backward_workspace_bytes": (_sz, [_i] * 5),
-    "zt_attn_forward_batched_keep": (_i, [_vp] * 6 + [_sz] + [_i] * 5 + [_vp]),
+    "zt_attn_forward_batched_keep": (_i, [_vp] * 6 + [_sz] + [_i] * 5 + [_vp, C.POINTER(C.c_ulonglong)]),
+    "zt_attn_backward_batched_kept": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp, C.c_ulonglong]),
+    "zt_attn_reserve": (_i, [_i] * 5),
+    "zt_attn_arena_bytes": (_sz, []),
+    "zt_attn_tc_saturated": (_i, [C.POINTER(C.c_uint)]),
     "zt_attn_rope_workspace_bytes": (_sz, [_i] * 5),
-    "zt_attn_forward_rope_batched": (_i, [_vp] * 6 + [_sz] + [_i] * 6 + [_d, _vp]),
-    "zt_attn_backward_rope_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 6 + [_d, _vp]),
+    "zt_attn_forward_rope_batched": (_i, [_vp] * 6 + [_sz] + [_i] * 6 + [_d, _vp, C.POINTER(C.c_ulonglong)]),
+    "zt_attn_backward_rope_batched": (_i, [_vp] * 11 + [_sz] + [_i] * 6 + [_d, _vp, C.c_ulonglong]),
     "zt_attn_decode": (_i, [_vp] * 7 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_decode_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_decode_static": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),
@@ -92,6 +96,14 @@ def tc_status() -> int:
     """0 unless a tensor-core kernel gave up on a bounded wait (synchronise first)."""
     v = C.c_int(0)
     if load().zt_attn_tc_status(C.byref(v)) != 0:
+        raise RuntimeError(last_error())
+    return v.value
+
+
+def tc_saturated() -> int:
+    """Backward thread blocks that met the bound on dS since the last call (synchronise first); 0 in a correct run."""
+    v = C.c_uint(0)
+    if load().zt_attn_tc_saturated(C.byref(v)) != 0:
         raise RuntimeError(last_error())
     return v.value
 

@@ -48,12 +48,14 @@ class BackwardWorkspace:
         self.shape = (batch, t, n_heads, n_kv_heads, head_dim)
         self.nbytes = int(_lib.load().zt_attn_backward_workspace_bytes(*self.shape))
         self.buf = torch.empty(max(self.nbytes, 16), dtype=torch.uint8, device=device)
+        self.token = 0  # of the planes the last forward(keep=self) left here; 0: none
 
 
 def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False, keep=None):
     """Batched attention.forward.  q [B, T, H*D] (or [T, H*D]); returns out (and lse [B, T, H]).
-    keep: a BackwardWorkspace of this shape; the backward that is given it next (same q, k, v, unchanged)
-    skips converting them again."""
+    keep: a BackwardWorkspace of this shape; the forward's operand planes of q, k, v are left in it, and a
+    backward given it with kept=True (the caller's word that q, k, v were not written in between) skips
+    converting them again."""
     import torch
     _head_config(n_heads, n_kv_heads, head_dim)
     squeeze = q.dim() == 2
@@ -73,10 +75,13 @@ def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False,
         raise DimensionMismatch("the workspace was sized for another shape")
     with torch.cuda.device(q.device):
         if keep is not None:
+            import ctypes
+            token = ctypes.c_ulonglong(0)
             rc = _lib.load().zt_attn_forward_batched_keep(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if want_lse else None,
                 keep.buf.data_ptr() if keep.nbytes else None, keep.nbytes, B, T, n_heads, n_kv_heads, head_dim,
-                _stream(q))
+                _stream(q), ctypes.byref(token))
+            keep.token = token.value
         else:
             rc = _lib.load().zt_attn_forward_batched(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
@@ -89,9 +94,11 @@ def attention_forward(q, k, v, n_heads, n_kv_heads, head_dim, *, want_lse=False,
     return (out, lse) if want_lse else out
 
 
-def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *, workspace=None):
+def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *, workspace=None, kept=False):
     """Batched autograd.attentionBackward from the forward's out and lse; returns dq, dk, dv.
-    workspace: a BackwardWorkspace of this shape (one is allocated per call otherwise)."""
+    workspace: a BackwardWorkspace of this shape (one is allocated per call otherwise).
+    kept: the workspace was the `keep` of the forward of these very q, k, v and they have not been written
+    since: the backward then uses the planes the forward left there (refused if they are gone)."""
     import torch
     _head_config(n_heads, n_kv_heads, head_dim)
     squeeze = q.dim() == 2
@@ -99,8 +106,8 @@ def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *
         q, k, v, out, lse, dout = q[None], k[None], v[None], out[None], lse[None], dout[None]
     _need_cuda_f32(q, k, v, out, lse, dout)
     B, T = q.shape[0], q.shape[1]
-    if (k.shape[1] != T or v.shape[1] != T or k.shape[2] != n_kv_heads * head_dim
-            or v.shape[2] != k.shape[2] or q.shape[2] != n_heads * head_dim):
+    if (k.shape[0] != B or v.shape[0] != B or k.shape[1] != T or v.shape[1] != T
+            or k.shape[2] != n_kv_heads * head_dim or v.shape[2] != k.shape[2] or q.shape[2] != n_heads * head_dim):
         raise DimensionMismatch("q/k/v shapes disagree with the head configuration")
     if dout.shape != q.shape or out.shape != q.shape or lse.shape != (B, T, n_heads):
         raise DimensionMismatch("dout/out/lse shapes disagree with q")
@@ -114,12 +121,17 @@ def attention_backward(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *
     else:
         ws_bytes = L.zt_attn_backward_workspace_bytes(B, T, n_heads, n_kv_heads, head_dim)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device) if ws_bytes else None
+    token = 0
+    if kept:
+        if workspace is None:
+            raise DimensionMismatch("kept=True needs the workspace the forward kept its planes in")
+        token, workspace.token = workspace.token, 0
     with torch.cuda.device(q.device):
-        rc = L.zt_attn_backward_batched(
+        rc = L.zt_attn_backward_batched_kept(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
             ws.data_ptr() if ws is not None else None, ws_bytes, B, T, n_heads, n_kv_heads, head_dim,
-            _stream(q))
+            _stream(q), token)
     if rc != 0:
         raise ConfigRefused(_lib.last_error())
     if squeeze:
@@ -140,6 +152,7 @@ class RopeWorkspace:
         if self.nbytes == 0:
             raise ConfigRefused("the shape is not admissible")
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.token = 0  # of the planes the last rope forward left here; 0: none
 
 
 def _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace):
@@ -166,19 +179,24 @@ def attention_forward_rope(q, k, v, n_heads, n_kv_heads, head_dim, *, pos=0, the
     B, T, workspace = _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace)
     out = torch.empty_like(q)
     lse = torch.empty((B, T, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
+    import ctypes
+    token = ctypes.c_ulonglong(0)
     with torch.cuda.device(q.device):
         rc = _lib.load().zt_attn_forward_rope_batched(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if want_lse else None,
-            workspace.buf.data_ptr(), workspace.nbytes, B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q))
+            workspace.buf.data_ptr(), workspace.nbytes, B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q),
+            ctypes.byref(token))
+    workspace.token = token.value
     if rc != 0:
         raise ConfigRefused(_lib.last_error())
     return (out, lse) if want_lse else out
 
 
 def attention_backward_rope(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_dim, *, pos=0, theta=ROPE_THETA,
-                            workspace=None):
+                            workspace=None, kept=False):
     """Gradients of the unrotated q and k (and of v): autograd.attentionBackward followed by
-    ropeBackward (src/autograd.zig:559-569,851-874)."""
+    ropeBackward (src/autograd.zig:559-569,851-874).  kept: as in attention_backward, for the workspace of the
+    rope forward of these q, k, v at this pos and theta."""
     import torch
     B, T, workspace = _rope_args(q, k, v, n_heads, n_kv_heads, head_dim, workspace)
     _need_cuda_f32(out, lse, dout)
@@ -186,11 +204,14 @@ def attention_backward_rope(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_d
         raise DimensionMismatch("dout/out/lse shapes disagree with q")
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty_like(lse)
+    token = 0
+    if kept:
+        token, workspace.token = workspace.token, 0
     with torch.cuda.device(q.device):
         rc = _lib.load().zt_attn_backward_rope_batched(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), workspace.buf.data_ptr(), workspace.nbytes,
-            B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q))
+            B, T, n_heads, n_kv_heads, head_dim, pos, theta, _stream(q), token)
     if rc != 0:
         raise ConfigRefused(_lib.last_error())
     return dq, dk, dv
@@ -231,6 +252,12 @@ def decode_attention(q, k_cache, v_cache, n_keys, n_heads, n_kv_heads, head_dim,
         workspace = DecodeWorkspace(B, n_ctx, n_heads, n_kv_heads, head_dim, q.device)
     if out is None:
         out = torch.empty_like(q)
+    else:
+        _need_cuda_f32(out)
+        if out.shape != q.shape or out.device != q.device:
+            raise DimensionMismatch("out must be a [B, H*D] tensor on q's device")
+    if k_cache.device != q.device or v_cache.device != q.device or n_keys.device != q.device:
+        raise DimensionMismatch("q, the caches and n_keys must live on one device")
     lse = torch.empty((B, n_heads), dtype=torch.float32, device=q.device) if want_lse else None
     with torch.cuda.device(q.device):
         rc = _lib.load().zt_attn_decode(
@@ -285,6 +312,7 @@ class AttnPipeline:
     def step(self, q, k, v, dout, out, dq, dk, dv, lse=None):
         """q, dout, out, dq: host [B, T, H*D]; k, v, dk, dv: host [B, T, Hkv*D]; lse: host [B, T, H] or
         None.  Reads q, k, v, dout and fills out, dq, dk, dv (and lse)."""
+        import ctypes
         import torch
         t, n_heads, n_kv_heads, head_dim = self.shape
         B = q.shape[0]
@@ -320,19 +348,20 @@ class AttnPipeline:
                     if b >= self.slots:
                         self.s_run.wait_event(self.free[sl])  # the slot's outputs have been read
                     st = self.s_run.cuda_stream
+                    token = ctypes.c_ulonglong(0)  # the slot's q, k, v stay untouched until its backward
                     rc = L.zt_attn_forward_batched_keep(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
                                                         d["out"].data_ptr(), d["lse"].data_ptr(),
                                                         d["ws"].data_ptr() if self.ws_bytes else None, self.ws_bytes,
-                                                        1, t, n_heads, n_kv_heads, head_dim, st)
+                                                        1, t, n_heads, n_kv_heads, head_dim, st, ctypes.byref(token))
                     self.done_f[sl].record(self.s_run)
                     self.s_run.wait_event(self.ready_b[sl])
                     if rc == 0:
-                        rc = L.zt_attn_backward_batched(
+                        rc = L.zt_attn_backward_batched_kept(
                             d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["out"].data_ptr(),
                             d["lse"].data_ptr(), d["dout"].data_ptr(), d["dq"].data_ptr(), d["dk"].data_ptr(),
                             d["dv"].data_ptr(), d["delta"].data_ptr(),
                             d["ws"].data_ptr() if self.ws_bytes else None, self.ws_bytes, 1, t, n_heads,
-                            n_kv_heads, head_dim, st)
+                            n_kv_heads, head_dim, st, token.value)
                     if rc != 0:
                         torch.cuda.synchronize(self.device)
                         raise ConfigRefused(_lib.last_error())
