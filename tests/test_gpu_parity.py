@@ -391,6 +391,8 @@ def test_refused_call_touches_nothing(zt, dev):
 TC_SHAPES = [  # B, T, H, Hkv, D -- multiples of the tiles, tails, one tile, several key tiles
     (1, 128, 4, 2, 32), (2, 129, 4, 2, 64), (1, 200, 8, 2, 128), (2, 256, 4, 4, 128), (1, 321, 6, 3, 64),
     (1, 384, 4, 1, 32), (1, 640, 8, 8, 128), (2, 513, 4, 2, 128), (1, 200, 8, 2, 96), (2, 384, 4, 4, 96),
+    # head_dim 256, and 192 zero-padded to it: one head per CTA, K fetched block by block (forward only)
+    (1, 128, 2, 1, 256), (2, 200, 4, 2, 192), (1, 513, 4, 1, 256), (1, 320, 3, 3, 192), (2, 704, 4, 2, 256),
 ]
 
 
@@ -410,7 +412,7 @@ def test_tensor_core_forward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, pa
         zt.lib.load().zt_attn_set_path(0)
     torch.cuda.synchronize()
     # (the 3xTF32 kernel has no padded-head form: head_dim 96 goes to the CUDA cores when it is asked for)
-    assert zt.lib.last_path() == ("simt" if (path == 2 and D == 96) else "tcgen05")
+    assert zt.lib.last_path() == ("simt" if (path == 2 and D in (96, 192, 256)) else "tcgen05")
     assert zt.lib.tc_status() == 0
     for b in range(B):
         ro, rl = oracle.attention_forward(q[b], k[b], v[b], H, Hkv, D, want_lse=True, threads=8)

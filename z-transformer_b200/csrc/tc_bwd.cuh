@@ -1304,7 +1304,7 @@ inline int launch_bwd_tc_d(const BwdMaps &m, const BwdParams &p, cudaStream_t st
 // zero-padded to the tile's width (at 32 the MMAs would cost the same at half the width, see the clock floor
 // above; at 96 a quarter of the tensor work is padding), outputs keep their own width.  The kernels write
 // their outputs in 32-column (128-wide tiles) or 16/32-column (64-wide) pieces, which is why only these two.
-inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : (dim == 96 ? 128 : dim); }
+inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : (dim == 96 ? 128 : (dim == 192 ? 256 : dim)); }
 
 inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).total_bytes;

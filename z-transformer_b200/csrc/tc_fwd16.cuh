@@ -440,6 +440,9 @@ inline int launch_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUte
     return ZT_LAUNCH("attn_fwd_tc16", stream, (attn_fwd_tc16<D><<<grid, kThreads, smem, stream>>>(kmap, vmap, qmap, p)));
 }
 
+// (tc_fwd16x.cuh)
+inline int launch_x(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
+                    cudaStream_t stream);
 // (tc_fwd16g.cuh)
 template <int D>
 inline int launch_g_d(const CUtensorMap &kmap, const CUtensorMap &vmap, const CUtensorMap &qmap, const Params &p,
@@ -453,7 +456,9 @@ inline size_t tc_fwd16_workspace_bytes(int batch, int T, int n_heads, int n_kv_h
 
 inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_keys, const void *q, const void *k,
                                const void *v, const void *out) {
-    if (!(dim == 32 || dim == 64 || dim == 96 || dim == 128) || q_offset != 0 || n_keys != T || T < 128 || batch < 1) return false;
+    if (!(dim == 32 || dim == 64 || dim == 96 || dim == 128 || dim == 192 || dim == 256) || q_offset != 0 || n_keys != T ||
+        T < 128 || batch < 1)
+        return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(q) || !al(k) || !al(v) || !al(out)) return false;
     const DeviceInfo *d = device_info();
@@ -487,6 +492,22 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     pa.t[1] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
     pa.t[2] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
     if (launch_prepass(pa, stream)) return 1;
+    if (td == 256) {
+        // head_dim 256 (and 192 padded to it): one head per CTA, K fetched block by block (attn_fwd_tc16x)
+        CUtensorMap kmap, vmap, qmap;
+        if (!make_half_tile_map(&kmap, w.k_planes, 2 * batch, T, wkv, 64, 64) ||
+            !make_half_tile_map(&vmap, w.v_planes, 2 * batch, T, wkv, td, 64) ||
+            !make_half_tile_map(&qmap, w.q_planes, 2 * batch, T, n_heads * td, td, 128))
+            return refuse("the TMA tensor maps for the forward could not be encoded.");
+        tcf16::Params p{};
+        p.q_planes = w.q_planes, p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v;
+        p.out = out, p.lse = lse;
+        p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+        p.dim_out = dim;
+        p.scale_log2 = kLog2e / sqrtf((float)dim);
+        g_last_path = "tcgen05";
+        return tcf16::launch_x(kmap, vmap, qmap, p, stream);
+    }
     // variant 0: two heads of a KV group per CTA (attn_fwd_tc16g) when the group has an even number of query heads
     // and that still gives every SM a CTA, one head per CTA (attn_fwd_tc16) otherwise; 1: one head per CTA;
     // 2: two heads per CTA whatever the number of CTAs (the group must be even).

@@ -18,6 +18,7 @@
 #include "tc_fwd.cuh"
 #include "tc_fwd16.cuh"
 #include "tc_fwd16g.cuh"
+#include "tc_fwd16x.cuh"
 #endif
 
 #include <mutex>
