@@ -36,8 +36,19 @@ TWIN_SHAPES = (
 SEEDS = {"q": 0xBEEF, "k": 0x1234, "v": 0x5678, "dout": 0x9ABC}
 
 
-def write_twin_dir(path: str, shapes=TWIN_SHAPES, threads: int = 0) -> list[str]:
-    """Writes manifest.tsv and the eight blobs of every shape into `path`; returns the tags."""
+def rising_scores(q, k, v, dout, head_dim):
+    """A transform for write_twin_dir: every score grows with the key's position, by more than 2^8 from one
+    64-key tile to the next (q shifted to positive values, k[s] raised in proportion to s).  A forward that
+    moves its running maximum lazily moves it in every tile on such data, which is what a negative control for
+    the maximum's correction needs; on the reference's own fill the maximum settles in the first tile."""
+    step = 12.0 / (64.0 * head_dim ** 0.5 * 1.4427)  # per key: 12 in log2 units per 64 keys at mean(q) = 1
+    rise = (np.arange(k.shape[0], dtype=np.float32) * np.float32(step))[:, None]
+    return q + np.float32(1.0), k + rise, v, dout
+
+
+def write_twin_dir(path: str, shapes=TWIN_SHAPES, threads: int = 0, transform=None) -> list[str]:
+    """Writes manifest.tsv and the eight blobs of every shape into `path`; returns the tags.
+    transform(q, k, v, dout, head_dim) -> (q, k, v, dout), when given, reshapes the reference's fill."""
     os.makedirs(path, exist_ok=True)
     threads = threads or max(1, len(os.sched_getaffinity(0)))
     rows = []
@@ -46,6 +57,8 @@ def write_twin_dir(path: str, shapes=TWIN_SHAPES, threads: int = 0) -> list[str]
         k = oracle.fill_lcg(T * Hkv * D, SEEDS["k"]).reshape(T, Hkv * D)
         v = oracle.fill_lcg(T * Hkv * D, SEEDS["v"]).reshape(T, Hkv * D)
         dout = oracle.fill_lcg(T * H * D, SEEDS["dout"]).reshape(T, H * D)
+        if transform is not None:
+            q, k, v, dout = (np.ascontiguousarray(x, dtype=np.float32) for x in transform(q, k, v, dout, D))
         best = float("inf")
         y = None
         for _ in range(3):

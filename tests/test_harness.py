@@ -96,3 +96,62 @@ def test_harness_scale_relative_gate_at_training_scale(twin_dir):
     assert "of max |ref|" in r.stdout
     r = run([twin_dir], ZT_HARNESS_DOUT_SCALE="1e-5", ZT_HARNESS_BWD_BROKEN="3")
     assert r.returncode == 1
+
+
+DEFECTS_HARNESS = os.path.join(ROOT, "z-transformer_b200", "zt_attn_harness_defects")
+
+
+def run_defects(args, **env):
+    e = dict(os.environ)
+    e.update(env)
+    return subprocess.run([DEFECTS_HARNESS, *args], capture_output=True, text=True, env=e, timeout=600)
+
+
+@pytest.mark.gpu
+def test_defects_compiled_into_the_kernels_are_caught(twin_dir):
+    """The reference compiles defects into its kernels and requires its gates to fail on each of them
+    (src/cuda/attn_kernels.cu:150-158,592-599,622-624; src/cuda/run-attn.sh:126-177).  The same here, for the
+    defects that live inside a kernel and cannot be imitated through the ABI: a dropped causal mask and a skipped
+    running-maximum correction in the forward (CUDA-core and tensor-core kernels alike), a dropped mask and a dropped
+    softmax Jacobian in the backward.  The switches exist only in the library built with -DZT_DEFECTS, which only
+    this harness binary links; with the switch at 0 that build passes every gate."""
+    assert os.path.exists(DEFECTS_HARNESS), "build the library first"
+    good = run_defects([twin_dir], ZT_HARNESS_KERNEL_DEFECT="0")
+    assert good.returncode == 0, good.stdout + good.stderr
+
+    def fwd_failures(out):
+        table = out.split("backward against")[0]
+        return len(re.findall(r"FAIL", table))
+
+    def signature(out):
+        m = re.search(r"max_abs_dq.*\n\s+ctx256\s+(\S+)\s+(\S+)\s+(\S+)", out)
+        return m.groups()
+
+    r = run_defects([twin_dir], ZT_HARNESS_KERNEL_DEFECT="1")
+    assert r.returncode == 1, f"the dropped causal mask inside the kernels passed the gate\n{r.stdout}"
+    assert "switched on" in r.stdout
+    # The running maximum: these kernels move it lazily (only when it grows by more than 2^8), so on the reference's
+    # fill, whose maximum settles in the first tile, there is no correction to skip.  A directory whose scores rise
+    # with the key position makes every tile move it: correct kernel passes, the defect fails.
+    import zt_twin
+    rising = twin_dir + "-rising"
+    zt_twin.write_twin_dir(rising, (("rise-32-T512", 512, 4, 2, 32, 5), ("rise-128-T256", 256, 8, 2, 128, 5),
+                                    ("rise-256-T256", 256, 2, 1, 256, 5), ("rise-64-T100", 100, 4, 2, 64, 5)),
+                           transform=zt_twin.rising_scores)
+    # (gradients on this data are a few units, not the 0.03 the backward's absolute gate was calibrated on: the
+    # backward is graded relative to max |ref| here, which ZT_HARNESS_DOUT_SCALE switches on)
+    r = run_defects([rising], ZT_HARNESS_KERNEL_DEFECT="0", ZT_HARNESS_DOUT_SCALE="0.5")
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = run_defects([rising], ZT_HARNESS_KERNEL_DEFECT="3", ZT_HARNESS_DOUT_SCALE="0.5")
+    assert r.returncode == 1, f"the skipped running-maximum correction passed the gate\n{r.stdout}"
+    assert fwd_failures(r.stdout) == 4, r.stdout  # tensor-core kernels (three widths) and the CUDA-core one
+    sigs = {}
+    for defect in ("11", "13"):
+        r = run_defects([twin_dir], ZT_HARNESS_KERNEL_DEFECT=defect)
+        assert r.returncode == 1, f"backward defect {defect} inside the kernels passed the gate\n{r.stdout}"
+        sigs[defect] = signature(r.stdout)
+    assert sigs["11"] != sigs["13"]
+    assert sigs["13"][2] == signature(good.stdout)[2], "dropping the Jacobian must not touch dv"
+    # the shipped library has no such switch: its harness refuses the request instead of pretending
+    assert run([twin_dir], ZT_HARNESS_KERNEL_DEFECT="1").returncode == 2
+    assert run_defects([twin_dir], ZT_HARNESS_KERNEL_DEFECT="5").returncode == 2

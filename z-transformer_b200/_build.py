@@ -10,6 +10,9 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libztattn.so")
 HOST_LIB_PATH = os.path.join(HERE, "libzthost.so")
 HARNESS_PATH = os.path.join(HERE, "zt_attn_harness")
+# the negative-control build: the same sources with defect switches compiled into the kernels (-DZT_DEFECTS)
+DEFECTS_LIB_PATH = os.path.join(HERE, "libztattn_defects.so")
+DEFECTS_HARNESS_PATH = os.path.join(HERE, "zt_attn_harness_defects")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]
@@ -55,8 +58,16 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if os.path.exists(harness_src) and (force or _stale(HARNESS_PATH, srcs)):
         # the twin-directory harness: a host program over the C ABI (csrc/zt_harness.cpp)
         cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-Wall", "-o", HARNESS_PATH, harness_src,
-               "-L" + HERE, "-lztattn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+               "-L" + HERE, "-lztattn", "-ldl", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
         subprocess.check_call(cmd)
+    if os.path.exists(harness_src) and (force or _stale(DEFECTS_HARNESS_PATH, srcs)):
+        # the library once more with the in-kernel defect switches, and the harness linked against THAT one;
+        # nothing else ever loads it
+        subprocess.check_call([_nvcc(), *NVCC_FLAGS, "-DZT_DEFECTS", "-o", DEFECTS_LIB_PATH,
+                               os.path.join(CSRC, "zt_attn.cu"), "-lcuda"])
+        subprocess.check_call([_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-Wall", "-o", DEFECTS_HARNESS_PATH,
+                               harness_src, "-L" + HERE, "-lztattn_defects", "-ldl", "-Xlinker", "-rpath", "-Xlinker",
+                               "$ORIGIN"])
     return LIB_PATH
 
 

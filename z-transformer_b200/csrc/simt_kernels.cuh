@@ -150,14 +150,14 @@ __global__ void __launch_bounds__(kSimtThreads) attn_fwd_simt(const SimtFwdParam
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = s0 + cg + 8 * i;
-            s[i] = (key <= pos && key < n_keys) ? s[i] * p.scale_log2 : -INFINITY;
+            s[i] = ((key <= pos || ZT_DEFECT(1)) && key < n_keys) ? s[i] * p.scale_log2 : -INFINITY;
             tmax = fmaxf(tmax, s[i]);
         }
         tmax = row_max8(tmax);
         const float m_new = fmaxf(m, tmax);
         // A row with nothing visible yet keeps m = -inf; exp2(-inf - -inf) is NaN, so
         // both factors are forced to zero in that case.
-        const float corr = (m_new == -INFINITY) ? 0.f : ex2(m - m_new);
+        const float corr = (m_new == -INFINITY) ? 0.f : ((ZT_DEFECT(3) && m != -INFINITY) ? 1.f : ex2(m - m_new));
         float psum = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt(const SimtBwdPa
     const int t = t0 + r;
     const int tc = t < p.T ? t : p.T - 1;
     const float lse2 = p.lse[b * p.lse_batch_stride + (long long)tc * p.n_heads + h] * kLog2e;
-    const float del = p.delta[b * p.lse_batch_stride + (long long)tc * p.n_heads + h];
+    const float del = ZT_DEFECT(13) ? 0.f : p.delta[b * p.lse_batch_stride + (long long)tc * p.n_heads + h];
     const int last_key = t0 + kTile < p.T ? t0 + kTile : p.T;
 
     float acc[kMaxColsPerThread];
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dq_simt(const SimtBwdPa
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = s0 + cg + 8 * i;
-            const float pe = (key <= t && key < p.T) ? ex2(s[i] * p.scale_log2 - lse2) : 0.f;
+            const float pe = ((key <= t || ZT_DEFECT(11)) && key < p.T) ? ex2(s[i] * p.scale_log2 - lse2) : 0.f;
             sS[r * (kTile + 1) + cg + 8 * i] = pe * (dp[i] - del);
         }
         __syncwarp();
@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkdv_simt(const SimtBwd
                 int t = t0 + threadIdx.x;
                 t = t < p.T ? t : p.T - 1;
                 sL[threadIdx.x] = lse[(long long)t * p.n_heads + h] * kLog2e;
-                sD[threadIdx.x] = delta[(long long)t * p.n_heads + h];
+                sD[threadIdx.x] = ZT_DEFECT(13) ? 0.f : delta[(long long)t * p.n_heads + h];
             }
             __syncthreads();
             float st[4], dpt[4];
@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(kSimtThreads) attn_bwd_dkdv_simt(const SimtBwd
             for (int i = 0; i < 4; ++i) {
                 const int rr = cg + 8 * i, t = t0 + rr;
                 const float pe =
-                    (key <= t && t < p.T && key < p.T) ? ex2(st[i] * p.scale_log2 - sL[rr]) : 0.f;
+                    ((key <= t || ZT_DEFECT(11)) && t < p.T && key < p.T) ? ex2(st[i] * p.scale_log2 - sL[rr]) : 0.f;
                 sP[kk * (kTile + 1) + rr] = pe;
                 sS[kk * (kTile + 1) + rr] = pe * (dpt[i] - sD[rr]);
             }

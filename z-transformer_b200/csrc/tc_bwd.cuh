@@ -696,7 +696,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             const int t = w.qi * BQ + tid;
             if (t >= p.T) return 0.f;
             const long long idx = ((long long)b * p.T + t) * p.n_heads + g * group + w.hh;
-            return set == 0 ? __ldg(p.lse + idx) * kLog2e - lse_shift : __ldg(p.delta + idx) * dfac;
+            return set == 0 ? __ldg(p.lse + idx) * kLog2e - lse_shift : (ZT_DEFECT(13) ? 0.f : __ldg(p.delta + idx) * dfac);
         };
         auto publish = [&](int it, float v) {
             if (threadIdx.x < 256 && tid < 64) (set == 0 ? sh->lse2 : sh->dels)[it & 1][tid] = v;
@@ -789,7 +789,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 // a step whose 64 query rows all lie past the tile's last key and inside the sequence needs no
                 // mask (most steps of a long sequence); the test is the same for every thread of the CTA
                 const int q_first = walk.qi * BQ;
-                if (q_first >= s0 + 127 && q_first + BQ <= p.T && s0 + 128 <= p.T) {
+                if ((q_first >= s0 + 127 || ZT_DEFECT(11)) && q_first + BQ <= p.T && s0 + 128 <= p.T) {
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
 #pragma unroll
@@ -803,7 +803,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
                             const int t = t0 + i + e;
-                            const bool vis = (key <= t) && (t < p.T) && (key < p.T);
+                            const bool vis = (key <= t || ZT_DEFECT(11)) && (t < p.T) && (key < p.T);
                             const float pe = ex2(__uint_as_float(rs[i + e]) * cs - sh->lse2[it & 1][set * 16 + i + e]);
                             pr[i + e] = vis ? pe : 0.f;
                         }
@@ -1099,7 +1099,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         // this row's scale: |dS| <= 2 |dout[t]| max |v[s]| (a shade more: P may round to just above 1) goes below 2^14
         const float cq = (t < p.T) ? pow2_for(2.02f * __ldg(p.rnorm + ridx) * __uint_as_float(p.vnmax[b * p.n_kv_heads + g]), 14) : 1.0f;
         const float c1 = cq / (mdo * mv);
-        const float dels = (t < p.T) ? __ldg(p.delta + ridx) * cq : 0.f;
+        const float dels = (t < p.T && !ZT_DEFECT(13)) ? __ldg(p.delta + ridx) * cq : 0.f;
         float ds_top = 0.f;  // largest |dS| of this thread, in the row's units
         bool saturated = false;  // a dS value of this thread met kDsBound (or was not a number)
         for (int j = 0; ok && j < n_tiles; ++j) {
@@ -1118,7 +1118,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             uint32_t dh[8], dl[8];
             const int key0 = j * BN + set * 16;
             // a key tile that ends before the query tile begins needs no mask; the same test for the whole CTA
-            if (j * BN + BN - 1 <= t0 && j * BN + BN <= p.T) {
+            if ((j * BN + BN - 1 <= t0 || ZT_DEFECT(11)) && j * BN + BN <= p.T) {
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
                     float dv[2];
@@ -1140,7 +1140,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = key0 + i + e;
-                        const bool vis = (key <= t) && (key < p.T);
+                        const bool vis = (key <= t || ZT_DEFECT(11)) && (key < p.T);
                         const float pe = ex2(__uint_as_float(rs[i + e]) * cs - lse2);
                         const float x = vis ? pe * (__uint_as_float(rd[i + e]) * c1 - dels) : 0.f;
                         const float ax = fabsf(x);

@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tc_fence_after();
             const int s0 = j * BN;
-            const bool diag = (s0 + BN - 1 > t0);
+            const bool diag = (s0 + BN - 1 > t0) && !ZT_DEFECT(1);
             uint32_t r0[32], r1[32];
             tmem_ld32(tmem + lane_base + cS, r0);
             tmem_ld32(tmem + lane_base + cS + 32, r1);
@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 factor = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - mt);
                 m_ref = mt;
             }
+            if (ZT_DEFECT(3) && j > 0) factor = 1.f;
             l *= factor;
             if (j > 1 && __any_sync(0xffffffffu, factor != 1.f)) {
                 // this set's O may only be touched once its previous P.V (tile j-2) has retired

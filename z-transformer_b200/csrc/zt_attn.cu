@@ -338,6 +338,18 @@ int zt_attn_reserve(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     return 0;
 }
 
+#ifdef ZT_DEFECTS
+// Only in the harness build: selects the defect the kernels compute with (zt_common.cuh); 0 is the correct kernel.
+int zt_attn_set_defect(int defect) {
+    if (need_device()) return 1;
+    if (cudaMemcpyToSymbol(g_defect, &defect, sizeof(int)) != cudaSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        return refuse("setting the defect failed: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+#endif
+
 size_t zt_attn_arena_bytes(void) {
     size_t held = 0;
     device_arena(0, nullptr, nullptr, &held);

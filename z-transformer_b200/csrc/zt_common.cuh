@@ -129,6 +129,24 @@ inline int optin_smem(const void *fn, size_t bytes) {
                   cudaGetErrorString(e));
 }
 
+// ---- in-kernel negative controls (the harness build only) ---------------------------------------
+// The reference compiles defects into its kernels as template variants and requires its parity gates
+// to catch every one of them (src/cuda/attn_kernels.cu:150-158,592-599,622-624; src/cuda/run-attn.sh:126-177).
+// The same here, for the defects that live INSIDE a kernel: built with -DZT_DEFECTS the kernels consult a
+// device word that zt_attn_set_defect writes; every defect computes wrong numbers from valid addresses.
+//   1  the causal mask is dropped in the forward (a query reads the keys after it in its diagonal tiles)
+//   3  the forward's running-maximum correction is skipped (sum and accumulator are never rescaled)
+//   11 the causal mask is dropped in the backward
+//   13 the softmax Jacobian is dropped in the backward (dS = P dP)
+// The shipped library is built without the macro: ZT_DEFECT(n) is then the constant false and no kernel
+// carries a switch.
+#ifdef ZT_DEFECTS
+static __device__ int g_defect;
+#define ZT_DEFECT(n) (g_defect == (n))
+#else
+#define ZT_DEFECT(n) false
+#endif
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 

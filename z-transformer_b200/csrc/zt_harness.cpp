@@ -24,6 +24,11 @@
 //                 3 the softmax Jacobian dropped (delta = 0: the batched backward is handed out = 0);
 //                   dv must then read exactly as in the correct run, dq and dk must not
 //                 4 the scale dropped
+//   * ZT_HARNESS_KERNEL_DEFECT=1|3|11|13 (only in zt_attn_harness_defects, which links the library built with
+//     -DZT_DEFECTS) switches on a defect compiled INTO the kernels, as the reference's ATTN_BROKEN template variants
+//     are (src/cuda/attn_kernels.cu:150-158,592-599,622-624): 1 the forward's causal mask dropped, 3 its
+//     running-maximum correction skipped, 11 the backward's causal mask dropped, 13 its softmax Jacobian dropped.
+//     Each must fail a gate; 13 must leave dv exactly right.
 //   * ZT_HARNESS_DOUT_SCALE=<x> multiplies dout (and, the backward being linear in it, the reference
 //     gradients) by x before the run and replaces the backward's absolute gate by a scale-relative one,
 //     max |got - ref| <= 1e-4 max |ref| per tensor (attn_rel_tol, src/train.zig:706).  The absolute
@@ -32,6 +37,7 @@
 // `--list <dir>` parses the manifest and checks every blob's size without touching the GPU.
 // Exit status: 0 all gates passed, 1 a gate failed or a file was unreadable, 2 usage.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <cmath>
@@ -179,6 +185,21 @@ int run(const std::string &dir) {
             return 2;
         }
         printf("harness: dout and the reference gradients scaled by %g; the backward gate is %.0e of max |ref|\n", dout_scale, kRelTol);
+    }
+    if (const char *e = getenv("ZT_HARNESS_KERNEL_DEFECT")) {
+        // a defect INSIDE the kernels: only a library built with -DZT_DEFECTS has the switch
+        typedef int (*set_defect_fn)(int);
+        set_defect_fn set_defect = reinterpret_cast<set_defect_fn>(dlsym(RTLD_DEFAULT, "zt_attn_set_defect"));
+        const int defect = atoi(e);
+        if (!set_defect) {
+            fprintf(stderr, "harness: ZT_HARNESS_KERNEL_DEFECT needs the defects build of the library (zt_attn_harness_defects)\n");
+            return 2;
+        }
+        if (!(defect == 0 || defect == 1 || defect == 3 || defect == 11 || defect == 13) || set_defect(defect) != 0) {
+            fprintf(stderr, "harness: ZT_HARNESS_KERNEL_DEFECT=%s is not a defect the kernels have (0, 1, 3, 11, 13)\n", e);
+            return 2;
+        }
+        if (defect) printf("harness: defect %d compiled into the kernels is switched on; a gate must fail\n", defect);
     }
     const bool relative_gate = dout_scale != 1.0;
     std::vector<FwdRow> frows(n);
