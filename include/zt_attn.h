@@ -199,6 +199,24 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
                                   int n_heads, int n_kv_heads, int dim, int pos, double theta,
                                   zt_stream_t stream, unsigned long long token);
 
+/* The projection on the output side of attention, y = ctx . wo (tensor.matmul(ctx, l.wo), src/model.zig:396;
+ * src/tensor.zig:78-106), for `batch` sequences of T rows: ctx [batch, T, k], wo [k, n] row-major, y [batch, T, n].
+ * On the tensor cores with the attention kernels' three-term f16 split (f32-class accuracy, f32 accumulation).
+ * The reference reduces in f32 in ascending k, so two correct implementations differ by f32 rounding of a
+ * k-term sum; tests gate max |got - ref| <= 1e-4 max |ref| (src/train.zig:706) rather than element-wise.
+ *   zt_proj_forward   y is assigned.
+ *   zt_proj_backward  the two gradients of that product (src/autograd.zig:553-557): dctx = dy . wo^T is assigned
+ *                     (inputGrad, :999-1022); dwo += ctx^T . dy is ACCUMULATED into the caller's dwo, as
+ *                     weightGrad accumulates into the layer's gradient (:958-972) -- zero it for a fresh one.
+ * Both take a caller workspace of zt_proj_workspace_bytes(batch, T, k, n) bytes (256-byte aligned) and allocate
+ * nothing.  Refusals: batch or T < 1; k or n not a multiple of 64 (there is no CUDA-core form of these calls);
+ * a missing, short or misaligned workspace; a device that is not sm_100. */
+size_t zt_proj_workspace_bytes(int batch, int T, int k, int n);
+int zt_proj_forward(const float *ctx, const float *wo, float *y, void *workspace, size_t workspace_bytes, int batch,
+                    int T, int k, int n, zt_stream_t stream);
+int zt_proj_backward(const float *ctx, const float *wo, const float *dy, float *dctx, float *dwo, void *workspace,
+                     size_t workspace_bytes, int batch, int T, int k, int n, zt_stream_t stream);
+
 /* KV-cache decode attention for a batch of sequences: decode.attnStep
  * (src/decode.zig:326-392) for every sequence at once, over device-resident
  * caches laid out as kv_cache.Layer lays them out (src/kv_cache.zig:60-95):

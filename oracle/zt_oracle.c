@@ -11,6 +11,8 @@
  *   src/autograd.zig:636-842   attentionBackward-> zto_attention_backward
  *   src/decode.zig:326-392     attnStep         -> zto_attn_step
  *   src/kv_cache.zig:60-135    Layer            -> zto_layer_*
+ *   src/tensor.zig:78-106      matmul           -> zto_matmul
+ *   src/autograd.zig:958-1022  weightGrad, inputGrad -> zto_weight_grad, zto_input_grad
  *   src/cuda/device.zig:162-182,489-501  bytesFor/toCInt/forwardBounds
  *                                               -> zto_bytes_for / zto_forward_bounds
  *
@@ -570,6 +572,61 @@ int zto_backward_window(const float *q, const float *k, const float *v, const fl
     }
     free(stats);
     return failed ? ZTO_OUT_OF_MEMORY : ZTO_OK;
+}
+
+/* ---- the projection on the output side of attention -------------------------------------------- */
+
+/*
+ * tensor.matmul (src/tensor.zig:78-106): out[i, j] = sum_k a[i, k] * b[k, j], every element its own f32
+ * accumulator over ascending k (the reference's eight lanes are never added to one another, so the scalar
+ * loop below rounds where it does).  model.zig:396 calls it as matmul(ctx, l.wo).
+ */
+int zto_matmul(const float *a, size_t a_rows, size_t a_cols, const float *b, size_t b_rows, size_t b_cols,
+               float *out, int threads) {
+    if (a_cols != b_rows) return ZTO_DIMENSION_MISMATCH;
+    if (threads < 1) threads = 1;
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long i = 0; i < (long)a_rows; ++i)
+        for (size_t j = 0; j < b_cols; ++j) {
+            float acc = 0.0f;
+            for (size_t k = 0; k < a_cols; ++k) acc += a[(size_t)i * a_cols + k] * b[k * b_cols + j];
+            out[(size_t)i * b_cols + j] = acc;
+        }
+    return ZTO_OK;
+}
+
+/*
+ * inputGrad (src/autograd.zig:999-1022): out[t, i] += sum_j dout[t, j] * w[i, j], the sum in an f32
+ * accumulator over ascending j, added to out once.
+ */
+int zto_input_grad(float *out, const float *dout, size_t rows, size_t dout_cols, const float *w, size_t w_rows,
+                   size_t w_cols, int threads) {
+    if (dout_cols != w_cols) return ZTO_DIMENSION_MISMATCH;
+    if (threads < 1) threads = 1;
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long t = 0; t < (long)rows; ++t)
+        for (size_t i = 0; i < w_rows; ++i) {
+            float acc = 0.0f;
+            for (size_t j = 0; j < w_cols; ++j) acc += dout[(size_t)t * dout_cols + j] * w[i * w_cols + j];
+            out[(size_t)t * w_rows + i] += acc;
+        }
+    return ZTO_OK;
+}
+
+/*
+ * weightGrad (src/autograd.zig:958-972): w[i, j] += input[t, i] * dout[t, j] for t ascending -- an f32
+ * read-modify-write per term, into whatever w already holds.
+ */
+int zto_weight_grad(float *w, const float *input, size_t rows, size_t in_cols, const float *dout, size_t dout_cols,
+                    int threads) {
+    if (threads < 1) threads = 1;
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long i = 0; i < (long)in_cols; ++i)
+        for (size_t t = 0; t < rows; ++t) {
+            const float scale = input[t * in_cols + (size_t)i];
+            for (size_t j = 0; j < dout_cols; ++j) w[(size_t)i * dout_cols + j] += scale * dout[t * dout_cols + j];
+        }
+    return ZTO_OK;
 }
 
 /* ---- kv_cache.Layer (src/kv_cache.zig:60-135), storage semantics only ------ */

@@ -77,6 +77,9 @@ def lib():
                                                          _fp, _fp, _fp]
         _lib.zto_backward_window.argtypes = [_fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, C.POINTER(_sz), _sz, _sz,
                                              _fp, _fp, _fp, C.c_int]
+        _lib.zto_matmul.argtypes = [_fp, _sz, _sz, _fp, _sz, _sz, _fp, C.c_int]
+        _lib.zto_input_grad.argtypes = [_fp, _fp, _sz, _sz, _fp, _sz, _sz, C.c_int]
+        _lib.zto_weight_grad.argtypes = [_fp, _fp, _sz, _sz, _fp, _sz, C.c_int]
         _lib.zto_attention_forward_rows.argtypes = [_fp, _fp, _fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz,
                                                     _sz, _sz]
         _lib.zto_sampled_step.argtypes = [_fp] * 8 + [_sz] * 7 + [C.c_int, C.c_int,
@@ -252,6 +255,31 @@ def attn_step_raw(q, k_cache, v_cache, n_keys, n_heads, n_kv_heads, head_dim, *,
                                v_cache.shape[1], n_keys, n_heads, n_kv_heads, head_dim, _p(out),
                                _p(lse), threads))
     return out, lse
+
+
+def matmul(a, b, *, threads=1) -> np.ndarray:
+    """tensor.matmul (src/tensor.zig:78-106): f32 accumulation over ascending k."""
+    a, b = _2d(a), _2d(b)
+    out = np.zeros((a.shape[0], b.shape[1]), dtype=np.float32)
+    _check(lib().zto_matmul(_p(a), a.shape[0], a.shape[1], _p(b), b.shape[0], b.shape[1], _p(out), threads))
+    return out
+
+
+def input_grad(dout, w, *, out=None, threads=1) -> np.ndarray:
+    """inputGrad (src/autograd.zig:999-1022): out += dout . w^T; a fresh zero tensor when out is None."""
+    dout, w = _2d(dout), _2d(w)
+    if out is None:
+        out = np.zeros((dout.shape[0], w.shape[0]), dtype=np.float32)
+    _check(lib().zto_input_grad(_p(out), _p(dout), dout.shape[0], dout.shape[1], _p(w), w.shape[0], w.shape[1], threads))
+    return out
+
+
+def weight_grad(w_grad, inp, dout, *, threads=1) -> np.ndarray:
+    """weightGrad (src/autograd.zig:958-972): w_grad += inp^T . dout, in place, rows in ascending order."""
+    inp, dout = _2d(inp), _2d(dout)
+    assert w_grad.dtype == np.float32 and w_grad.flags.c_contiguous and w_grad.shape == (inp.shape[1], dout.shape[1])
+    _check(lib().zto_weight_grad(_p(w_grad), _p(inp), inp.shape[0], inp.shape[1], _p(dout), dout.shape[1], threads))
+    return w_grad
 
 
 KIND_QUERY_HEADED, KIND_KV_HEADED, KIND_PER_ROW = 0, 1, 2

@@ -1,0 +1,133 @@
+"""The projection on the output side of attention and the attention block step, through the C ABI, against the
+oracle's restatements of tensor.matmul (src/tensor.zig:78-106), inputGrad / weightGrad (src/autograd.zig:958-1022)
+and the block's call order (src/model.zig:372-396, src/autograd.zig:553-569).
+
+Gate: the reference reduces a projection in f32 in ascending k, so two correct implementations differ by the f32
+rounding of a k-term sum, which no element-wise bar of 1e-4 of |ref| survives where ref is small.  The reference's
+own gate for tensors downstream of such sums is relative to the tensor's largest magnitude:
+max |got - ref| <= 1e-4 max |ref| (attn_rel_tol, src/train.zig:706; src/cuda/attn.cu:103-113).  That gate is used
+here; the attention-only outputs keep the element-wise bar of the rest of this suite.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REL = 1e-4  # src/train.zig:706
+
+
+def rel_close(got, ref, what):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    err = np.abs(got - ref)
+    worst = float(np.where(np.isnan(err), np.inf, err).max())
+    assert worst <= REL * float(np.abs(ref).max()), (what, worst, float(np.abs(ref).max()))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    return torch.device("cuda:0")
+
+
+def cu(x, dev):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+
+PROJ_SHAPES = [  # B, T, k, n: one tile; tails in rows and columns; a contraction cut into pieces (k, n, T > 1024)
+    (1, 128, 128, 128), (2, 200, 192, 64), (1, 77, 64, 320), (2, 300, 2112, 128), (1, 1300, 128, 1088),
+]
+
+
+@pytest.mark.parametrize("B,T,k,n", PROJ_SHAPES)
+def test_projection_forward_and_gradients_match_oracle(zt, dev, oracle, B, T, k, n):
+    rng = np.random.default_rng(B * 1000 + T)
+    ctx = rng.standard_normal((B, T, k)).astype(np.float32)
+    wo = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    dy = rng.standard_normal((B, T, n)).astype(np.float32)
+    dwo0 = rng.standard_normal((k, n)).astype(np.float32)  # weightGrad adds to what is there
+    ws = zt.ProjWorkspace(B, T, k, n, dev)
+    tctx, two, tdy, tdwo = cu(ctx, dev), cu(wo, dev), cu(dy, dev), cu(dwo0, dev)
+    y = zt.proj_forward(tctx, two, workspace=ws)
+    assert zt.lib.last_path() == "tcgen05"
+    dctx = zt.proj_backward(tctx, two, tdy, tdwo, workspace=ws)
+    torch.cuda.synchronize()
+    assert zt.lib.tc_status() == 0
+    ref_dwo = dwo0.copy()
+    for b in range(B):
+        rel_close(y[b].cpu().numpy(), oracle.matmul(ctx[b], wo, threads=8), f"y[{b}]")
+        rel_close(dctx[b].cpu().numpy(), oracle.input_grad(dy[b], wo, threads=8), f"dctx[{b}]")
+        oracle.weight_grad(ref_dwo, ctx[b], dy[b], threads=8)
+    rel_close(tdwo.cpu().numpy(), ref_dwo, "dwo")
+
+
+def test_projection_known_answers(zt, dev):
+    """The literals of src/tensor_test.zig:113-156, embedded in the corner of a 64-multiple shape (zeros elsewhere:
+    they add nothing), exact."""
+    a = np.zeros((1, 2, 64), np.float32)
+    b = np.zeros((64, 64), np.float32)
+    a[0, :, :3] = [[1, 2, 3], [4, 5, 6]]
+    b[:3, :2] = [[7, 8], [9, 10], [11, 12]]
+    y = zt.proj_forward(cu(a, dev), cu(b, dev)).cpu().numpy()
+    assert y[0, :, :2].tolist() == [[58.0, 64.0], [139.0, 154.0]] and not y[0, :, 2:].any()
+
+
+def test_projection_refusals(zt, dev):
+    L = zt.lib.load()
+    L.zt_attn_set_verbose(0)
+    x = torch.zeros((1, 8, 100), device=dev)
+    w = torch.zeros((100, 64), device=dev)
+    with pytest.raises(zt.device.ConfigRefused, match="multiples of 64"):
+        zt.proj_forward(x, w)
+    x2, w2 = torch.zeros((1, 8, 64), device=dev), torch.zeros((64, 64), device=dev)
+    y = torch.zeros((1, 8, 64), device=dev)
+    rc = L.zt_proj_forward(x2.data_ptr(), w2.data_ptr(), y.data_ptr(), None, 0, 1, 8, 64, 64, None)
+    assert rc == 1 and "workspace" in zt.lib.last_error()
+    L.zt_attn_set_verbose(1)
+
+
+BLOCK_SHAPES = [  # B, T, H, Hkv, D, d_model, pos
+    (1, 256, 4, 2, 32, 128, 0),      # the reference model's block (src/model.zig:92-102)
+    (2, 200, 4, 2, 64, 192, 37), (1, 384, 8, 2, 128, 256, 5),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,d_model,pos", BLOCK_SHAPES)
+def test_attention_block_step_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, d_model, pos):
+    """rope -> attention -> wo, and back: dwo, dq, dk, dv against the oracle's composition of the same calls, with
+    the upstream gradient at the size a training step supplies (1e-5 of the activations, src/cuda/attn.cu:103-113),
+    where an absolute gate would pass anything and the scale-relative one still bites."""
+    rng = np.random.default_rng(T + D)
+    q = rng.standard_normal((B, T, H * D)).astype(np.float32)
+    k = rng.standard_normal((B, T, Hkv * D)).astype(np.float32)
+    v = rng.standard_normal((B, T, Hkv * D)).astype(np.float32)
+    wo = (rng.standard_normal((H * D, d_model)) / np.sqrt(H * D)).astype(np.float32)
+    dy = (rng.standard_normal((B, T, d_model)) * 1e-5).astype(np.float32)
+    block = zt.AttentionBlock(B, T, H, Hkv, D, d_model, device=dev)
+    tq, tk, tv, two, tdy = (cu(x, dev) for x in (q, k, v, wo, dy))
+    y = block.forward(tq, tk, tv, two, pos=pos)
+    dwo = torch.zeros_like(two)
+    dq, dk, dv = block.backward(tdy, dwo)
+    torch.cuda.synchronize()
+    assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    ref_dwo = np.zeros_like(wo)
+    for b in range(B):
+        qr, kr = oracle.rope_forward(q[b], pos, D), oracle.rope_forward(k[b], pos, D)
+        ctx = oracle.attention_forward(qr, kr, v[b], H, Hkv, D, threads=8)
+        rel_close(y[b].cpu().numpy(), oracle.matmul(ctx, wo, threads=8), f"y[{b}]")
+        dctx = oracle.input_grad(dy[b], wo, threads=8)
+        oracle.weight_grad(ref_dwo, ctx, dy[b], threads=8)
+        rdq, rdk, rdv = oracle.attention_backward(qr, kr, v[b], dctx, H, Hkv, D, threads=8)
+        rel_close(dq[b].cpu().numpy(), oracle.rope_backward(rdq, pos, D), f"dq[{b}]")
+        rel_close(dk[b].cpu().numpy(), oracle.rope_backward(rdk, pos, D), f"dk[{b}]")
+        rel_close(dv[b].cpu().numpy(), rdv, f"dv[{b}]")
+    rel_close(dwo.cpu().numpy(), ref_dwo, "dwo")
+    # a corrupted step must fail the same gate (a gate never seen to fail is not known to be one): dy of the
+    # wrong sign in one sequence
+    with pytest.raises(AssertionError):
+        bad = tdy.clone()
+        bad[0] = -bad[0]
+        block.forward(tq, tk, tv, two, pos=pos)
+        dq2, _, _ = block.backward(bad, torch.zeros_like(two))
+        torch.cuda.synchronize()
+        rel_close(dq2[0].cpu().numpy(), dq[0].cpu().numpy(), "corrupted step")

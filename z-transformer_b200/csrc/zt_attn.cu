@@ -19,6 +19,7 @@
 #include "tc_fwd16.cuh"
 #include "tc_fwd16g.cuh"
 #include "tc_fwd16x.cuh"
+#include "tc_gemm.cuh"
 #endif
 
 #include <mutex>
@@ -663,6 +664,131 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     // (a quarter of dq's bytes here, flushed from its accumulator many times) takes a pass in place.
     if (!dq_in_kernel && launch_rope_apply(dq, dq, w.table, batch, T, n_heads * dim, dim, true, s)) return 1;
     return launch_rope_apply(dk, dk, w.table, batch, T, n_kv_heads * dim, dim, true, s);
+}
+
+// ---- the projection after attention: y = ctx . wo, and its gradients ------------------------------------------
+namespace {
+struct ProjWorkspace {
+    uint32_t *amax_ctx, *amax_w, *amax_dy;  // [batch], [1], [batch]
+    __half *ctx_planes, *w_planes, *dy_planes;
+    size_t total_bytes, header_bytes;
+};
+ProjWorkspace proj_workspace(void *base, int batch, int T, int k, int n) {
+    auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+    ProjWorkspace w{};
+    char *c = static_cast<char *>(base);
+    w.amax_ctx = reinterpret_cast<uint32_t *>(c), w.amax_w = w.amax_ctx + batch, w.amax_dy = w.amax_w + 1;
+    w.header_bytes = up((size_t)(2 * batch + 1) * sizeof(uint32_t));
+    size_t off = w.header_bytes;
+    w.ctx_planes = reinterpret_cast<__half *>(c + off), off += up((size_t)2 * batch * T * k * sizeof(__half));
+    w.w_planes = reinterpret_cast<__half *>(c + off), off += up((size_t)2 * k * n * sizeof(__half));
+    w.dy_planes = reinterpret_cast<__half *>(c + off), off += up((size_t)2 * batch * T * n * sizeof(__half));
+    w.total_bytes = off;
+    return w;
+}
+int check_proj(const void *workspace, size_t workspace_bytes, int batch, int T, int k, int n) {
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (T < 1) return refuse("T %d is not launchable.", T);
+    if (k < 64 || n < 64 || k % 64 != 0 || n % 64 != 0)
+        return refuse("a projection of %d x %d is refused: both extents must be multiples of 64 (the tensor-core "
+                      "tiles' column blocks); there is no CUDA-core form of this call.", k, n);
+    const size_t need = proj_workspace(nullptr, batch, T, k, n).total_bytes;
+    if (!workspace || workspace_bytes < need)
+        return refuse("the projection needs %zu bytes of workspace, %zu were given.", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return refuse("the projection workspace must be 256-byte aligned.");
+    if (need_device()) return 1;
+#ifdef ZT_NO_TC
+    return refuse("this build has no tensor-core kernels.");
+#else
+    const DeviceInfo *d = device_info();
+    if (!d || d->cc_major != 10 || get_encode_tiled() == nullptr) return refuse("the projection needs an sm_100 device.");
+    return 0;
+#endif
+}
+#ifndef ZT_NO_TC
+// planes of x [batch][rows][width] with one scale per batch item
+int proj_planes(const float *x, uint32_t *amax, __half *planes, int batch, int rows, int width, cudaStream_t s) {
+    tcb::PrepassArgs pa{};
+    pa.n = 1, pa.batch = batch, pa.T = rows;
+    pa.t[0] = {x, amax, planes, width, width, width, width, nullptr};
+    return tcb::launch_prepass(pa, s);
+}
+#endif
+}  // namespace
+
+size_t zt_proj_workspace_bytes(int batch, int T, int k, int n) {
+    if (batch < 1 || T < 1 || k < 1 || n < 1) return 0;
+    return proj_workspace(nullptr, batch, T, k, n).total_bytes;
+}
+
+int zt_proj_forward(const float *ctx, const float *w, float *y, void *workspace, size_t workspace_bytes, int batch, int T,
+                    int k, int n, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (!ctx || !w || !y) return refuse("a null device pointer was passed.");
+    if (check_proj(workspace, workspace_bytes, batch, T, k, n)) return 1;
+#ifndef ZT_NO_TC
+    cudaStream_t s = (cudaStream_t)stream;
+    const ProjWorkspace ws = proj_workspace(workspace, batch, T, k, n);
+    const int pieces = (k + tcg::kPiece - 1) / tcg::kPiece;
+    if (cudaMemsetAsync(ws.amax_ctx, 0, ws.header_bytes, s) != cudaSuccess ||
+        (pieces > 1 && cudaMemsetAsync(y, 0, (size_t)batch * T * n * sizeof(float), s) != cudaSuccess)) {
+        cudaGetLastError();
+        return refuse("could not clear the projection's buffers");
+    }
+    if (proj_planes(ctx, ws.amax_ctx, ws.ctx_planes, batch, T, k, s)) return 1;
+    if (proj_planes(w, ws.amax_w, ws.w_planes, 1, k, n, s)) return 1;
+    CUtensorMap amap, bmap;
+    if (!tcg::make_plane_map(&amap, ws.ctx_planes, 2 * batch, T, k, 1, 128) ||   // rows x K, K-major
+        !tcg::make_plane_map(&bmap, ws.w_planes, 2, k, n, 2, 64))                // K x N, N-major
+        return refuse("the TMA tensor maps for the projection could not be encoded.");
+    tcg::GemmParams p{};
+    p.c = y, p.ldc = n, p.c_batch_stride = (long long)T * n, p.m_rows = T, p.n_cols = n, p.depth = k, p.pieces = pieces;
+    p.batch = batch, p.amax_a = ws.amax_ctx, p.amax_b = ws.amax_w, p.a_shared = 0, p.b_shared = 1;
+    g_last_path = "tcgen05";
+    return tcg::launch_gemm<false, true>(amap, bmap, p, s);
+#else
+    return 1;
+#endif
+}
+
+int zt_proj_backward(const float *ctx, const float *w, const float *dy, float *dctx, float *dw, void *workspace,
+                     size_t workspace_bytes, int batch, int T, int k, int n, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (!ctx || !w || !dy || !dctx || !dw) return refuse("a null device pointer was passed.");
+    if (check_proj(workspace, workspace_bytes, batch, T, k, n)) return 1;
+#ifndef ZT_NO_TC
+    cudaStream_t s = (cudaStream_t)stream;
+    const ProjWorkspace ws = proj_workspace(workspace, batch, T, k, n);
+    const int pieces_in = (n + tcg::kPiece - 1) / tcg::kPiece;   // inputGrad contracts over n
+    const int pieces_w = (T + tcg::kPiece - 1) / tcg::kPiece;    // weightGrad contracts over a sequence's rows
+    if (cudaMemsetAsync(ws.amax_ctx, 0, ws.header_bytes, s) != cudaSuccess ||
+        (pieces_in > 1 && cudaMemsetAsync(dctx, 0, (size_t)batch * T * k * sizeof(float), s) != cudaSuccess)) {
+        cudaGetLastError();
+        return refuse("could not clear the projection's buffers");
+    }
+    if (proj_planes(ctx, ws.amax_ctx, ws.ctx_planes, batch, T, k, s)) return 1;
+    if (proj_planes(w, ws.amax_w, ws.w_planes, 1, k, n, s)) return 1;
+    if (proj_planes(dy, ws.amax_dy, ws.dy_planes, batch, T, n, s)) return 1;
+    CUtensorMap dy_k, w_k, ctx_m, dy_n;
+    if (!tcg::make_plane_map(&dy_k, ws.dy_planes, 2 * batch, T, n, 1, 128) ||   // A: rows x N, K-major (contraction over n)
+        !tcg::make_plane_map(&w_k, ws.w_planes, 2, k, n, 1, 128) ||             // B: w's rows are dctx's columns, K-major
+        !tcg::make_plane_map(&ctx_m, ws.ctx_planes, 2 * batch, T, k, 2, 64) ||  // A: ctx^T, rows are the contraction
+        !tcg::make_plane_map(&dy_n, ws.dy_planes, 2 * batch, T, n, 2, 64))      // B: rows x N, N-major
+        return refuse("the TMA tensor maps for the projection could not be encoded.");
+    g_last_path = "tcgen05";
+    tcg::GemmParams p{};
+    // inputGrad (src/autograd.zig:999-1022): dctx = dy . w^T, assigned
+    p.c = dctx, p.ldc = k, p.c_batch_stride = (long long)T * k, p.m_rows = T, p.n_cols = k, p.depth = n, p.pieces = pieces_in;
+    p.batch = batch, p.amax_a = ws.amax_dy, p.amax_b = ws.amax_w, p.a_shared = 0, p.b_shared = 1;
+    if (tcg::launch_gemm<false, false>(dy_k, w_k, p, s)) return 1;
+    // weightGrad (src/autograd.zig:958-972): dw += ctx^T . dy, every sequence and every piece of it added in
+    tcg::GemmParams g{};
+    g.c = dw, g.ldc = n, g.c_batch_stride = 0, g.m_rows = k, g.n_cols = n, g.depth = T, g.pieces = pieces_w;
+    g.batch = batch, g.amax_a = ws.amax_ctx, g.amax_b = ws.amax_dy, g.a_shared = 0, g.b_shared = 0;
+    return tcg::launch_gemm<true, true>(ctx_m, dy_n, g, s);
+#else
+    return 1;
+#endif
 }
 
 size_t zt_attn_decode_workspace_bytes(int batch, int n_ctx, int n_heads, int n_kv_heads, int dim) {

@@ -217,6 +217,100 @@ def attention_backward_rope(q, k, v, out, lse, dout, n_heads, n_kv_heads, head_d
     return dq, dk, dv
 
 
+class ProjWorkspace:
+    """Caller-owned scratch of the projection calls for one (batch, T, k, n) shape."""
+
+    def __init__(self, batch, t, k, n, device="cuda"):
+        import torch
+        self.shape = (batch, t, k, n)
+        self.nbytes = int(_lib.load().zt_proj_workspace_bytes(batch, t, k, n))
+        self.buf = torch.empty(max(self.nbytes, 16), dtype=torch.uint8, device=device)
+
+
+def _proj_args(ctx, wo, workspace):
+    _need_cuda_f32(ctx, wo)
+    if ctx.dim() != 3 or wo.dim() != 2 or ctx.shape[2] != wo.shape[0] or wo.device != ctx.device:
+        raise DimensionMismatch("the projection takes ctx [B, T, k] and wo [k, n] on one device")
+    B, T, k = ctx.shape
+    n = wo.shape[1]
+    if workspace is None:
+        workspace = ProjWorkspace(B, T, k, n, ctx.device)
+    elif workspace.shape != (B, T, k, n):
+        raise DimensionMismatch("the workspace was sized for another shape")
+    return B, T, k, n, workspace
+
+
+def proj_forward(ctx, wo, *, workspace=None):
+    """tensor.matmul(ctx, l.wo) (src/model.zig:396) for a batch: ctx [B, T, k], wo [k, n] -> y [B, T, n]."""
+    import torch
+    B, T, k, n, workspace = _proj_args(ctx, wo, workspace)
+    y = torch.empty((B, T, n), dtype=torch.float32, device=ctx.device)
+    with torch.cuda.device(ctx.device):
+        rc = _lib.load().zt_proj_forward(ctx.data_ptr(), wo.data_ptr(), y.data_ptr(), workspace.buf.data_ptr(),
+                                         workspace.nbytes, B, T, k, n, _stream(ctx))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return y
+
+
+def proj_backward(ctx, wo, dy, dwo, *, workspace=None):
+    """The projection's gradients (src/autograd.zig:553-557): returns dctx = dy . wo^T and ADDS ctx^T . dy into the
+    caller's dwo [k, n] (weightGrad accumulates into the layer's gradient)."""
+    import torch
+    B, T, k, n, workspace = _proj_args(ctx, wo, workspace)
+    _need_cuda_f32(dy, dwo)
+    if tuple(dy.shape) != (B, T, n) or tuple(dwo.shape) != (k, n) or dy.device != ctx.device or dwo.device != ctx.device:
+        raise DimensionMismatch("dy must be [B, T, n] and dwo [k, n] on ctx's device")
+    dctx = torch.empty_like(ctx)
+    with torch.cuda.device(ctx.device):
+        rc = _lib.load().zt_proj_backward(ctx.data_ptr(), wo.data_ptr(), dy.data_ptr(), dctx.data_ptr(), dwo.data_ptr(),
+                                          workspace.buf.data_ptr(), workspace.nbytes, B, T, k, n, _stream(ctx))
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return dctx
+
+
+class AttentionBlock:
+    """The attention part of a transformer block as a training step runs it, device-resident, over the C ABI:
+
+        forward   ctx = attention(rope(q), rope(k), v)      (src/model.zig:372-393)
+                  y   = ctx . wo                            (src/model.zig:396)
+        backward  dctx = dy . wo^T, dwo += ctx^T . dy       (src/autograd.zig:553-557)
+                  dq, dk, dv = ropeBackward(attentionBackward(...))   (src/autograd.zig:559-569)
+
+    q, k are the projections before rope.forward; row r sits at position pos + r.  The reference's trainer calls
+    attentionBackward at src/autograd.zig:559 on the CPU only (its CUDA backward has no call site); this is that
+    call site for the device path.  All scratch is sized once, here; a step allocates only its outputs."""
+
+    def __init__(self, batch, t, n_heads, n_kv_heads, head_dim, d_model, *, theta=ROPE_THETA, device="cuda"):
+        _head_config(n_heads, n_kv_heads, head_dim)
+        self.shape = (batch, t, n_heads, n_kv_heads, head_dim)
+        self.d_model, self.theta = d_model, theta
+        self.rope_ws = RopeWorkspace(batch, t, n_heads, n_kv_heads, head_dim, device)
+        self.proj_ws = ProjWorkspace(batch, t, n_heads * head_dim, d_model, device)
+        self.saved = None
+
+    def forward(self, q, k, v, wo, *, pos=0):
+        B, T, H, Hkv, D = self.shape
+        ctx, lse = attention_forward_rope(q, k, v, H, Hkv, D, pos=pos, theta=self.theta, workspace=self.rope_ws,
+                                          want_lse=True)
+        y = proj_forward(ctx, wo, workspace=self.proj_ws)
+        self.saved = (q, k, v, wo, ctx, lse, pos)
+        return y
+
+    def backward(self, dy, dwo):
+        """Returns dq, dk, dv (of the unrotated q, k) and adds the projection's weight gradient into dwo.  The
+        caller's word, as with kept=True elsewhere: q, k, v have not been written since forward()."""
+        if self.saved is None:
+            raise DimensionMismatch("backward() needs the forward() of the same step")
+        q, k, v, wo, ctx, lse, pos = self.saved
+        self.saved = None
+        B, T, H, Hkv, D = self.shape
+        dctx = proj_backward(ctx, wo, dy, dwo, workspace=self.proj_ws)
+        return attention_backward_rope(q, k, v, ctx, lse, dctx, H, Hkv, D, pos=pos, theta=self.theta,
+                                       workspace=self.rope_ws, kept=self.rope_ws.token != 0)
+
+
 class DecodeWorkspace:
     """Caller-owned scratch of zt_attn_decode for one (batch, n_ctx, heads, dim) shape."""
 
