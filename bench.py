@@ -532,6 +532,52 @@ def run_ours(args):
                         "the dQ kernel's epilogue, one in-place pass over dk; credited FLOPs unchanged"}
         del rws, q, k, v, do
 
+    # ---- the attention part of a block: rope -> attention -> wo (src/model.zig:372-396) -------------------------
+    # one call (the attention kernel's epilogue leaves ctx as the projection's operand planes) against the two calls
+    # one after the other, timed alternately so that clock drift under the power cap falls on both alike
+    block = None
+    if world == 1 and not args.small and not args.no_extras:
+        d_model = H * D
+        q, do = (torch.randn((B, T, H * D), generator=gen, device=dev) for _ in range(2))
+        k, v = (torch.randn((B, T, Hkv * D), generator=gen, device=dev) for _ in range(2))
+        wo = torch.randn((H * D, d_model), generator=gen, device=dev) / float(H * D) ** 0.5
+        blk = zt.AttentionBlock(B, T, H, Hkv, D, d_model, device=dev)
+        times = {False: [], True: []}
+        for f in (False, True):
+            for _ in range(3):
+                blk.forward(q, k, v, wo, fused=f)
+        for rnd in range(6):
+            for f in ((False, True) if rnd % 2 == 0 else (True, False)):
+                torch.cuda.synchronize(dev)
+                e0.record()
+                for _ in range(3):
+                    blk.forward(q, k, v, wo, fused=f)
+                e1.record()
+                torch.cuda.synchronize(dev)
+                times[f].append(e0.elapsed_time(e1) / 3)
+        dwo = torch.zeros_like(wo)
+        blk.forward(q, k, v, wo)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(3):
+            blk.forward(q, k, v, wo)
+            blk.backward(do, dwo)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        step_ms = e0.elapsed_time(e1) / 3
+        proj_flops = 2.0 * B * T * (H * D) * d_model
+        fused_ms, two_ms = statistics.median(times[True]), statistics.median(times[False])
+        block = {"config": f"rope + attention + wo, d_model {d_model}, at the headline shape",
+                 "forward_ms_fused": fused_ms, "forward_ms_two_calls": two_ms,
+                 "saved_ms": two_ms - fused_ms,
+                 "hbm_bytes_not_moved": 3 * B * T * H * D * 4,
+                 "forward_backward_ms": step_ms,
+                 "forward_backward_tflops": (3.5 * F + 3.0 * proj_flops) / (step_ms * 1e-3) / 1e12,
+                 "note": "fused: zt_attn_block_forward; the projection's passes over ctx (4 B read for the maximum, 4 B "
+                         "read + 4 B written for the planes, per element) do not run; credited flops: attention 3.5 F "
+                         "plus three projection products (forward, inputGrad, weightGrad)"}
+        del q, k, v, do, wo, dwo, blk
+
     # ---- end to end with host buffers (rank-local) ----------------------------------------------------
     # Every sequence's q, k, v, dout go up from pinned host memory and its out, dq, dk, dv come back,
     # inside the timed region.  Two ways:
@@ -756,7 +802,8 @@ def run_ours(args):
             "sharding": (f"the batch of 8 split over {world} ranks ({Bl} per GPU); NCCL all-gather of out, dq, dk, dv "
                          "to every rank inside the step, overlapped with the next kernels") if strong else
                         ("one GPU" if world == 1 else "replicas"),
-            "roofline": roofline, "issued_mma": issued, "phases": phases, "weak": weak, "rope": rope, "kernels": klist,
+            "roofline": roofline, "issued_mma": issued, "phases": phases, "weak": weak, "rope": rope, "block": block,
+            "kernels": klist,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "host_cpus": cpu_binding, "pcie": pcie,

@@ -217,6 +217,23 @@ int zt_proj_forward(const float *ctx, const float *wo, float *y, void *workspace
 int zt_proj_backward(const float *ctx, const float *wo, const float *dy, float *dctx, float *dwo, void *workspace,
                      size_t workspace_bytes, int batch, int T, int k, int n, zt_stream_t stream);
 
+/* The forward of the attention part of a block in one call: zt_attn_forward_rope_batched followed by
+ * zt_proj_forward on its output (src/model.zig:372-396), with the two fused where it pays: on the tensor-core path
+ * the attention kernel's epilogue writes ctx a second time as the f16 operand planes of the projection, straight
+ * into the projection's workspace, so the projection's own passes over ctx (one read for the maximum, one read and
+ * one write for the planes) do not run -- an output row is a convex combination of rows of v, so its scale is
+ * known from v's maxima before the row exists.  (Fusing the product itself into the attention kernel would have
+ * every (query tile, head) CTA add a [128, d_model] partial product into y: n_heads / 2 times y's bytes in
+ * atomic traffic, which costs more than the round trip it saves.)  ctx [batch, T, n_heads*dim] and lse are
+ * written as by the rope forward (the backward needs them), y is [batch, T, d_model]; wo is [n_heads*dim, d_model].
+ * Both workspaces are the caller's (zt_attn_rope_workspace_bytes, zt_proj_workspace_bytes with k = n_heads*dim,
+ * n = d_model); *host_token as in zt_attn_forward_rope_batched.  Refusals: those of the two calls.
+ * The backward of the block is zt_proj_backward followed by zt_attn_backward_rope_batched. */
+int zt_attn_block_forward(const float *q, const float *k, const float *v, const float *wo, float *ctx, float *lse,
+                          float *y, void *rope_workspace, size_t rope_workspace_bytes, void *proj_workspace,
+                          size_t proj_workspace_bytes, int batch, int T, int n_heads, int n_kv_heads, int dim,
+                          int d_model, int pos, double theta, zt_stream_t stream, unsigned long long *host_token);
+
 /* KV-cache decode attention for a batch of sequences: decode.attnStep
  * (src/decode.zig:326-392) for every sequence at once, over device-resident
  * caches laid out as kv_cache.Layer lays them out (src/kv_cache.zig:60-95):

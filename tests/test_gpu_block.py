@@ -105,7 +105,9 @@ def test_attention_block_step_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, d
     dy = (rng.standard_normal((B, T, d_model)) * 1e-5).astype(np.float32)
     block = zt.AttentionBlock(B, T, H, Hkv, D, d_model, device=dev)
     tq, tk, tv, two, tdy = (cu(x, dev) for x in (q, k, v, wo, dy))
-    y = block.forward(tq, tk, tv, two, pos=pos)
+    y_two_calls = block.forward(tq, tk, tv, two, pos=pos, fused=False)
+    y = block.forward(tq, tk, tv, two, pos=pos)  # one call: the attention epilogue writes the projection's planes
+    assert torch.equal(y, y_two_calls) or float((y - y_two_calls).abs().max()) <= 1e-6 * float(y.abs().max())
     dwo = torch.zeros_like(two)
     dq, dk, dv = block.backward(tdy, dwo)
     torch.cuda.synchronize()

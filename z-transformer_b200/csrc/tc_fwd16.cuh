@@ -52,7 +52,30 @@ struct Params {
     int dim_out;  // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
     int ahead;    // attn_fwd_tc16 prefetches the query tile of the block this many places on in launch order; 0: none
     float scale_log2;
+    // When set, the epilogue also leaves out as f16 hi/lo planes ([2][B][T][H * dim_out], one power-of-two scale per
+    // sequence) for the projection that follows (tc_gemm.cuh): the GEMM then needs no pass of its own over out.
+    __half *o_planes;
+    long long o_plane_stride;  // elements from the hi plane to the lo plane
 };
+
+// The scale of a sequence's out planes.  An output row is a convex combination of rows of v, so |out| <= max |v|
+// over the sequence's KV heads: the power of two that puts that maximum just under 2^15 fits out as well.
+__device__ __forceinline__ float out_plane_mult(const Params &p, int b) {
+    uint32_t top = 0;
+    for (int g = 0; g < p.n_kv_heads; ++g) top = max(top, p.amax_v[b * p.n_kv_heads + g]);
+    return block_mult(top);
+}
+// Four consecutive elements of out at element index idx, and their planes when asked for.
+__device__ __forceinline__ void store_out4(const Params &p, long long idx, float4 o4, float mo) {
+    *reinterpret_cast<float4 *>(p.out + idx) = o4;
+    if (p.o_planes) {
+        uint2 hw, lw;
+        split_pack(o4.x * mo, o4.y * mo, hw.x, lw.x);
+        split_pack(o4.z * mo, o4.w * mo, hw.y, lw.y);
+        *reinterpret_cast<uint2 *>(p.o_planes + idx) = hw;
+        *reinterpret_cast<uint2 *>(p.o_planes + p.o_plane_stride + idx) = lw;
+    }
+}
 
 __device__ __forceinline__ bool fwait(uint64_t *bar, uint32_t parity, Shared *sh) {
     for (uint32_t i = 0; i < (1u << 20); ++i) {
@@ -393,12 +416,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int lane = threadIdx.x & 31;
             const int ch = lane & (CH - 1);
             const long long wo = (long long)p.n_heads * p.dim_out;
+            const float mo = p.o_planes ? out_plane_mult(p, b) : 1.f;
 #pragma unroll 4
             for (int i = 0; i < 16; i += RPI) {
                 const int r = warp * 16 + i + lane / CH;
                 const float4 o4 = *reinterpret_cast<const float4 *>(sK + r * (D * 4) + ((ch ^ (r & (CH - 1))) << 4));
                 if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
-                    *reinterpret_cast<float4 *>(p.out + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = o4;
+                    store_out4(p, ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4, o4, mo);
             }
         }
     }
@@ -468,9 +492,11 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 
 // `in_backward_workspace`: lay the planes out where the backward's workspace keeps them (tc_bwd.cuh
 // bwd_workspace), so that a backward given the same workspace can use them as they are.
+// out_planes (optional): where the kernel also leaves out as f16 hi/lo planes, [2][batch][T][n_heads * dim] halves.
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
-                           const float2 *rope = nullptr, bool in_backward_workspace = false, int variant = 0) {
+                           const float2 *rope = nullptr, bool in_backward_workspace = false, int variant = 0,
+                           __half *out_planes = nullptr) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
     tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
@@ -505,6 +531,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
         p.out = out, p.lse = lse;
         p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
         p.dim_out = dim;
+        p.o_planes = out_planes, p.o_plane_stride = (long long)batch * T * n_heads * dim;
         p.scale_log2 = kLog2e / sqrtf((float)dim);
         g_last_path = "tcgen05";
         return tcf16::launch_x(kmap, vmap, qmap, p, stream);
@@ -522,6 +549,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.out = out, p.lse = lse;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
+    p.o_planes = out_planes, p.o_plane_stride = (long long)batch * T * n_heads * dim;
     p.ahead = device_info() ? device_info()->sm_count : 0;  // one CTA per SM
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";

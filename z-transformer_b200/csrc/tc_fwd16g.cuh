@@ -315,12 +315,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             constexpr int RPI = 32 / CH;  // rows per store instruction
             const int ch = lane & (CH - 1);
             const long long wo = (long long)p.n_heads * p.dim_out;
+            const float mo = p.o_planes ? out_plane_mult(p, b) : 1.f;
 #pragma unroll 4
             for (int i = 0; i < 32; i += RPI) {
                 const int r = (warp & 3) * 32 + i + lane / CH;
                 const float4 o4 = *reinterpret_cast<const float4 *>(stage + r * (D * 4) + ((ch ^ (r & (CH - 1))) << 4));
                 if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
-                    *reinterpret_cast<float4 *>(p.out + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = o4;
+                    store_out4(p, ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4, o4, mo);
             }
         }
     }

@@ -313,6 +313,7 @@ __global__ void __launch_bounds__(kThreadsX, 1)
         mbar_arrive_warp(&sh->staged);
         if (__all_sync(0xffffffffu, xwait(&sh->staged, 0, sh)) && !sh->abort) {
             const long long wo = (long long)p.n_heads * p.dim_out;
+            const float mo = p.o_planes ? out_plane_mult(p, b) : 1.f;
             // a warp stores its 32 rows; a row is 64 chunks: two instructions of 32 lanes each
 #pragma unroll 4
             for (int i = 0; i < 32; ++i) {
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kThreadsX, 1)
                     const int ch = half * 32 + lane;
                     const float4 o4 = *reinterpret_cast<const float4 *>(stage + r * (D * 4) + ((ch ^ (r & 31)) << 4));
                     if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
-                        *reinterpret_cast<float4 *>(p.out + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = o4;
+                        store_out4(p, ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4, o4, mo);
                 }
             }
         }

@@ -588,11 +588,14 @@ size_t zt_attn_rope_workspace_bytes(int batch, int T, int n_heads, int n_kv_head
     return rope_workspace(nullptr, batch, T, n_heads, n_kv_heads, dim).total_bytes;
 }
 
-int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
-                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream,
-                                 unsigned long long *host_token) {
+// zt_attn_forward_rope_batched; with out_planes the tensor-core kernel also leaves out as f16 planes there and
+// *planes_written says whether it did (false off the tensor-core path).
+static int forward_rope_impl(const float *q, const float *k, const float *v, float *out, float *lse,
+                             void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                             int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream,
+                             unsigned long long *host_token, __half *out_planes, bool *planes_written) {
     g_last_error[0] = 0;
+    if (planes_written) *planes_written = false;
     if (host_token) *host_token = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
@@ -609,9 +612,10 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
         w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim)) {
         // the planes (rotated q and k among them) go where the backward keeps its own: the rope backward that
         // follows with the same workspace, tensors, pos and theta converts only dout
-        if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, 0)) return 1;
+        if (launch_fwd_tc16(q, k, v, out, lse, w.inner, batch, T, n_heads, n_kv_heads, dim, s, w.table, true, 0, out_planes)) return 1;
         const unsigned long long token = note_kept_planes(w.inner, batch, T, n_heads, n_kv_heads, dim, true, pos, theta);
         if (host_token) *host_token = token;
+        if (planes_written) *planes_written = out_planes != nullptr;
         return 0;
     }
 #endif
@@ -619,6 +623,14 @@ int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v,
     if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
     if (launch_rope_apply(k, w.k_rot, w.table, batch, T, n_kv_heads * dim, dim, false, s)) return 1;
     return forward_impl(w.q_rot, w.k_rot, v, out, lse, batch, T, n_heads, n_kv_heads, dim, 0, T, s);
+}
+
+int zt_attn_forward_rope_batched(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, int pos, double theta, zt_stream_t stream,
+                                 unsigned long long *host_token) {
+    return forward_rope_impl(q, k, v, out, lse, workspace, workspace_bytes, batch, T, n_heads, n_kv_heads, dim, pos, theta,
+                             stream, host_token, nullptr, nullptr);
 }
 
 int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v, const float *out,
@@ -721,21 +733,33 @@ size_t zt_proj_workspace_bytes(int batch, int T, int k, int n) {
     return proj_workspace(nullptr, batch, T, k, n).total_bytes;
 }
 
-int zt_proj_forward(const float *ctx, const float *w, float *y, void *workspace, size_t workspace_bytes, int batch, int T,
-                    int k, int n, zt_stream_t stream) {
-    g_last_error[0] = 0;
-    if (!ctx || !w || !y) return refuse("a null device pointer was passed.");
-    if (check_proj(workspace, workspace_bytes, batch, T, k, n)) return 1;
 #ifndef ZT_NO_TC
-    cudaStream_t s = (cudaStream_t)stream;
+// amax_ctx[b] = max over the sequence's KV heads of max |v|: the scale the forward's epilogue gave out's planes
+__global__ void seq_amax_kernel(const uint32_t *__restrict__ amax_v, uint32_t *__restrict__ amax_ctx, int n_kv_heads) {
+    uint32_t top = 0;
+    for (int g = 0; g < n_kv_heads; ++g) top = max(top, amax_v[blockIdx.x * n_kv_heads + g]);
+    amax_ctx[blockIdx.x] = top;
+}
+#endif
+
+// y = ctx . w.  ctx_planes_from: null (ctx is converted here), or the [batch, n_kv_heads] maxima of v that scaled the
+// planes the attention kernel has already left in the workspace.
+static int proj_forward_impl(const float *ctx, const float *w, float *y, void *workspace, int batch, int T, int k, int n,
+                             cudaStream_t s, bool header_cleared, const uint32_t *ctx_planes_from, int n_kv_heads) {
+#ifndef ZT_NO_TC
     const ProjWorkspace ws = proj_workspace(workspace, batch, T, k, n);
     const int pieces = (k + tcg::kPiece - 1) / tcg::kPiece;
-    if (cudaMemsetAsync(ws.amax_ctx, 0, ws.header_bytes, s) != cudaSuccess ||
+    if ((!header_cleared && cudaMemsetAsync(ws.amax_ctx, 0, ws.header_bytes, s) != cudaSuccess) ||
         (pieces > 1 && cudaMemsetAsync(y, 0, (size_t)batch * T * n * sizeof(float), s) != cudaSuccess)) {
         cudaGetLastError();
         return refuse("could not clear the projection's buffers");
     }
-    if (proj_planes(ctx, ws.amax_ctx, ws.ctx_planes, batch, T, k, s)) return 1;
+    if (ctx_planes_from) {
+        if (ZT_LAUNCH("seq_amax_kernel", s, (seq_amax_kernel<<<(unsigned)batch, 1, 0, s>>>(ctx_planes_from, ws.amax_ctx, n_kv_heads))))
+            return 1;
+    } else if (proj_planes(ctx, ws.amax_ctx, ws.ctx_planes, batch, T, k, s)) {
+        return 1;
+    }
     if (proj_planes(w, ws.amax_w, ws.w_planes, 1, k, n, s)) return 1;
     CUtensorMap amap, bmap;
     if (!tcg::make_plane_map(&amap, ws.ctx_planes, 2 * batch, T, k, 1, 128) ||   // rows x K, K-major
@@ -747,6 +771,48 @@ int zt_proj_forward(const float *ctx, const float *w, float *y, void *workspace,
     g_last_path = "tcgen05";
     return tcg::launch_gemm<false, true>(amap, bmap, p, s);
 #else
+    return 1;
+#endif
+}
+
+int zt_proj_forward(const float *ctx, const float *w, float *y, void *workspace, size_t workspace_bytes, int batch, int T,
+                    int k, int n, zt_stream_t stream) {
+    g_last_error[0] = 0;
+    if (!ctx || !w || !y) return refuse("a null device pointer was passed.");
+    if (check_proj(workspace, workspace_bytes, batch, T, k, n)) return 1;
+    return proj_forward_impl(ctx, w, y, workspace, batch, T, k, n, (cudaStream_t)stream, false, nullptr, 0);
+}
+
+int zt_attn_block_forward(const float *q, const float *k, const float *v, const float *wo, float *ctx, float *lse, float *y,
+                          void *rope_ws, size_t rope_ws_bytes, void *proj_workspace_, size_t proj_workspace_bytes,
+                          int batch, int T, int n_heads, int n_kv_heads, int dim, int d_model, int pos, double theta,
+                          zt_stream_t stream, unsigned long long *host_token) {
+    g_last_error[0] = 0;
+    if (host_token) *host_token = 0;
+    if (!q || !k || !v || !wo || !ctx || !y) return refuse("a null device pointer was passed.");
+    if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
+    if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
+    const int kdim = n_heads * dim;
+    if (check_proj(proj_workspace_, proj_workspace_bytes, batch, T, kdim, d_model)) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+#ifndef ZT_NO_TC
+    const ProjWorkspace pw = proj_workspace(proj_workspace_, batch, T, kdim, d_model);
+    if (cudaMemsetAsync(pw.amax_ctx, 0, pw.header_bytes, s) != cudaSuccess) {
+        cudaGetLastError();
+        return refuse("could not clear the projection's buffers");
+    }
+    bool planes_written = false;
+    if (forward_rope_impl(q, k, v, ctx, lse, rope_ws, rope_ws_bytes, batch, T, n_heads, n_kv_heads, dim, pos,
+                          theta, stream, host_token, pw.ctx_planes, &planes_written))
+        return 1;
+    const uint32_t *from = nullptr;
+    if (planes_written) {
+        const RopeWorkspace rw = rope_workspace(rope_ws, batch, T, n_heads, n_kv_heads, dim);
+        from = tcb::bwd_workspace(rw.inner, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).amax_v;
+    }
+    return proj_forward_impl(ctx, wo, y, proj_workspace_, batch, T, kdim, d_model, s, true, from, n_kv_heads);
+#else
+    (void)s, (void)lse, (void)rope_ws, (void)rope_ws_bytes, (void)pos, (void)theta;
     return 1;
 #endif
 }

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "zt_proj_workspace_bytes": (_sz, [_i] * 4),
     "zt_proj_forward": (_i, [_vp] * 4 + [_sz] + [_i] * 4 + [_vp]),
     "zt_proj_backward": (_i, [_vp] * 6 + [_sz] + [_i] * 4 + [_vp]),
+    "zt_attn_block_forward": (_i, [_vp] * 8 + [_sz, _vp, _sz] + [_i] * 7 + [_d, _vp, C.POINTER(C.c_ulonglong)]),
     "zt_attn_decode": (_i, [_vp] * 7 + [_sz] + [_i] * 5 + [_vp]),
     "zt_attn_decode_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_decode_static": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),

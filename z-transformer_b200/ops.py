@@ -290,11 +290,34 @@ class AttentionBlock:
         self.proj_ws = ProjWorkspace(batch, t, n_heads * head_dim, d_model, device)
         self.saved = None
 
-    def forward(self, q, k, v, wo, *, pos=0):
+    def forward(self, q, k, v, wo, *, pos=0, fused=True):
+        """y = (attention(rope(q), rope(k), v)) . wo.  fused: one call of zt_attn_block_forward (the attention
+        kernel's epilogue leaves ctx as the projection's operand planes); otherwise the two calls one after the
+        other -- same numbers, one more pass over ctx."""
+        import ctypes
+        import torch
         B, T, H, Hkv, D = self.shape
-        ctx, lse = attention_forward_rope(q, k, v, H, Hkv, D, pos=pos, theta=self.theta, workspace=self.rope_ws,
-                                          want_lse=True)
-        y = proj_forward(ctx, wo, workspace=self.proj_ws)
+        if not fused:
+            ctx, lse = attention_forward_rope(q, k, v, H, Hkv, D, pos=pos, theta=self.theta, workspace=self.rope_ws,
+                                              want_lse=True)
+            y = proj_forward(ctx, wo, workspace=self.proj_ws)
+        else:
+            _, _, _ = _rope_args(q, k, v, H, Hkv, D, self.rope_ws)
+            _need_cuda_f32(wo)
+            if tuple(wo.shape) != (H * D, self.d_model) or wo.device != q.device:
+                raise DimensionMismatch("wo must be [n_heads * head_dim, d_model] on q's device")
+            ctx = torch.empty_like(q)
+            lse = torch.empty((B, T, H), dtype=torch.float32, device=q.device)
+            y = torch.empty((B, T, self.d_model), dtype=torch.float32, device=q.device)
+            token = ctypes.c_ulonglong(0)
+            with torch.cuda.device(q.device):
+                rc = _lib.load().zt_attn_block_forward(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), wo.data_ptr(), ctx.data_ptr(), lse.data_ptr(), y.data_ptr(),
+                    self.rope_ws.buf.data_ptr(), self.rope_ws.nbytes, self.proj_ws.buf.data_ptr(), self.proj_ws.nbytes,
+                    B, T, H, Hkv, D, self.d_model, pos, self.theta, _stream(q), ctypes.byref(token))
+            self.rope_ws.token = token.value
+            if rc != 0:
+                raise ConfigRefused(_lib.last_error())
         self.saved = (q, k, v, wo, ctx, lse, pos)
         return y
 
