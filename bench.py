@@ -324,56 +324,141 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    def prefill_run(Bl, Hl, Hkvl, Tl, steps, warmup, gather, sample_clocks=False):
+    def prefill_run(Bl, Hl, Hkvl, Tl, steps, warmup, gather, sample_clocks=False, push="auto"):
         """`steps` forward+backward passes over this rank's Bl sequences of Hl/Hkvl heads (device-resident inputs).
-        gather: None, or "batch" / "heads": the all-gather that returns out, dq, dk, dv to every rank is part of
-        every step, issued on a second stream so that it overlaps the kernels that follow (the outputs are
-        double-buffered: a step's kernels never write what an earlier step's gather still reads)."""
+        gather: None, or "batch" / "heads": every rank ends each step with every rank's out, dq, dk, dv, in one of
+        two ways (push):
+          "kernel"  out and dq (4/5 of the bytes) are not gathered by a collective: the kernels' epilogues store every
+                    row into all ranks' gathered tensors as they store it locally (peer stores over NVLink,
+                    zt_attn_*_peers); dk and dv, flushed many times per CTA, go by one NCCL all-gather on a second
+                    stream, which also tells a rank that its peers' kernels have finished writing to it.  Costs nothing
+                    while the bytes a rank must send fit easily into the time its kernels run;
+          "nccl"    plain kernels, then NCCL all-gathers on the second stream beside the next step's kernels: out as
+                    soon as the forward has it, dq + dk + dv (one buffer, one collective) after the backward.  Better
+                    when the step is NVLink-bound (the transfer takes about as long as the kernels): the peer stores
+                    would hold the SMs at the end of every CTA.
+          "auto"    times a few steps of the kernels alone and picks "kernel" when the bytes a rank must send, at the
+                    measured 770 GB/s per direction, take less than half that time.
+        Outputs are double-buffered: a step's kernels never write what an earlier step's gather still reads."""
         q, do = (torch.randn((Bl, Tl, Hl * D), generator=gen, device=dev) for _ in range(2))
         k, v = (torch.randn((Bl, Tl, Hkvl * D), generator=gen, device=dev) for _ in range(2))
-        n_sets = 2 if gather else 1
-        outs = [dict(out=torch.empty_like(q), dq=torch.empty_like(q), dk=torch.empty_like(k), dv=torch.empty_like(v))
-                for _ in range(n_sets)]
         lse, delta = (torch.empty((Bl, Tl, Hl), device=dev) for _ in range(2))
         ws_bytes = L.zt_attn_backward_workspace_bytes(Bl, Tl, Hl, Hkvl, D)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-        gathered = None
-        if gather:
-            gathered = {n: torch.empty((world,) + tuple(x.shape), device=dev) for n, x in outs[0].items()}
-        comm_done = [torch.cuda.Event() for _ in range(n_sets)]
-        ev_out, ev_grad = torch.cuda.Event(), torch.cuda.Event()
         stream = main_stream.cuda_stream
         token = ctypes.c_ulonglong(0)
+        nq, nk = q.numel(), k.numel()
 
-        def step(i, with_gather=True):
-            o = outs[i % n_sets]
-            if gather and with_gather and i >= n_sets:
-                main_stream.wait_event(comm_done[i % n_sets])
-            # the training pair: the forward leaves its f16 planes of q, k, v in the backward's workspace
+        def plain_set():
+            pack = torch.empty(2 * nq + 2 * nk, device=dev)  # out | dq | dk | dv: the gradients are one buffer
+            return {"pack": pack, "out": pack[:nq].view_as(q), "dq": pack[nq:2 * nq].view_as(q),
+                    "dk": pack[2 * nq:2 * nq + nk].view_as(k), "dv": pack[2 * nq + nk:].view_as(v)}
+
+        def plain_step(o):
             rc = L.zt_attn_forward_batched_keep(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
                                                 lse.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D, stream,
                                                 ctypes.byref(token))
-            if gather and with_gather:
-                ev_out.record(main_stream)
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(ev_out)
-                    dist.all_gather_into_tensor(gathered["out"], o["out"])
-            rc |= L.zt_attn_backward_batched_kept(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
-                                                  lse.data_ptr(), do.data_ptr(), o["dq"].data_ptr(), o["dk"].data_ptr(),
-                                                  o["dv"].data_ptr(), delta.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl,
-                                                  Hl, Hkvl, D, stream, token.value)
+            return rc
+
+        def plain_backward(o):
+            return L.zt_attn_backward_batched_kept(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
+                                                   lse.data_ptr(), do.data_ptr(), o["dq"].data_ptr(), o["dk"].data_ptr(),
+                                                   o["dv"].data_ptr(), delta.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl,
+                                                   Hl, Hkvl, D, stream, token.value)
+
+        def timed_steps(fn, n):
+            barrier()
+            e0.record()
+            for i in range(n):
+                fn(i)
+            e1.record()
+            barrier()
+            return max_over_ranks(e0.elapsed_time(e1) / n)
+
+        base = plain_set()
+
+        def compute_only(i):
+            if plain_step(base) or plain_backward(base):
+                raise RuntimeError("libztattn refused the step: " + zt.lib.last_error())
+
+        sent = int((2 * nq + 2 * nk) * 4 * (world - 1)) if gather else 0
+        res = {}
+        if gather:
+            for i in range(max(warmup, 3)):
+                compute_only(i)
+            res["compute_ms"] = timed_steps(compute_only, max(3, min(steps, 5)))
+            res["nvlink_floor_ms"] = sent / 770e9 * 1e3
+            if push == "auto":
+                push = "kernel" if res["nvlink_floor_ms"] < 0.5 * res["compute_ms"] else "nccl"
+            res["push"] = push
+        n_sets = 2 if gather else 1
+        outs = []
+        for s_ in range(n_sets):
+            if not gather:
+                outs.append(base)
+            elif push == "nccl":
+                o = plain_set()
+                o["out_all"] = torch.empty((world,) + tuple(q.shape), device=dev)
+                o["grads_all"] = torch.empty((world, nq + 2 * nk), device=dev)
+                outs.append(o)
+            else:
+                o = {"dkdv": torch.empty(2 * nk, device=dev)}
+                o["dk"], o["dv"] = o["dkdv"][:nk].view_as(k), o["dkdv"][nk:].view_as(v)
+                o["g_out"] = zt.sharding.GatheredOutput(q.shape, world, rank, dev)
+                o["g_dq"] = zt.sharding.GatheredOutput(q.shape, world, rank, dev)
+                o["out"], o["dq"] = o["g_out"].local, o["g_dq"].local
+                o["out_peers"], o["dq_peers"] = o["g_out"].peer_pointers(), o["g_dq"].peer_pointers()
+                o["dkdv_all"] = torch.empty((world, 2 * nk), device=dev)
+                outs.append(o)
+        comm_done = [torch.cuda.Event() for _ in range(n_sets)]
+        ev_grad, ev_out = torch.cuda.Event(), torch.cuda.Event()
+
+        def side_by_side(o):
+            """[G, 1, T, Hs D] -> [1, T, H D]: the ranks' column slices laid side by side (KV-head sharding)."""
+            if push == "nccl":
+                gts = (o["out_all"], o["grads_all"][:, :nq].reshape((world,) + tuple(q.shape)),
+                       o["grads_all"][:, nq:nq + nk].reshape((world,) + tuple(k.shape)),
+                       o["grads_all"][:, nq + nk:].reshape((world,) + tuple(v.shape)))
+            else:
+                gts = (o["g_out"].gathered, o["g_dq"].gathered, o["dkdv_all"][:, :nk].reshape((world,) + tuple(k.shape)),
+                       o["dkdv_all"][:, nk:].reshape((world,) + tuple(v.shape)))
+            for gt in gts:
+                gt.movedim(0, -2).reshape(*gt.shape[1:-1], world * gt.shape[-1]).contiguous()
+
+        def step(i):
+            o = outs[i % n_sets]
+            if gather and i >= n_sets:
+                main_stream.wait_event(comm_done[i % n_sets])
+            # the training pair: the forward leaves its f16 planes of q, k, v in the backward's workspace
+            if gather and push == "kernel":
+                rc = L.zt_attn_forward_batched_keep_peers(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
+                                                          lse.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D,
+                                                          stream, ctypes.byref(token), *o["out_peers"])
+                rc |= L.zt_attn_backward_batched_kept_peers(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
+                                                            lse.data_ptr(), do.data_ptr(), o["dq"].data_ptr(),
+                                                            o["dk"].data_ptr(), o["dv"].data_ptr(), delta.data_ptr(),
+                                                            ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D, stream,
+                                                            token.value, *o["dq_peers"])
+            else:
+                rc = plain_step(o)
+                if gather:  # "nccl": out leaves while the backward runs
+                    ev_out.record(main_stream)
+                    with torch.cuda.stream(comm_stream):
+                        comm_stream.wait_event(ev_out)
+                        dist.all_gather_into_tensor(o["out_all"], o["out"])
+                rc |= plain_backward(o)
             if rc != 0:
                 raise RuntimeError("libztattn refused the step: " + zt.lib.last_error())
-            if gather and with_gather:
+            if gather:
                 ev_grad.record(main_stream)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(ev_grad)
-                    for n in ("dq", "dk", "dv"):
-                        dist.all_gather_into_tensor(gathered[n], o[n])
-                    if gather == "heads":  # [G, T, Hs D] -> [T, H D]: the ranks' column slices side by side
-                        for n in ("out", "dq", "dk", "dv"):
-                            g = gathered[n]
-                            g.movedim(0, -2).reshape(*g.shape[1:-1], world * g.shape[-1]).contiguous()
+                    if push == "kernel":
+                        dist.all_gather_into_tensor(o["dkdv_all"], o["dkdv"])
+                    else:
+                        dist.all_gather_into_tensor(o["grads_all"], o["pack"][nq:])
+                    if gather == "heads":
+                        side_by_side(o)
                     comm_done[i % n_sets].record(comm_stream)
 
         def drain():
@@ -402,28 +487,8 @@ def run_ours(args):
         kernels = zt.lib.profile_read()
         zt.lib.profile(False)
         clocks = sampler.stop() if sampler else None
-        res = {"ms_per_step": max_over_ranks(e0.elapsed_time(e1) / steps), "kernels": kernels, "launches": int(launches),
-               "clocks": clocks}
-        if gather:
-            # the phases by themselves: the kernels with no gather, and the four gathers with nothing beside them
-            nph = max(3, min(steps, 5))
-            barrier()
-            e0.record()
-            for i in range(nph):
-                step(i, with_gather=False)
-            e1.record()
-            barrier()
-            res["compute_ms"] = max_over_ranks(e0.elapsed_time(e1) / nph)
-            o = outs[0]
-            barrier()
-            e0.record()
-            for _ in range(nph):
-                for n in ("out", "dq", "dk", "dv"):
-                    dist.all_gather_into_tensor(gathered[n], o[n])
-            e1.record()
-            barrier()
-            res["gather_ms"] = max_over_ranks(e0.elapsed_time(e1) / nph)
-            res["gather_bytes_per_rank"] = int(sum(x.numel() for x in o.values()) * 4 * (world - 1))
+        res.update({"ms_per_step": max_over_ranks(e0.elapsed_time(e1) / steps), "kernels": kernels,
+                    "launches": int(launches), "clocks": clocks, "bytes_sent_per_rank": sent})
         return res
 
     # ---- the headline step ------------------------------------------------------------------------------------
@@ -432,7 +497,7 @@ def run_ours(args):
     weak_res = None
     if strong:
         # the job's 8 sequences split over the ranks, outputs gathered; then the replica run for comparison
-        main = prefill_run(B // world, H, Hkv, T, args.steps, args.warmup, "batch", sample_clocks=True)
+        main = prefill_run(B // world, H, Hkv, T, args.steps, args.warmup, "batch", sample_clocks=True, push=args.gather)
         weak_res = prefill_run(B, H, Hkv, T, max(3, args.steps // 2), args.warmup, None)
         Bl = B // world
         value = 3.5 * F / (main["ms_per_step"] * 1e-3) / 1e12
@@ -489,12 +554,13 @@ def run_ours(args):
 
     phases = None
     if strong:
-        phases = {"compute_ms": main["compute_ms"], "gather_ms_alone": main["gather_ms"],
-                  "step_ms_overlapped": ms_step, "gather_bytes_received_per_rank": main["gather_bytes_per_rank"],
-                  "gather_busbw_gbs": main["gather_bytes_per_rank"] / (main["gather_ms"] * 1e-3) / 1e9,
-                  "limiter": "gather" if main["gather_ms"] > main["compute_ms"] else "compute",
-                  "note": "NCCL all_gather_into_tensor of out, dq, dk, dv (f32) to every rank; in the step it runs on "
-                          "a second stream beside the next kernels, outputs double-buffered"}
+        phases = {"compute_ms": main["compute_ms"], "step_ms": ms_step, "gather": main["push"],
+                  "bytes_sent_per_rank": main["bytes_sent_per_rank"], "nvlink_floor_ms": main["nvlink_floor_ms"],
+                  "limiter": "NVLink" if main["nvlink_floor_ms"] > 0.8 * main["compute_ms"] else "compute",
+                  "note": "compute: the step's kernels alone. step: with every rank receiving every rank's out, dq, dk, dv "
+                          "('kernel': out and dq stored by the kernels' epilogues into every rank's gathered tensors, dk + dv "
+                          "by one NCCL all-gather; 'nccl': NCCL all-gathers on a second stream beside the next kernels). "
+                          "nvlink_floor: the bytes a rank must send per step over the measured 770 GB/s per direction"}
     weak = None
     if weak_res:
         weak = {"value": world * 3.5 * F / (weak_res["ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -729,15 +795,16 @@ def run_ours(args):
         # all-gathered and laid side by side
         sh = zt.sharding.shard_kv_heads(H, Hkv, world, rank)
         T4 = 32768
-        r4 = prefill_run(1, sh.n_heads, sh.n_kv_heads, T4, 3, 3, "heads" if world > 1 else None)
+        r4 = prefill_run(1, sh.n_heads, sh.n_kv_heads, T4, 3, 3, "heads" if world > 1 else None, push=args.gather)
         F4 = fwd_flops(1, T4, H, D)
         long_context = {"config": "T 32768, batch 1, 32/8 heads, head_dim 128, fwd+bwd; KV heads sharded over the ranks",
                         "ms_per_step": r4["ms_per_step"], "tflops": 3.5 * F4 / (r4["ms_per_step"] * 1e-3) / 1e12,
                         "frac_of_tf32_peak_per_gpu": 3.5 * F4 / (r4["ms_per_step"] * 1e-3) / 1e12 / world / tf32_sust,
                         "scaling": "strong", "kv_heads_per_gpu": sh.n_kv_heads}
         if world > 1:
-            long_context.update({"compute_ms": r4["compute_ms"], "gather_ms_alone": r4["gather_ms"],
-                                 "gather_bytes_received_per_rank": r4["gather_bytes_per_rank"]})
+            long_context.update({"compute_ms": r4["compute_ms"], "gather": r4["push"],
+                                 "bytes_sent_per_rank": r4["bytes_sent_per_rank"],
+                                 "nvlink_floor_ms": r4["nvlink_floor_ms"]})
         # ragged decode: 256 sequences, lengths uniform in [1, 16384], balanced longest-first over the ranks
         rng = np.random.default_rng(0)
         lengths = rng.integers(1, 16385, size=256)
@@ -799,8 +866,8 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": cfg,
-            "sharding": (f"the batch of 8 split over {world} ranks ({Bl} per GPU); NCCL all-gather of out, dq, dk, dv "
-                         "to every rank inside the step, overlapped with the next kernels") if strong else
+            "sharding": (f"the batch of 8 split over {world} ranks ({Bl} per GPU); every rank ends the step with every "
+                         f"rank's out, dq, dk, dv (gather: {main['push']})") if strong else
                         ("one GPU" if world == 1 else "replicas"),
             "roofline": roofline, "issued_mma": issued, "phases": phases, "weak": weak, "rope": rope, "block": block,
             "kernels": klist,
@@ -982,6 +1049,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--gather", choices=["auto", "kernel", "nccl"], default="auto",
+                    help="N > 1: how the sharded outputs reach every rank (see prefill_run); auto picks by the "
+                         "ratio of transfer to kernel time")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the 32k prefill and the ragged decode (extra keys `long_context`, `ragged_decode`)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

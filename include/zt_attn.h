@@ -172,6 +172,30 @@ int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v
                                   int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
                                   unsigned long long token);
 
+/* The training pair with the all-gather of out and dq done inside the kernels.  When independent sequences (or KV
+ * groups) are sharded over the GPUs of a box and every GPU wants every shard's outputs, the gather that follows the
+ * kernels moves as many bytes as the kernels write and, as an NCCL collective, competes with them for SMs.  These
+ * two calls are zt_attn_forward_batched_keep and zt_attn_backward_batched_kept given, besides their own out / dq,
+ * up to 7 PEER copies of it: device pointers into other GPUs' memory (mapped into this process: CUDA IPC, VMM
+ * handles, torch symmetric memory), each pointing at the place this rank's shard has in that GPU's gathered tensor.
+ * The kernel's epilogue stores every output row to all of them as it stores it locally -- plain stores over NVLink,
+ * no loads from peer memory, no waits on a peer -- so when the kernel has finished (and the peers know it has: any
+ * stream-ordered collective or barrier after it will do, e.g. the all-gather of dk and dv, which are small) the
+ * gathered out and dq are complete everywhere.  host_*_peers is a host array of n_peers device pointers, 16-byte
+ * aligned, each with room for the whole out / dq of this call.  Refusals: those of the plain calls; n_peers
+ * outside 0..7; a null or misaligned peer pointer; a shape or workspace with which the plain call would leave the
+ * tensor-core path (the CUDA-core kernels write no peer copies).  No reference counterpart (the reference is one
+ * GPU). */
+int zt_attn_forward_batched_keep_peers(const float *q, const float *k, const float *v, float *out, float *lse,
+                                       void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                       int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token,
+                                       float *const *host_out_peers, int n_peers);
+int zt_attn_backward_batched_kept_peers(const float *q, const float *k, const float *v, const float *out,
+                                        const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                        float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                        int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                                        unsigned long long token, float *const *host_dq_peers, int n_peers);
+
 /* Attention with the rotary position embedding of its input side fused in: q and k are the
  * projections BEFORE rope.forward (src/rope.zig:21-55; the reference rotates them first,
  * src/model.zig:372-375 and src/decode.zig:244-246); row r sits at absolute position pos + r,

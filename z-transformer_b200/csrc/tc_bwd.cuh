@@ -268,6 +268,7 @@ struct BwdParams {
     const uint32_t *vnmax;   // [B, Hkv] bit pattern of the largest Euclidean norm of a row of v
     uint32_t *dsmax;         // [B, Hkv] bit pattern of max |dS| (true units): written by the dQ kernel, read by dK/dV
     float *dq, *dk, *dv;
+    PeerList dq_peers;       // dq is also stored here (same element index), see zt_common.cuh
     int batch, T, n_heads, n_kv_heads;
     int dim_out;     // the tensors' head_dim: the tile's D, or 32 under a tile padded to 64
     const float2 *rope_t;  // null, or the (cos, sin) table transposed, [dim_out / 2][T]: dq leaves as R^T of what was computed
@@ -1227,8 +1228,11 @@ __global__ void __launch_bounds__(kKvThreads, 1)
             for (int i = 0; i < 8; i += RPI) {
                 const int r = warp * 8 + i + lane / CH;
                 const float4 a = *reinterpret_cast<const float4 *>(sK + r * (D * 4) + ((ch ^ (r & (CH - 1))) << 4));
-                if (t0 + r < p.T && ch * 4 < p.dim_out)  // (a padded tile's upper columns are not the tensor's)
-                    *reinterpret_cast<float4 *>(p.dq + ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4) = a;
+                if (t0 + r < p.T && ch * 4 < p.dim_out) {  // (a padded tile's upper columns are not the tensor's)
+                    const long long idx = ((long long)b * p.T + t0 + r) * wo + (long long)h * p.dim_out + ch * 4;
+                    *reinterpret_cast<float4 *>(p.dq + idx) = a;
+                    for (int pr = 0; pr < p.dq_peers.n; ++pr) *reinterpret_cast<float4 *>(p.dq_peers.ptr[pr] + idx) = a;
+                }
             }
         }
     }
@@ -1314,7 +1318,7 @@ inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_hea
 inline int launch_bwd_tc(const float *q, const float *k, const float *v, const float *dout, const float *lse,
                          const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
                          int n_heads, int n_kv_heads, int dim, cudaStream_t stream, const float2 *rope = nullptr,
-                         const float2 *rope_t = nullptr, bool qkv_planes_kept = false) {
+                         const float2 *rope_t = nullptr, bool qkv_planes_kept = false, const PeerList *dq_peers = nullptr) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernels' D; the planes' head width
     const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, td);
@@ -1361,6 +1365,7 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
     p.rnorm = w.rnorm, p.vnmax = w.vnmax, p.dsmax = w.dsmax;
     p.dq = dq, p.dk = dk, p.dv = dv;
+    if (dq_peers) p.dq_peers = *dq_peers;
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
     p.rope_t = rope_t;

@@ -56,6 +56,7 @@ struct Params {
     // sequence) for the projection that follows (tc_gemm.cuh): the GEMM then needs no pass of its own over out.
     __half *o_planes;
     long long o_plane_stride;  // elements from the hi plane to the lo plane
+    PeerList out_peers;        // out is also stored here (same element index), see zt_common.cuh
 };
 
 // The scale of a sequence's out planes.  An output row is a convex combination of rows of v, so |out| <= max |v|
@@ -68,6 +69,7 @@ __device__ __forceinline__ float out_plane_mult(const Params &p, int b) {
 // Four consecutive elements of out at element index idx, and their planes when asked for.
 __device__ __forceinline__ void store_out4(const Params &p, long long idx, float4 o4, float mo) {
     *reinterpret_cast<float4 *>(p.out + idx) = o4;
+    for (int r = 0; r < p.out_peers.n; ++r) *reinterpret_cast<float4 *>(p.out_peers.ptr[r] + idx) = o4;
     if (p.o_planes) {
         uint2 hw, lw;
         split_pack(o4.x * mo, o4.y * mo, hw.x, lw.x);
@@ -496,7 +498,7 @@ inline bool tc_fwd16_supported(int batch, int T, int dim, int q_offset, int n_ke
 inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float *out, float *lse, void *ws,
                            int batch, int T, int n_heads, int n_kv_heads, int dim, cudaStream_t stream,
                            const float2 *rope = nullptr, bool in_backward_workspace = false, int variant = 0,
-                           __half *out_planes = nullptr) {
+                           __half *out_planes = nullptr, const PeerList *out_peers = nullptr) {
     using namespace tcb;
     const int td = tc_tile_dim(dim);  // the kernel's D; the planes' head width (head_dim 32 is zero-padded to 64)
     tcf16::Workspace w = tcf16::workspace(ws, batch, T, n_heads, n_kv_heads, td);
@@ -532,6 +534,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
         p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
         p.dim_out = dim;
         p.o_planes = out_planes, p.o_plane_stride = (long long)batch * T * n_heads * dim;
+        if (out_peers) p.out_peers = *out_peers;
         p.scale_log2 = kLog2e / sqrtf((float)dim);
         g_last_path = "tcgen05";
         return tcf16::launch_x(kmap, vmap, qmap, p, stream);
@@ -550,6 +553,7 @@ inline int launch_fwd_tc16(const float *q, const float *k, const float *v, float
     p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
     p.dim_out = dim;
     p.o_planes = out_planes, p.o_plane_stride = (long long)batch * T * n_heads * dim;
+    if (out_peers) p.out_peers = *out_peers;
     p.ahead = device_info() ? device_info()->sm_count : 0;  // one CTA per SM
     p.scale_log2 = kLog2e / sqrtf((float)dim);
     g_last_path = "tcgen05";

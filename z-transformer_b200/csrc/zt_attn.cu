@@ -205,7 +205,8 @@ bool take_kept_planes(const void *workspace, unsigned long long token, int batch
 static int backward_impl(const float *q, const float *k, const float *v, const float *out, const float *lse,
                          float *delta, const float *dout, float *dq, float *dk, float *dv,
                          void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                         int n_kv_heads, int dim, cudaStream_t stream, bool kept = false) {
+                         int n_kv_heads, int dim, cudaStream_t stream, bool kept = false,
+                         const PeerList *dq_peers = nullptr) {
 #ifndef ZT_NO_TC
     if (g_path.load() != 1 && workspace &&
         workspace_bytes >= backward_workspace(batch, T, n_heads, n_kv_heads, dim) &&
@@ -215,9 +216,11 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
         float *rnorm = tcb::bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).rnorm;
         if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
-                             dim, stream, nullptr, nullptr, kept);
+                             dim, stream, nullptr, nullptr, kept, dq_peers);
     }
 #endif
+    if (dq_peers && dq_peers->n > 0)
+        return refuse("peer copies of dq are written by the tensor-core backward only, which does not take this shape.");
     (void)workspace, (void)workspace_bytes, (void)kept;
     if (launch_delta(out, dout, delta, nullptr, (long long)batch * T * n_heads, dim, stream)) return 1;
     SimtBwdParams p{};
@@ -478,9 +481,23 @@ int zt_attn_forward_batched(const float *q, const float *k, const float *v, floa
                         (cudaStream_t)stream);
 }
 
-int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
-                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
-                                 int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token) {
+static int check_peers(float *const *host_peers, int n_peers, PeerList *list) {
+    list->n = 0;
+    if (n_peers < 0 || n_peers > kMaxPeers) return refuse("%d peer copies is outside 0 .. %d.", n_peers, kMaxPeers);
+    if (n_peers > 0 && !host_peers) return refuse("a null list of peer pointers was passed.");
+    for (int i = 0; i < n_peers; ++i) {
+        if (!host_peers[i] || (reinterpret_cast<uintptr_t>(host_peers[i]) & 15u) != 0)
+            return refuse("peer pointer %d is null or not 16-byte aligned.", i);
+        list->ptr[i] = host_peers[i];
+    }
+    list->n = n_peers;
+    return 0;
+}
+
+static int forward_keep_impl(const float *q, const float *k, const float *v, float *out, float *lse,
+                             void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                             int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token,
+                             const PeerList *out_peers) {
     g_last_error[0] = 0;
     if (host_token) *host_token = 0;
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
@@ -495,7 +512,8 @@ int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v,
     if ((keep_path == 0 || keep_path == 6 || keep_path == 7) && need > 0 && workspace && workspace_bytes >= need &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
-        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true, keep_path == 6 ? 1 : (keep_path == 7 ? 2 : 0)))
+        if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true,
+                            keep_path == 6 ? 1 : (keep_path == 7 ? 2 : 0), nullptr, out_peers))
             return 1;
         const unsigned long long token = note_kept_planes(workspace, batch, T, n_heads, n_kv_heads, dim);
         if (host_token) *host_token = token;
@@ -504,7 +522,28 @@ int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v,
 #endif
     // shapes the f16-split kernels do not take: the ordinary forward, nothing kept
     (void)workspace, (void)workspace_bytes;
+    if (out_peers && out_peers->n > 0)
+        return refuse("peer copies of out are written by the forward that keeps its planes in a workspace only (a "
+                      "tensor-core shape and a backward workspace are needed).");
     return forward_impl(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, 0, T, s);
+}
+
+int zt_attn_forward_batched_keep(const float *q, const float *k, const float *v, float *out, float *lse,
+                                 void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                 int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token) {
+    return forward_keep_impl(q, k, v, out, lse, workspace, workspace_bytes, batch, T, n_heads, n_kv_heads, dim, stream,
+                             host_token, nullptr);
+}
+
+int zt_attn_forward_batched_keep_peers(const float *q, const float *k, const float *v, float *out, float *lse,
+                                       void *workspace, size_t workspace_bytes, int batch, int T, int n_heads,
+                                       int n_kv_heads, int dim, zt_stream_t stream, unsigned long long *host_token,
+                                       float *const *host_out_peers, int n_peers) {
+    g_last_error[0] = 0;
+    PeerList peers{};
+    if (check_peers(host_out_peers, n_peers, &peers)) return 1;
+    return forward_keep_impl(q, k, v, out, lse, workspace, workspace_bytes, batch, T, n_heads, n_kv_heads, dim, stream,
+                             host_token, &peers);
 }
 
 size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
@@ -513,12 +552,11 @@ size_t zt_attn_backward_workspace_bytes(int batch, int T, int n_heads, int n_kv_
     return backward_workspace(batch, T, n_heads, n_kv_heads, dim);
 }
 
-int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v, const float *out,
-                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
-                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
-                                  int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
-                                  unsigned long long token) {
-    g_last_error[0] = 0;
+static int backward_kept_impl(const float *q, const float *k, const float *v, const float *out,
+                              const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                              float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                              int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                              unsigned long long token, const PeerList *dq_peers) {
     if (batch < 1 || batch > 65535) return refuse("batch %d is not launchable (1 .. 65535).", batch);
     if (check_geometry(T, n_heads, n_kv_heads, dim)) return 1;
     if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv || !delta)
@@ -537,7 +575,29 @@ int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v
                       "are gone (pass 0 to convert q, k, v again).", token);
     if (workspace) drop_kept_planes(workspace);
     return backward_impl(q, k, v, out, lse, delta, dout, dq, dk, dv, workspace, workspace_bytes, batch, T, n_heads,
-                         n_kv_heads, dim, s, kept);
+                         n_kv_heads, dim, s, kept, dq_peers);
+}
+
+int zt_attn_backward_batched_kept(const float *q, const float *k, const float *v, const float *out,
+                                  const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                  float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                  int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                                  unsigned long long token) {
+    g_last_error[0] = 0;
+    return backward_kept_impl(q, k, v, out, lse, dout, dq, dk, dv, delta, workspace, workspace_bytes, batch, T, n_heads,
+                              n_kv_heads, dim, stream, token, nullptr);
+}
+
+int zt_attn_backward_batched_kept_peers(const float *q, const float *k, const float *v, const float *out,
+                                        const float *lse, const float *dout, float *dq, float *dk, float *dv,
+                                        float *delta, void *workspace, size_t workspace_bytes, int batch, int T,
+                                        int n_heads, int n_kv_heads, int dim, zt_stream_t stream,
+                                        unsigned long long token, float *const *host_dq_peers, int n_peers) {
+    g_last_error[0] = 0;
+    PeerList peers{};
+    if (check_peers(host_dq_peers, n_peers, &peers)) return 1;
+    return backward_kept_impl(q, k, v, out, lse, dout, dq, dk, dv, delta, workspace, workspace_bytes, batch, T, n_heads,
+                              n_kv_heads, dim, stream, token, &peers);
 }
 
 int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,

@@ -147,6 +147,15 @@ static __device__ int g_defect;
 #define ZT_DEFECT(n) false
 #endif
 
+// Copies of an output tensor in other GPUs' memory (peer device pointers, mapped into this process): a kernel that
+// is given them stores every output element there as well as locally, so the all-gather of that output happens
+// inside the kernel, element by element over NVLink, instead of as a collective after it.
+constexpr int kMaxPeers = 7;
+struct PeerList {
+    float *ptr[kMaxPeers];
+    int n;
+};
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 

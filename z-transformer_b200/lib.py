@@ -34,6 +34,9 @@ _SIGNATURES = {
     "zt_attn_backward_workspace_bytes": (_sz, [_i] * 5),
     "zt_attn_forward_batched_keep": (_i, [_vp] * 6 + [_sz] + [_i] * 5 + [_vp, C.POINTER(C.c_ulonglong)]),
     "zt_attn_backward_batched_kept": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp, C.c_ulonglong]),
+    "zt_attn_forward_batched_keep_peers": (_i, [_vp] * 6 + [_sz] + [_i] * 5 + [_vp, C.POINTER(C.c_ulonglong),
+                                                 C.POINTER(_vp), _i]),
+    "zt_attn_backward_batched_kept_peers": (_i, [_vp] * 11 + [_sz] + [_i] * 5 + [_vp, C.c_ulonglong, C.POINTER(_vp), _i]),
     "zt_attn_reserve": (_i, [_i] * 5),
     "zt_attn_arena_bytes": (_sz, []),
     "zt_attn_tc_saturated": (_i, [C.POINTER(C.c_uint)]),

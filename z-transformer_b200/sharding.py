@@ -115,3 +115,88 @@ def gather_sequences(local, inverse, world: int, group=None):
     g = gather_batch(local, world, group)
     idx = torch.as_tensor(inverse, dtype=torch.long, device=g.device)
     return g.index_select(0, idx)
+
+
+class GatheredOutput:
+    """An output tensor that every rank's kernels fill in place on every rank: [world, *shard_shape] floats in
+    symmetric memory (one allocation per rank, all mapped into each other's address space).  Rank r's kernels are
+    given `local` (its shard's place in its own copy) as their output and `peer_pointers()` (the same place in every
+    other rank's copy) as peer copies; once all ranks' kernels have finished -- any collective or barrier ordered
+    after them tells -- `gathered` holds every shard on every rank, with no all-gather of this tensor.
+
+    Needs NCCL-initialised torch.distributed, one rank per GPU on one node (torch symmetric memory maps the peers'
+    buffers through CUDA virtual-memory handles)."""
+
+    def __init__(self, shard_shape, world: int, rank: int, device, group=None):
+        import math
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank = world, rank
+        self.shard_shape = tuple(int(x) for x in shard_shape)
+        self.gathered = symm_mem.empty((world,) + self.shard_shape, dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.gathered, group if group is not None else dist.group.WORLD)
+        shard_bytes = 4 * math.prod(self.shard_shape)
+        self.local = self.gathered[rank]
+        self._peers = [int(self.handle.buffer_ptrs[r]) + rank * shard_bytes for r in range(world) if r != rank]
+
+    def peer_tensors(self):
+        """This rank's shard's place in every OTHER rank's copy, as tensors: `t.copy_(self.local)` on a side stream
+        is a device-to-device copy over NVLink by the copy engines (no SM is involved), the way to push a shard that
+        was written locally when the kernels' own epilogues should not carry the peer stores (a step whose kernels
+        are about as short as the transfer: the stores would hold the SMs)."""
+        import torch
+        if not hasattr(self, "_peer_tensors"):
+            full = (self.world,) + self.shard_shape
+            self._peer_tensors = [self.handle.get_buffer(r, full, torch.float32)[self.rank]
+                                  for r in range(self.world) if r != self.rank]
+        return self._peer_tensors
+
+    def peer_pointers(self):
+        """(ctypes array of the peers' device pointers, count) for the *_peers entry points."""
+        import ctypes
+        arr = (ctypes.c_void_p * max(1, len(self._peers)))(*self._peers)
+        return arr, len(self._peers)
+
+
+def forward_keep_gathered(q, k, v, out: GatheredOutput, lse, workspace, n_heads, n_kv_heads, head_dim):
+    """zt_attn_forward_batched_keep_peers on this rank's shard: out lands in out.local and in every peer's copy.
+    Returns the token for the kept planes (0 when the shape left the tensor-core path: the call is then refused)."""
+    import ctypes
+
+    import torch
+
+    from . import lib as _lib
+    from .device import ConfigRefused
+    B, T = q.shape[0], q.shape[1]
+    peers, n = out.peer_pointers()
+    token = ctypes.c_ulonglong(0)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_forward_batched_keep_peers(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.local.data_ptr(), lse.data_ptr(), workspace.buf.data_ptr(),
+            workspace.nbytes, B, T, n_heads, n_kv_heads, head_dim, torch.cuda.current_stream(q.device).cuda_stream,
+            ctypes.byref(token), peers, n)
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
+    return token.value
+
+
+def backward_kept_gathered(q, k, v, out_local, lse, dout, dq: GatheredOutput, dk, dv, delta, workspace, token, n_heads,
+                           n_kv_heads, head_dim):
+    """zt_attn_backward_batched_kept_peers: dq lands in dq.local and in every peer's copy; dk, dv stay local (they are
+    a quarter of dq's bytes and are flushed many times per CTA: gather them with gather_batch / gather_heads)."""
+    import torch
+
+    from . import lib as _lib
+    from .device import ConfigRefused
+    B, T = q.shape[0], q.shape[1]
+    peers, n = dq.peer_pointers()
+    with torch.cuda.device(q.device):
+        rc = _lib.load().zt_attn_backward_batched_kept_peers(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out_local.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+            dq.local.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), workspace.buf.data_ptr(),
+            workspace.nbytes, B, T, n_heads, n_kv_heads, head_dim, torch.cuda.current_stream(q.device).cuda_stream,
+            token, peers, n)
+    if rc != 0:
+        raise ConfigRefused(_lib.last_error())
