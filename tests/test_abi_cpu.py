@@ -98,6 +98,35 @@ def test_backward_and_extension_refusals(zt):
     L.zt_attn_set_verbose(1)
 
 
+def test_newer_extension_refusals(zt):
+    """Refusals that are decided on the host, before any device is looked at: peer lists, the projection's shapes and
+    workspace, a stale token's form, the reserve call's geometry."""
+    L = zt.lib.load()
+    L.zt_attn_set_verbose(0)
+    p = ctypes.c_void_p(256)
+    tok = ctypes.c_ulonglong(7)
+    peers = (ctypes.c_void_p * 8)(*([256] * 8))
+    # more than seven peer copies; a null list; a misaligned peer
+    assert L.zt_attn_forward_batched_keep_peers(p, p, p, p, p, p, 1 << 30, 1, 128, 4, 2, 64, None, ctypes.byref(tok),
+                                                peers, 8) == 1
+    assert "peer copies" in zt.lib.last_error() and tok.value == 7  # refused before the token was touched
+    assert L.zt_attn_forward_batched_keep_peers(p, p, p, p, p, p, 1 << 30, 1, 128, 4, 2, 64, None, None, None, 2) == 1
+    assert "null list" in zt.lib.last_error()
+    bad = (ctypes.c_void_p * 2)(256, 260)
+    assert L.zt_attn_backward_batched_kept_peers(*([p] * 11), 1 << 30, 1, 128, 4, 2, 64, None, 0, bad, 2) == 1
+    assert "16-byte aligned" in zt.lib.last_error()
+    # the projection: extents that are not multiples of 64, a missing workspace
+    assert L.zt_proj_forward(p, p, p, p, 1 << 30, 1, 8, 100, 64, None) == 1 and "multiples of 64" in zt.lib.last_error()
+    assert L.zt_proj_backward(p, p, p, p, p, None, 0, 1, 8, 64, 64, None) == 1 and "workspace" in zt.lib.last_error()
+    assert L.zt_proj_workspace_bytes(2, 100, 128, 64) > 2 * (2 * 100 * 128 + 128 * 64 + 2 * 100 * 64)
+    assert L.zt_proj_workspace_bytes(0, 100, 128, 64) == 0
+    # reserve: the geometry checks of every launching call
+    assert L.zt_attn_reserve(1, 0, 4, 2, 64) == 1 and "T 0" in zt.lib.last_error()
+    assert L.zt_attn_reserve(1, 128, 5, 2, 64) == 1 and "group" in zt.lib.last_error()
+    assert L.zt_attn_arena_bytes() >= 0
+    L.zt_attn_set_verbose(1)
+
+
 def test_no_cpu_fallback_without_a_device(zt):
     """A well-formed call on a machine without a GPU is refused, never computed on the host."""
     import torch
