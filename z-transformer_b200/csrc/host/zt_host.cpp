@@ -59,6 +59,13 @@ Error Attn::init(uint64_t t_, uint64_t n_heads_, uint64_t n_kv_heads_, uint64_t 
             return e;
         }
     }
+    // The library's own scratch for this shape (the operand planes of its tensor-core kernels live in a per-device
+    // arena, the reference's signatures having no workspace argument) is sized here, with the holder's buffers, so
+    // that forward() and backward() never allocate: the one line a maintainer adds to device.Attn.init.
+    if (zt_attn_reserve(1, ct, ch, ckv, cd) != 0) {
+        deinitPartial(N_BUFFERS);
+        return Error::DeviceAllocFailed;
+    }
     t = t_, n_heads = n_heads_, n_kv_heads = n_kv_heads_, dim = dim_;
     c_t = ct, c_heads = ch, c_kv_heads = ckv, c_dim = cd;
     return Error::Ok;

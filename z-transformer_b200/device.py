@@ -121,6 +121,13 @@ class Attn:
         except RuntimeError as e:  # torch's allocator failing is cudaMalloc failing
             self._buf.clear()
             raise DeviceAllocFailed(str(e)) from e
+        # the library's own scratch for this shape is sized with the holder's buffers, so that forward() and
+        # backward() never allocate (the one line a maintainer adds to device.Attn.init)
+        if self.device.type == "cuda":
+            with torch.cuda.device(self.device):
+                if L.zt_attn_reserve(1, self.c_t, self.c_heads, self.c_kv_heads, self.c_dim) != 0:
+                    self._buf.clear()
+                    raise DeviceAllocFailed(_lib.last_error())
 
     def __getattr__(self, name):
         buf = self.__dict__.get("_buf", {})
