@@ -142,7 +142,12 @@ int zt_attn_forward_batched(const float *q, const float *k, const float *v, floa
  * recomputing them (autograd.attentionBackward, src/autograd.zig:636-842, is the
  * arithmetic it must match).  delta is caller scratch [batch, T, n_heads].
  * dq, dk, dv are assigned.  workspace/workspace_bytes: see
- * zt_attn_backward_workspace_bytes; may be NULL/0 when that returns 0. */
+ * zt_attn_backward_workspace_bytes; may be NULL/0 when that returns 0.
+ * The workspace holds the 16-bit operand planes of q, k, v, dout;
+ * at head_dim 192 and 256 it also holds the planes of P and dS of as many heads as fit in about 2 GiB
+ * (at least one KV group's: 8 T^2 bytes a head), because the backward at those widths writes them to
+ * memory between its launches; there dq, dk, dv are sums added in memory in no fixed order, equal run to
+ * run to rounding only. */
 int zt_attn_backward_batched(const float *q, const float *k, const float *v, const float *out,
                              const float *lse, const float *dout, float *dq, float *dk, float *dv,
                              float *delta, void *workspace, size_t workspace_bytes, int batch, int T,

@@ -494,6 +494,69 @@ def test_tensor_core_backward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D):
         close(dv[b].cpu().numpy(), rdv, f"item {b} dv")
 
 
+TC_BWD_WIDE_SHAPES = [  # B, T, H, Hkv, D, keep -- head_dim 256, and 192 zero-padded to it: the unfused form
+    (1, 128, 2, 1, 256, False), (2, 200, 4, 2, 192, False), (1, 513, 4, 1, 256, True), (1, 320, 3, 3, 192, True),
+    (2, 704, 4, 2, 256, False),
+    # contractions longer than one piece of 1024: several CTAs add into one output tile
+    (1, 1300, 4, 2, 256, True), (1, 2304, 4, 1, 192, False),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,keep", TC_BWD_WIDE_SHAPES)
+def test_wide_head_backward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, keep):
+    """head_dim 192 and 256: P and dS go through memory as operand planes (bwd_wide_scores), dQ, dK, dV are three
+    products over them (gemm_tri).  With and without the planes of q, k, v that the forward leaves in the workspace."""
+    q = oracle.fill_normal((B, T, H * D), 61, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 61, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 61, 2)
+    do = oracle.fill_normal((B, T, H * D), 61, 3)
+    zt.lib.load().zt_attn_set_path(0)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    ws = zt.BackwardWorkspace(B, T, H, Hkv, D, dev)
+    assert ws.nbytes > 0
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True, keep=ws if keep else None)
+    assert (ws.token != 0) == keep
+    dq, dk, dv = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D, workspace=ws, kept=keep)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05"
+    assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    for b in range(B):
+        rdq, rdk, rdv = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D, threads=8)
+        close(dq[b].cpu().numpy(), rdq, f"item {b} dq")
+        close(dk[b].cpu().numpy(), rdk, f"item {b} dk")
+        close(dv[b].cpu().numpy(), rdv, f"item {b} dv")
+
+
+def test_wide_head_backward_rows_of_very_different_size(zt, dev, oracle):
+    """The wide-head backward scales dS per query row and moves the row's factor onto a second copy of Q for dK (whose
+    contraction runs across rows).  Rows of dout from 1e-4 to 1e2 times the rest -- 2^20, beyond the 2^12 the factor
+    may span, and inside what the planes of dout hold (one scale per KV group: rows 2^25 below the largest are
+    lost to the f16 split whatever dS does) -- and an all-zero row: every KV group against its own largest gradient,
+    and each row of dq against its own size."""
+    T, H, Hkv, D = 384, 4, 2, 256
+    q, k, v, do = normal_inputs(oracle, T, H, Hkv, D, 64)
+    fac = np.ones(T, np.float32)
+    fac[5::7] = 1e-2
+    fac[6::11] = 1e2
+    fac[3::13] = 1e-4
+    do *= fac[:, None]
+    do[17] = 0.0
+    o, lse, dq, dk, dv = run_fwd_bwd(zt, dev, q, k, v, do, H, Hkv, D)
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    rdq, rdk, rdv = oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)
+    g = H // Hkv
+    for name, got, ref, w in (("dk", dk, rdk, D), ("dv", dv, rdv, D)):
+        for kv in range(Hkv):
+            a, r = got[:, kv * w:(kv + 1) * w].astype(np.float64), ref[:, kv * w:(kv + 1) * w].astype(np.float64)
+            assert np.max(np.abs(a - r)) <= 1e-4 * np.max(np.abs(r)), (name, kv)
+    # dq row by row: a row's gradient scales with that row of dout, and so does the bar (its absolute part covers
+    # rows whose gradient cancels, like row 0, where dS = p (dp - delta) is zero in exact arithmetic)
+    a, r = dq.astype(np.float64), rdq.astype(np.float64)
+    row_top = np.max(np.abs(r), axis=1)
+    assert np.all(np.max(np.abs(a - r), axis=1) <= 1e-4 * row_top + 1e-5 * fac), "dq"
+    assert np.all(a[17] == 0.0)
+
+
 def test_tensor_core_backward_uneven_magnitudes(zt, dev, oracle):
     """Heads and tensors of very different scale: the per-(sequence, KV group) power-of-two scaling of
     the 16-bit split must keep every group inside the tolerance."""
@@ -547,6 +610,8 @@ def test_attn_pipeline_matches_batched_calls(zt, dev):
 ROPE_SHAPES = [  # B, T, H, Hkv, D, pos -- tensor-core shapes (the rotation rides in the pre-pass) and CUDA-core ones
     (1, 256, 8, 2, 128, 0), (2, 200, 4, 2, 64, 37), (1, 384, 4, 1, 32, 5), (1, 150, 6, 3, 128, 1000),
     (1, 96, 4, 2, 64, 3), (1, 160, 8, 2, 96, 11),
+    # head_dim 256 and 192: rotated copies, then the unfused tensor-core backward
+    (1, 200, 4, 2, 256, 9), (2, 320, 4, 1, 192, 0),
 ]
 
 
@@ -569,7 +634,8 @@ def test_rope_fused_forward_backward_matches_oracle(zt, dev, oracle, B, T, H, Hk
     torch.cuda.synchronize()
     assert zt.lib.tc_status() == 0
     for a, b_ in zip((dq, dk, dv), again):
-        assert torch.equal(a, b_)
+        # (the wide heads' dk, dv are sums that several CTAs add in memory, in no fixed order)
+        assert torch.equal(a, b_) if D <= 128 else bool(((a - b_).abs() <= 2e-6 + 2e-5 * a.abs()).all())
     for b in range(B):
         qr, kr = oracle.rope_forward(q[b], pos, D), oracle.rope_forward(k[b], pos, D)
         ro, rl = oracle.attention_forward(qr, kr, v[b], H, Hkv, D, want_lse=True, threads=4)
@@ -733,7 +799,8 @@ def _violations(got, ref):
 @pytest.mark.parametrize("which,mag", [(("do",), 1e2), (("v",), 1e2), (("v", "do"), 1e2), (("v",), 1e3), (("do",), 1e3),
                                        (("v", "do"), 1e3)],
                          ids=["dout-x100", "v-x100", "v+dout-x100", "v-x1000", "dout-x1000", "v+dout-x1000"])
-def test_tensor_core_backward_outliers_inside_a_kv_group(zt, dev, oracle, which, mag):
+@pytest.mark.parametrize("D", [128, 256])
+def test_tensor_core_backward_outliers_inside_a_kv_group(zt, dev, oracle, which, mag, D):
     """The operand planes carry one power-of-two scale per (sequence, KV group), so what stresses the f16 split is a
     wide range INSIDE a group: here one element in a thousand of v and/or dout is 100 or 1000 times the rest (all
     in one KV group).  dS is scaled per query row in the dQ kernel and from the group's measured maximum in the
@@ -743,7 +810,7 @@ def test_tensor_core_backward_outliers_inside_a_kv_group(zt, dev, oracle, which,
     per-row scale a quarter of dq and a third of dk missed it at a HUNDRED times).  Outliers in q and k are a
     different matter: scores of 10^3 and more lose |score| 2^-23 in any f32 accumulation, on the CUDA-core path
     and in the reference's own kernels alike, and are not this library's to fix."""
-    T, H, Hkv, D = 512, 4, 1, 128
+    T, H, Hkv = 512, 4, 1
     q, k, v, do = _outlier_inputs(T, H, Hkv, D, which, mag)
     ref_o, ref_lse = oracle.attention_forward(q, k, v, H, Hkv, D, want_lse=True, threads=8)
     ref = dict(zip(("dq", "dk", "dv"), oracle.attention_backward(q, k, v, do, H, Hkv, D, threads=8)))
@@ -755,12 +822,20 @@ def test_tensor_core_backward_outliers_inside_a_kv_group(zt, dev, oracle, which,
         finally:
             zt.lib.load().zt_attn_set_path(0)
         assert zt.lib.last_path() == ("tcgen05" if path == 0 else "simt")
-        close(o, ref_o, "out")
+        if D <= 128 or mag <= 1e2:
+            close(o, ref_o, "out")
+        else:  # (v a thousand times the bulk at 256 columns: 3 of 524288 elements of out miss the bar, near zeros)
+            assert _violations(o, ref_o) <= 8
         close(lse, ref_lse, "lse")
         counts[path] = {n: _violations(x, ref[n]) for n, x in (("dq", dq), ("dk", dk), ("dv", dv))}
     assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
     n_q, n_k = T * H * D, T * Hkv * D
-    if mag <= 1e2:
+    if D == 256:
+        # the unfused form, twice the terms per sum.  Measured at a hundred times: dq 0..156 of 524288 (CUDA cores
+        # 0..53), dk <= 4, dv 0; at a thousand: dq <= 317 (7), dk <= 134 (8), dv <= 6 (0)
+        lim = (2000, 16384, 65536) if mag <= 1e2 else (1000, 100, 1000)
+        assert counts[0]["dq"] <= n_q // lim[0] and counts[0]["dk"] <= n_k // lim[1] and counts[0]["dv"] <= n_k // lim[2], counts
+    elif mag <= 1e2:
         assert counts[0]["dq"] == 0 and counts[0]["dv"] <= 2 and counts[0]["dk"] <= 8, counts
     else:
         # measured: dq 1..64, dk 40..335, dv 0..33 of 262144 / 65536 elements (CUDA cores: 0..2, 6..33, 0)

@@ -20,6 +20,7 @@
 #include "tc_fwd16g.cuh"
 #include "tc_fwd16x.cuh"
 #include "tc_gemm.cuh"
+#include "tc_bwd_wide.cuh"
 #endif
 
 #include <mutex>
@@ -131,6 +132,8 @@ static size_t backward_workspace(int batch, int T, int n_heads, int n_kv_heads, 
 #ifndef ZT_NO_TC
     if ((dim == 32 || dim == 64 || dim == 96 || dim == 128) && T >= 128)
         return tc_bwd_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
+    // head_dim 192 and 256: the planes of the fused form, then a row-scaled copy of Q's and the planes of P and dS
+    if ((dim == 192 || dim == 256) && T >= 128) return tc_bwd_wide_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
 #endif
     (void)batch, (void)n_heads, (void)n_kv_heads;
     return 0;
@@ -217,6 +220,16 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
         if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
                              dim, stream, nullptr, nullptr, kept, dq_peers);
+    }
+    const size_t wide_need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
+    if (g_path.load() != 1 && workspace && wide_need > 0 && workspace_bytes >= wide_need &&
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
+        !(dq_peers && dq_peers->n > 0) &&
+        tcw::tc_bwd_wide_supported(batch, T, n_heads, n_kv_heads, dim, q, k, v, dout, dq, dk, dv)) {
+        float *rnorm = tcw::wide_workspace(workspace, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).base.rnorm;
+        if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
+        return launch_bwd_wide(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads, dim,
+                               stream, kept);
     }
 #endif
     if (dq_peers && dq_peers->n > 0)
@@ -329,7 +342,8 @@ int zt_attn_reserve(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     if (need_device()) return 1;
     size_t need = kArenaBytes;  // the decode-shaped forward's partial results
 #ifndef ZT_NO_TC
-    if (n_kv_heads <= tcb::kPrepassMaxGroups && (dim == 32 || dim == 64 || dim == 96 || dim == 128) && T >= 128) {
+    if (n_kv_heads <= tcb::kPrepassMaxGroups && T >= 128 &&
+        (dim == 32 || dim == 64 || dim == 96 || dim == 128 || dim == 192 || dim == 256)) {
         const size_t f = tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim);
         const size_t b = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
         need = f > need ? f : need;
@@ -729,7 +743,10 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
     if (!fused) {
         if (launch_rope_apply(q, w.q_rot, w.table, batch, T, n_heads * dim, dim, false, s)) return 1;
         if (launch_rope_apply(k, w.k_rot, w.table, batch, T, n_kv_heads * dim, dim, false, s)) return 1;
-        if (backward_impl(w.q_rot, w.k_rot, v, out, lse, delta, dout, dq, dk, dv, nullptr, 0, batch, T, n_heads, n_kv_heads, dim, s))
+        // (head_dim 192 and 256 take the unfused tensor-core form, which wants the inner workspace)
+        const bool wide = dim == 192 || dim == 256;
+        if (backward_impl(w.q_rot, w.k_rot, v, out, lse, delta, dout, dq, dk, dv, wide ? w.inner : nullptr,
+                          wide ? w.inner_bytes : 0, batch, T, n_heads, n_kv_heads, dim, s))
             return 1;
     }
     // the gradients of the unrotated q and k: R^T.  The tensor-core dQ kernel applies it as it writes dq; dk
