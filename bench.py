@@ -509,12 +509,12 @@ def run_ours(args):
     Fl = fwd_flops(Bl, T, H, D)  # of one rank's launch
 
     # ---- roofline of the dominant kernel (by summed device time over the timed region) ----------
-    # Algorithmic operations credited per launch: forward 2 GEMMs = F; key-outer backward kernel
-    # S, dP, dV, dK = 2 F; query-outer backward kernel dQ = 0.5 F (its recomputed S and dP are
-    # overhead, not credited); together the backward's 2.5 F.
+    # Algorithmic operations credited per launch: forward 2 GEMMs = F; the fused backward kernel S, dP, dV, dK, dQ
+    # = 2.5 F.  In the two-kernel form the key-outer kernel (S, dP, dV, dK) = 2 F and the query-outer one dQ = 0.5 F
+    # (its recomputed S and dP are overhead, not credited).
     credit = {"attn_fwd_simt": Fl, "attn_fwd_tc": Fl, "attn_fwd_tc16": Fl, "attn_fwd_tc16g": Fl, "attn_fwd_tc16x": Fl,
               "attn_bwd_dkdv_simt": 2.0 * Fl, "attn_bwd_dq_simt": 0.5 * Fl, "attn_bwd_dkdv_tc": 2.0 * Fl,
-              "attn_bwd_dq_tc": 0.5 * Fl}
+              "attn_bwd_dq_tc": 0.5 * Fl, "attn_bwd_fused_tc": 2.5 * Fl}
     total_kernel_ms = sum(ms for _, ms in kernels.values()) or 1.0
     klist = []
     for name, (n, ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
@@ -540,17 +540,23 @@ def run_ours(args):
                     "burst_peak": tf32_burst,
                     "step_frac": step_tflops / tf32_sust, "step_frac_of_burst_peak": step_tflops / tf32_burst}
 
-    # MMA work issued per step by the f16-split kernels: every credited product is three kind::f16 MMAs, and
-    # the dQ kernel recomputes S and dP.  Forward 2 GEMMs, dK/dV kernel 4, dQ kernel 3, of 0.5 F each.
+    # MMA work issued per step by the f16-split kernels: every credited product is three kind::f16 MMAs.  Forward 2
+    # products of 0.5 F each; the fused backward 5 (the two-kernel form 4 + 3: its dQ kernel recomputes S and dP).
     issued = None
-    if {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels) and ({"attn_fwd_tc16", "attn_fwd_tc16g"} & set(kernels)):
-        issued_flop = 3.0 * (2 + 4 + 3) * 0.5 * Fl
+    n_products = None
+    if {"attn_fwd_tc16", "attn_fwd_tc16g"} & set(kernels):
+        if "attn_bwd_fused_tc" in kernels:
+            n_products = 2 + 5
+        elif {"attn_bwd_dkdv_tc", "attn_bwd_dq_tc"} <= set(kernels):
+            n_products = 2 + 4 + 3
+    if n_products:
+        issued_flop = 3.0 * n_products * 0.5 * Fl
         t_s = (main.get("compute_ms") or ms_step) * 1e-3
         issued = {"flop_per_step": issued_flop, "f16_tflops": issued_flop / t_s / 1e12,
                   "of_bf16_sustained_peak": issued_flop / t_s / 1e12 / peaks["bf16_tflops_sustained"],
                   "credited_over_issued": 3.5 * Fl / issued_flop,
-                  "note": "kind::f16 MMA flops issued (3 per credited product, S and dP recomputed in the dQ "
-                          "kernel, masked halves of diagonal tiles not counted) against the measured bf16 GEMM peak"}
+                  "note": "kind::f16 MMA flops issued (3 per credited product; masked halves of diagonal tiles not "
+                          "counted) against the measured bf16 GEMM peak"}
 
     phases = None
     if strong:

@@ -51,8 +51,12 @@ def _rank_main(rank, world, port, results):
         dv_all = zt.sharding.gather_batch(dv, world)            # every peer's kernels have finished writing to it
         torch.cuda.synchronize()
         ok &= torch.equal(g_out.gathered.view(B, T, H * D), o_ref)
-        ok &= torch.equal(g_dq.gathered.view(B, T, H * D), dq_ref)
-        ok &= torch.equal(dk_all, dk_ref) and torch.equal(dv_all, dv_ref)
+        # (the references come from the fused backward; the call that also stores dq into the peers runs the
+        # two-kernel form, whose dS is scaled differently: equal to rounding, not bit for bit)
+        def near(a, b):
+            return bool(((a - b).abs() <= 2e-6 + 2e-5 * b.abs()).all())
+        ok &= near(g_dq.gathered.view(B, T, H * D), dq_ref)
+        ok &= near(dk_all, dk_ref) and near(dv_all, dv_ref)
     ok &= zt.lib.tc_status() == 0
     results[rank] = bool(ok)
     dist.barrier()

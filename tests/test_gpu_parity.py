@@ -39,6 +39,17 @@ def cu(x, dev):
     return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
 
 
+def same_gradients(got, want, D):
+    """dq, dk, dv of two runs on the same inputs.  Bit for bit, except dq at head_dim 96 and 128 (the fused backward:
+    every key tile's CTA adds its share of dq in memory, in no fixed order) and all three at 192 and 256 (the unfused
+    one): those agree to rounding."""
+    for name, a, b in zip(("dq", "dk", "dv"), got, want):
+        if D in (192, 256) or (D in (96, 128) and name == "dq"):
+            assert bool(((a - b).abs() <= 2e-6 + 2e-5 * b.abs()).all()), name
+        else:
+            assert torch.equal(a, b), name
+
+
 def lcg_inputs(oracle, T, H, Hkv, D):
     q = oracle.fill_lcg(T * H * D, 0xBEEF).reshape(T, H * D)
     k = oracle.fill_lcg(T * Hkv * D, 0x1234).reshape(T, Hkv * D)
@@ -633,9 +644,7 @@ def test_rope_fused_forward_backward_matches_oracle(zt, dev, oracle, B, T, H, Hk
     again = zt.attention_backward_rope(tq, tk, tv, o, lse, tdo, H, Hkv, D, pos=pos, workspace=ws)
     torch.cuda.synchronize()
     assert zt.lib.tc_status() == 0
-    for a, b_ in zip((dq, dk, dv), again):
-        # (the wide heads' dk, dv are sums that several CTAs add in memory, in no fixed order)
-        assert torch.equal(a, b_) if D <= 128 else bool(((a - b_).abs() <= 2e-6 + 2e-5 * a.abs()).all())
+    same_gradients((dq, dk, dv), again, D)
     for b in range(B):
         qr, kr = oracle.rope_forward(q[b], pos, D), oracle.rope_forward(k[b], pos, D)
         ro, rl = oracle.attention_forward(qr, kr, v[b], H, Hkv, D, want_lse=True, threads=4)
@@ -665,8 +674,8 @@ def test_rope_calls_refuse_bad_arguments(zt, dev):
 
 @pytest.mark.parametrize("path", [0, 7, 6], ids=["auto", "2heads", "1head"])
 def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
-    """zt_attn_forward_batched_keep + zt_attn_backward_batched_kept (same workspace, the forward's token) give bit
-    for bit what the unpaired calls give.  Reuse happens only on the caller's word: a plain backward with that
+    """zt_attn_forward_batched_keep + zt_attn_backward_batched_kept (same workspace, the forward's token) give what the
+    unpaired calls give (bit for bit, dq to rounding: see same_gradients).  Reuse happens only on the caller's word: a plain backward with that
     workspace converts everything again, whatever the pointers are; a spent or stale token is refused."""
     B, T, H, Hkv, D = 2, 300, 8, 2, 128
     g = torch.Generator(device=dev).manual_seed(9)
@@ -683,8 +692,7 @@ def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
             got = zt.attention_backward(q, k, v, o1, l1, do, H, Hkv, D, workspace=ws, kept=True)
             assert ws.token == 0
             assert torch.equal(o1, o0) and torch.equal(l1, l0)
-            for a, b in zip(got, ref):
-                assert torch.equal(a, b)
+            same_gradients(got, ref, D)
         # q is rewritten IN PLACE between the keep and a plain backward (same pointers, same workspace): the
         # plain backward never looks at kept planes, so the gradients are those of the new q
         qm = q.clone()
@@ -693,8 +701,7 @@ def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
         o2, l2 = zt.attention_forward(qm, k, v, H, Hkv, D, want_lse=True)
         want2 = zt.attention_backward(qm, k, v, o2, l2, do, H, Hkv, D)
         got2 = zt.attention_backward(qm, k, v, o2, l2, do, H, Hkv, D, workspace=ws)
-        for a, b in zip(got2, want2):
-            assert torch.equal(a, b)
+        same_gradients(got2, want2, D)
         # that backward rewrote the workspace: the token of the keep before it is stale now, and is refused
         stale = ws.token
         assert stale != 0
@@ -704,8 +711,7 @@ def test_forward_keep_hands_its_planes_to_the_backward(zt, dev, path):
         zt.lib.load().zt_attn_set_verbose(1)
         # and without a token the original tensors give the original gradients
         got3 = zt.attention_backward(q, k, v, o0, l0, do, H, Hkv, D, workspace=ws)
-        for a, b in zip(got3, ref):
-            assert torch.equal(a, b)
+        same_gradients(got3, ref, D)
     finally:
         zt.lib.load().zt_attn_set_path(0)
         zt.lib.load().zt_attn_set_verbose(1)
@@ -772,8 +778,8 @@ def test_training_pair_is_capturable_in_a_cuda_graph(zt, dev):
     for _ in range(3):
         graph.replay()
     torch.cuda.synchronize()
-    for got, ref in zip((out, lse, dq, dk, dv), want):
-        assert torch.equal(got, ref)
+    assert torch.equal(out, want[0]) and torch.equal(lse, want[1])
+    same_gradients((dq, dk, dv), want[2:], D)
     assert zt.lib.tc_status() == 0
 
 

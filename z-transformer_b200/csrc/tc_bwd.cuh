@@ -1247,6 +1247,7 @@ struct BwdWorkspace {
     uint32_t *amax_q, *amax_k, *amax_v, *amax_do, *vnmax, *dsmax;  // six [batch, n_kv_heads] arrays, in this order
     __half *q_planes, *do_planes, *k_planes, *v_planes;
     float *rnorm;  // [batch, T, n_heads]
+    __half *qs_planes;  // the row-scaled copy of q's planes (the fused and the wide-head backward read it for dK)
     size_t total_bytes, amax_bytes;
 };
 
@@ -1267,6 +1268,7 @@ inline BwdWorkspace bwd_workspace(void *base, int batch, int T, int n_heads, int
     w.k_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
     w.v_planes = reinterpret_cast<__half *>(c + off), off += up(kh);
     w.rnorm = reinterpret_cast<float *>(c + off), off += up((size_t)batch * T * n_heads * sizeof(float));
+    w.qs_planes = reinterpret_cast<__half *>(c + off), off += up(qh);
     w.total_bytes = off;
     return w;
 }
@@ -1312,69 +1314,6 @@ inline int tc_tile_dim(int dim) { return dim == 32 ? 64 : (dim == 96 ? 128 : (di
 
 inline size_t tc_bwd_workspace_bytes(int batch, int T, int n_heads, int n_kv_heads, int dim) {
     return tcb::bwd_workspace(nullptr, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).total_bytes;
-}
-
-// delta must already hold sum_j dout*out.  dq, dk, dv are assigned.
-inline int launch_bwd_tc(const float *q, const float *k, const float *v, const float *dout, const float *lse,
-                         const float *delta, float *dq, float *dk, float *dv, void *workspace, int batch, int T,
-                         int n_heads, int n_kv_heads, int dim, cudaStream_t stream, const float2 *rope = nullptr,
-                         const float2 *rope_t = nullptr, bool qkv_planes_kept = false, const PeerList *dq_peers = nullptr) {
-    using namespace tcb;
-    const int td = tc_tile_dim(dim);  // the kernels' D; the planes' head width
-    const BwdWorkspace w = bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, td);
-    const int group = n_heads / n_kv_heads;
-    const int wq_src = n_heads * dim, wkv_src = n_kv_heads * dim;
-    const int wq = n_heads * td, wkv = n_kv_heads * td;
-    // With the planes of q, k, v kept by the forward (and their maxima beside them), only dout is converted.
-    const size_t n_amax = (size_t)batch * n_kv_heads;
-    // (with kept planes the maxima of q, k, v stay; those of dout, the row norms of v and max |dS| start from zero)
-    if (cudaMemsetAsync(qkv_planes_kept ? w.amax_do : w.amax_q, 0,
-                        qkv_planes_kept ? 3 * n_amax * sizeof(uint32_t) : w.amax_bytes, stream) != cudaSuccess) {
-        cudaGetLastError();
-        return refuse("could not clear the backward workspace header");
-    }
-    PrepassArgs pa{};
-    pa.batch = batch, pa.T = T;
-    pa.t[0] = {dout, w.amax_do, w.do_planes, wq_src, group * dim, dim, td, nullptr};
-    pa.n = 1;
-    if (!qkv_planes_kept) {
-        pa.t[1] = {q, w.amax_q, w.q_planes, wq_src, group * dim, dim, td, rope};
-        pa.t[2] = {k, w.amax_k, w.k_planes, wkv_src, dim, dim, td, rope};
-        pa.t[3] = {v, w.amax_v, w.v_planes, wkv_src, dim, dim, td, nullptr};
-        pa.n = 4;
-    }
-    if (launch_prepass(pa, stream)) return 1;
-    {
-        const dim3 gv((unsigned)((T + 255) / 256), (unsigned)n_kv_heads, (unsigned)batch);
-        if (ZT_LAUNCH("bwd_vnorm_kernel", stream, (bwd_vnorm_kernel<<<gv, 256, 0, stream>>>(v, w.vnmax, T, n_kv_heads, dim))))
-            return 1;
-    }
-    BwdMaps m;
-    if (!make_half_tile_map(&m.k128, w.k_planes, 2 * batch, T, wkv, td, 128) ||
-        !make_half_tile_map(&m.v128, w.v_planes, 2 * batch, T, wkv, td, 128) ||
-        !make_half_tile_map(&m.q64, w.q_planes, 2 * batch, T, wq, td, 64) ||
-        !make_half_tile_map(&m.g64, w.do_planes, 2 * batch, T, wq, td, 64) ||
-        !make_half_tile_map(&m.k64, w.k_planes, 2 * batch, T, wkv, td, 64) ||
-        !make_half_tile_map(&m.v64, w.v_planes, 2 * batch, T, wkv, td, 64) ||
-        !make_half_tile_map(&m.q128, w.q_planes, 2 * batch, T, wq, td, 128) ||
-        !make_half_tile_map(&m.g128, w.do_planes, 2 * batch, T, wq, td, 128))
-        return refuse("the TMA tensor maps for the backward could not be encoded.");
-    BwdParams p{};
-    p.lse = lse, p.delta = delta;
-    p.k_planes = w.k_planes, p.v_planes = w.v_planes, p.q_planes = w.q_planes, p.do_planes = w.do_planes;
-    p.amax_q = w.amax_q, p.amax_k = w.amax_k, p.amax_v = w.amax_v, p.amax_do = w.amax_do;
-    p.rnorm = w.rnorm, p.vnmax = w.vnmax, p.dsmax = w.dsmax;
-    p.dq = dq, p.dk = dk, p.dv = dv;
-    if (dq_peers) p.dq_peers = *dq_peers;
-    p.batch = batch, p.T = T, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
-    p.dim_out = dim;
-    p.rope_t = rope_t;
-    p.scale = 1.0f / sqrtf((float)dim), p.scale_log2 = kLog2e / sqrtf((float)dim);
-    // P in [0, 1] is split after a multiplication by 2^10 (its low piece then stays a normal f16 down to p ~ 2^-14).
-    // dS is scaled inside the kernels (see "The scale of dS" above).
-    p.p_scale = ldexpf(1.0f, 10);
-    g_last_path = "tcgen05";
-    return td == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
 }
 
 }  // namespace zt

@@ -495,7 +495,6 @@ constexpr size_t kScratchLimit = (size_t)16 << 30;   // one KV group's planes be
 
 struct WideWorkspace {
     tcb::BwdWorkspace base;   // the fused backward's layout first: the forward may have left q, k, v planes there
-    __half *qs_planes;        // the row-scaled copy of Q's planes
     __half *p_planes, *ds_planes;
     int Tp, unit_cap;
     size_t total_bytes;
@@ -520,7 +519,6 @@ inline WideWorkspace wide_workspace(void *ws, int batch, int T, int n_heads, int
     w.unit_cap = wide_unit_cap(batch, T, n_heads, n_kv_heads);
     char *c = static_cast<char *>(ws);
     size_t off = w.base.total_bytes;
-    w.qs_planes = reinterpret_cast<__half *>(c + off), off += up((size_t)2 * batch * T * n_heads * td * sizeof(__half));
     const size_t planes = (size_t)2 * w.unit_cap * w.Tp * w.Tp * sizeof(__half);
     w.p_planes = reinterpret_cast<__half *>(c + off), off += up(planes);
     w.ds_planes = reinterpret_cast<__half *>(c + off), off += up(planes);
@@ -591,7 +589,7 @@ inline int launch_bwd_wide(const float *q, const float *k, const float *v, const
             return 1;
         const long long n8 = (long long)batch * T * wq / 8;
         if (ZT_LAUNCH("wide_qscaled_kernel", stream,
-                      (wide_qscaled_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(w.q_planes, ww.qs_planes, w.rnorm, rnmax,
+                      (wide_qscaled_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(w.q_planes, w.qs_planes, w.rnorm, rnmax,
                                                                                              w.vnmax, batch, T, n_heads, n_kv_heads, td))))
             return 1;
     }
@@ -604,7 +602,7 @@ inline int launch_bwd_wide(const float *q, const float *k, const float *v, const
         !make_half_tile_map(&g_k, w.do_planes, 2 * batch, T, wq, 64, 128) ||
         !make_half_tile_map(&v_k, w.v_planes, 2 * batch, T, wkv, 64, 128) ||
         !make_half_tile_map(&k_n, w.k_planes, 2 * batch, T, wkv, 128, 64) ||
-        !make_half_tile_map(&qs_n, ww.qs_planes, 2 * batch, T, wq, 128, 64) ||
+        !make_half_tile_map(&qs_n, w.qs_planes, 2 * batch, T, wq, 128, 64) ||
         !make_half_tile_map(&g_n, w.do_planes, 2 * batch, T, wq, 128, 64) ||
         !make_half_tile_map(&ds_k, ww.ds_planes, 2 * cap, Tp, Tp, 64, 128) ||
         !make_half_tile_map(&ds_m, ww.ds_planes, 2 * cap, Tp, Tp, 128, 64) ||

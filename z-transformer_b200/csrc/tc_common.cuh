@@ -45,6 +45,14 @@ __device__ __forceinline__ void mbar_arrive_warp(uint64_t *bar) {
     __syncwarp();
     if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
+// The same without the release: for hand-offs of TMEM contents only, which tcgen05.wait and the tcgen05 fences
+// order by themselves.  A releasing arrival also waits for the thread's earlier global stores and reductions
+// to be performed -- a round trip to L2 that the waiting tensor core has no use for.
+__device__ __forceinline__ void mbar_arrive_warp_relaxed(uint64_t *bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0)
+        asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");

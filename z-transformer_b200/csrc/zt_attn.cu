@@ -21,6 +21,7 @@
 #include "tc_fwd16x.cuh"
 #include "tc_gemm.cuh"
 #include "tc_bwd_wide.cuh"
+#include "tc_bwd_fused.cuh"
 #endif
 
 #include <mutex>
@@ -99,7 +100,7 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
     const long long kv_bs = (long long)n_keys * n_kv_heads * dim;
 #ifndef ZT_NO_TC
     const int path = g_path.load();
-    if ((path == 0 || path == 6 || path == 7) && n_kv_heads <= tcb::kPrepassMaxGroups &&
+    if ((path == 0 || path == 6 || path == 7 || path == 8) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, q_offset, n_keys, q, k, v, out)) {
         // The f16-split forward keeps its operand planes in the per-device arena (no entry point
         // of the forward takes a workspace); see device_arena for when that allocates.
@@ -113,7 +114,7 @@ static int forward_impl(const float *q, const float *k, const float *v, float *o
             return launch_fwd_tc16(q, k, v, out, lse, arena, batch, T, n_heads, n_kv_heads, dim, stream, nullptr, false,
                                    path == 6 ? 1 : (path == 7 ? 2 : 0));
     }
-    if ((path == 0 || path == 2 || path == 6 || path == 7) &&
+    if ((path == 0 || path == 2 || path == 6 || path == 7 || path == 8) &&
         tc_fwd_supported(batch, T, n_heads, n_kv_heads, dim, q_offset, n_keys, q, k, v, out)) {
         return launch_fwd_tc(q, k, v, out, lse, batch, T, n_heads, n_kv_heads, dim, stream);
     }
@@ -219,7 +220,7 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
         float *rnorm = tcb::bwd_workspace(workspace, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).rnorm;
         if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
         return launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads,
-                             dim, stream, nullptr, nullptr, kept, dq_peers);
+                             dim, stream, nullptr, nullptr, kept, dq_peers, g_path.load() == 8);
     }
     const size_t wide_need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
     if (g_path.load() != 1 && workspace && wide_need > 0 && workspace_bytes >= wide_need &&
@@ -304,7 +305,9 @@ size_t zt_attn_bwd_dkdv_shmem(int dim) { return 2u * (size_t)dim * sizeof(float)
 const char *zt_attn_last_error(void) { return g_last_error; }
 const char *zt_attn_last_path(void) { return g_last_path; }
 void zt_attn_set_verbose(int on) { g_verbose.store(on ? 1 : 0); }
-int zt_attn_set_path(int path) { return g_path.exchange((path == 1 || path == 2 || path == 6 || path == 7) ? path : 0); }
+int zt_attn_set_path(int path) {
+    return g_path.exchange((path == 1 || path == 2 || path == 6 || path == 7 || path == 8) ? path : 0);
+}
 unsigned long long zt_attn_launch_count(void) { return g_launches.load(); }
 
 int zt_attn_tc_status(int *host_status) {
@@ -523,7 +526,7 @@ static int forward_keep_impl(const float *q, const float *k, const float *v, flo
 #ifndef ZT_NO_TC
     const size_t need = backward_workspace(batch, T, n_heads, n_kv_heads, dim);
     const int keep_path = g_path.load();
-    if ((keep_path == 0 || keep_path == 6 || keep_path == 7) && need > 0 && workspace && workspace_bytes >= need &&
+    if ((keep_path == 0 || keep_path == 6 || keep_path == 7 || keep_path == 8) && need > 0 && workspace && workspace_bytes >= need &&
         (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out)) {
         if (launch_fwd_tc16(q, k, v, out, lse, workspace, batch, T, n_heads, n_kv_heads, dim, s, nullptr, true,
@@ -681,7 +684,7 @@ static int forward_rope_impl(const float *q, const float *k, const float *v, flo
     drop_kept_planes(w.inner);
     if (launch_rope_table(w.table, w.table_t, T, dim, pos, theta, s)) return 1;
 #ifndef ZT_NO_TC
-    if ((g_path.load() == 0) && n_kv_heads <= tcb::kPrepassMaxGroups &&
+    if ((g_path.load() == 0 || g_path.load() == 8) && n_kv_heads <= tcb::kPrepassMaxGroups &&
         tc_fwd16_supported(batch, T, dim, 0, T, q, k, v, out) &&
         w.inner_bytes >= tc_fwd16_workspace_bytes(batch, T, n_heads, n_kv_heads, dim)) {
         // the planes (rotated q and k among them) go where the backward keeps its own: the rope backward that
@@ -731,13 +734,15 @@ int zt_attn_backward_rope_batched(const float *q, const float *k, const float *v
 #ifndef ZT_NO_TC
     fused = g_path.load() != 1 && w.inner_bytes > 0 && n_kv_heads <= tcb::kPrepassMaxGroups &&
             tcb::tc_bwd_supported(batch, T, dim, q, k, v, dout, dq, dk, dv);
-    // the dQ kernel's epilogue rotates whole 16- or 32-column pieces: not at head_dim 96, whose halves are 48 wide
-    dq_in_kernel = fused && dim != 96;
+    // the dQ kernel's epilogue rotates whole 16- or 32-column pieces: not at head_dim 96, whose halves are 48 wide;
+    // and the fused backward adds partial sums into dq, which can only be rotated once they are complete
+    const bool two_kernels = g_path.load() == 8;
+    dq_in_kernel = fused && dim != 96 && !tc_bwd_takes_fused(dim, two_kernels, nullptr);
     if (fused && launch_delta(out, dout, delta, tcb::bwd_workspace(w.inner, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).rnorm,
                               (long long)batch * T * n_heads, dim, s))
         return 1;
     if (fused && launch_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, w.inner, batch, T, n_heads, n_kv_heads, dim, s,
-                               w.table, dq_in_kernel ? w.table_t : nullptr, kept))
+                               w.table, dq_in_kernel ? w.table_t : nullptr, kept, nullptr, two_kernels))
         return 1;
 #endif
     if (!fused) {
