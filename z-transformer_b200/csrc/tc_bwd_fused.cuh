@@ -58,8 +58,9 @@ __device__ __forceinline__ void fgive_up(FusedShared *sh, int code) {
 // K hi, K lo, V lo, dS hi + lo, two Q slots, one dO slot (each 32 KB at head_dim 128)
 __host__ __device__ constexpr size_t fused_smem_bytes() { return 7 * (size_t)(128 * 128 * 2) + sizeof(FusedShared); }
 
-// grid (n_kv_heads, ceil(T / 128), batch), 576 threads: 16 row warps, a TMA warp, an MMA warp.
-__global__ void __launch_bounds__(kKvThreads, 1)
+// grid (n_kv_heads, ceil(T / 128), batch), 608 threads: 16 row warps, a TMA warp, two MMA warps.
+constexpr int kFusedThreads = (kKvRowWarps + 3) * 32;
+__global__ void __launch_bounds__(kFusedThreads, 1)
     attn_bwd_fused_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap gmap,
                       const BwdParams p) {
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) mbar_init(&sh->full_q[i], 1), mbar_init(&sh->free_q[i], 1);
-        mbar_init(&sh->full_g, 1), mbar_init(&sh->free_g, 1);
+        mbar_init(&sh->full_g, 1), mbar_init(&sh->free_g, 2);  // (freed by two readers: dP^T and dV)
         mbar_init(&sh->k_full, 1);
         mbar_init(&sh->a_ready, kKvRowWarps);
         mbar_init(&sh->st_full, 1);
@@ -96,9 +97,9 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         mbar_init(&sh->dq_done, 1);
         mbar_init(&sh->dq_free, kKvRowWarps);
         mbar_init(&sh->ld_ready, kKvRowWarps);
-        mbar_init(&sh->flush_ready, 1);
+        mbar_init(&sh->flush_ready, 2);  // (dK's issuer and dV's)
         mbar_init(&sh->flush_done, kKvRowWarps);
-        mbar_init(&sh->all_done, 1);
+        mbar_init(&sh->all_done, 2);
         sh->abort = (smem_u32(smem) & 1023u) ? 60 : 0;
         if (sh->abort) atomicMax(&g_tc_status, 60);
         mbar_fence_init();
@@ -162,26 +163,22 @@ __global__ void __launch_bounds__(kKvThreads, 1)
         }
         __syncwarp();
     } else if (warp == kKvRowWarps + 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ MMA issuer of the P side: S^T and dV.
+        // Two threads issue this kernel's MMAs.  One thread issues a kind::f16 MMA of N <= 64 every ~50 clocks,
+        // which for the 96 MMAs of a step is as long as the tensor pipe needs to execute them; two threads
+        // together keep the pipe fed.  The split follows the TMEM buffers, so that every overwrite of a buffer
+        // is ordered by one thread's issue order: this one owns S^T / P^T (S^T(it+2) after dV(it+1)), the other
+        // dP^T / dS^T and dQ^T.  What crosses between them goes through the row threads' barriers.
         if (elect_one()) {
-            constexpr uint32_t id_s = idesc_f16(128, BQ, false, false);   // S^T, dP^T: A K-major (or TMEM), B K-major
-            constexpr uint32_t id_a = idesc_f16(128, D, false, true);     // dK, dV: A in TMEM, B the query tile N-major
-            constexpr uint32_t id_q = idesc_f16(128, BQ, true, true);     // dQ^T: A = K read M-major, B = dS^T N-major
-            bool ok = !sh->abort && fwait(&sh->k_full, 0, sh) && fwait(&sh->a_ready, 0, sh);
+            constexpr uint32_t id_s = idesc_f16(128, BQ, false, false);   // S^T: A = K, B = the query tile, both K-major
+            constexpr uint32_t id_a = idesc_f16(128, D, false, true);     // dV: A in TMEM, B the dO tile N-major
+            bool ok = !sh->abort && fwait(&sh->k_full, 0, sh);
             if (!ok) fgive_up(sh, 62);
             tc_fence_after();
             const uint64_t bkh = desc_kmajor(smem_u32(sKh)), bkl = desc_kmajor(smem_u32(sKl));
-            const uint64_t bvl = desc_kmajor(smem_u32(sVl));
-            const uint64_t mkh = desc_mnmajor_16b(smem_u32(sKh), 128 * 128), mkl = desc_mnmajor_16b(smem_u32(sKl), 128 * 128);
-            const uint64_t mdh = desc_mnmajor_16b(smem_u32(sDS), DSP), mdl = desc_mnmajor_16b(smem_u32(sDS) + DSP, DSP);
             const uint32_t q_u32 = smem_u32(sQ), g_u32 = smem_u32(sG);
             auto wait_q = [&](int j) -> bool {
                 if (!fwait(&sh->full_q[j & 1], (uint32_t)((j >> 1) & 1), sh)) return false;
-                tc_fence_after();
-                return true;
-            };
-            auto wait_g = [&](int j) -> bool {
-                if (!fwait(&sh->full_g, (uint32_t)(j & 1), sh)) return false;
                 tc_fence_after();
                 return true;
             };
@@ -201,8 +198,69 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                 }
                 mma_commit(&sh->st_full);
             };
-            // dP^T(j) = V dO^T
-            auto issue_dp = [&]() {
+            // dV(j) += P^T dO: P^T's 16-column windows hold hi halves in their first 8 columns, lo in the last 8.
+            // Waits for P^T(j) and for dO(j); `restart`: the accumulators were flushed after step j-1.
+            int n_flush = 0;
+            auto issue_dv = [&](int j, bool restart, bool flush_after) -> bool {
+                if (!fwait(&sh->p_ready, (uint32_t)(j & 1), sh) || !fwait(&sh->full_g, (uint32_t)(j & 1), sh)) return false;
+                if (restart && j > 0 && !fwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) return false;
+                tc_fence_after();
+                const uint64_t mgh = desc_mnmajor_16b(g_u32, BQ * 128), mgl = desc_mnmajor_16b(g_u32 + QP, BQ * 128);
+#pragma unroll
+                for (int kk = 0; kk < BQ / 16; ++kk) {
+                    const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
+                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16, dgh, id_a, (kk > 0 || !restart) ? 1u : 0u);
+                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16, dgl, id_a, 1);
+                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16 + 8, dgh, id_a, 1);
+                }
+                mma_commit(&sh->free_g);  // (one of two arrivals: the other issuer's dP^T(j) reads the same tile)
+                if (flush_after) {
+                    mma_commit(&sh->flush_ready);  // (one of two: the other issuer's dK(j))
+                    ++n_flush;
+                }
+                return true;
+            };
+            // walk.* describe step `it`; step it+1's restart flag is step it's flush flag
+            if (ok) {
+                if (!wait_q(0)) { fgive_up(sh, 63); ok = false; }
+                else {
+                    issue_st(0);
+                    if (!issue_dv(0, true, walk.flush)) { fgive_up(sh, 64); ok = false; }
+                    else if (n_it > 1) {
+                        if (!wait_q(1)) { fgive_up(sh, 63); ok = false; }
+                        else issue_st(1);
+                    }
+                }
+            }
+            for (int it = 0; ok && it + 1 < n_it; ++it) {
+                const bool restart = walk.flush;
+                walk.next();  // now step it+1
+                if (!issue_dv(it + 1, restart, walk.flush)) { fgive_up(sh, 64); break; }
+                if (it + 2 < n_it) {
+                    if (!wait_q(it + 2)) { fgive_up(sh, 63); break; }
+                    issue_st(it + 2);
+                }
+            }
+            mma_commit(&sh->all_done);  // (one of two)
+        }
+        __syncwarp();
+    } else if (warp == kKvRowWarps + 2) {
+        // ------------------------------------------------------------------ MMA issuer of the dS side: dP^T, dK, dQ^T
+        if (elect_one()) {
+            constexpr uint32_t id_s = idesc_f16(128, BQ, false, false);   // dP^T: A = V (TMEM hi, shared lo), B = the dO tile K-major
+            constexpr uint32_t id_a = idesc_f16(128, D, false, true);     // dK: A in TMEM, B the query tile N-major
+            constexpr uint32_t id_q = idesc_f16(128, BQ, true, true);     // dQ^T: A = K read M-major, B = dS^T N-major
+            bool ok = !sh->abort && fwait(&sh->k_full, 0, sh) && fwait(&sh->a_ready, 0, sh);
+            if (!ok) fgive_up(sh, 62);
+            tc_fence_after();
+            const uint64_t bvl = desc_kmajor(smem_u32(sVl));
+            const uint64_t mkh = desc_mnmajor_16b(smem_u32(sKh), 128 * 128), mkl = desc_mnmajor_16b(smem_u32(sKl), 128 * 128);
+            const uint64_t mdh = desc_mnmajor_16b(smem_u32(sDS), DSP), mdl = desc_mnmajor_16b(smem_u32(sDS) + DSP, DSP);
+            const uint32_t q_u32 = smem_u32(sQ), g_u32 = smem_u32(sG);
+            // dP^T(j) = V dO^T (waits for dO(j))
+            auto issue_dp = [&](int j) -> bool {
+                if (!fwait(&sh->full_g, (uint32_t)(j & 1), sh)) return false;
+                tc_fence_after();
                 const uint64_t bgh = desc_kmajor(g_u32), bgl = desc_kmajor(g_u32 + QP);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -214,38 +272,26 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                     mma_ts_f16(tmem + cDPT, tmem + cVh + kk * 8, dgl, id_s, 1);
                     mma_ss_f16(tmem + cDPT, dvl, dgh, id_s, 1);
                 }
+                mma_commit(&sh->free_g);  // (one of two arrivals: dV(j) reads the same tile)
                 mma_commit(&sh->dp_full);
+                return true;
             };
-            // dV += P^T dO: P^T's 16-column windows hold hi halves in their first 8 columns, lo in the last 8
-            auto issue_dv = [&](uint32_t acc0) {
-                const uint64_t mgh = desc_mnmajor_16b(g_u32, BQ * 128), mgl = desc_mnmajor_16b(g_u32 + QP, BQ * 128);
+            auto issue_dq = [&](int kk0) {
 #pragma unroll
-                for (int kk = 0; kk < BQ / 16; ++kk) {
-                    const uint64_t dgh = desc_advance(mgh, kk * 2048), dgl = desc_advance(mgl, kk * 2048);
-                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16, dgh, id_a, kk > 0 ? 1u : acc0);
-                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16, dgl, id_a, 1);
-                    mma_ts_f16(tmem + cDV, tmem + cST + kk * 16 + 8, dgh, id_a, 1);
+                for (int kk = kk0; kk < kk0 + 4; ++kk) {
+                    const uint64_t dkh = desc_advance(mkh, kk * 2048), dkl = desc_advance(mkl, kk * 2048);
+                    const uint64_t ddh = desc_advance(mdh, kk * 2048), ddl = desc_advance(mdl, kk * 2048);
+                    mma_ss_f16(tmem + cDQT, dkh, ddh, id_q, kk > 0);
+                    mma_ss_f16(tmem + cDQT, dkh, ddl, id_q, 1);
+                    mma_ss_f16(tmem + cDQT, dkl, ddh, id_q, 1);
                 }
-                mma_commit(&sh->free_g);
             };
             int n_flush = 0;
-            if (ok) {
-                if (!wait_q(0) || !wait_g(0)) { fgive_up(sh, 63); ok = false; }
-                else {
-                    issue_st(0), issue_dp();
-                    if (!fwait(&sh->p_ready, 0, sh)) { fgive_up(sh, 64); ok = false; }
-                    else {
-                        tc_fence_after();
-                        issue_dv(0u);
-                        if (n_it > 1) {
-                            if (!wait_q(1)) { fgive_up(sh, 63); ok = false; }
-                            else issue_st(1);
-                        }
-                    }
-                }
-            }
+            if (ok && !issue_dp(0)) { fgive_up(sh, 63); ok = false; }
             for (int it = 0; ok && it < n_it; ++it, walk.next()) {
                 if (!fwait(&sh->ds_ready, (uint32_t)(it & 1), sh)) { fgive_up(sh, 64); break; }
+                // the accumulators restart at a step after a flush: the row threads must have added them to memory
+                if (walk.fresh && it > 0 && !fwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { fgive_up(sh, 67); break; }
                 tc_fence_after();
                 {
                     // dK += dS^T Q~
@@ -259,50 +305,24 @@ __global__ void __launch_bounds__(kKvThreads, 1)
                         mma_ts_f16(tmem + cDK, tmem + cDPT + kk * 16, dql, id_a, 1);
                         mma_ts_f16(tmem + cDK, tmem + cDPT + kk * 16 + 8, dqh, id_a, 1);
                     }
-                    mma_commit(&sh->free_q[it & 1]);
+                    mma_commit(&sh->free_q[it & 1]);  // (S^T(it), the tile's other reader, retired before dS(it) could be formed)
+                    if (walk.flush) {
+                        mma_commit(&sh->flush_ready);  // (one of two: the other issuer's dV(it))
+                        ++n_flush;
+                    }
                 }
-                // dQ^T(it) = K^T dS^T over this CTA's 128 keys, in two halves with dP^T(it+1) between them.  After
-                // dP^T(it+1) the tensor core still has half of dQ^T(it), dV(it+1) and S^T(it+2) to do while the row threads
-                // form dS of step it+1 (the longest hand-off of a step); before it, the first half gives dO's one
-                // slot -- released by dV(it) only at the end of the last step -- the time to fill.
-                // dQ^T's columns must have been read out first.
+                // dQ^T(it) = K^T dS^T over this CTA's 128 keys, in two halves with dP^T(it+1) between them: after
+                // dP^T(it+1) this thread still has half of dQ^T(it) to issue while the row threads form dS of step
+                // it+1 (the longest hand-off of a step); before it, the first half gives dO's one slot -- released
+                // by dV(it) -- the time to fill.  dQ^T's columns must have been read out first.
                 if (it >= 1 && !fwait(&sh->dq_free, (uint32_t)((it - 1) & 1), sh)) { fgive_up(sh, 65); break; }
                 tc_fence_after();
-                auto issue_dq = [&](int kk0) {
-#pragma unroll
-                    for (int kk = kk0; kk < kk0 + 4; ++kk) {
-                        const uint64_t dkh = desc_advance(mkh, kk * 2048), dkl = desc_advance(mkl, kk * 2048);
-                        const uint64_t ddh = desc_advance(mdh, kk * 2048), ddl = desc_advance(mdl, kk * 2048);
-                        mma_ss_f16(tmem + cDQT, dkh, ddh, id_q, kk > 0);
-                        mma_ss_f16(tmem + cDQT, dkh, ddl, id_q, 1);
-                        mma_ss_f16(tmem + cDQT, dkl, ddh, id_q, 1);
-                    }
-                };
                 issue_dq(0);
-                if (it + 1 < n_it) {
-                    if (!wait_g(it + 1)) { fgive_up(sh, 63); break; }
-                    issue_dp();
-                }
+                if (it + 1 < n_it && !issue_dp(it + 1)) { fgive_up(sh, 63); break; }
                 issue_dq(4);
                 mma_commit(&sh->dq_done);  // dS^T(it) in shared memory has been read; dQ^T(it) can be read out
-                if (walk.flush) {
-                    mma_commit(&sh->flush_ready);
-                    ++n_flush;
-                }
-                if (it + 1 < n_it) {
-                    if (!fwait(&sh->p_ready, (uint32_t)((it + 1) & 1), sh)) { fgive_up(sh, 64); break; }
-                    // the accumulators restart at step it+1: the row threads must have added them to memory
-                    if (walk.flush && !fwait(&sh->flush_done, (uint32_t)((n_flush - 1) & 1), sh)) { fgive_up(sh, 67); break; }
-                    tc_fence_after();
-                    issue_dv(walk.flush ? 0u : 1u);
-                    if (it + 2 < n_it) {
-                        if (!wait_q(it + 2)) { fgive_up(sh, 63); break; }
-                        issue_st(it + 2);
-                    }
-                } else {
-                    mma_commit(&sh->all_done);
-                }
             }
+            mma_commit(&sh->all_done);  // (one of two)
         }
         __syncwarp();
     } else {
@@ -587,7 +607,7 @@ inline int launch_bwd_fused(const CUtensorMap &k128, const CUtensorMap &v128, co
     const size_t smem = fused_smem_bytes();
     if (optin_smem((const void *)attn_bwd_fused_tc, smem)) return 1;
     const dim3 grid((unsigned)p.n_kv_heads, (unsigned)((p.T + 127) / 128), (unsigned)p.batch);
-    return ZT_LAUNCH("attn_bwd_fused_tc", stream, (attn_bwd_fused_tc<<<grid, kKvThreads, smem, stream>>>(k128, v128, qs64, g64, p)));
+    return ZT_LAUNCH("attn_bwd_fused_tc", stream, (attn_bwd_fused_tc<<<grid, kFusedThreads, smem, stream>>>(k128, v128, qs64, g64, p)));
 }
 
 }  // namespace tcf
