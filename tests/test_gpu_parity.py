@@ -538,6 +538,37 @@ def test_wide_head_backward_matches_oracle(zt, dev, oracle, B, T, H, Hkv, D, kee
         close(dv[b].cpu().numpy(), rdv, f"item {b} dv")
 
 
+@pytest.mark.parametrize("B,T,H,Hkv,D", [(2, 513, 4, 2, 128), (1, 321, 6, 3, 96), (1, 704, 4, 2, 256), (2, 200, 4, 2, 192)])
+def test_backward_forms_of_path_8_match_oracle(zt, dev, oracle, B, T, H, Hkv, D):
+    """zt_attn_set_path(8): at head_dim 128 and 96 the two-kernel backward (dQ's kernel first, then dK/dV's: dq, dk, dv
+    bit-reproducible, the form that can also store dq into peers' memory); at 192 and 256 the scores kernel that
+    loads every operand per tile.  Both against the oracle, and against the default forms to rounding."""
+    q = oracle.fill_normal((B, T, H * D), 67, 0)
+    k = oracle.fill_normal((B, T, Hkv * D), 67, 1)
+    v = oracle.fill_normal((B, T, Hkv * D), 67, 2)
+    do = oracle.fill_normal((B, T, H * D), 67, 3)
+    tq, tk, tv, tdo = (cu(x, dev) for x in (q, k, v, do))
+    o, lse = zt.attention_forward(tq, tk, tv, H, Hkv, D, want_lse=True)
+    default = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    zt.lib.load().zt_attn_set_path(8)
+    try:
+        got = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+        again = zt.attention_backward(tq, tk, tv, o, lse, tdo, H, Hkv, D)
+    finally:
+        zt.lib.load().zt_attn_set_path(0)
+    torch.cuda.synchronize()
+    assert zt.lib.last_path() == "tcgen05" and zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0
+    for a, b_, c in zip(got, again, default):
+        if D <= 128:
+            assert torch.equal(a, b_)
+        assert bool(((a - c).abs() <= 4e-6 + 4e-5 * c.abs()).all())
+    for b in range(B):
+        rdq, rdk, rdv = oracle.attention_backward(q[b], k[b], v[b], do[b], H, Hkv, D, threads=8)
+        close(got[0][b].cpu().numpy(), rdq, f"item {b} dq")
+        close(got[1][b].cpu().numpy(), rdk, f"item {b} dk")
+        close(got[2][b].cpu().numpy(), rdv, f"item {b} dv")
+
+
 def test_wide_head_backward_rows_of_very_different_size(zt, dev, oracle):
     """The wide-head backward scales dS per query row and moves the row's factor onto a second copy of Q for dK (whose
     contraction runs across rows).  Rows of dout from 1e-4 to 1e2 times the rest -- 2^20, beyond the 2^12 the factor

@@ -230,7 +230,7 @@ static int backward_impl(const float *q, const float *k, const float *v, const f
         float *rnorm = tcw::wide_workspace(workspace, batch, T, n_heads, n_kv_heads, tc_tile_dim(dim)).base.rnorm;
         if (launch_delta(out, dout, delta, rnorm, (long long)batch * T * n_heads, dim, stream)) return 1;
         return launch_bwd_wide(q, k, v, dout, lse, delta, dq, dk, dv, workspace, batch, T, n_heads, n_kv_heads, dim,
-                               stream, kept);
+                               stream, kept, g_path.load() == 8);
     }
 #endif
     if (dq_peers && dq_peers->n > 0)
