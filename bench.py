@@ -328,10 +328,12 @@ def run_ours(args):
         """`steps` forward+backward passes over this rank's Bl sequences of Hl/Hkvl heads (device-resident inputs).
         gather: None, or "batch" / "heads": every rank ends each step with every rank's out, dq, dk, dv, in one of
         two ways (push):
-          "kernel"  out and dq (4/5 of the bytes) are not gathered by a collective: the kernels' epilogues store every
-                    row into all ranks' gathered tensors as they store it locally (peer stores over NVLink,
-                    zt_attn_*_peers); dk and dv, flushed many times per CTA, go by one NCCL all-gather on a second
-                    stream, which also tells a rank that its peers' kernels have finished writing to it.  Costs nothing
+          "kernel"  out (2/5 of the bytes) is not gathered by a collective: the forward's epilogue stores every row into
+                    all ranks' gathered tensors as it stores it locally (peer stores over NVLink,
+                    zt_attn_forward_batched_keep_peers); dq + dk + dv go by one NCCL all-gather on a second stream,
+                    which also tells a rank that its peers' kernels have finished writing to it.  (The backward that
+                    stores dq into peers as well, zt_attn_backward_batched_kept_peers, is the two-kernel form at
+                    head_dim 128: a quarter slower than the fused one, which adds dq's shares in memory.)  Costs nothing
                     while the bytes a rank must send fit easily into the time its kernels run;
           "nccl"    plain kernels, then NCCL all-gathers on the second stream beside the next step's kernels: out as
                     soon as the forward has it, dq + dk + dv (one buffer, one collective) after the backward.  Better
@@ -402,26 +404,23 @@ def run_ours(args):
                 o["grads_all"] = torch.empty((world, nq + 2 * nk), device=dev)
                 outs.append(o)
             else:
-                o = {"dkdv": torch.empty(2 * nk, device=dev)}
-                o["dk"], o["dv"] = o["dkdv"][:nk].view_as(k), o["dkdv"][nk:].view_as(v)
+                o = {"grads": torch.empty(nq + 2 * nk, device=dev)}
+                o["dq"], o["dk"] = o["grads"][:nq].view_as(q), o["grads"][nq:nq + nk].view_as(k)
+                o["dv"] = o["grads"][nq + nk:].view_as(v)
                 o["g_out"] = zt.sharding.GatheredOutput(q.shape, world, rank, dev)
-                o["g_dq"] = zt.sharding.GatheredOutput(q.shape, world, rank, dev)
-                o["out"], o["dq"] = o["g_out"].local, o["g_dq"].local
-                o["out_peers"], o["dq_peers"] = o["g_out"].peer_pointers(), o["g_dq"].peer_pointers()
-                o["dkdv_all"] = torch.empty((world, 2 * nk), device=dev)
+                o["out"] = o["g_out"].local
+                o["out_peers"] = o["g_out"].peer_pointers()
+                o["grads_all"] = torch.empty((world, nq + 2 * nk), device=dev)
                 outs.append(o)
         comm_done = [torch.cuda.Event() for _ in range(n_sets)]
         ev_grad, ev_out = torch.cuda.Event(), torch.cuda.Event()
 
         def side_by_side(o):
             """[G, 1, T, Hs D] -> [1, T, H D]: the ranks' column slices laid side by side (KV-head sharding)."""
-            if push == "nccl":
-                gts = (o["out_all"], o["grads_all"][:, :nq].reshape((world,) + tuple(q.shape)),
-                       o["grads_all"][:, nq:nq + nk].reshape((world,) + tuple(k.shape)),
-                       o["grads_all"][:, nq + nk:].reshape((world,) + tuple(v.shape)))
-            else:
-                gts = (o["g_out"].gathered, o["g_dq"].gathered, o["dkdv_all"][:, :nk].reshape((world,) + tuple(k.shape)),
-                       o["dkdv_all"][:, nk:].reshape((world,) + tuple(v.shape)))
+            gts = (o["out_all"] if push == "nccl" else o["g_out"].gathered,
+                   o["grads_all"][:, :nq].reshape((world,) + tuple(q.shape)),
+                   o["grads_all"][:, nq:nq + nk].reshape((world,) + tuple(k.shape)),
+                   o["grads_all"][:, nq + nk:].reshape((world,) + tuple(v.shape)))
             for gt in gts:
                 gt.movedim(0, -2).reshape(*gt.shape[1:-1], world * gt.shape[-1]).contiguous()
 
@@ -434,11 +433,7 @@ def run_ours(args):
                 rc = L.zt_attn_forward_batched_keep_peers(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
                                                           lse.data_ptr(), ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D,
                                                           stream, ctypes.byref(token), *o["out_peers"])
-                rc |= L.zt_attn_backward_batched_kept_peers(q.data_ptr(), k.data_ptr(), v.data_ptr(), o["out"].data_ptr(),
-                                                            lse.data_ptr(), do.data_ptr(), o["dq"].data_ptr(),
-                                                            o["dk"].data_ptr(), o["dv"].data_ptr(), delta.data_ptr(),
-                                                            ws.data_ptr(), ws_bytes, Bl, Tl, Hl, Hkvl, D, stream,
-                                                            token.value, *o["dq_peers"])
+                rc |= plain_backward(o)
             else:
                 rc = plain_step(o)
                 if gather:  # "nccl": out leaves while the backward runs
@@ -453,10 +448,7 @@ def run_ours(args):
                 ev_grad.record(main_stream)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(ev_grad)
-                    if push == "kernel":
-                        dist.all_gather_into_tensor(o["dkdv_all"], o["dkdv"])
-                    else:
-                        dist.all_gather_into_tensor(o["grads_all"], o["pack"][nq:])
+                    dist.all_gather_into_tensor(o["grads_all"], o["grads"] if push == "kernel" else o["pack"][nq:])
                     if gather == "heads":
                         side_by_side(o)
                     comm_done[i % n_sets].record(comm_stream)
@@ -564,8 +556,8 @@ def run_ours(args):
                   "bytes_sent_per_rank": main["bytes_sent_per_rank"], "nvlink_floor_ms": main["nvlink_floor_ms"],
                   "limiter": "NVLink" if main["nvlink_floor_ms"] > 0.8 * main["compute_ms"] else "compute",
                   "note": "compute: the step's kernels alone. step: with every rank receiving every rank's out, dq, dk, dv "
-                          "('kernel': out and dq stored by the kernels' epilogues into every rank's gathered tensors, dk + dv "
-                          "by one NCCL all-gather; 'nccl': NCCL all-gathers on a second stream beside the next kernels). "
+                          "('kernel': out stored by the forward's epilogue into every rank's gathered tensor, dq + dk + dv by one "
+                          "NCCL all-gather; 'nccl': NCCL all-gathers on a second stream beside the next kernels). "
                           "nvlink_floor: the bytes a rank must send per step over the measured 770 GB/s per direction"}
     weak = None
     if weak_res:
@@ -600,8 +592,9 @@ def run_ours(args):
         rope = {"ms_per_step": rope_ms, "plain_ms_per_step": ms_step, "extra_ms": rope_ms - ms_step,
                 "tflops": world * 3.5 * F / (rope_ms * 1e-3) / 1e12,
                 "kernels": {n: {"launches": c_, "ms_per_launch": ms / c_} for n, (c_, ms) in rk.items()},
-                "note": "q, k handed over unrotated; rotation inside the pre-pass (forward and backward), R^T inside "
-                        "the dQ kernel's epilogue, one in-place pass over dk; credited FLOPs unchanged"}
+                "note": "q, k handed over unrotated; rotation inside the pre-pass (forward and backward); R^T as one in-place "
+                        "pass each over dq and dk (the fused backward adds dq's shares in memory, so dq is rotated once "
+                        "it is complete); credited FLOPs unchanged"}
         del rws, q, k, v, do
 
     # ---- the attention part of a block: rope -> attention -> wo (src/model.zig:372-396) -------------------------
