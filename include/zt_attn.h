@@ -127,7 +127,7 @@ void zt_attn_set_verbose(int on);
  * every SM a CTA, one head per CTA otherwise), 1 = CUDA-core kernels only, 2 = as 0 but the forward
  * uses the 3xTF32 kernel instead of the f16-split one, 6 = the f16-split forward with one head per
  * CTA, 7 = with two heads per CTA whatever the number of CTAs, 8 = as 0 but the backward takes its
- * earlier forms: at head_dim 96 and 128 two kernels (dQ's, then dK/dV's) instead of the fused one --
+ * earlier forms: up to head_dim 128 two kernels (dQ's, then dK/dV's) instead of the fused one --
  * slower by a quarter, and the only form whose dq is bit-reproducible run to run (the fused kernel
  * adds every key tile's share of dq in memory, in no fixed order: equal to rounding) -- and at 192
  * and 256 the scores kernel that loads every operand per tile.  Any other value selects 0.  For

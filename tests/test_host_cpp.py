@@ -146,4 +146,7 @@ def test_cpp_pipeline_matches_the_batched_calls(host, zt):
     out, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
     dq, dk, dv = zt.attention_backward(q, k, v, out, lse, do, H, Hkv, D)
     for name, got, want in (("out", hout, out), ("lse", hlse, lse), ("dq", hdq, dq), ("dk", hdk, dk), ("dv", hdv, dv)):
-        assert torch.equal(got, want.cpu()), name
+        if name == "dq":  # (a sum over key tiles made in memory by the fused backward: equal run to run to rounding)
+            assert bool(((got - want.cpu()).abs() <= 2e-6 + 2e-5 * want.cpu().abs()).all())
+        else:
+            assert torch.equal(got, want.cpu()), name

@@ -1,4 +1,4 @@
-// The backward at head_dim 128 (and 96 padded to it) as ONE tensor-core kernel: dK, dV and dQ from one
+// The backward at head_dim 64 and 128 (and 32, 96 padded to them) as ONE tensor-core kernel: dK, dV and dQ from one
 // computation of S^T and dP^T.
 //
 // tc_bwd.cuh computes S and dP twice: once in the dK/dV kernel (a CTA per 128 keys, query tiles walked) and
@@ -55,25 +55,30 @@ __device__ __forceinline__ void fgive_up(FusedShared *sh, int code) {
     sh->abort = code;
     atomicMax(&g_tc_status, code);
 }
-// K hi, K lo, V lo, dS hi + lo, two Q slots, one dO slot (each 32 KB at head_dim 128)
-__host__ __device__ constexpr size_t fused_smem_bytes() { return 7 * (size_t)(128 * 128 * 2) + sizeof(FusedShared); }
+// K hi, K lo, V lo; dS hi + lo (32 KB); two Q slots and one dO slot (each 32 KB at head_dim 128)
+template <int D>
+__host__ __device__ constexpr size_t fused_smem_bytes() {
+    return 3 * (size_t)(128 * D * 2) + 2 * (size_t)(128 * 128) + 6 * (size_t)(64 * D * 2) + sizeof(FusedShared);
+}
 
 // grid (n_kv_heads, ceil(T / 128), batch), 608 threads: 16 row warps, a TMA warp, two MMA warps.
 constexpr int kFusedThreads = (kKvRowWarps + 3) * 32;
+template <int D>
 __global__ void __launch_bounds__(kFusedThreads, 1)
     attn_bwd_fused_tc(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap gmap,
                       const BwdParams p) {
-    constexpr int D = 128, NB = D / 64, W2 = D / 2, BQ = 64;
+    static_assert(D == 64 || D == 128, "tile widths of this kernel");
+    constexpr int NB = D / 64, W2 = D / 2, BQ = 64;
     constexpr int KP = 128 * D * 2, QP = BQ * D * 2;  // bytes of one plane of a K tile / a query tile
-    constexpr int cVh = 0, cST = 64, cDPT = 128, cDQT = 192, cDV = 256, cDK = 384;
+    constexpr int cVh = 0, cST = 64, cDPT = 128, cDQT = 192, cDV = 256, cDK = 256 + D;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sKh = smem, *sKl = smem + KP, *sVl = smem + 2 * KP;  // V's hi plane sits in TMEM
+    constexpr int DSP = 128 * 128;  // bytes of one plane of dS^T: 128 key rows of 64 halves
     uint8_t *sDS = smem + 3 * KP;                                 // dS^T hi (16 KB), lo (16 KB): rows are keys
-    uint8_t *sQ = smem + 4 * KP;                                  // slot s: Qh, Ql at sQ + s * 2 QP + {0, 1} QP
+    uint8_t *sQ = sDS + 2 * DSP;                                  // slot s: Qh, Ql at sQ + s * 2 QP + {0, 1} QP
     uint8_t *sG = sQ + 2 * 2 * QP;                                // dOh, dOl
     FusedShared *sh = reinterpret_cast<FusedShared *>(sG + 2 * QP);
-    constexpr int DSP = 128 * 128;  // bytes of one plane of dS^T: 128 key rows of 64 halves
 
     const int warp = threadIdx.x >> 5;
     const int g = blockIdx.x, kt = (int)blockIdx.y, b = blockIdx.z;
@@ -254,7 +259,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if (!ok) fgive_up(sh, 62);
             tc_fence_after();
             const uint64_t bvl = desc_kmajor(smem_u32(sVl));
-            const uint64_t mkh = desc_mnmajor_16b(smem_u32(sKh), 128 * 128), mkl = desc_mnmajor_16b(smem_u32(sKl), 128 * 128);
+            // dQ^T's A operand is the K tile read M-major: M = the head's columns.  At 128 columns that is the two
+            // 64-column blocks of one plane (16 KB apart), and a product is the usual three terms.  At 64 columns M
+            // would be 64, half a tensor-core tile: instead the hi plane and the lo plane (KP apart) are read as ONE
+            // 128-row operand, so that accumulator rows 0..63 hold Kh^T dS and rows 64..127 Kl^T dS; with dS hi and
+            // dS lo as the two B operands that is all four terms in two MMAs, and the read-out adds the two halves.
+            const uint64_t mkh = desc_mnmajor_16b(smem_u32(sKh), D == 128 ? 128 * 128 : KP);
+            const uint64_t mkl = desc_mnmajor_16b(smem_u32(sKl), 128 * 128);
             const uint64_t mdh = desc_mnmajor_16b(smem_u32(sDS), DSP), mdl = desc_mnmajor_16b(smem_u32(sDS) + DSP, DSP);
             const uint32_t q_u32 = smem_u32(sQ), g_u32 = smem_u32(sG);
             // dP^T(j) = V dO^T (waits for dO(j))
@@ -283,7 +294,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                     const uint64_t ddh = desc_advance(mdh, kk * 2048), ddl = desc_advance(mdl, kk * 2048);
                     mma_ss_f16(tmem + cDQT, dkh, ddh, id_q, kk > 0);
                     mma_ss_f16(tmem + cDQT, dkh, ddl, id_q, 1);
-                    mma_ss_f16(tmem + cDQT, dkl, ddh, id_q, 1);
+                    if (D == 128) mma_ss_f16(tmem + cDQT, dkl, ddh, id_q, 1);
                 }
             };
             int n_flush = 0;
@@ -452,7 +463,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                 }
             }
             // now r[4 q4 + e] = dQ^T[head column 4 (lane / 4) + e of this warp's 32][query row 16 set + 4 q4 + (lane & 3)]
-            const int d0 = (warp & 3) * 32 + (lane & ~3);
+            // (at 64 columns the accumulator's rows 64..127 are the K lo half of the same columns: both halves add)
+            const int d0 = ((warp & 3) * 32 + (lane & ~3)) & (D - 1);
             if (d0 < p.dim_out) {
                 const long long wq = (long long)p.n_heads * p.dim_out;
 #pragma unroll
@@ -602,21 +614,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     if (warp == kKvRowWarps + 1) tmem_dealloc(tmem, 512);
 }
 
-inline int launch_bwd_fused(const CUtensorMap &k128, const CUtensorMap &v128, const CUtensorMap &qs64, const CUtensorMap &g64,
-                            const BwdParams &p, cudaStream_t stream) {
-    const size_t smem = fused_smem_bytes();
-    if (optin_smem((const void *)attn_bwd_fused_tc, smem)) return 1;
+template <int D>
+inline int launch_bwd_fused_d(const CUtensorMap &k128, const CUtensorMap &v128, const CUtensorMap &qs64, const CUtensorMap &g64,
+                              const BwdParams &p, cudaStream_t stream) {
+    size_t smem = fused_smem_bytes<D>();
+    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it allocates all of TMEM
+    if (optin_smem((const void *)attn_bwd_fused_tc<D>, smem)) return 1;
     const dim3 grid((unsigned)p.n_kv_heads, (unsigned)((p.T + 127) / 128), (unsigned)p.batch);
-    return ZT_LAUNCH("attn_bwd_fused_tc", stream, (attn_bwd_fused_tc<<<grid, kFusedThreads, smem, stream>>>(k128, v128, qs64, g64, p)));
+    return ZT_LAUNCH("attn_bwd_fused_tc", stream, (attn_bwd_fused_tc<D><<<grid, kFusedThreads, smem, stream>>>(k128, v128, qs64, g64, p)));
+}
+inline int launch_bwd_fused(int td, const CUtensorMap &k128, const CUtensorMap &v128, const CUtensorMap &qs64, const CUtensorMap &g64,
+                            const BwdParams &p, cudaStream_t stream) {
+    return td == 64 ? launch_bwd_fused_d<64>(k128, v128, qs64, g64, p, stream)
+                    : launch_bwd_fused_d<128>(k128, v128, qs64, g64, p, stream);
 }
 
 }  // namespace tcf
 
-// Which backward a head_dim-`dim` call takes: the fused kernel at tile width 128 (head_dim 128 and 96) unless the
+// Which backward a head_dim-`dim` call takes: the fused kernel at tile widths 64 and 128 (head_dim 32 ... 128) unless the
 // two-kernel form is asked for (zt_attn_set_path(8)) or dq must also be stored into peers' memory (the fused
 // kernel adds partial sums into dq, which a plain peer store cannot follow).
 inline bool tc_bwd_takes_fused(int dim, bool two_kernels, const PeerList *dq_peers) {
-    return tc_tile_dim(dim) == 128 && !two_kernels && !(dq_peers && dq_peers->n > 0);
+    const int td = tc_tile_dim(dim);
+    return (td == 64 || td == 128) && !two_kernels && !(dq_peers && dq_peers->n > 0);
 }
 
 // delta and the row norms of dout (workspace rnorm) must already be there.  dq, dk, dv are assigned.
@@ -696,7 +716,7 @@ inline int launch_bwd_tc(const float *q, const float *k, const float *v, const f
     // dS is scaled inside the kernels (see "The scale of dS" in tc_bwd.cuh and the head of this file).
     p.p_scale = ldexpf(1.0f, 10);
     g_last_path = "tcgen05";
-    if (fused) return tcf::launch_bwd_fused(m.k128, m.v128, m.q64, m.g64, p, stream);
+    if (fused) return tcf::launch_bwd_fused(td, m.k128, m.v128, m.q64, m.g64, p, stream);
     return td == 64 ? launch_bwd_tc_d<64>(m, p, stream) : launch_bwd_tc_d<128>(m, p, stream);
 }
 
