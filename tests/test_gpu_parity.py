@@ -581,6 +581,40 @@ def test_backward_forms_of_path_8_match_oracle(zt, dev, oracle, B, T, H, Hkv, D)
         close(got[2][b].cpu().numpy(), rdv, f"item {b} dv")
 
 
+def test_backward_forms_agree_on_random_shapes(zt, dev):
+    """Thirty shapes drawn with a fixed seed (every tensor-core width, sequence lengths with every kind of tail, one
+    to three sequences, groups of one to four heads): the default backward (fused kernel; unfused at 192/256), the
+    forms of path 8 and the CUDA-core kernels agree to rounding, and no kernel gives up a wait or clamps a dS."""
+    rng = np.random.default_rng(20261126)
+    L = zt.lib.load()
+    for case in range(30):
+        D = int(rng.choice([32, 64, 96, 128, 192, 256]))
+        group = int(rng.choice([1, 2, 3, 4]))
+        Hkv = int(rng.choice([1, 2, 3]))
+        H = Hkv * group
+        B = int(rng.choice([1, 2, 3]))
+        T = int(rng.integers(128, 1100 if D <= 128 else 700))
+        g = torch.Generator(device=dev).manual_seed(1000 + case)
+        q, do = (torch.randn((B, T, H * D), generator=g, device=dev) for _ in range(2))
+        k, v = (torch.randn((B, T, Hkv * D), generator=g, device=dev) for _ in range(2))
+        do *= float(rng.choice([1e-3, 1.0, 30.0]))
+        o, lse = zt.attention_forward(q, k, v, H, Hkv, D, want_lse=True)
+        res = {}
+        for path in (0, 8, 1):
+            L.zt_attn_set_path(path)
+            try:
+                res[path] = zt.attention_backward(q, k, v, o, lse, do, H, Hkv, D)
+            finally:
+                L.zt_attn_set_path(0)
+            assert zt.lib.last_path() == ("simt" if path == 1 else "tcgen05"), (case, path)
+        torch.cuda.synchronize()
+        assert zt.lib.tc_status() == 0 and zt.lib.tc_saturated() == 0, case
+        for name, a, b_, c in zip(("dq", "dk", "dv"), res[0], res[8], res[1]):
+            top = float(c.abs().max())
+            assert float((a - c).abs().max()) <= 3e-5 * top, (case, (B, T, H, Hkv, D), name, "default vs CUDA cores")
+            assert float((b_ - c).abs().max()) <= 3e-5 * top, (case, (B, T, H, Hkv, D), name, "path 8 vs CUDA cores")
+
+
 def test_wide_head_backward_rows_of_very_different_size(zt, dev, oracle):
     """The wide-head backward scales dS per query row and moves the row's factor onto a second copy of Q for dK (whose
     contraction runs across rows).  Rows of dout from 1e-4 to 1e2 times the rest -- 2^20, beyond the 2^12 the factor
