@@ -28,6 +28,10 @@
 //                            dS, dQ += dS K over the causal key tiles of 64; dq assigned.
 // Both kernels issue S (and dP) one or two tiles ahead into TMEM buffers of their own and spread
 // the row work of a tile over four warp sets; see the comment above each.
+// These two are the backward's first form: today's default folds dQ into the dK/dV kernel (tc_bwd_fused.cuh,
+// which also holds launch_bwd_tc, the host side of both forms); they run when the two-kernel form is asked
+// for, and for the call that also stores dq into peers' memory.  The pre-pass kernels and the walk (Walk)
+// below serve both forms.
 // Every wait is bounded (see tc_common.cuh); a wait that gives up raises g_tc_status.
 #pragma once
 
@@ -266,7 +270,8 @@ struct BwdParams {
     const uint32_t *amax_q, *amax_k, *amax_v, *amax_do;  // [B, Hkv] bit patterns of max |x|
     const float *rnorm;      // [B, T, H] Euclidean norm of each row of dout (bwd_rownorm_kernel)
     const uint32_t *vnmax;   // [B, Hkv] bit pattern of the largest Euclidean norm of a row of v
-    uint32_t *dsmax;         // [B, Hkv] bit pattern of max |dS| (true units): written by the dQ kernel, read by dK/dV
+    uint32_t *dsmax;         // [B, Hkv] bit pattern of max |dS| (true units): written by the dQ kernel, read by dK/dV;
+                             // for the fused kernel the same words hold the largest row norm of dout instead
     float *dq, *dk, *dv;
     PeerList dq_peers;       // dq is also stored here (same element index), see zt_common.cuh
     int batch, T, n_heads, n_kv_heads;
